@@ -1,0 +1,162 @@
+"""Generates the golden vectors in this directory. Run once in the build container, where the reference checkout and
+transformers are present; the tests only read the .npz files.
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+packers.npz   outputs of the reference's own pure-torch packers (kernels/stream_decoder.py prepare_w8,
+              kernels/fast_encoder.py quantize_rows maths, kernels/sparse.py prune_24_magnitude / compress_24) on seeded
+              inputs. kernels/cuda_ext.py (the JIT build, needs a GPU) is stubbed out before import; nothing else of
+              the reference runs.
+decoder_small.npz  transformers' CohereAsrDecoder + proj_out (the reference's FAST=0 arithmetic) on a small seeded
+              model, ragged batch, full logits per step.
+decoder_config1.npz  the same model class at the benchmark architecture (8 layers, 1024 wide, 16 heads x 64, GELU, vocab
+              16384), batch 1, memory [1, 125, 1024], 10-token prompt + 64 forced new tokens, seed 0, fp32: greedy
+              argmax of all 73 steps and the logits at every 64th vocabulary entry.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+import cohere_inference_b200 as cib  # noqa: E402
+from cohere_inference_b200.synth import config1_inputs, synthetic_model  # noqa: E402
+
+
+def reference_packers(ref: str):
+    sys.path.insert(0, ref)
+    stub = types.ModuleType("kernels.cuda_ext")
+    stub.ext = None
+    sys.modules["kernels.cuda_ext"] = stub
+    tri = types.ModuleType("kernels.decoder_kernels")  # Triton kernels: not needed by the packers
+    tri.linear = None
+    sys.modules["kernels.decoder_kernels"] = tri
+    from kernels.sparse import compress_24, prune_24_magnitude
+    from kernels.stream_decoder import prepare_w8
+    return prepare_w8, prune_24_magnitude, compress_24
+
+
+def make_packers(ref: str) -> None:
+    prepare_w8, prune_24_magnitude, compress_24 = reference_packers(ref)
+    rng = np.random.default_rng(0)
+    out = {}
+    cases = {"a": (48, 64), "b": (16, 256), "c": (32, 1024)}
+    for name, (n, k) in cases.items():
+        w = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        if name == "a":
+            w[3] = 0  # an all-zero row: scale clamps at 1e-12 / 127
+            w[5, :8] = [0.5, -0.5, 0.25, 0.25, 0, 0, 0, 1e-3]  # ties and zeros inside groups of four
+            w[7] *= 1e-9
+        t = torch.from_numpy(w)
+        u8, s = prepare_w8(t)
+        pruned = prune_24_magnitude(t)
+        sp = pruned.float().abs().amax(1).clamp_min(1e-12) / 127  # quantize_rows' maths (fast_encoder.py:60-63)
+        qp = torch.round(pruned.float() / sp[:, None]).clamp(-127, 127).to(torch.int8)
+        kept, words = compress_24(qp)
+        out.update({f"{name}_w": w, f"{name}_u8": u8.numpy(), f"{name}_s": s.numpy(), f"{name}_pruned": pruned.numpy(),
+                    f"{name}_qp": qp.numpy(), f"{name}_sp": sp.numpy(), f"{name}_kept": kept.numpy(),
+                    f"{name}_words": words.numpy()})
+    # a hand-made int8 matrix with 0, 1 and 2 nonzeros per group in every position pattern
+    pat = []
+    for i0 in range(4):
+        for i1 in range(i0 + 1, 4):
+            g = [0, 0, 0, 0]
+            g[i0], g[i1] = 5 + i0, -(7 + i1)
+            pat.append(g)
+    for i0 in range(4):
+        g = [0, 0, 0, 0]
+        g[i0] = -3 - i0
+        pat.append(g)
+    pat.append([0, 0, 0, 0])
+    pat += pat[:5]
+    q = np.array(pat, dtype=np.int8).reshape(2, 32)
+    kept, words = compress_24(torch.from_numpy(q))
+    out.update({"p_q": q, "p_kept": kept.numpy(), "p_words": words.numpy()})
+    np.savez_compressed(os.path.join(HERE, "packers.npz"), **out)
+
+
+def hf_model(synth):
+    from transformers.models.cohere_asr import modeling_cohere_asr as m
+    from transformers.models.cohere_asr.configuration_cohere_asr import CohereAsrConfig
+    c = synth.config
+    cfg = CohereAsrConfig(vocab_size=c.vocab_size, hidden_size=c.hidden_size, num_hidden_layers=c.num_hidden_layers,
+                          num_attention_heads=c.num_attention_heads, num_key_value_heads=c.num_key_value_heads,
+                          head_dim=c.head_dim, intermediate_size=c.intermediate_size, hidden_act=c.hidden_act,
+                          max_position_embeddings=c.max_position_embeddings,
+                          encoder_config=dict(hidden_size=c.encoder_hidden_size, num_hidden_layers=1))
+    model = m.CohereAsrForConditionalGeneration(cfg).eval()
+    missing, unexpected = model.load_state_dict(synth.state_dict(), strict=False)
+    assert not unexpected and all(k.startswith("model.encoder") for k in missing), (missing[:5], unexpected[:5])
+    return model
+
+
+@torch.no_grad()
+def hf_teacher_forced(model, memory: torch.Tensor, tokens: torch.Tensor) -> np.ndarray:
+    """Logits (B, steps, V) of feeding tokens[:, t] at position t with a KV cache, one token per call: the manual loop
+    over model.model.decoder + proj_out (generate() cannot take a bare encoder output for this model)."""
+    dec, past, rows = model.model.decoder, None, []
+    for t in range(tokens.shape[1]):
+        o = dec(input_ids=tokens[:, t:t + 1], encoder_hidden_states=memory, past_key_values=past, use_cache=True)
+        past = o.past_key_values
+        rows.append(model.proj_out(o.last_hidden_state[:, -1]).float().numpy())
+    return np.stack(rows, 1)
+
+
+@torch.no_grad()
+def hf_greedy(model, memory: torch.Tensor, prompt: torch.Tensor, new: int):
+    """Greedy decode with the prompt forced: returns (tokens fed (steps,), logits (steps, V), argmax (steps,))."""
+    dec, past = model.model.decoder, None
+    tok, fed, lg, am = prompt[:, :1], [], [], []
+    steps = prompt.shape[1] - 1 + new
+    for t in range(steps):
+        o = dec(input_ids=tok, encoder_hidden_states=memory, past_key_values=past, use_cache=True)
+        past = o.past_key_values
+        logits = model.proj_out(o.last_hidden_state[:, -1]).float()
+        a = int(logits.argmax(-1))
+        fed.append(int(tok)), lg.append(logits[0].numpy()), am.append(a)
+        nxt = int(prompt[0, t + 1]) if t + 1 < prompt.shape[1] else a
+        tok = torch.tensor([[nxt]])
+    return np.array(fed), np.stack(lg), np.array(am)
+
+
+def make_decoder_small() -> None:
+    out = {}
+    for tag, heads, hd, act, bias in (("gelu", 4, 16, "gelu", 0.05), ("relu", 2, 32, "relu", 0.0)):
+        synth = synthetic_model(1, heads=heads, head_dim=hd, act=act, layers=2, hidden=64, ffn=128, vocab=96,
+                                max_pos=32, bias_std=bias)
+        model = hf_model(synth)
+        g = torch.Generator().manual_seed(1)
+        lens = [7, 3, 5]
+        memory = torch.randn(3, 7, 64, generator=g)
+        tokens = torch.randint(0, 96, (3, 6), generator=g)
+        # per row on its own (no padding mask needed): ragged encoder lengths
+        logits = np.stack([hf_teacher_forced(model, memory[r:r + 1, :lens[r]], tokens[r:r + 1])[0] for r in range(3)])
+        out.update({f"{tag}_memory": memory.numpy(), f"{tag}_lens": np.array(lens), f"{tag}_tokens": tokens.numpy(),
+                    f"{tag}_logits": logits})
+    np.savez_compressed(os.path.join(HERE, "decoder_small.npz"), **out)
+
+
+def make_config1() -> None:
+    synth = synthetic_model(0)
+    model = hf_model(synth)
+    memory, prompt = (torch.from_numpy(a) for a in config1_inputs(0))
+    fed, logits, am = hf_greedy(model, memory, prompt, 64)
+    np.savez_compressed(os.path.join(HERE, "decoder_config1.npz"), memory_checksum=np.float64(memory.double().sum()),
+                        prompt=prompt.numpy(), fed=fed, argmax=am, logits_sub=logits[:, ::64].astype(np.float32),
+                        top2_gap=np.sort(logits, -1)[:, -1] - np.sort(logits, -1)[:, -2])
+
+
+if __name__ == "__main__":
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    make_packers(ref)
+    make_decoder_small()
+    make_config1()
+    print("ok", cib.__name__)

@@ -1,0 +1,310 @@
+"""Benchmark of the decoder token loop: decoded tokens/s at batch 64 with weight-only int8 (BASELINE config 3).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" of this benchmark is one pass of the hot path over one batch: 64 sequences (encoder lengths uniform in
+[50, 375], 10-token prompts) decoded for 448 new tokens each = 457 CUDA-graph replays of the decoding step. K passes
+are timed after W warm-up passes.
+
+  value      decoded tokens/s over all GPUs with the inputs resident in HBM: the timed region is the token loop
+             (admit + 457 replays) on the decoder stream, CUDA events, max over ranks.
+  e2e        the same metric through the public API from host buffers: pinned host encoder memory -> device,
+             fill_cross (cross-K/V prefill), admit, 457 replays, finished rows read back to the host.
+  roofline   the dominant kernel (attention over the bf16 KV cache): algorithmic KV bytes per launch / its launch
+             duration measured here with CUDA events, against the measured HBM copy bandwidth; `step` gives the same
+             for the whole decoding step (weights + KV bytes / replay time).
+  cpu_baseline / --impl reference   the reference's CPU arithmetic (transformers fp32 decoder, else the numpy port) on
+             the host cores, on a bounded sample of the same workload.
+With --gpus N (launched by torchrun, one rank per GPU) every rank decodes its own batch: replicas, no collective on
+the token loop; NCCL only for the barriers, the max over ranks and one stats gather.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH, PROMPT, NEW, FRAMES = 64, 10, 448, (50, 375)
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak() -> tuple[float, str]:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region (read-only queries)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i].lower().startswith("active")
+                                                         for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def make_inputs(seed: int):
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(FRAMES[0], FRAMES[1] + 1, BATCH).tolist()
+    memory = torch.from_numpy(rng.standard_normal((sum(lens), 1024), dtype=np.float32))
+    prompts = [torch.from_numpy(rng.integers(0, 16384, PROMPT).astype(np.int64)) for _ in range(BATCH)]
+    return lens, memory, prompts
+
+
+def run_ours(args) -> None:
+    from cohere_inference_b200 import StreamDecoder, dataparallel as dp, native as nv, synthetic_model
+    rank, local, world = dp.init()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch N > 1 with torch.distributed.run)"
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    model = synthetic_model(0).to(dev)
+    dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
+                        int8=True, eos=-1)
+    lens, memory_host, prompts = make_inputs(1000 + rank)
+    memory_host = memory_host.pin_memory()
+    memory_dev = memory_host.to(dev)
+    slots = list(range(BATCH))
+    steps_per_pass = PROMPT - 1 + NEW
+    out_host = torch.zeros(BATCH, dec.out.shape[1], dtype=torch.long).pin_memory()
+    step_events: list = []
+
+    def token_loop(record: bool):
+        dec.admit(slots, prompts, lens)
+        b = dec.set_active(slots)
+        for _ in range(steps_per_pass):
+            dec.step(b)
+            if record:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(dec.stream)
+                step_events.append(ev)
+
+    def resident_pass(record=False):
+        """Inputs in HBM: cross K/V already in the slot caches; the timed region is the token loop."""
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(dec.stream)
+        if record:
+            step_events.append(s)
+        token_loop(record)
+        e.record(dec.stream)
+        return s, e
+
+    def e2e_pass():
+        """Host buffers in, host tokens out, everything on the decoder stream."""
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(dec.stream):
+            s.record(dec.stream)
+            mem = memory_host.to(dev, non_blocking=True)
+            dec.fill_cross(mem, lens, slots)
+        token_loop(False)
+        with torch.cuda.stream(dec.stream):
+            out_host.copy_(dec.out[:BATCH], non_blocking=True)
+            e.record(dec.stream)
+        return s, e
+
+    with torch.cuda.stream(dec.stream):
+        dec.fill_cross(memory_dev, lens, slots)
+    for _ in range(args.warmup):
+        resident_pass()
+    dec.stream.synchronize()
+    dp.barrier(dev)
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clocks:
+        t_wall = time.perf_counter()
+        pairs = [resident_pass(record=True) for _ in range(args.steps)]
+        dec.stream.synchronize()
+        t_wall = time.perf_counter() - t_wall
+        dp.barrier(dev)
+        torch.cuda.synchronize()
+    dec.check_status()
+    ms = sum(s.elapsed_time(e) for s, e in pairs)
+    ms = dp.max_over_ranks(ms, dev)
+    tokens = BATCH * NEW * args.steps
+    value = world * tokens / (ms / 1e3)
+    # drop the gaps between passes (admit + set_active): keep intervals that end at a step event of the same pass
+    per_pass = steps_per_pass + 1
+    step_ms = [a.elapsed_time(b) for i, (a, b) in enumerate(zip(step_events[:-1], step_events[1:]))
+               if (i + 1) % per_pass != 0]
+    p50 = statistics.median(step_ms)
+
+    # ---- algorithmic bytes of the passes (exact positions and lengths) and the step's roofline
+    total_bytes = sum(dec.step_bytes([min(t, steps_per_pass)] * BATCH, lens) for t in range(steps_per_pass))
+    peak, peak_kind = measured_peak()
+    loop_ms = sum(step_ms) / args.steps
+    step_gbs = total_bytes / (loop_ms / 1e3) / 1e9
+
+    # ---- the dominant kernel alone: cross-attention over all rows, cycling the layers so no launch finds its
+    # cache in L2 (one layer's cross K/V is ~56 MB, the eight together ~450 MB > the 126 MB L2)
+    lib, L = nv.lib(), len(dec.layers)
+    kv_bytes = sum(lens) * 2 * 1024 * 2
+    reps = 10
+    with torch.cuda.stream(dec.stream):
+        ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for timed in (False, True):
+            if timed:
+                ks.record(dec.stream)
+            for i in range(reps * L):
+                ly = i % L
+                nv.check(lib.b200dec_attention(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
+                                               nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
+                                               dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
+                                               nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status), 0,
+                                               nv.stream_ptr(dec.stream)))
+            if timed:
+                ke.record(dec.stream)
+    dec.stream.synchronize()
+    attn_us = ks.elapsed_time(ke) * 1e3 / (reps * L)
+    attn_gbs = kv_bytes / (attn_us / 1e6) / 1e9
+
+    # ---- end to end through the public API, host buffers
+    for _ in range(min(args.warmup, 2)):
+        e2e_pass()
+    dec.stream.synchronize()
+    dp.barrier(dev)
+    torch.cuda.synchronize()
+    pairs = [e2e_pass() for _ in range(args.steps)]
+    dec.stream.synchronize()
+    dp.barrier(dev)
+    e2e_ms = dp.max_over_ranks(sum(s.elapsed_time(e) for s, e in pairs), dev)
+    e2e_value = world * tokens / (e2e_ms / 1e3)
+    assert (out_host[:, PROMPT:PROMPT + NEW] != dec.pad).any()
+
+    all_stats = dp.gather_stats(dict(steps=steps_per_pass * args.steps, new_tokens=tokens, bytes=total_bytes * args.steps,
+                                     gpu_us=int(ms * 1e3)), dev)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        from oracle import cpu_baseline
+        r = cpu_baseline.time_cpu(synthetic_model(0), BATCH, args.cpu_steps)
+        cpu = {"value": round(r["tokens_per_s"], 1), "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
+               "sample": r["sample"], "ms_per_step": round(r["ms_per_step"], 2)}
+    if rank == 0:
+        line = {
+            "metric": "decoded tokens/s at batch 64, weight-only int8", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights x fp16, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "BASELINE config 3: 8 layers x 1024, 16 heads x 64, GELU, vocab 16384; batch 64 per GPU, "
+                                   "encoder lengths U[50,375], 10-token prompts + 448 new tokens, one CUDA graph per "
+                                   "decoding step; a bench step = one pass = 457 replays",
+                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "bf16", "parallelism": f"dp{world} replicas",
+                       "l2": "inputs larger than L2: each replay streams ~0.2-1.9 GB of KV cache and weights",
+                       "weights": "seed-0 random init N(0, 0.02)"},
+            "p50_step_ms": round(p50, 4),
+            "tokens_per_s_per_gpu": round(value / world, 1),
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(memory_host.numel() * 4),
+                    "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
+                    "ms_per_step": round(e2e_ms / args.steps, 3)},
+            "gpu_launches": dec.launches_per_step * steps_per_pass * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "attention_kernel<64,false> (cross-attention, 64 rows x 16 heads)",
+                         "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
+                         "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
+                         "traffic": None,
+                         "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
+                                  "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
+                                  "frac_of_8TBs": round(step_gbs / 8000, 4)}},
+            "cpu_baseline": cpu,
+            "clocks": clocks.summary(),
+            "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in all_stats],
+            "wall_s": round(t_wall, 3),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def run_reference(args) -> None:
+    """The reference's own CPU implementation of the path (transformers, FAST=0 arithmetic) on the host cores, on a
+    bounded sample of the same workload. Rank 0 alone runs it."""
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    from cohere_inference_b200 import synthetic_model
+    from oracle import cpu_baseline
+    model = synthetic_model(0)
+    runs = []
+    for i in range(args.warmup + args.steps):
+        r = cpu_baseline.time_cpu(model, BATCH, args.cpu_steps, seed=1000)
+        if i >= args.warmup:
+            runs.append(r)
+        if i == 0 and r["seconds"] + r["prefill_s"] > 60:  # slow host: one sample is the bounded budget
+            runs = [r]
+            break
+    secs, toks = sum(r["seconds"] for r in runs), sum(r["batch"] * r["steps"] for r in runs)
+    value = toks / secs
+    r = runs[-1]
+    line = {"impl": "reference", "metric": "decoded tokens/s at batch 64, weight-only int8", "value": round(value, 1),
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(runs), "warmup": args.warmup,
+            "ms_per_step": round(1e3 * secs / len(runs), 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32 (CPU)", "data": "synthetic",
+            "config": {"workload": "BASELINE config 3 shapes on the host CPU: batch 64, encoder lengths U[50,375]; each "
+                                   f"step a bounded sample of {args.cpu_steps} cached greedy decoding steps",
+                       "batch_per_gpu": BATCH},
+            "cpu_baseline": {"value": round(value, 1), "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
+                             "sample": r["sample"]},
+            "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-steps", type=int, default=32, help="decoding steps of the bounded CPU sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -13,13 +13,11 @@ __all__ = ["DecoderConfig", "synthetic_model", "synthetic_requests", "config1_in
 
 
 def __getattr__(name):
+    import importlib
     if name == "StreamDecoder":
-        from .stream_decoder import StreamDecoder
-        return StreamDecoder
+        return importlib.import_module(__name__ + ".stream_decoder").StreamDecoder
     if name == "DecodeScheduler":
-        from .scheduler import DecodeScheduler
-        return DecodeScheduler
-    if name == "native":
-        from . import native
-        return native
+        return importlib.import_module(__name__ + ".scheduler").DecodeScheduler
+    if name in ("native", "packing", "scheduler", "stream_decoder", "synth", "build"):
+        return importlib.import_module(__name__ + "." + name)
     raise AttributeError(name)

@@ -1,0 +1,228 @@
+// Attention of one new token per row over its slot's bf16 KV cache: the step's dominant HBM stream.
+//
+// One CTA of 128 threads per (head, row, key split). A key (or value) vector of D = 64 / 128 bf16 is read by
+// D / 8 lanes with one 16-byte load each, so a warp instruction fetches 4 (D = 64) or 2 (D = 128) whole vectors as
+// contiguous 128 / 256-byte runs; each lane group walks its keys four at a time (4 key + 4 value loads in flight
+// per thread, ~16 KB per CTA), with an online softmax per group in fp32 (exp2 on pre-scaled scores). The groups are
+// merged in shared memory. With more than one split the partial (max, sum, output) goes to a workspace and the last
+// CTA of the (row, head) to arrive merges them (a counter it then resets, so the kernel replays inside CUDA graphs;
+// nobody spins). Self-attention also appends: the row's new key and value (fp32 columns of the fused qkv
+// projection) are rounded to bf16 into the cache at position n[slot] and attended from registers.
+//
+// Cache layout (slots + 1, H, cap, D): all keys of one (slot, head) are one contiguous run, the unit a CTA streams.
+#include "common.cuh"
+
+using namespace b200dec_detail;
+
+namespace {
+
+constexpr int MAX_SPLITS = 16;
+constexpr int NTHREADS = 128;
+
+struct AttnArgs {
+  const int* active;
+  const float* q;  // (rows, ldq)
+  __nv_bfloat16* k;
+  __nv_bfloat16* v;
+  const int* n;
+  void* out;
+  float* part;
+  int* count;
+  int* status;
+  int ldq, H, cap, slots, out_kind, rows, splits;
+  float scale_log2;  // head_dim^-0.5 * log2(e)
+};
+
+template <int D, bool SELF>
+__global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
+  constexpr int LPK = D / 8;           // lanes per key
+  constexpr int NG = NTHREADS / LPK;   // key groups per CTA
+  constexpr int U = 4;                 // keys in flight per group
+  __shared__ float s_m[NG], s_l[NG];
+  __shared__ float s_acc[NG][D + 4];
+  __shared__ int s_last;
+
+  const int h = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, nsp = p.splits;
+  const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
+  pdl_trigger();
+  pdl_wait();
+
+  int s = p.active[r];
+  if (s < 0 || s > p.slots) {
+    if (tid == 0) atomicOr(p.status, B200DEC_ST_SLOT_RANGE);
+    s = p.slots;
+  }
+  int n = p.n[s];
+  if (SELF ? (n < 0 || n >= p.cap) : (n < 1 || n > p.cap)) {
+    if (tid == 0) atomicOr(p.status, SELF ? B200DEC_ST_POS_RANGE : B200DEC_ST_FRAMES_RANGE);
+    n = SELF ? max(0, min(n, p.cap - 1)) : max(1, min(n, p.cap));
+  }
+
+  // the query, pre-scaled so that scores are in log2 units
+  float q[8];
+  {
+    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * 8;
+    const float4 a = ld_cg_f4(qp), b = ld_cg_f4(qp + 4);
+    q[0] = a.x * p.scale_log2, q[1] = a.y * p.scale_log2, q[2] = a.z * p.scale_log2, q[3] = a.w * p.scale_log2;
+    q[4] = b.x * p.scale_log2, q[5] = b.y * p.scale_log2, q[6] = b.z * p.scale_log2, q[7] = b.w * p.scale_log2;
+  }
+  const size_t base = ((size_t)s * p.H + h) * p.cap * D + gl * 8;
+  float m = -1e30f, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  auto attend = [&](const uint4& kk, const uint4& vv, bool valid) {
+    float d = q[0] * bf16_lo(kk.x) + q[1] * bf16_hi(kk.x) + q[2] * bf16_lo(kk.y) + q[3] * bf16_hi(kk.y) +
+              q[4] * bf16_lo(kk.z) + q[5] * bf16_hi(kk.z) + q[6] * bf16_lo(kk.w) + q[7] * bf16_hi(kk.w);
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    const float sc = valid ? d : -INFINITY;
+    const float mn = fmaxf(m, sc), a = exp2f(m - mn), e = exp2f(sc - mn);
+    l = l * a + e;
+    acc[0] = acc[0] * a + e * bf16_lo(vv.x), acc[1] = acc[1] * a + e * bf16_hi(vv.x);
+    acc[2] = acc[2] * a + e * bf16_lo(vv.y), acc[3] = acc[3] * a + e * bf16_hi(vv.y);
+    acc[4] = acc[4] * a + e * bf16_lo(vv.z), acc[5] = acc[5] * a + e * bf16_hi(vv.z);
+    acc[6] = acc[6] * a + e * bf16_lo(vv.w), acc[7] = acc[7] * a + e * bf16_hi(vv.w);
+    m = mn;
+  };
+
+  if (SELF && sp == 0 && tid < 32) {
+    // The new key and value: rounded to bf16 into the cache at position n, and attended as stored. `attend` shuffles
+    // across the warp, so all of warp 0 goes through it with only group 0 (lanes 0 .. LPK-1) valid.
+    const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 8;
+    const float* vp = kp + p.H * D;
+    const float4 k0 = ld_cg_f4(kp), k1 = ld_cg_f4(kp + 4), v0 = ld_cg_f4(vp), v1 = ld_cg_f4(vp + 4);
+    const uint4 kk = make_uint4(pack_bf16(k0.x, k0.y), pack_bf16(k0.z, k0.w), pack_bf16(k1.x, k1.y),
+                                pack_bf16(k1.z, k1.w));
+    const uint4 vv = make_uint4(pack_bf16(v0.x, v0.y), pack_bf16(v0.z, v0.w), pack_bf16(v1.x, v1.y),
+                                pack_bf16(v1.z, v1.w));
+    if (grp == 0) {
+      *reinterpret_cast<uint4*>(p.k + base + (size_t)n * D) = kk;
+      *reinterpret_cast<uint4*>(p.v + base + (size_t)n * D) = vv;
+    }
+    attend(kk, vv, grp == 0);
+  }
+
+  // cached keys [start, end) of this split, group g taking start + g, + NG, ...
+  const int chunk = (n + nsp - 1) / nsp, start = sp * chunk, end = min(n, start + chunk);
+  const __nv_bfloat16* kb = p.k + base;
+  const __nv_bfloat16* vb = p.v + base;
+  // whole-warp trip count: every lane runs the same number of iterations (shuffles), invalid keys are masked
+  const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
+  for (int j0 = first; j0 < end; j0 += NG * U) {
+    const int j = j0 + (grp % (32 / LPK));
+    uint4 kk[U], vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int jj = j + u * NG;
+      const bool ok = jj < end;
+      kk[u] = ok ? ld_stream16(kb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+      vv[u] = ok ? ld_stream16(vb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (j0 + u * NG < end) attend(kk[u], vv[u], j + u * NG < end);  // warp-uniform condition
+    }
+  }
+
+  // merge the groups
+  if (gl == 0) s_m[grp] = m, s_l[grp] = l;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s_acc[grp][gl * 8 + i] = acc[i];
+  __syncthreads();
+  float M = -1e30f, L = 0.f, O = 0.f;
+  if (tid < D) {
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) M = fmaxf(M, s_m[gi]);
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      const float w = exp2f(s_m[gi] - M);
+      L += w * s_l[gi];
+      O += w * s_acc[gi][tid];
+    }
+  }
+  auto store = [&](float val) {
+    const size_t o = (size_t)r * p.H * D + h * D + tid;
+    if (p.out_kind == B200DEC_OUT_F16)
+      reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(clamp_h(val));
+    else
+      reinterpret_cast<float*>(p.out)[o] = val;
+  };
+  if (nsp == 1) {
+    if (tid < D) store(O / L);
+    return;
+  }
+  // split: partial to the workspace, the last CTA of this (row, head) merges
+  const int item = r * p.H + h;
+  float* part = p.part + ((size_t)item * MAX_SPLITS + sp) * (D + 2);
+  if (tid < D) part[tid] = O;
+  if (tid == 0) part[D] = M, part[D + 1] = L;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(p.count + item, 1) == nsp - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid < D) {
+    const float* pb = p.part + (size_t)item * MAX_SPLITS * (D + 2);
+    float MM = -1e30f;
+    for (int i = 0; i < nsp; ++i) MM = fmaxf(MM, __ldcg(pb + i * (D + 2) + D));
+    float LL = 0.f, OO = 0.f;
+    for (int i = 0; i < nsp; ++i) {
+      const float w = exp2f(__ldcg(pb + i * (D + 2) + D) - MM);
+      LL += w * __ldcg(pb + i * (D + 2) + D + 1);
+      OO += w * __ldcg(pb + i * (D + 2) + tid);
+    }
+    store(OO / LL);
+  }
+  if (tid == 0) p.count[item] = 0;
+}
+
+int pick_splits(int rows, int heads, int cap) {
+  // enough CTAs for every SM to hold several, but at least ~32 keys per split
+  const int items = rows * heads;
+  int s = (4 * 148 + items - 1) / items;
+  const int by_len = cap / 32 > 1 ? cap / 32 : 1;
+  if (s > by_len) s = by_len;
+  if (s > MAX_SPLITS) s = MAX_SPLITS;
+  return s < 1 ? 1 : s;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim) {
+  return (int64_t)rows * heads * MAX_SPLITS * (head_dim + 2);
+}
+
+int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                      const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
+                      int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream) {
+  B200_REQUIRE(active && q && kcache && vcache && n && out && status, "attention: null pointer");
+  B200_REQUIRE(head_dim == 64 || head_dim == 128, "attention: head_dim %d (64 or 128)", head_dim);
+  B200_REQUIRE(rows >= 1 && rows <= 65535 && heads >= 1 && cap >= 1, "attention: rows %d heads %d cap %d", rows,
+               heads, cap);
+  B200_REQUIRE(ldq % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
+                   ((uintptr_t)vcache & 15) == 0, "attention: alignment");
+  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "attention: out_kind");
+  AttnArgs p{};
+  p.active = active, p.q = q, p.k = (__nv_bfloat16*)kcache, p.v = (__nv_bfloat16*)vcache, p.n = n, p.out = out;
+  p.part = part, p.count = count, p.status = status;
+  p.ldq = ldq, p.H = heads, p.cap = cap, p.slots = slots, p.out_kind = out_kind, p.rows = rows;
+  p.splits = (part && count) ? pick_splits(rows, heads, cap) : 1;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const dim3 grid(heads, rows, p.splits);
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
+  if (head_dim == 64)
+    e = self ? launch_kernel(attention_kernel<64, true>, grid, dim3(NTHREADS), 0, s, 0, pdl, p)
+             : launch_kernel(attention_kernel<64, false>, grid, dim3(NTHREADS), 0, s, 0, pdl, p);
+  else
+    e = self ? launch_kernel(attention_kernel<128, true>, grid, dim3(NTHREADS), 0, s, 0, pdl, p)
+             : launch_kernel(attention_kernel<128, false>, grid, dim3(NTHREADS), 0, s, 0, pdl, p);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // extern "C"

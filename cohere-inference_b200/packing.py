@@ -1,0 +1,156 @@
+"""Weight packers on the GPU with the reference's names and results, and the tiled weights the step kernels read.
+
+prepare_w8 / quantize_rows / prune_24_magnitude / compress_24 return the same tensors as the reference functions
+(kernels/stream_decoder.py:41-48, kernels/fast_encoder.py:60-63, kernels/sparse.py:26-46), bit for bit, computed by the
+library's kernels. PackedLinear holds one projection re-tiled for csrc/linear.cu together with the operands the
+reference-format tensors were made from, so tests can check both.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import native as nv
+
+
+def _f32(w: torch.Tensor) -> torch.Tensor:
+    assert w.is_cuda and w.dim() == 2
+    return w.detach().float().contiguous()
+
+
+def quantize_rows(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """int8 (N, K), fp32 scales (N,): s = max(absmax, 1e-12) / 127, q = clamp(round(w / s), -127, 127)."""
+    w = _f32(w)
+    n, k = w.shape
+    q = torch.empty(n, k, dtype=torch.int8, device=w.device)
+    s = torch.empty(n, dtype=torch.float32, device=w.device)
+    nv.check(nv.lib().b200dec_quantize_rows(nv.ptr(w), n, k, nv.ptr(q), nv.ptr(s), nv.stream_ptr()))
+    return q, s
+
+
+def prepare_w8(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """The reference's dec_w8_linear operand: uint8 = int8 + 128, K reordered within every 16 (W8_PERM), fp32 scales."""
+    w = _f32(w)
+    n, k = w.shape
+    u = torch.empty(n, k, dtype=torch.uint8, device=w.device)
+    s = torch.empty(n, dtype=torch.float32, device=w.device)
+    nv.check(nv.lib().b200dec_prepare_w8(nv.ptr(w), n, k, nv.ptr(u), nv.ptr(s), nv.stream_ptr()))
+    return u, s
+
+
+def prune_24_magnitude(w: torch.Tensor) -> torch.Tensor:
+    """w with the two smallest-magnitude values of every four along K set to zero (fp32 result)."""
+    w = _f32(w)
+    out = torch.empty_like(w)
+    nv.check(nv.lib().b200dec_prune24(nv.ptr(w), w.shape[0], w.shape[1], nv.ptr(out), nv.stream_ptr()))
+    return out
+
+
+def compress_24(q: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """int8 (N, K) with at most two nonzeros per four -> kept values int8 (N, K/2), selectors int32 (N, K/32)."""
+    assert q.is_cuda and q.dtype == torch.int8 and q.dim() == 2 and q.shape[1] % 32 == 0
+    q = q.contiguous()
+    n, k = q.shape
+    kept = torch.empty(n, k // 2, dtype=torch.int8, device=q.device)
+    words = torch.empty(n, k // 32, dtype=torch.int32, device=q.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=q.device)
+    nv.check(nv.lib().b200dec_compress24(nv.ptr(q), n, k, nv.ptr(kept), nv.ptr(words), nv.ptr(bad), nv.stream_ptr()))
+    assert int(bad.item()) == 0, "more than two nonzero values in a group of four"
+    return kept, words
+
+
+# (N, K) -> (warps per CTA, CTAs per cluster along K) by weight kind: CTAs = N / (16 warps) * ksplit, K / ksplit in
+# {128, 256, 512}. Chosen so every projection spreads over about one CTA per SM (148) or two.
+TILE_CONFIG = {
+    (3072, 1024): (4, 4),
+    (1024, 1024): (4, 8),
+    (4096, 1024): (4, 4),
+    (1024, 4096): (4, 8),
+    (16384, 1024): (8, 2),
+}
+
+
+def tile_config(n: int, k: int, kind: int, split_rows128: bool = False) -> tuple[int, int]:
+    warps, ksplit = TILE_CONFIG.get((n, k), (4, max(1, k // 256)))
+    if split_rows128 and k // ksplit > 256:  # a split fp32 operand of 128 rows fits shared memory up to 256 per CTA
+        ksplit = k // 256
+    while k // ksplit > 512:
+        ksplit *= 2
+    assert ksplit in (1, 2, 4, 8) and k // ksplit in (128, 256, 512), (n, k, ksplit)
+    assert (16 * warps) % (8 * ksplit) == 0
+    return warps, ksplit
+
+
+@dataclass
+class PackedLinear:
+    kind: int
+    n: int
+    k: int
+    tiled: torch.Tensor
+    meta: torch.Tensor | None
+    scale: torch.Tensor | None
+    bias: torch.Tensor | None
+    warps: int
+    ksplit: int
+    # reference-format operands (kept only when keep_reference=True)
+    q: torch.Tensor | None = None
+    kept: torch.Tensor | None = None
+    words: torch.Tensor | None = None
+
+    def struct(self) -> nv.Weight:
+        return nv.Weight(nv.ptr(self.tiled), nv.ptr(self.meta), nv.ptr(self.scale), nv.ptr(self.bias), self.n, self.k,
+                         self.kind, self.warps, self.ksplit)
+
+    def stream_bytes(self) -> int:
+        """Bytes a step reads for this projection: weights (+ selectors) + 4 B scale + bias per channel as stored."""
+        b = self.tiled.numel() * self.tiled.element_size()
+        if self.meta is not None:
+            b += self.meta.numel() * 4
+        if self.scale is not None:
+            b += self.n * 4
+        if self.bias is not None:
+            b += self.n * 4
+        return b
+
+
+def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep_reference: bool = False,
+                split_rows128: bool = False) -> PackedLinear:
+    """One (N, K) projection into the streaming layout of the given kind (native.W_BF16 / W_INT8 / W_INT8_24)."""
+    w = _f32(weight)
+    n, k = w.shape
+    lib = nv.lib()
+    warps, ksplit = tile_config(n, k, kind, split_rows128)
+    b = None if bias is None else bias.detach().float().contiguous()
+    dev = w.device
+    tiled = torch.empty(lib.b200dec_tiled_bytes(kind, n, k), dtype=torch.uint8, device=dev)
+    meta = scale = q = kept = words = None
+    if kind == nv.W_BF16:
+        wb = w.to(torch.bfloat16).contiguous()
+        nv.check(lib.b200dec_tile_bf16(nv.ptr(wb), n, k, nv.ptr(tiled), nv.stream_ptr()))
+    elif kind == nv.W_INT8:
+        q, scale = quantize_rows(w)
+        nv.check(lib.b200dec_tile_int8(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
+    elif kind == nv.W_INT8_24:
+        q, scale = quantize_rows(prune_24_magnitude(w))
+        kept, words = compress_24(q)
+        meta = torch.empty(lib.b200dec_tiled_meta_bytes(kind, n, k) // 4, dtype=torch.int32, device=dev)
+        nv.check(lib.b200dec_tile_24(nv.ptr(kept), nv.ptr(words), n, k, nv.ptr(tiled), nv.ptr(meta), nv.stream_ptr()))
+    else:
+        raise ValueError(kind)
+    torch.cuda.current_stream().synchronize()  # the temporaries above may be freed once the tilers are done
+    if not keep_reference:
+        q = kept = words = None
+    return PackedLinear(kind, n, k, tiled, meta, scale, b, warps, ksplit, q, kept, words)
+
+
+def dequantized(weight: torch.Tensor, kind: int) -> torch.Tensor:
+    """fp32 weights the packed projection multiplies by (what an fp32 comparison should use)."""
+    w = _f32(weight)
+    if kind == nv.W_BF16:
+        return w.to(torch.bfloat16).float()
+    if kind == nv.W_INT8_24:
+        w = prune_24_magnitude(w)
+    q, s = quantize_rows(w)
+    return q.float() * s[:, None]

@@ -1,0 +1,306 @@
+"""Greedy decoding with continuous batching on one B200: the reference's StreamDecoder API over the b200dec kernels.
+
+Drop-in for kernels/stream_decoder.py:65-276 of the reference: the same constructor arguments, attributes (`device`,
+`out`, `flags`, `stream`, `eos`, `max_new_tokens`, `buckets`, `slots`, `dummy`) and methods (`fill_cross`, `admit`,
+`set_active`, `step`, `reset`, `bucket`) with the same meaning, so the reference's Pipeline (kernels/pipeline.py) can
+drive it unchanged. Row r of a step works on slot active[r]; rows past the live ones point at the dummy slot; a step
+is one CUDA-graph launch per bucket of row counts; the prompt is fed by the steps themselves as forced tokens; the
+end flags are copied to pinned host memory by the graph.
+
+What differs underneath: every kernel is hand-written CUDA for sm_100a behind a C-ABI (include/b200dec.h), there is no
+Triton and no cuBLAS on the step; `int8=True` quantises every projection (also o, cross q, cross o and the cross K/V
+projections), `ffn_sparse=True` additionally stores fc1/fc2 2:4; the residual stream is fp32; heads x head_dim may be
+8 x 128 or 16 x 64 and the feed-forward activation ReLU or GELU (read from model.config).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.nn.functional as F
+
+from . import native as nv
+from .packing import PackedLinear, dequantized, pack_linear
+
+ACTS = {"relu": nv.ACT_RELU, "gelu": nv.ACT_GELU}
+
+
+class _Layer:
+    """Packed projections and fp32 norms of one decoder layer (reference: _Layer, stream_decoder.py:51-62)."""
+
+    def __init__(self, layer, kind: int, ffn_kind: int, wide: bool, keep_reference: bool):
+        sa, ca = layer.self_attn, layer.encoder_attn
+        dev = sa.q_proj.weight.device
+        f = lambda t: t.detach().float().contiguous()  # noqa: E731
+        self.norms = [(f(m.weight), f(m.bias), float(m.eps)) for m in
+                      (layer.input_layernorm, layer.post_attention_layernorm, layer.final_layernorm)]
+        cat = lambda *p: torch.cat([f(x) for x in p]).contiguous()  # noqa: E731
+        pk = lambda w, b, k: pack_linear(w, b, k, keep_reference, wide)  # noqa: E731
+        self.qkv = pk(cat(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight),
+                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), kind)
+        self.o = pk(sa.o_proj.weight, sa.o_proj.bias, kind)
+        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, kind)
+        self.co = pk(ca.o_proj.weight, ca.o_proj.bias, kind)
+        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, ffn_kind)
+        self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, ffn_kind)
+        assert dev.type == "cuda"
+
+    def projections(self) -> list[PackedLinear]:
+        return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
+
+
+class StreamDecoder:
+    BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 80, 96, 112, 128)
+
+    def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
+                 max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
+                 eos: int | None = None, record: bool = False, pdl: bool = True, graphs: bool = True,
+                 head_split: bool = True, keep_reference: bool = False):
+        """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
+        int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
+        accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
+        magnitude-pruned 2:4 and stored compressed (needs int8). eos: overrides config.eos_token_id (-1: never end on
+        a token). record: keep the last step's logits and every slot's un-forced argmax (teacher forcing, tests).
+        pdl: chain the step's kernels with programmatic dependent launch. graphs: capture one CUDA graph per bucket
+        (False: launch the kernels directly, for debugging)."""
+        nv.lib()  # fail now, loudly, if the CUDA library is missing
+        assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
+        dec, cfg = model.model.decoder, model.config
+        self.embed_src = dec.embed_tokens.weight
+        dev = self.embed_src.device
+        assert dev.type == "cuda", "StreamDecoder needs the model on a CUDA device: there is no CPU path"
+        self.device = dev
+        self.buckets = tuple(b for b in (buckets or self.BUCKETS) if b <= slots)
+        self.model, self.max_new_tokens = model, max_new_tokens
+        self.h, self.d, self.width = cfg.num_attention_heads, cfg.head_dim, cfg.hidden_size
+        assert self.width == 1024 and (self.h, self.d) in ((8, 128), (16, 64)), "1024 wide, 8 x 128 or 16 x 64 heads"
+        self.eos = cfg.eos_token_id if eos is None else eos
+        self.pad = cfg.pad_token_id
+        self.scale = self.d ** -0.5
+        self.int8, self.ffn_sparse, self.pdl, self.use_graphs = int8, ffn_sparse, pdl, graphs
+        self.act = ACTS[cfg.hidden_act]
+        kind = nv.W_INT8 if int8 else nv.W_BF16
+        ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
+        self.a_kind = nv.A_F16 if int8 else nv.A_F32_SPLIT
+        self.head_a_kind = nv.A_F32_SPLIT if (head_split or not int8) else nv.A_F16
+        wide = max(self.buckets) > 64  # split fp32 operands of > 64 rows: at most 256 of K per CTA
+        with torch.cuda.device(dev):
+            f = lambda t: t.detach().float().contiguous()  # noqa: E731
+            self.embed = dec.embed_tokens.weight.detach().to(torch.bfloat16).contiguous()
+            self.pos_table = dec.pos_emb.weight.detach().to(torch.bfloat16).contiguous()
+            self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
+            ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
+            self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
+            self.layers = [_Layer(layer, kind, ffn_kind, wide and self.a_kind == nv.A_F32_SPLIT, keep_reference)
+                           for layer in dec.layers]
+            self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, kind, keep_reference,
+                                    wide and self.head_a_kind == nv.A_F32_SPLIT)
+            # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection, kept as the
+            # fp32 values the quantised (or bf16) weights stand for
+            self.proj = (dequantized(dec.proj.weight, kind), f(dec.proj.bias))
+            self.cross_w = torch.cat([dequantized(w, kind) for layer in dec.layers
+                                      for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)])
+            self.cross_b = torch.cat([f(b) for layer in dec.layers
+                                      for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)])
+            L, S = len(self.layers), slots
+            self.slots, self.dummy = S, S
+            self.max_prompt = max_prompt
+            self.seq = max_prompt + max_new_tokens + 1
+            assert self.seq <= self.max_pos, "positions exceed the learned position table"
+            self.frames = int(model.model.encoder._get_subsampling_output_length(
+                torch.tensor([int(max_audio_s * 100) + 1])).item())
+            bf = dict(device=dev, dtype=torch.bfloat16)
+            self.self_k = torch.zeros(L, S + 1, self.h, self.seq, self.d, **bf)
+            self.self_v = torch.zeros_like(self.self_k)
+            self.cross_k = torch.zeros(L, S + 1, self.h, self.frames, self.d, **bf)
+            self.cross_v = torch.zeros_like(self.cross_k)
+            i32 = dict(device=dev, dtype=torch.int32)
+            self.cross_len = torch.ones(S + 1, **i32)
+            self.tok = torch.full((S + 1,), self.pad, device=dev, dtype=torch.long)
+            self.pos = torch.zeros(S + 1, **i32)
+            self.plen = torch.ones(S + 1, **i32)
+            self.limit = torch.zeros(S + 1, **i32)
+            self.finished = torch.ones(S + 1, device=dev, dtype=torch.uint8)
+            self.forced = torch.full((S + 1, max_prompt), self.pad, device=dev, dtype=torch.long)
+            self.out = torch.full((S + 1, self.seq + 1), self.pad, device=dev, dtype=torch.long)
+            bm = max(self.buckets)
+            self.active = torch.full((bm,), S, **i32)
+            self.status = torch.zeros(1, **i32)
+            adt = torch.float16 if self.a_kind == nv.A_F16 else torch.float32
+            hdt = torch.float16 if self.head_a_kind == nv.A_F16 else torch.float32
+            f32 = dict(device=dev, dtype=torch.float32)
+            self.x = torch.zeros(bm, self.width, **f32)
+            self.hn = torch.zeros(bm, self.width, device=dev, dtype=adt)
+            self.hn_head = torch.zeros(bm, self.width, device=dev, dtype=hdt)
+            self.qkv = torch.zeros(bm, 3 * self.width, **f32)
+            self.cq = torch.zeros(bm, self.width, **f32)
+            self.att = torch.zeros(bm, self.width, device=dev, dtype=adt)
+            self.ffn = self.layers[0].fc1.n
+            self.mid = torch.zeros(bm, self.ffn, device=dev, dtype=adt)
+            lib = nv.lib()
+            self.attn_part = torch.zeros(lib.b200dec_attention_scratch_floats(bm, self.h, self.d), **f32)
+            self.attn_count = torch.zeros(bm * self.h, **i32)
+            self.head_partials = lib.b200dec_head_partials(C.byref(self.head.struct()))
+            self.head_max = torch.zeros(bm, self.head_partials, **f32)
+            self.head_idx = torch.zeros(bm, self.head_partials, **i32)
+            self.logits = torch.zeros(bm, self.vocab, **f32) if record else None
+            self.argmax = torch.zeros(S + 1, device=dev, dtype=torch.long) if record else None
+            # host side: the end flags after each step (pinned, copied by the step itself)
+            self.flags = torch.ones(S + 1, dtype=torch.uint8).pin_memory()
+            self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+            self.stream = torch.cuda.Stream(device=dev, priority=-1)
+            self._build_plan()
+            self.launches_per_step = lib.b200dec_step_launches(C.byref(self.plan), 1)
+            self.weight_bytes = sum(p.stream_bytes() for ly in self.layers for p in ly.projections()) + \
+                self.head.stream_bytes()
+            if graphs:
+                self._capture()
+            else:
+                self.reset()
+                self.stream.synchronize()
+
+    # ---- the step ------------------------------------------------------------------------------------------------
+
+    def _build_plan(self) -> None:
+        L = len(self.layers)
+        self._layer_structs = (nv.Layer * L)()
+        for i, ly in enumerate(self.layers):
+            s = self._layer_structs[i]
+            s.ln1, s.ln2, s.ln3 = (nv.norm(*n) for n in ly.norms)
+            s.qkv, s.o, s.cq, s.co = ly.qkv.struct(), ly.o.struct(), ly.cq.struct(), ly.co.struct()
+            s.fc1, s.fc2 = ly.fc1.struct(), ly.fc2.struct()
+            s.self_k, s.self_v = nv.ptr(self.self_k[i]), nv.ptr(self.self_v[i])
+            s.cross_k, s.cross_v = nv.ptr(self.cross_k[i]), nv.ptr(self.cross_v[i])
+        p = nv.Plan()
+        p.layers, p.heads, p.head_dim, p.act = L, self.h, self.d, self.act
+        p.slots, p.seq, p.frames, p.vocab = self.slots, self.seq, self.frames, self.vocab
+        p.max_prompt, p.out_cols, p.pad, p.eos = self.max_prompt, self.out.shape[1], self.pad, self.eos
+        p.a_kind, p.max_pos, p.head_a_kind, p.pdl = self.a_kind, self.max_pos, self.head_a_kind, int(self.pdl)
+        p.embed, p.pos_table = nv.ptr(self.embed), nv.ptr(self.pos_table)
+        p.emb_ln, p.final_ln = nv.norm(*self.emb_ln), nv.norm(*self.final_ln)
+        p.layer = C.cast(self._layer_structs, C.POINTER(nv.Layer))
+        p.head = self.head.struct()
+        for name in ("active", "tok", "pos", "plen", "limit", "cross_len", "finished", "forced", "out", "status", "x",
+                     "hn", "hn_head", "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
+                     "logits", "argmax"):
+            setattr(p, name, nv.ptr(getattr(self, name)))
+        self.plan = p
+
+    def _step(self, b: int) -> None:
+        """Bucket b's kernels and the flags' copy on the current stream (reference: _step, stream_decoder.py:176-199)."""
+        nv.check(nv.lib().b200dec_step(C.byref(self.plan), b, nv.stream_ptr()))
+        self.flags.copy_(self.finished, non_blocking=True)
+
+    @torch.no_grad()
+    def _capture(self) -> None:
+        pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.device(self.device), torch.cuda.stream(self.stream):
+            for b in reversed(self.buckets):
+                self._step(b)  # sets the kernels' shared-memory attributes and surfaces launch errors before capture
+                torch.cuda.current_stream().synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=pool, stream=self.stream):
+                    self._step(b)
+                self.graphs[b] = g
+            self.reset()
+        self.stream.synchronize()
+        self.check_status()
+
+    def reset(self) -> None:
+        """All slots free (on the decoder stream)."""
+        with torch.cuda.stream(self.stream):
+            self.finished.fill_(1)
+            self.pos.zero_()
+            self.cross_len.fill_(1)
+            self.active.fill_(self.dummy)
+            self.status.zero_()
+            self.attn_count.zero_()
+
+    def check_status(self) -> None:
+        """Synchronises the decoder stream and raises if a kernel met an index outside its tables (the kernels clamp
+        the index, set a bit and go on, so the context stays usable)."""
+        self.stream.synchronize()
+        st = int(self.status.item())
+        if st:
+            names = [n for n, bit in (("token id", nv.ST_TOKEN_RANGE), ("position", nv.ST_POS_RANGE),
+                                      ("frame count", nv.ST_FRAMES_RANGE), ("slot", nv.ST_SLOT_RANGE)) if st & bit]
+            raise nv.NativeError("decoder kernels saw out-of-range " + ", ".join(names))
+
+    # ---- host side -----------------------------------------------------------------------------------------------
+
+    def bucket(self, rows: int) -> int:
+        return next(b for b in self.buckets if b >= rows)
+
+    @torch.no_grad()
+    def fill_cross(self, hidden: torch.Tensor, lengths: list[int], slots: list[int]) -> None:
+        """Cross-attention keys and values of packed encoder frames (sum(lengths), enc_dim) into the given slots, on
+        the current stream (the caller orders the decoder stream after it)."""
+        assert hidden.shape[0] == sum(lengths) and len(lengths) == len(slots)
+        assert all(1 <= n <= self.frames for n in lengths), "frames per piece outside 1..%d" % self.frames
+        assert all(0 <= s < self.slots for s in slots)
+        kv = F.linear(F.linear(hidden.float(), *self.proj), self.cross_w, self.cross_b).contiguous()
+        slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lengths))
+        frame_of = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths])
+        slot_of, frame_of = slot_of.to(self.device, non_blocking=True), frame_of.to(self.device, non_blocking=True)
+        nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
+                                             nv.ptr(self.cross_v), kv.shape[0], len(self.layers), self.slots + 1,
+                                             self.h, self.d, self.frames, nv.stream_ptr()))
+        kv.record_stream(torch.cuda.current_stream())
+
+    def admit(self, slots: list[int], prompts: list[torch.Tensor], frames: list[int],
+              max_new: list[int] | None = None) -> None:
+        """Start decoding in the given slots (on the decoder stream): the prompt forced, cross_len frames of audio."""
+        n = len(slots)
+        assert all(0 <= s < self.slots for s in slots) and all(1 <= len(p) <= self.max_prompt for p in prompts)
+        assert all(1 <= f <= self.frames for f in frames)
+        new = max_new or [self.max_new_tokens] * n
+        assert all(1 <= m <= self.max_new_tokens for m in new)
+        idx = torch.tensor(slots, dtype=torch.long)
+        forced = torch.full((n, self.max_prompt), self.pad, dtype=torch.long)
+        plen = torch.tensor([len(p) for p in prompts], dtype=torch.int32)
+        for i, p in enumerate(prompts):
+            forced[i, :len(p)] = torch.as_tensor(p, dtype=torch.long)
+        limit = plen - 1 + torch.tensor(new, dtype=torch.int32)
+        with torch.cuda.stream(self.stream):
+            d = lambda t: t.to(self.device, non_blocking=True)  # noqa: E731
+            di = d(idx)
+            self.forced[di] = d(forced)
+            self.out[di] = self.pad
+            self.out[di, :self.max_prompt] = d(forced)
+            self.tok[di] = d(forced[:, 0].contiguous())
+            self.pos[di] = 0
+            self.plen[di] = d(plen)
+            self.limit[di] = d(limit)
+            self.cross_len[di] = d(torch.tensor(frames, dtype=torch.int32))
+            self.finished[di] = 0
+        self.flags[idx] = 0
+
+    def set_active(self, slots: list[int]) -> int:
+        """The active list for the next steps (on the decoder stream); returns the bucket."""
+        b = self.bucket(max(1, len(slots)))
+        host = torch.full((b,), self.dummy, dtype=torch.int32)
+        host[:len(slots)] = torch.tensor(slots, dtype=torch.int32)
+        with torch.cuda.stream(self.stream):
+            self.active[:b].copy_(host.pin_memory(), non_blocking=True)
+        return b
+
+    def step(self, bucket: int) -> None:
+        with torch.cuda.stream(self.stream):
+            if self.use_graphs:
+                self.graphs[bucket].replay()
+            else:
+                self._step(bucket)
+
+    # ---- accounting ------------------------------------------------------------------------------------------------
+
+    def step_bytes(self, positions, frames, rows: int | None = None) -> int:
+        """Algorithmic HBM bytes of one step whose live rows are at `positions` with `frames` encoder frames each
+        (rows: the bucket, counting padding rows on the dummy slot as position 0 / 1 frame): every projection's
+        weights once, each row's keys and values of both attentions in all layers, the appended key and value, the
+        two embedding rows."""
+        L, d = len(self.layers), self.width
+        pad = (rows or len(positions)) - len(positions)
+        kv = sum((int(p) + 1) + int(t) for p, t in zip(positions, frames)) + pad * 2
+        n = len(positions) + pad
+        return self.weight_bytes + L * 2 * d * 2 * kv + n * L * 2 * d * 2 + n * 2 * d * 2

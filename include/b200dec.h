@@ -1,0 +1,173 @@
+/* b200dec: C-ABI of the B200 (sm_100a) decoder token loop.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*, a cudaStream_t), launches
+ * on that stream and returns 0, or a nonzero code with a message in b200dec_last_error(). No entry point allocates,
+ * frees, synchronises or throws, so all of them may be called while the stream is being captured into a CUDA graph.
+ * The caller owns every buffer. Citations name the interface of the reference project (kadirnar/cohere-inference) that
+ * each entry point replaces, as file:line inside that project.
+ *
+ * Conventions: d_model is 1024; "rows" are the rows of one decoding step (row r works on slot active[r]); a16 = IEEE
+ * half activations, f32 = float. Weight matrices are (N, K) row-major on the reference side and are re-tiled once by
+ * the b200dec_tile_* calls into the streaming layout of the GEMM kernels (described in csrc/linear.cu).
+ */
+#ifndef B200DEC_H
+#define B200DEC_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2 };   /* weight storage of one projection */
+enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1 };                       /* activation operand of a projection */
+enum { B200DEC_OUT_F16 = 0, B200DEC_OUT_F32 = 1, B200DEC_OUT_F32_ADD = 2 };/* store, or add into an fp32 residual */
+enum { B200DEC_ACT_NONE = 0, B200DEC_ACT_RELU = 1, B200DEC_ACT_GELU = 2 };
+enum { B200DEC_OK = 0, B200DEC_EINVAL = 1, B200DEC_ECUDA = 2, B200DEC_EARCH = 3 };
+
+/* bits of the device status word (written by kernels, never cleared by them) */
+enum { B200DEC_ST_TOKEN_RANGE = 1, B200DEC_ST_POS_RANGE = 2, B200DEC_ST_FRAMES_RANGE = 4, B200DEC_ST_SLOT_RANGE = 8 };
+
+/* One projection y = a W^T (* scale) + bias in the tiled layout. */
+typedef struct b200dec_weight {
+  const void* w;       /* tiled weights: int8 (+128), bf16, or the kept values of a 2:4 matrix */
+  const void* meta;    /* tiled 2:4 selectors, else NULL */
+  const float* scale;  /* per output channel, int8 kinds; NULL for bf16 */
+  const float* bias;   /* per output channel or NULL */
+  int32_t n, k;        /* logical shape */
+  int32_t kind;        /* B200DEC_W_* */
+  int32_t warps;       /* output tile of a CTA = 16 * warps channels (4 or 8) */
+  int32_t ksplit;      /* CTAs of a cluster sharing K (1, 2, 4 or 8): K / ksplit in {128, 256, 512} */
+} b200dec_weight;
+
+typedef struct b200dec_norm {
+  const float* w;
+  const float* b;
+  float eps;
+  int32_t _pad;
+} b200dec_norm;
+
+typedef struct b200dec_layer {
+  b200dec_norm ln1, ln2, ln3;
+  b200dec_weight qkv, o, cq, co, fc1, fc2;
+  void* self_k;   /* bf16 (slots + 1, H, seq, D) */
+  void* self_v;
+  const void* cross_k; /* bf16 (slots + 1, H, frames, D) */
+  const void* cross_v;
+} b200dec_layer;
+
+/* Everything one decoding step touches. Replaces the argument lists of StreamDecoder._step
+ * (kernels/stream_decoder.py:176-199). */
+typedef struct b200dec_plan {
+  int32_t layers, heads, head_dim, act;      /* act: B200DEC_ACT_* of the feed-forward */
+  int32_t slots, seq, frames, vocab;         /* dummy slot = slots; caches hold seq / frames positions */
+  int32_t max_prompt, out_cols, pad, eos;    /* forced (slots+1, max_prompt), out (slots+1, out_cols) */
+  int32_t a_kind, max_pos;                   /* B200DEC_A_*: operand precision of the layer projections */
+  int32_t head_a_kind, pdl;                  /* operand precision of the vocabulary projection; pdl != 0 chains
+                                                the kernels with programmatic dependent launch */
+  const void* embed;  /* bf16 (vocab, 1024) */
+  const void* pos_table; /* bf16 (max_pos, 1024) */
+  b200dec_norm emb_ln, final_ln;
+  const b200dec_layer* layer;  /* host array of `layers` entries */
+  b200dec_weight head;
+  /* slot state (slots + 1 entries each) */
+  const int32_t* active;  /* (rows) */
+  int64_t* tok;
+  int32_t* pos;
+  const int32_t* plen;
+  const int32_t* limit;
+  const int32_t* cross_len;
+  uint8_t* finished;
+  const int64_t* forced;
+  int64_t* out;
+  int32_t* status;        /* one word, B200DEC_ST_* bits */
+  /* scratch owned by the caller */
+  float* x;       /* (max rows, 1024) residual stream */
+  void* hn;       /* (max rows, 1024) a16 or f32 by a_kind */
+  void* hn_head;  /* (max rows, 1024) a16 or f32 by head_a_kind */
+  float* qkv;     /* (max rows, 3072) */
+  float* cq;      /* (max rows, 1024) */
+  void* att;      /* (max rows, 1024) a16 or f32 */
+  void* mid;      /* (max rows, ffn) a16 or f32 */
+  float* attn_part;    /* b200dec_attention_scratch_floats() floats */
+  int32_t* attn_count; /* rows * heads counters, zero on entry and on exit */
+  float* head_max;     /* (max rows, b200dec_head_partials()) */
+  int32_t* head_idx;
+  /* optional recording (tests, teacher forcing); NULL in production */
+  float* logits;       /* (rows, vocab) */
+  int64_t* argmax;     /* (slots + 1): the un-forced greedy choice of each slot's last step */
+} b200dec_plan;
+
+const char* b200dec_last_error(void);
+int b200dec_version(void);
+
+/* ---- packing (init time) ------------------------------------------------------------------------------------ */
+
+/* Per-row symmetric int8: s = max(absmax, 1e-12) / 127, q = clamp(rint(w / s), -127, 127).
+ * Replaces quantize_rows (kernels/fast_encoder.py:60-63) and the arithmetic of prepare_w8
+ * (kernels/stream_decoder.py:45-46). */
+int b200dec_quantize_rows(const float* w, int n, int k, int8_t* q, float* scale, void* stream);
+/* The reference's dec_w8_linear layout: uint8 = q + 128, bytes of every 16 along K permuted by W8_PERM.
+ * Replaces prepare_w8 (kernels/stream_decoder.py:38-48), bit for bit. */
+int b200dec_prepare_w8(const float* w, int n, int k, uint8_t* u8, float* scale, void* stream);
+/* Zero the two smallest |w| of every four along K (lower index first on ties).
+ * Replaces prune_24_magnitude (kernels/sparse.py:42-46). */
+int b200dec_prune24(const float* w, int n, int k, float* out, void* stream);
+/* kept values (n, k/2) and selector words (n, k/32) of a 2:4 int8 matrix; *bad (device) is set to 1 if some group
+ * of four holds more than two nonzeros. Replaces compress_24 (kernels/sparse.py:26-39), bit for bit. */
+int b200dec_compress24(const int8_t* q, int n, int k, int8_t* kept, int32_t* words, int32_t* bad, void* stream);
+/* Streaming layouts of the GEMM kernels (no counterpart in the reference: its layout is prepare_w8's). */
+int64_t b200dec_tiled_bytes(int kind, int n, int k);      /* bytes of the weight part */
+int64_t b200dec_tiled_meta_bytes(int kind, int n, int k); /* bytes of the selector part (0 unless 2:4) */
+int b200dec_tile_int8(const int8_t* q, int n, int k, void* tiled, void* stream);
+int b200dec_tile_bf16(const void* w_bf16, int n, int k, void* tiled, void* stream);
+int b200dec_tile_24(const int8_t* kept, const int32_t* words, int n, int k, void* tiled, void* meta, void* stream);
+
+/* ---- step kernels ------------------------------------------------------------------------------------------- */
+
+/* x = LN_emb(embed[tok[s]] + pos_table[pos[s]]), hn = LN_1(x), s = active[r].
+ * Replaces dec_embed (kernels/csrc/decoder_ops.cu:24-54, 208-219). */
+int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
+                     const void* pos_table, int vocab, int max_pos, b200dec_norm ln0, b200dec_norm ln1, float* x,
+                     void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
+/* hn = LN(x) for an fp32 residual stream that the preceding projection already added into
+ * (B200DEC_OUT_F32_ADD). Replaces dec_add_ln (kernels/csrc/decoder_ops.cu:56-83, 221-231). */
+int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream);
+/* out = act(a W^T * scale + bias) for rows <= 128. Replaces dec_w8_linear (kernels/csrc/dec_w8.cu:46-234), the
+ * Triton _linear (kernels/decoder_kernels.py:19-66) and the cuBLAS F.linear of kernels/stream_decoder.py:23-27. */
+int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, void* out, int out_kind,
+                   int ldo, int act, int pdl, void* stream);
+/* Vocabulary projection fused with the per-tile argmax: writes, per row, b200dec_head_partials(w) (max, first index)
+ * pairs; logits (rows, n) fp32 optional. Replaces the head projection + the scan of dec_pick
+ * (kernels/stream_decoder.py:173-174, 197; kernels/csrc/decoder_ops.cu:106-147). */
+int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, float* part_max,
+                        int32_t* part_idx, float* logits, int pdl, void* stream);
+int b200dec_head_partials(const b200dec_weight* w);
+/* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and
+ * finished slots change nothing. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
+int b200dec_pick(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows,
+                 int dummy, int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
+                 const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
+                 int pdl, void* stream);
+/* One new token per row against its slot's cache. self != 0: q | k | v in qkv (rows, 3 * H * D) fp32, the new key and
+ * value are written at n[s] and attended, keys 0..n[s]; else q (rows, H * D) over n[s] frames. Caches bf16
+ * (slots + 1, H, cap, D). Replaces dec_attention (kernels/csrc/decoder_ops.cu:85-104, 235-261; dec_attn.cuh:84-188). */
+int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                      const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
+                      int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
+int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim);
+/* Packed cross keys/values kv (nrows, L * 2 * H * D) fp32, row i = frame frame_of[i] of slot slot_of[i], into the
+ * bf16 slot caches (L, slots + 1, H, frames, D). Replaces dec_scatter_kv (kernels/csrc/decoder_ops.cu:163-173,
+ * 316-327). */
+int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
+                       int nrows, int layers, int slots_plus_1, int heads, int head_dim, int frames, void* stream);
+/* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
+ * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
+int b200dec_step(const b200dec_plan* plan, int rows, void* stream);
+/* Kernels b200dec_step launches for `rows` rows (for launch accounting). */
+int b200dec_step_launches(const b200dec_plan* plan, int rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

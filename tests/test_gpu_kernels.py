@@ -1,0 +1,372 @@
+"""Per-kernel parity on a B200, every call through the C-ABI (ctypes): the packers bit-exact against the reference's
+outputs (tests/golden/packers.npz) and the numpy oracle, the tiled layouts against their specification, each step
+kernel against fp32 numpy on the same seeded inputs."""
+
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import packers as op
+from oracle.decoder import activation, bf16_round, layer_norm
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nv():
+    from cohere_inference_b200 import native
+    native.lib()
+    return native
+
+
+@pytest.fixture(scope="module")
+def pk():
+    from cohere_inference_b200 import packing
+    return packing
+
+
+def cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+# ---- packers -----------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("case", ["a", "b", "c"])
+def test_packers_bit_exact_vs_reference(pk, golden_dir, case):
+    g = np.load(os.path.join(golden_dir, "packers.npz"))
+    w = cuda(g[f"{case}_w"])
+    u8, s = pk.prepare_w8(w)
+    assert np.array_equal(u8.cpu().numpy(), g[f"{case}_u8"])
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), g[f"{case}_s"].view(np.uint32))
+    q, s2 = pk.quantize_rows(w)
+    assert np.array_equal(q.cpu().numpy(), op.unpermute_w8(g[f"{case}_u8"])) and torch.equal(s, s2)
+    pruned = pk.prune_24_magnitude(w).cpu().numpy()
+    rows = np.ones(pruned.shape[0], bool)
+    if case == "a":
+        rows[[3, 5]] = False  # exact ties: the reference leaves the choice to torch.topk
+    assert np.array_equal(pruned[rows], g[f"{case}_pruned"][rows])
+    assert np.array_equal(pruned, op.prune_24_magnitude(g[f"{case}_w"]))  # and the documented tie rule everywhere
+    kept, words = pk.compress_24(cuda(g[f"{case}_qp"]))
+    assert np.array_equal(kept.cpu().numpy(), g[f"{case}_kept"])
+    assert np.array_equal(words.cpu().numpy(), g[f"{case}_words"])
+
+
+def test_compress_patterns_and_rejects_dense(pk, golden_dir):
+    g = np.load(os.path.join(golden_dir, "packers.npz"))
+    kept, words = pk.compress_24(cuda(g["p_q"]))
+    assert np.array_equal(kept.cpu().numpy(), g["p_kept"]) and np.array_equal(words.cpu().numpy(), g["p_words"])
+    with pytest.raises(AssertionError):
+        pk.compress_24(torch.ones(16, 32, dtype=torch.int8, device="cuda"))
+
+
+def test_tiled_layouts(nv, pk):
+    rng = np.random.default_rng(3)
+    n, k = 64, 256
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    # int8: byte [nt][kb][h][lane = 4 g + t][e] = q[16 nt + g + 8 h][64 kb + 16 t + e] + 128
+    p = pk.pack_linear(cuda(w), None, nv.W_INT8, keep_reference=True)
+    q = p.q.cpu().numpy()
+    t = p.tiled.cpu().numpy().reshape(n // 16, k // 64, 2, 8, 4, 16)
+    want = (q.astype(np.int16) + 128).astype(np.uint8).reshape(n // 16, 2, 8, k // 64, 4, 16).transpose(0, 3, 1, 2, 4, 5)
+    assert np.array_equal(t, want)
+    assert np.array_equal(q, op.quantize_rows(w)[0])
+    # bf16: element [nt][kb][h][lane][e] = w[16 nt + g + 8 h][32 kb + 8 t + e]
+    p = pk.pack_linear(cuda(w), None, nv.W_BF16)
+    t = p.tiled.view(torch.bfloat16).float().cpu().numpy().reshape(n // 16, k // 32, 2, 8, 4, 8)
+    want = bf16_round(w).reshape(n // 16, 2, 8, k // 32, 4, 8).transpose(0, 3, 1, 2, 4, 5)
+    assert np.array_equal(t, want)
+    # 2:4: value byte [nt][kb][h][lane][2 s + j] = kept[row][2 G + j], G = 32 kb + 2 (4 (s / 2) + t) + (s & 1);
+    # selector nibble s of word [nt][kb][h][lane] = the selector of group G
+    p = pk.pack_linear(cuda(w), None, nv.W_INT8_24, keep_reference=True)
+    kept, words = p.kept.cpu().numpy(), p.words.cpu().numpy().view(np.uint32)
+    qd = op.quantize_rows(op.prune_24_magnitude(w))[0]
+    k2, w2 = op.compress_24(qd)
+    assert np.array_equal(kept, k2) and np.array_equal(words, w2.view(np.uint32))
+    tv = p.tiled.cpu().numpy().view(np.int8).reshape(n // 16, k // 128, 2, 8, 4, 8, 2)
+    tm = p.meta.cpu().numpy().view(np.uint32).reshape(n // 16, k // 128, 2, 8, 4)
+    nib = (words[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 15
+    nib = nib.reshape(n, k // 4)
+    for nt in range(n // 16):
+        for kb in range(k // 128):
+            for h in range(2):
+                for g in range(8):
+                    row = nt * 16 + g + 8 * h
+                    for tt in range(4):
+                        m = 0
+                        for s in range(8):
+                            G = kb * 32 + 2 * (4 * (s // 2) + tt) + (s & 1)
+                            assert tv[nt, kb, h, g, tt, s, 0] == kept[row, 2 * G]
+                            assert tv[nt, kb, h, g, tt, s, 1] == kept[row, 2 * G + 1]
+                            m |= int(nib[row, G]) << (4 * s)
+                        assert tm[nt, kb, h, g, tt] == m
+
+
+# ---- projections ---------------------------------------------------------------------------------------------------------
+
+SHAPES = [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (16384, 1024)]
+
+
+def _linear_case(nv, pk, kind, a_kind, n, k, rows, act, out_kind, seed, bias=True):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.1).astype(np.float32) if bias else None
+    a = rng.standard_normal((rows, k)).astype(np.float32)
+    x0 = rng.standard_normal((rows, n)).astype(np.float32)
+    p = pk.pack_linear(cuda(w), None if b is None else cuda(b), kind)
+    wd = pk.dequantized(cuda(w), kind).cpu().numpy()
+    if a_kind == nv.A_F16:
+        a_dev = cuda(a.astype(np.float16))
+        a_ref = a.astype(np.float16).astype(np.float32)
+    else:
+        a_dev, a_ref = cuda(a), a
+    y = a_ref.astype(np.float64) @ wd.astype(np.float64).T + (0 if b is None else b)
+    y = activation({nv.ACT_NONE: "none", nv.ACT_RELU: "relu", nv.ACT_GELU: "gelu"}[act], y.astype(np.float32)) \
+        if act != nv.ACT_NONE else y.astype(np.float32)
+    if out_kind == nv.OUT_F16:
+        out = torch.zeros(rows, n, dtype=torch.float16, device="cuda")
+    else:
+        out = cuda(x0) if out_kind == nv.OUT_F32_ADD else torch.zeros(rows, n, device="cuda")
+    ws = p.struct()
+    nv.check(nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a_dev), a_kind, k, rows, nv.ptr(out), out_kind, n, act, 0,
+                                     nv.stream_ptr()))
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    if out_kind == nv.OUT_F32_ADD:
+        y = y + x0
+    return got, y
+
+
+@pytest.mark.parametrize("n,k", SHAPES)
+@pytest.mark.parametrize("rows", [1, 8, 13, 64, 128])
+def test_linear_int8(nv, pk, n, k, rows):
+    got, want = _linear_case(nv, pk, nv.W_INT8, nv.A_F16, n, k, rows, nv.ACT_NONE, nv.OUT_F32, seed=n + rows)
+    # operands are exact (fp16 activations given, int8 weights): only the fp32 accumulation order differs
+    np.testing.assert_allclose(got, want, atol=2e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("kind,a_kind", [("W_INT8", "A_F32_SPLIT"), ("W_BF16", "A_F32_SPLIT"), ("W_INT8_24", "A_F16")])
+@pytest.mark.parametrize("n,k", [(1024, 1024), (4096, 1024), (1024, 4096)])
+@pytest.mark.parametrize("rows", [3, 64, 100])
+def test_linear_kinds(nv, pk, kind, a_kind, n, k, rows):
+    got, want = _linear_case(nv, pk, getattr(nv, kind), getattr(nv, a_kind), n, k, rows, nv.ACT_NONE, nv.OUT_F32,
+                             seed=7 * n + rows)
+    # split operand: ~2^-21 relative on the activations
+    np.testing.assert_allclose(got, want, atol=3e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("act", ["ACT_RELU", "ACT_GELU"])
+@pytest.mark.parametrize("out_kind", ["OUT_F16", "OUT_F32_ADD"])
+def test_linear_epilogues(nv, pk, act, out_kind):
+    got, want = _linear_case(nv, pk, nv.W_INT8, nv.A_F16, 4096, 1024, 24, getattr(nv, act), getattr(nv, out_kind), 11)
+    tol = 2e-3 if out_kind == "OUT_F16" else 2e-4
+    np.testing.assert_allclose(got, want, atol=tol, rtol=1e-3 if out_kind == "OUT_F16" else 1e-5)
+
+
+def test_linear_no_bias_and_pdl_flag(nv, pk):
+    got, want = _linear_case(nv, pk, nv.W_INT8, nv.A_F16, 1024, 1024, 5, nv.ACT_NONE, nv.OUT_F32, 5, bias=False)
+    np.testing.assert_allclose(got, want, atol=2e-4, rtol=1e-5)
+
+
+def test_linear_rejects_bad_arguments(nv, pk):
+    p = pk.pack_linear(torch.zeros(1024, 1024, device="cuda"), None, nv.W_INT8)
+    ws = p.struct()
+    a = torch.zeros(4, 1024, dtype=torch.float16, device="cuda")
+    out = torch.zeros(4, 1024, device="cuda")
+    rc = nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, 1024, 129, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
+                                 nv.stream_ptr())
+    assert rc == 1 and b"rows" in nv.lib().b200dec_last_error()
+    ws.ksplit = 3
+    assert nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, 1024, 4, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
+                                   nv.stream_ptr()) == 1
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("rows", [1, 7, 64, 128])
+@pytest.mark.parametrize("a_kind", ["A_F16", "A_F32_SPLIT"])
+def test_head_argmax(nv, pk, rows, a_kind):
+    rng = np.random.default_rng(rows)
+    n, k = 16384, 1024
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    a = rng.standard_normal((rows, k)).astype(np.float32)
+    p = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8, split_rows128=rows > 64 and a_kind == "A_F32_SPLIT")
+    wd = pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy()
+    if a_kind == "A_F16":
+        a_dev, a_ref = cuda(a.astype(np.float16)), a.astype(np.float16).astype(np.float32)
+    else:
+        a_dev, a_ref = cuda(a), a
+    ws = p.struct()
+    np_ = nv.lib().b200dec_head_partials(C.byref(ws))
+    pm = torch.zeros(rows, np_, device="cuda")
+    pi = torch.zeros(rows, np_, dtype=torch.int32, device="cuda")
+    logits = torch.zeros(rows, n, device="cuda")
+    nv.check(nv.lib().b200dec_head_argmax(C.byref(ws), nv.ptr(a_dev), getattr(nv, a_kind), k, rows, nv.ptr(pm),
+                                          nv.ptr(pi), nv.ptr(logits), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    want = (a_ref.astype(np.float64) @ wd.astype(np.float64).T + b).astype(np.float32)
+    lg = logits.cpu().numpy()
+    np.testing.assert_allclose(lg, want, atol=3e-4, rtol=1e-5)
+    # the partials are exactly the first-index maxima of the kernel's own logits, tile by tile
+    tile = n // np_
+    t = lg.reshape(rows, np_, tile)
+    assert np.array_equal(pm.cpu().numpy(), t.max(-1))
+    assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * tile)
+
+
+# ---- row kernels ---------------------------------------------------------------------------------------------------------
+
+def test_embed_ln_and_layer_norm(nv):
+    rng = np.random.default_rng(5)
+    vocab, max_pos, S, rows = 512, 64, 6, 5
+    emb = bf16_round((rng.standard_normal((vocab, 1024)) * 0.02).astype(np.float32))
+    ptab = bf16_round((rng.standard_normal((max_pos, 1024)) * 0.02).astype(np.float32))
+    lnp = [(1 + 0.1 * rng.standard_normal(1024)).astype(np.float32) if i % 2 == 0 else
+           (0.1 * rng.standard_normal(1024)).astype(np.float32) for i in range(4)]
+    active = np.array([3, 0, 6, 5, 1], np.int32)
+    tok = rng.integers(0, vocab, S + 1).astype(np.int64)
+    pos = rng.integers(0, max_pos, S + 1).astype(np.int32)
+    d = {k: cuda(v) for k, v in dict(w0=lnp[0], b0=lnp[1], w1=lnp[2], b1=lnp[3]).items()}
+    x = torch.zeros(rows, 1024, device="cuda")
+    hn = torch.zeros(rows, 1024, dtype=torch.float16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(cuda(active)), nv.ptr(cuda(tok)), nv.ptr(cuda(pos)),
+                                       nv.ptr(cuda(emb).to(torch.bfloat16)), nv.ptr(cuda(ptab).to(torch.bfloat16)), vocab,
+                                       max_pos, nv.norm(d["w0"], d["b0"], 1e-5), nv.norm(d["w1"], d["b1"], 1e-5),
+                                       nv.ptr(x), nv.ptr(hn), nv.OUT_F16, rows, nv.ptr(status), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    want_x = layer_norm(emb[tok[active]] + ptab[pos[active]], lnp[0], lnp[1], 1e-5)
+    want_h = layer_norm(want_x, lnp[2], lnp[3], 1e-5)
+    np.testing.assert_allclose(x.cpu().numpy(), want_x, atol=2e-5, rtol=1e-5)
+    np.testing.assert_allclose(hn.float().cpu().numpy(), want_h, atol=3e-3, rtol=1e-3)
+    assert int(status.item()) == 0
+    h32 = torch.zeros(rows, 1024, device="cuda")
+    nv.check(nv.lib().b200dec_layer_norm(nv.ptr(x), nv.norm(d["w1"], d["b1"], 1e-5), nv.ptr(h32), nv.OUT_F32, rows, 0,
+                                         nv.stream_ptr()))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(h32.cpu().numpy(), layer_norm(x.cpu().numpy(), lnp[2], lnp[3], 1e-5), atol=2e-5, rtol=1e-5)
+
+
+def test_embed_out_of_range_sets_status_not_a_fault(nv):
+    """A token id or position outside its table is clamped and reported through the status word."""
+    emb = torch.zeros(16, 1024, dtype=torch.bfloat16, device="cuda")
+    ones, zeros = torch.ones(1024, device="cuda"), torch.zeros(1024, device="cuda")
+    x = torch.zeros(1, 1024, device="cuda")
+    hn = torch.zeros(1, 1024, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    n = nv.norm(ones, zeros, 1e-5)
+    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(torch.zeros(1, dtype=torch.int32, device="cuda")),
+                                       nv.ptr(torch.tensor([99], device="cuda")),
+                                       nv.ptr(torch.tensor([77], dtype=torch.int32, device="cuda")), nv.ptr(emb),
+                                       nv.ptr(emb), 16, 16, n, n, nv.ptr(x), nv.ptr(hn), nv.OUT_F32, 1, nv.ptr(status), 0,
+                                       nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == nv.ST_TOKEN_RANGE | nv.ST_POS_RANGE
+
+
+def _attention_ref(q, k, v, scale):
+    s = (k.astype(np.float64) @ q.astype(np.float64)) * scale
+    p = np.exp(s - s.max())
+    p /= p.sum()
+    return (p @ v.astype(np.float64)).astype(np.float32)
+
+
+@pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
+@pytest.mark.parametrize("rows", [1, 5, 64])
+@pytest.mark.parametrize("self_", [0, 1])
+def test_attention(nv, H, D, rows, self_):
+    rng = np.random.default_rng(rows * 10 + H + self_)
+    S, cap = max(rows, 4) + 2, 96
+    kc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
+    vc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
+    active = rng.permutation(S)[:rows].astype(np.int32)
+    n = rng.integers(0 if self_ else 1, cap - 1, S + 1).astype(np.int32)
+    n[active[0]] = 0 if self_ else 1  # shortest case
+    if rows > 1:
+        n[active[1]] = cap - 1 if self_ else cap  # longest case
+    ld = 3 * H * D if self_ else H * D
+    q = rng.standard_normal((rows, ld)).astype(np.float32)
+    kd, vd = cuda(kc).to(torch.bfloat16), cuda(vc).to(torch.bfloat16)
+    lib = nv.lib()
+    part = torch.zeros(lib.b200dec_attention_scratch_floats(rows, H, D), device="cuda")
+    count = torch.zeros(rows * H, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(rows, H * D, device="cuda")
+    scale = D ** -0.5
+    for _ in range(2):  # twice: the split counters must have been reset
+        nv.check(lib.b200dec_attention(self_, nv.ptr(cuda(active)), nv.ptr(cuda(q)), ld, nv.ptr(kd), nv.ptr(vd),
+                                       nv.ptr(cuda(n)), S, H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, nv.ptr(part),
+                                       nv.ptr(count), nv.ptr(status), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(count.abs().sum().item()) == 0
+    got = out.cpu().numpy()
+    k_after = kd.float().cpu().numpy()
+    for r in range(rows):
+        s = active[r]
+        for h in range(H):
+            qq = q[r, h * D:(h + 1) * D]
+            if self_:
+                kn = bf16_round(q[r, (H + h) * D:(H + h + 1) * D])
+                vn = bf16_round(q[r, (2 * H + h) * D:(2 * H + h + 1) * D])
+                assert np.array_equal(k_after[s, h, n[s]], kn)
+                K = np.concatenate([kc[s, h, :n[s]], kn[None]])
+                V = np.concatenate([vc[s, h, :n[s]], vn[None]])
+            else:
+                K, V = kc[s, h, :n[s]], vc[s, h, :n[s]]
+            np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=2e-5, rtol=1e-4)
+
+
+def test_pick_semantics(nv):
+    """dec_pick's bookkeeping: forced prompt tokens, greedy after it, end at eos or the limit, dummy and finished rows
+    untouched, ties to the lowest index."""
+    S, P, cols, np_ = 5, 4, 12, 8
+    active = np.array([0, 1, 2, 5, 3], np.int32)  # 5 = dummy
+    pm = np.full((5, np_), -1.0, np.float32)
+    pi = np.tile(np.arange(np_, dtype=np.int32) * 10, (5, 1))
+    pm[0, 3] = 2.0                       # slot 0: inside the prompt -> forced token wins
+    pm[1, 2] = pm[1, 6] = 1.5            # slot 1: tie -> index 20
+    pm[2, 7] = 9.0                       # slot 2: argmax 70 = eos -> finished
+    pm[4, 1] = 3.0                       # slot 3: already finished -> untouched
+    pos = np.array([0, 3, 5, 7, 2, 0], np.int32)
+    plen = np.array([3, 2, 2, 2, 2, 1], np.int32)
+    limit = np.array([9, 4, 9, 9, 9, 0], np.int32)
+    fin = np.array([0, 0, 0, 1, 0, 1], np.uint8)
+    forced = np.arange((S + 1) * P, dtype=np.int64).reshape(S + 1, P) + 100
+    d = {k: cuda(v) for k, v in dict(pm=pm, pi=pi, active=active, pos=pos, plen=plen, limit=limit, fin=fin,
+                                     forced=forced).items()}
+    tok = torch.zeros(S + 1, dtype=torch.long, device="cuda")
+    out = torch.full((S + 1, cols), -1, dtype=torch.long, device="cuda")
+    arg = torch.full((S + 1,), -1, dtype=torch.long, device="cuda")
+    nv.check(nv.lib().b200dec_pick(nv.ptr(d["pm"]), nv.ptr(d["pi"]), np_, nv.ptr(d["active"]), 5, S, nv.ptr(tok),
+                                   nv.ptr(d["pos"]), nv.ptr(d["fin"]), nv.ptr(d["forced"]), P, nv.ptr(d["plen"]),
+                                   nv.ptr(d["limit"]), nv.ptr(out), cols, 70, nv.ptr(arg), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    tok, out, arg = tok.cpu().numpy(), out.cpu().numpy(), arg.cpu().numpy()
+    pos2, fin2 = d["pos"].cpu().numpy(), d["fin"].cpu().numpy()
+    assert (tok[0], pos2[0], fin2[0], out[0, 1], arg[0]) == (101, 1, 0, 101, 30)
+    assert (tok[1], pos2[1], fin2[1], out[1, 4], arg[1]) == (20, 4, 1, 20, 20)      # limit reached
+    assert (tok[2], pos2[2], fin2[2], out[2, 6]) == (70, 6, 1, 70)                  # eos
+    assert (tok[3], pos2[3], fin2[3]) == (0, 7, 1) and (out[3] == -1).all()         # finished: untouched
+    assert (pos2[5], fin2[5]) == (0, 1) and arg[5] == -1                             # dummy: untouched
+
+
+def test_scatter_kv(nv):
+    rng = np.random.default_rng(9)
+    L, S1, H, D, T = 2, 4, 16, 64, 10
+    lengths, slots = [3, 10, 1], [2, 0, 3]
+    kv = rng.standard_normal((sum(lengths), L * 2 * H * D)).astype(np.float32)
+    slot_of = np.repeat(np.array(slots, np.int32), lengths)
+    frame_of = np.concatenate([np.arange(n, dtype=np.int32) for n in lengths])
+    ck = torch.zeros(L, S1, H, T, D, dtype=torch.bfloat16, device="cuda")
+    cv = torch.zeros_like(ck)
+    nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(cuda(kv)), nv.ptr(cuda(slot_of)), nv.ptr(cuda(frame_of)), nv.ptr(ck),
+                                         nv.ptr(cv), kv.shape[0], L, S1, H, D, T, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    want_k, want_v = np.zeros((L, S1, H, T, D), np.float32), np.zeros((L, S1, H, T, D), np.float32)
+    r = bf16_round(kv).reshape(-1, L, 2, H, D)
+    for i in range(kv.shape[0]):
+        want_k[:, slot_of[i], :, frame_of[i]] = r[i, :, 0]
+        want_v[:, slot_of[i], :, frame_of[i]] = r[i, :, 1]
+    assert np.array_equal(ck.float().cpu().numpy(), want_k) and np.array_equal(cv.float().cpu().numpy(), want_v)

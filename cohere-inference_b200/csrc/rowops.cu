@@ -78,7 +78,7 @@ struct EmbedArgs {
   float* x;
   void* hn;
   int* status;
-  int vocab, max_pos, hn_kind, rows;
+  int vocab, max_pos, slots, hn_kind, rows;
 };
 
 __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
@@ -86,7 +86,11 @@ __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
   pdl_trigger();
   pdl_wait();
   if (row >= p.rows) return;
-  const int s = p.active[row];
+  int s = p.active[row];
+  if (s < 0 || s > p.slots) {
+    if (lane == 0) atomicOr(p.status, B200DEC_ST_SLOT_RANGE);
+    s = p.slots;
+  }
   int64_t t = p.tok[s];
   int ps = p.pos[s];
   if (t < 0 || t >= p.vocab) {
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   pdl_wait();
   if (row >= p.rows) return;
   const int s = p.active[row];
-  if (s == p.dummy) return;
+  if (s < 0 || s >= p.dummy) return;  // the dummy slot (and anything outside the table) never advances
   float best = -INFINITY;
   int arg = 0x7fffffff;
   for (int i = lane; i < p.partials; i += 32) {
@@ -294,13 +298,13 @@ __global__ void compress24_kernel(const int8_t* __restrict__ q, int n, int k, in
 namespace b200dec_detail {
 
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
-                  const void* pos_table, int vocab, int max_pos, b200dec_norm ln0, b200dec_norm ln1, float* x, void* hn,
-                  int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
+                  const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
+                  void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
   B200_REQUIRE(active && tok && pos && embed && pos_table && x && hn && status && ln0.w && ln0.b && ln1.w && ln1.b,
                "embed_ln: null pointer");
   B200_REQUIRE(rows >= 1, "embed_ln: rows %d", rows);
   EmbedArgs p{active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, hn, status,
-              vocab, max_pos, hn_kind, rows};
+              vocab, max_pos, slots, hn_kind, rows};
   const cudaError_t e = launch_kernel(embed_ln_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, 0,
                                       pdl, p);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "embed_ln launch: %s", cudaGetErrorString(e));
@@ -338,10 +342,10 @@ const char* b200dec_last_error(void) { return error_buffer(); }
 int b200dec_version(void) { return 1; }
 
 int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
-                     const void* pos_table, int vocab, int max_pos, b200dec_norm ln0, b200dec_norm ln1, float* x,
-                     void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
-  return embed_ln_impl(active, tok, pos, embed, pos_table, vocab, max_pos, ln0, ln1, x, hn, hn_kind, rows, status, pdl,
-                       stream);
+                     const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
+                     float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
+  return embed_ln_impl(active, tok, pos, embed, pos_table, vocab, max_pos, slots, ln0, ln1, x, hn, hn_kind, rows, status,
+                       pdl, stream);
 }
 
 int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream) {

@@ -10,8 +10,8 @@ int linear_impl(const b200dec_weight* w, const void* a, int a_kind, int lda, int
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, float* pmax, int* pidx,
               float* logits, int pdl, void* stream);
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
-                  const void* pos_table, int vocab, int max_pos, b200dec_norm ln0, b200dec_norm ln1, float* x, void* hn,
-                  int hn_kind, int rows, int32_t* status, int pdl, void* stream);
+                  const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
+                  void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
 int layer_norm_impl(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream);
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
@@ -45,9 +45,8 @@ int b200dec_step(const b200dec_plan* pl, int rows, void* stream) {
   const float scale = 1.0f / sqrtf((float)pl->head_dim);
   const int ffn = pl->layer[0].fc1.n;
 
-  B200_TRY(embed_ln_impl(pl->active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->emb_ln,
-                         pl->layer[0].ln1, pl->x, pl->layers ? pl->hn : pl->hn_head, pl->layers ? ok_a : ok_head, rows,
-                         pl->status, pdl, stream));
+  B200_TRY(embed_ln_impl(pl->active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
+                         pl->emb_ln, pl->layer[0].ln1, pl->x, pl->hn, ok_a, rows, pl->status, pdl, stream));
   for (int i = 0; i < pl->layers; ++i) {
     const b200dec_layer& ly = pl->layer[i];
     const bool last = i + 1 == pl->layers;

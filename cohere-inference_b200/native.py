@@ -65,7 +65,7 @@ PROTOTYPES = {
     "b200dec_tile_int8": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_bf16": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_24": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp, vp]),
-    "b200dec_embed_ln": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, Norm, Norm, vp, vp, C.c_int, C.c_int, vp,
+    "b200dec_embed_ln": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, Norm, Norm, vp, vp, C.c_int, C.c_int, vp,
                                    C.c_int, vp]),
     "b200dec_layer_norm": (C.c_int, [vp, Norm, vp, C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_linear": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.c_int, C.c_int, vp, C.c_int, C.c_int, C.c_int,

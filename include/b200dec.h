@@ -125,11 +125,11 @@ int b200dec_tile_24(const int8_t* kept, const int32_t* words, int n, int k, void
 
 /* ---- step kernels ------------------------------------------------------------------------------------------- */
 
-/* x = LN_emb(embed[tok[s]] + pos_table[pos[s]]), hn = LN_1(x), s = active[r].
+/* x = LN_emb(embed[tok[s]] + pos_table[pos[s]]), hn = LN_1(x), s = active[r] in 0..slots (slots = the dummy).
  * Replaces dec_embed (kernels/csrc/decoder_ops.cu:24-54, 208-219). */
 int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
-                     const void* pos_table, int vocab, int max_pos, b200dec_norm ln0, b200dec_norm ln1, float* x,
-                     void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
+                     const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
+                     float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
 /* hn = LN(x) for an fp32 residual stream that the preceding projection already added into
  * (B200DEC_OUT_F32_ADD). Replaces dec_add_ln (kernels/csrc/decoder_ops.cu:56-83, 221-231). */
 int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream);

@@ -232,9 +232,12 @@ def test_embed_ln_and_layer_norm(nv):
     x = torch.zeros(rows, 1024, device="cuda")
     hn = torch.zeros(rows, 1024, dtype=torch.float16, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(cuda(active)), nv.ptr(cuda(tok)), nv.ptr(cuda(pos)),
-                                       nv.ptr(cuda(emb).to(torch.bfloat16)), nv.ptr(cuda(ptab).to(torch.bfloat16)), vocab,
-                                       max_pos, nv.norm(d["w0"], d["b0"], 1e-5), nv.norm(d["w1"], d["b1"], 1e-5),
+    # every device operand is held in a variable until the synchronize: a temporary would be freed (and its block
+    # reused by the next allocation) before the asynchronous kernel reads it
+    a_d, t_d, p_d = cuda(active), cuda(tok), cuda(pos)
+    e_d, pt_d = cuda(emb).to(torch.bfloat16), cuda(ptab).to(torch.bfloat16)
+    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(a_d), nv.ptr(t_d), nv.ptr(p_d), nv.ptr(e_d), nv.ptr(pt_d), vocab,
+                                       max_pos, S, nv.norm(d["w0"], d["b0"], 1e-5), nv.norm(d["w1"], d["b1"], 1e-5),
                                        nv.ptr(x), nv.ptr(hn), nv.OUT_F16, rows, nv.ptr(status), 0, nv.stream_ptr()))
     torch.cuda.synchronize()
     want_x = layer_norm(emb[tok[active]] + ptab[pos[active]], lnp[0], lnp[1], 1e-5)
@@ -257,13 +260,15 @@ def test_embed_out_of_range_sets_status_not_a_fault(nv):
     hn = torch.zeros(1, 1024, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     n = nv.norm(ones, zeros, 1e-5)
-    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(torch.zeros(1, dtype=torch.int32, device="cuda")),
-                                       nv.ptr(torch.tensor([99], device="cuda")),
-                                       nv.ptr(torch.tensor([77], dtype=torch.int32, device="cuda")), nv.ptr(emb),
-                                       nv.ptr(emb), 16, 16, n, n, nv.ptr(x), nv.ptr(hn), nv.OUT_F32, 1, nv.ptr(status), 0,
-                                       nv.stream_ptr()))
+    active = torch.tensor([0, 7], dtype=torch.int32, device="cuda")  # slot 7 is outside the 0..2 table
+    tok = torch.tensor([99, 0, 0], device="cuda")
+    pos = torch.tensor([77, 0, 0], dtype=torch.int32, device="cuda")
+    x = torch.zeros(2, 1024, device="cuda")
+    hn = torch.zeros(2, 1024, device="cuda")
+    nv.check(nv.lib().b200dec_embed_ln(nv.ptr(active), nv.ptr(tok), nv.ptr(pos), nv.ptr(emb), nv.ptr(emb), 16, 16, 2,
+                                       n, n, nv.ptr(x), nv.ptr(hn), nv.OUT_F32, 2, nv.ptr(status), 0, nv.stream_ptr()))
     torch.cuda.synchronize()
-    assert int(status.item()) == nv.ST_TOKEN_RANGE | nv.ST_POS_RANGE
+    assert int(status.item()) == nv.ST_TOKEN_RANGE | nv.ST_POS_RANGE | nv.ST_SLOT_RANGE
 
 
 def _attention_ref(q, k, v, scale):
@@ -295,9 +300,10 @@ def test_attention(nv, H, D, rows, self_):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = torch.zeros(rows, H * D, device="cuda")
     scale = D ** -0.5
+    a_d, q_d, n_d = cuda(active), cuda(q), cuda(n)  # held until the synchronize
     for _ in range(2):  # twice: the split counters must have been reset
-        nv.check(lib.b200dec_attention(self_, nv.ptr(cuda(active)), nv.ptr(cuda(q)), ld, nv.ptr(kd), nv.ptr(vd),
-                                       nv.ptr(cuda(n)), S, H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, nv.ptr(part),
+        nv.check(lib.b200dec_attention(self_, nv.ptr(a_d), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd),
+                                       nv.ptr(n_d), S, H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, nv.ptr(part),
                                        nv.ptr(count), nv.ptr(status), 0, nv.stream_ptr()))
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and int(count.abs().sum().item()) == 0
@@ -361,7 +367,8 @@ def test_scatter_kv(nv):
     frame_of = np.concatenate([np.arange(n, dtype=np.int32) for n in lengths])
     ck = torch.zeros(L, S1, H, T, D, dtype=torch.bfloat16, device="cuda")
     cv = torch.zeros_like(ck)
-    nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(cuda(kv)), nv.ptr(cuda(slot_of)), nv.ptr(cuda(frame_of)), nv.ptr(ck),
+    kv_d, so_d, fo_d = cuda(kv), cuda(slot_of), cuda(frame_of)  # held until the synchronize
+    nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(kv_d), nv.ptr(so_d), nv.ptr(fo_d), nv.ptr(ck),
                                          nv.ptr(cv), kv.shape[0], L, S1, H, D, T, nv.stream_ptr()))
     torch.cuda.synchronize()
     want_k, want_v = np.zeros((L, S1, H, T, D), np.float32), np.zeros((L, S1, H, T, D), np.float32)

@@ -105,7 +105,7 @@ def run_ours(args) -> None:
     torch.cuda.set_device(dev)
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
-                        int8=True, eos=-1)
+                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains)
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -231,7 +231,7 @@ def run_ours(args) -> None:
             "config": {"workload": "BASELINE config 3: 8 layers x 1024, 16 heads x 64, GELU, vocab 16384; batch 64 per GPU, "
                                    "encoder lengths U[50,375], 10-token prompts + 448 new tokens, one CUDA graph per "
                                    "decoding step; a bench step = one pass = 457 replays",
-                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "bf16", "parallelism": f"dp{world} replicas",
+                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "bf16", "parallelism": f"dp{world} replicas", "chains_per_step": len(dec.row_ranges(BATCH)),
                        "l2": "inputs larger than L2: each replay streams ~0.2-1.9 GB of KV cache and weights",
                        "weights": "seed-0 random init N(0, 0.02)"},
             "p50_step_ms": round(p50, 4),
@@ -239,7 +239,7 @@ def run_ours(args) -> None:
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(memory_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
                     "ms_per_step": round(e2e_ms / args.steps, 3)},
-            "gpu_launches": dec.launches_per_step * steps_per_pass * args.steps,
+            "gpu_launches": dec.launches_per_step * len(dec.row_ranges(BATCH)) * steps_per_pass * args.steps,
             "roofline": {"bound": "hbm", "kernel": "attention_kernel<64,false> (cross-attention, 64 rows x 16 heads)",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
@@ -255,6 +255,42 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
+
+
+def run_profile(args) -> None:
+    """A short run for a profiler: the config-3 batch at a mid-sequence position, kernels launched directly (no graph),
+    3 warm-up steps, then `--profile N` steps between cudaProfilerStart/Stop (use ncu --profile-from-start off).
+    --profile-slots / --profile-pos size the case (a capture with many passes wants a small one)."""
+    from cohere_inference_b200 import StreamDecoder, synthetic_model
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B = args.profile_slots
+    dec = StreamDecoder(synthetic_model(0).to(dev), slots=B, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
+                        buckets=(B,), int8=True, eos=-1, graphs=False, ffn_sparse=args.sparse)
+    rng = np.random.default_rng(1000)
+    lens = rng.integers(FRAMES[0], FRAMES[1] + 1, B).tolist()
+    prompts = [torch.from_numpy(rng.integers(0, 16384, PROMPT).astype(np.int64)) for _ in range(B)]
+    slots = list(range(B))
+    with torch.cuda.stream(dec.stream):
+        dec.fill_cross(torch.randn(sum(lens), 1024, device=dev), lens, slots)
+    dec.admit(slots, prompts, lens)
+    b = dec.set_active(slots)
+    with torch.cuda.stream(dec.stream):
+        dec.pos[:B] = args.profile_pos  # the self cache below this position holds zeros: same bytes, same time
+        dec.plen[:B] = 1
+    for _ in range(3):
+        dec.step(b)
+    dec.stream.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(args.profile):
+        dec.step(b)
+    dec.stream.synchronize()
+    torch.cuda.profiler.stop()
+    dec.check_status()
+    kv = sum(lens) * 2 * 1024 * 2
+    print(json.dumps({"profile_steps": args.profile, "rows": B, "pos": args.profile_pos + 3, "sum_frames": sum(lens),
+                      "cross_kv_bytes_per_launch": kv, "self_kv_bytes_per_launch": B * (args.profile_pos + 4) * 4096,
+                      "weight_bytes": dec.weight_bytes, "launches_per_step": dec.launches_per_step}))
 
 
 def run_reference(args) -> None:
@@ -298,9 +334,19 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=32, help="decoding steps of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
+    ap.add_argument("--pdl", type=int, default=1, help="which launches are programmatic: 1 projection after projection, "
+                    "2 attention, 4 projection after attention (sum them)")
+    ap.add_argument("--chains", type=int, default=2, help="concurrent kernel chains a step's rows are split into")
+    ap.add_argument("--profile", type=int, default=0, help="profiler mode: this many directly launched steps")
+    ap.add_argument("--profile-slots", type=int, default=BATCH)
+    ap.add_argument("--profile-pos", type=int, default=225)
+    ap.add_argument("--sparse", action="store_true", help="profiler mode: 2:4 feed-forward weights")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.profile:
+        run_profile(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -1,0 +1,538 @@
+// Small-M projection kernel: out (rows, N) = act(A (rows, K) x W^T * scale + bias), rows <= 128. See linear.cu for
+// the design notes and the tiled weight layouts; this header holds the kernel template and its launcher so that each
+// weight kind compiles in its own translation unit.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace b200dec_detail {
+
+namespace cg = cooperative_groups;
+
+struct LinArgs {
+  const uint8_t* w;
+  const uint32_t* meta;
+  const float* scale;
+  const float* bias;
+  const void* a;
+  const float* ln_w;     // LayerNorm folded in (a = fp32 residual stream) when non-null: gamma ...
+  const float* ln_g;     // ... g[n] = sum_k gamma[k] W[n][k] ...
+  const float* ln_bias;  // ... and sum_k beta[k] W[n][k], both of the dequantised weights
+  void* out;
+  float* part_max;
+  int* part_idx;
+  float* logits;
+  float ln_eps;
+  int lda, ldo, rows, N, out_kind, act, head;
+#ifdef B200DEC_STAMPS
+  long long* stamps;  // per CTA 8 clock64() values at the phase boundaries (latency studies only)
+#endif
+};
+
+#ifdef B200DEC_STAMPS
+#define B200_STAMP(i)                                                                                        \
+  do {                                                                                                       \
+    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = clock64(); \
+  } while (0)
+#else
+#define B200_STAMP(i)
+#endif
+
+template <int WT>
+struct WTraits;
+template <>
+struct WTraits<B200DEC_W_INT8> {
+  static constexpr int KPB = 64, STEPS = 4, PAD = 16;
+};
+template <>
+struct WTraits<B200DEC_W_BF16> {
+  static constexpr int KPB = 32, STEPS = 2, PAD = 64;
+};
+template <>
+struct WTraits<B200DEC_W_INT8_24> {
+  static constexpr int KPB = 128, STEPS = 8, PAD = 64;
+};
+
+DEVI void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+DEVI void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 4 offset-binary bytes (q + 128, k .. k+3) -> half2(q0, q1), half2(q2, q3); exact: 0x64uu is the half 1024 + uu
+DEVI void widen_u8(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t x0 = __byte_perm(w, 0x64646464u, 0x4140);
+  const uint32_t x1 = __byte_perm(w, 0x64646464u, 0x4342);
+  const __half2 magic = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1152
+  const __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&x0), magic);
+  const __half2 r1 = __hsub2(*reinterpret_cast<const __half2*>(&x1), magic);
+  lo = *reinterpret_cast<const uint32_t*>(&r0);
+  hi = *reinterpret_cast<const uint32_t*>(&r1);
+}
+
+DEVI float act_fn(float v, int act) {
+  if (act == B200DEC_ACT_RELU) return fmaxf(v, 0.f);
+  if (act == B200DEC_ACT_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  return v;
+}
+
+// 4 fp32 activations -> their 16-bit operand: the nearest half / bf16 and, when split, the rounded remainder
+template <bool BF, bool SPLIT>
+DEVI void to_operand(float4 v, uint2& hi, uint2& lo) {
+  if constexpr (BF) {
+    hi = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+    if constexpr (SPLIT)
+      lo = make_uint2(pack_bf16(v.x - bf16_lo(hi.x), v.y - bf16_hi(hi.x)),
+                      pack_bf16(v.z - bf16_lo(hi.y), v.w - bf16_hi(hi.y)));
+  } else {
+    const float c0 = clamp_h(v.x), c1 = clamp_h(v.y), c2 = clamp_h(v.z), c3 = clamp_h(v.w);
+    const __half2 h01 = __floats2half2_rn(c0, c1), h23 = __floats2half2_rn(c2, c3);
+    hi = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+    if constexpr (SPLIT) {
+      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+      lo = make_uint2(pack_f16(c0 - f01.x, c1 - f01.y), pack_f16(c2 - f23.x, c3 - f23.y));
+    }
+  }
+}
+
+template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+struct LinSmem {
+  static constexpr int RS = KSLICE * 2 + WTraits<WT>::PAD;  // bytes per staged activation row
+  static constexpr int BN = NW * 16;
+  static constexpr int A_BYTES = MB * RS * (SPLIT ? 2 : 1);
+  static constexpr int RECV_BYTES = MB * BN * 4;       // [KSPLIT][MB][BN / KSPLIT] partial sums pushed by the cluster
+  static constexpr int RED_BYTES = MB * (BN + 4) * 4;  // this CTA's partial tile, transposed for the push
+  // fp32 source rows are first copied asynchronously into shared memory (slices up to 256 wide; wider ones are
+  // converted straight from registers); the copy shares its bytes with the partial tile, which is written later
+  static constexpr bool RAW_STAGE = (LN || SPLIT) && KSLICE <= 256;
+  static constexpr int RAW_BYTES = RAW_STAGE ? MB * KSLICE * 4 : 0;
+  static constexpr int SCRATCH_BYTES = RAW_BYTES > RED_BYTES ? RAW_BYTES : RED_BYTES;
+  static constexpr int STATS_BYTES = LN ? KSPLIT * MB * 8 : 0;  // [KSPLIT][MB] (sum, sum of squares) of each slice
+  static constexpr int OFF_A = 0, OFF_RECV = OFF_A + A_BYTES, OFF_RED = OFF_RECV + RECV_BYTES,
+                       OFF_STATS = OFF_RED + SCRATCH_BYTES, TOTAL = OFF_STATS + STATS_BYTES;
+};
+
+// WT: weight storage. SPLIT: the activation operand is two 16-bit halves (hi + lo) of an fp32 value, else one fp16.
+// LN: the operand is LayerNorm(a) of the fp32 rows a with the normalisation folded into the epilogue: with a per-row
+// shift c (the mean of the row's first four values) the kernel multiplies (a - c) * gamma, every CTA also sums its
+// slice's (a - c) and (a - c)^2, and the finishing CTA applies  y = rstd * (acc * scale - (mean - c) * g) + bias',
+// which equals LayerNorm(a) W^T + bias exactly (g and bias' are precomputed per output channel). NW warps = 16 NW
+// channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
+template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+__global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
+  using T = WTraits<WT>;
+  using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
+  constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
+  constexpr int RS = S::RS, LDR = BN + 4, CPR = BN / KSPLIT, GPR = CPR / 4, NB = MB / 8, NBG = NB < 8 ? NB : 8;
+  constexpr bool BF = WT == B200DEC_W_BF16;
+  constexpr bool F32SRC = LN || SPLIT;  // the source rows are fp32
+  static_assert(CPR % 8 == 0, "each CTA finishes a multiple of 8 channels");
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ uint32_t lut[32];
+  unsigned char* a_hi = smem + S::OFF_A;
+  unsigned char* a_lo = a_hi + MB * RS;
+  float* recv = reinterpret_cast<float*>(smem + S::OFF_RECV);
+  float* red = reinterpret_cast<float*>(smem + S::OFF_RED);
+  float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const int nt16 = blockIdx.y * NW + warp;  // this warp's 16 channels
+  const int k0 = rank * KSLICE;
+
+  B200_STAMP(0);
+  // ---- prologue: the warp's whole weight slice into registers (independent of the previous kernel) -------------
+  uint4 wr[NBLK][2];
+  uint32_t mr[WT == B200DEC_W_INT8_24 ? NBLK : 1][2];
+  {
+    const size_t blk0 = (size_t)nt16 * (K / KPB) + k0 / KPB;
+    const uint8_t* wp = p.w + blk0 * 1024 + lane * 16;
+#pragma unroll
+    for (int b = 0; b < NBLK; ++b) {
+      wr[b][0] = ld_stream16(wp + (size_t)b * 1024);
+      wr[b][1] = ld_stream16(wp + (size_t)b * 1024 + 512);
+    }
+    if constexpr (WT == B200DEC_W_INT8_24) {
+      const uint32_t* mp = p.meta + blk0 * 64 + lane;
+#pragma unroll
+      for (int b = 0; b < NBLK; ++b) {
+        mr[b][0] = ld_stream4(mp + (size_t)b * 64);
+        mr[b][1] = ld_stream4(mp + (size_t)b * 64 + 32);
+      }
+      // byte-permute controls: dense byte q of a group takes kept byte 0/1 (even step) or 2/3 (odd step) of the
+      // register when q is the first / second kept position, else the zero byte (index 4 = 0x80)
+      if (tid < 32) {
+        const int i0 = tid & 3, i1 = (tid >> 2) & 3, odd = tid >> 4;
+        uint32_t ctl = 0;
+        for (int q = 0; q < 4; ++q) {
+          uint32_t sel = 4;
+          if (q == i1) sel = odd ? 3 : 1;
+          if (q == i0) sel = odd ? 2 : 0;
+          ctl |= sel << (4 * q);
+        }
+        lut[tid] = ctl;
+      }
+    }
+  }
+  B200_STAMP(1);
+  pdl_wait();
+  B200_STAMP(2);
+
+  // ---- stage the activations of this K slice ---------------------------------------------------------------------
+  const int ntiles = (p.rows + 7) >> 3, rows8 = ntiles * 8;
+  if constexpr (!F32SRC) {
+    constexpr int CH = KSLICE / 8;  // 16-byte chunks per row
+    const __half* A = reinterpret_cast<const __half*>(p.a);
+    for (int i = tid; i < rows8 * CH; i += NT) {
+      const int r = i / CH, c = i % CH;
+      if (r < p.rows)
+        cp_async16(a_hi + r * RS + c * 16, A + (size_t)r * p.lda + k0 + c * 8);
+      else
+        *reinterpret_cast<uint4*>(a_hi + r * RS + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_wait_all();
+  } else {
+    // fp32 rows: 8 lanes per row, each with KSLICE / 32 independent 16-byte loads in flight; converted (and, for the
+    // folded LayerNorm, shifted, scaled by gamma and summed) on the way to shared memory
+    constexpr int J = KSLICE / 32;
+    constexpr int RPG = (MB + NT / 8 - 1) / (NT / 8);  // rows per 8-lane group
+    const float* A = reinterpret_cast<const float*>(p.a);
+    const int l8 = tid & 7;
+    float* raw = red;  // the async copy of the fp32 rows (RAW_STAGE)
+    float shift[RPG];
+    if constexpr (S::RAW_STAGE) {
+      constexpr int CH = KSLICE / 4;
+      for (int i = tid; i < p.rows * CH; i += NT) {
+        const int r = i / CH, c = i % CH;
+        cp_async16(raw + r * KSLICE + c * 4, A + (size_t)r * p.lda + k0 + c * 4);
+      }
+    }
+    if constexpr (LN) {  // the rows' shifts, fetched while the copies are in flight
+#pragma unroll
+      for (int it = 0; it < RPG; ++it) {
+        const int r = (tid >> 3) + it * (NT / 8);
+        shift[it] = 0.f;
+        if (r < p.rows) {
+          const float4 f = ld_cg_f4(A + (size_t)r * p.lda);
+          shift[it] = 0.25f * (f.x + f.y + f.z + f.w);
+        }
+      }
+    }
+    if constexpr (S::RAW_STAGE) {
+      cp_async_wait_all();
+      __syncthreads();
+    }
+#pragma unroll
+    for (int it = 0; it < RPG; ++it) {
+      const int r = (tid >> 3) + it * (NT / 8);
+      if (r >= rows8) break;  // whole warps leave together (rows8 % 8 == 0, 4 groups per warp)
+      const bool live = r < p.rows;
+      float4 v[J];
+      const float c = LN ? shift[it] : 0.f;
+      if (live) {
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          if constexpr (S::RAW_STAGE) v[j] = *reinterpret_cast<const float4*>(raw + r * KSLICE + (j * 8 + l8) * 4);
+          else v[j] = ld_cg_f4(A + (size_t)r * p.lda + k0 + (j * 8 + l8) * 4);
+        }
+      }
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        uint2 hi = make_uint2(0, 0), lo = make_uint2(0, 0);
+        if (live) {
+          float4 x = v[j];
+          if constexpr (LN) {
+            const float4 gm = *reinterpret_cast<const float4*>(p.ln_w + k0 + (j * 8 + l8) * 4);
+            x.x -= c, x.y -= c, x.z -= c, x.w -= c;
+            s1 += (x.x + x.y) + (x.z + x.w);
+            s2 += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+            x.x *= gm.x, x.y *= gm.y, x.z *= gm.z, x.w *= gm.w;
+          }
+          to_operand<BF, SPLIT>(x, hi, lo);
+        }
+        *reinterpret_cast<uint2*>(a_hi + r * RS + (j * 8 + l8) * 8) = hi;
+        if constexpr (SPLIT) *reinterpret_cast<uint2*>(a_lo + r * RS + (j * 8 + l8) * 8) = lo;
+      }
+      if constexpr (LN) {
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+          s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+          s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+        }
+        if (live && l8 < KSPLIT) cluster.map_shared_rank(stats, l8)[rank * MB + r] = make_float2(s1, s2);
+      }
+    }
+  }
+  __syncthreads();
+  B200_STAMP(3);
+  pdl_trigger();  // the next kernel may start its weight prefetch while this one multiplies
+
+  // ---- multiply: consecutive MMAs go to different accumulators (up to 8 row tiles in flight) ----------------------
+  float acc[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nb][e] = 0.f;
+
+#pragma unroll
+  for (int b = 0; b < NBLK; ++b) {
+    uint32_t af[STEPS][4];  // weight fragments of the block's steps
+    if constexpr (WT == B200DEC_W_INT8) {
+      const uint32_t r0[4] = {wr[b][0].x, wr[b][0].y, wr[b][0].z, wr[b][0].w};
+      const uint32_t r1[4] = {wr[b][1].x, wr[b][1].y, wr[b][1].z, wr[b][1].w};
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        widen_u8(r0[s], af[s][0], af[s][2]);
+        widen_u8(r1[s], af[s][1], af[s][3]);
+      }
+    } else if constexpr (WT == B200DEC_W_BF16) {
+      af[0][0] = wr[b][0].x, af[0][2] = wr[b][0].y, af[1][0] = wr[b][0].z, af[1][2] = wr[b][0].w;
+      af[0][1] = wr[b][1].x, af[0][3] = wr[b][1].y, af[1][1] = wr[b][1].z, af[1][3] = wr[b][1].w;
+    } else {
+      const uint32_t r0[4] = {wr[b][0].x ^ 0x80808080u, wr[b][0].y ^ 0x80808080u, wr[b][0].z ^ 0x80808080u,
+                              wr[b][0].w ^ 0x80808080u};
+      const uint32_t r1[4] = {wr[b][1].x ^ 0x80808080u, wr[b][1].y ^ 0x80808080u, wr[b][1].z ^ 0x80808080u,
+                              wr[b][1].w ^ 0x80808080u};
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const uint32_t c0 = lut[((mr[b][0] >> (4 * s)) & 15u) | ((s & 1) << 4)];
+        const uint32_t c1 = lut[((mr[b][1] >> (4 * s)) & 15u) | ((s & 1) << 4)];
+        widen_u8(__byte_perm(r0[s >> 1], 0x80808080u, c0), af[s][0], af[s][2]);
+        widen_u8(__byte_perm(r1[s >> 1], 0x80808080u, c1), af[s][1], af[s][3]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < STEPS / 2; ++c) {  // one 16-byte chunk of a row = the lane's k-values of two steps
+      int col;                             // first k of the chunk inside the slice
+      if constexpr (WT == B200DEC_W_INT8) col = b * 64 + t * 16 + c * 8;
+      else if constexpr (WT == B200DEC_W_BF16) col = b * 32 + t * 8;
+      else col = b * 128 + (4 * c + t) * 8;
+#pragma unroll
+      for (int n0 = 0; n0 < NB; n0 += NBG) {
+        if (n0 < ntiles) {
+          uint4 h[NBG], l[SPLIT ? NBG : 1];
+#pragma unroll
+          for (int i = 0; i < NBG; ++i) {
+            h[i] = *reinterpret_cast<const uint4*>(a_hi + ((n0 + i) * 8 + g) * RS + col * 2);
+            if constexpr (SPLIT) l[i] = *reinterpret_cast<const uint4*>(a_lo + ((n0 + i) * 8 + g) * RS + col * 2);
+          }
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+#pragma unroll
+            for (int i = 0; i < NBG; ++i) {
+              if (n0 + i < ntiles) {
+                const uint32_t b0 = e ? h[i].z : h[i].x, b1 = e ? h[i].w : h[i].y;
+                if constexpr (BF) mma_bf16(acc[n0 + i], af[2 * c + e], b0, b1);
+                else mma_f16(acc[n0 + i], af[2 * c + e], b0, b1);
+              }
+            }
+            if constexpr (SPLIT) {
+#pragma unroll
+              for (int i = 0; i < NBG; ++i) {
+                if (n0 + i < ntiles) {
+                  const uint32_t b0 = e ? l[i].z : l[i].x, b1 = e ? l[i].w : l[i].y;
+                  if constexpr (BF) mma_bf16(acc[n0 + i], af[2 * c + e], b0, b1);
+                  else mma_f16(acc[n0 + i], af[2 * c + e], b0, b1);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  B200_STAMP(4);
+
+  // ---- partial tile -> the CTAs that own its channels (distributed shared memory), one cluster barrier ------------
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    if (nb < ntiles) {
+      const int r = nb * 8 + 2 * t, c = warp * 16 + g;
+      red[r * LDR + c] = acc[nb][0];
+      red[(r + 1) * LDR + c] = acc[nb][1];
+      red[r * LDR + c + 8] = acc[nb][2];
+      red[(r + 1) * LDR + c + 8] = acc[nb][3];
+    }
+  }
+  __syncthreads();
+  for (int it = tid; it < p.rows * (BN / 4); it += NT) {
+    const int r = it / (BN / 4), ch = (it % (BN / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(red + r * LDR + ch);
+    float* dst = cluster.map_shared_rank(recv, ch / CPR) + (rank * MB + r) * CPR + (ch % CPR);
+    *reinterpret_cast<float4*>(dst) = v;
+  }
+  // this thread's share of the finished tile: row r, channels n .. n+3; the residual it adds to is fetched now so
+  // that its latency overlaps the barrier
+  const int items = p.rows * GPR;
+  const bool one_item = items <= NT;  // the common case: at most one item per thread
+  float4 resid = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (one_item && tid < items && !p.head && p.out_kind == B200DEC_OUT_F32_ADD)
+    resid = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + (size_t)(tid / GPR) * p.ldo +
+                                                   blockIdx.y * BN + rank * CPR + (tid % GPR) * 4));
+  B200_STAMP(5);
+  cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this
+  B200_STAMP(6);
+
+  const int padded = (items + 31) & ~31;
+  for (int it = tid; it < padded; it += NT) {
+    const bool live = it < items;
+    const int r = live ? it / GPR : 0, c4 = live ? it % GPR : 0;
+    const int n = blockIdx.y * BN + rank * CPR + c4 * 4;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+#pragma unroll
+      for (int q = 0; q < KSPLIT; ++q) {  // fixed rank order: the same bits whatever the timing
+        const float4 v = *reinterpret_cast<const float4*>(recv + (q * MB + r) * CPR + c4 * 4);
+        s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+      }
+      if (p.scale) {
+        const float4 sc = *reinterpret_cast<const float4*>(p.scale + n);
+        s.x *= sc.x, s.y *= sc.y, s.z *= sc.z, s.w *= sc.w;
+      }
+      if constexpr (LN) {
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int q = 0; q < KSPLIT; ++q) {
+          const float2 st = stats[q * MB + r];
+          s1 += st.x, s2 += st.y;
+        }
+        const float dm = s1 * (1.f / K);  // mean - shift
+        const float rstd = rsqrtf(fmaxf(s2 * (1.f / K) - dm * dm, 0.f) + p.ln_eps);
+        const float4 gg = *reinterpret_cast<const float4*>(p.ln_g + n);
+        const float4 lb = *reinterpret_cast<const float4*>(p.ln_bias + n);
+        s.x = rstd * (s.x - dm * gg.x) + lb.x, s.y = rstd * (s.y - dm * gg.y) + lb.y;
+        s.z = rstd * (s.z - dm * gg.z) + lb.z, s.w = rstd * (s.w - dm * gg.w) + lb.w;
+      }
+      if (p.bias) {
+        const float4 bb = *reinterpret_cast<const float4*>(p.bias + n);
+        s.x += bb.x, s.y += bb.y, s.z += bb.z, s.w += bb.w;
+      }
+      s.x = act_fn(s.x, p.act), s.y = act_fn(s.y, p.act), s.z = act_fn(s.z, p.act), s.w = act_fn(s.w, p.act);
+      if (!p.head) {
+        if (p.out_kind == B200DEC_OUT_F16) {
+          *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)r * p.ldo + n) =
+              make_uint2(pack_f16(s.x, s.y), pack_f16(s.z, s.w));
+        } else {
+          float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)r * p.ldo + n);
+          if (p.out_kind == B200DEC_OUT_F32_ADD) {
+            const float4 x = one_item ? resid : __ldcg(o);
+            s.x += x.x, s.y += x.y, s.z += x.z, s.w += x.w;
+          }
+          *o = s;
+        }
+      } else if (p.logits) {
+        *reinterpret_cast<float4*>(p.logits + (size_t)r * p.N + n) = s;
+      }
+    }
+    if (p.head) {
+      // first index of the maximum over this CTA's channels of row r (NaN never wins): GPR consecutive lanes
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      if (live) {
+        const float v[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (v[e] > best) best = v[e], arg = n + e;
+      }
+#pragma unroll
+      for (int o = 1; o < GPR && o < 32; o <<= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+      }
+      if (live && c4 == 0) {
+        const int np = (p.N / BN) * KSPLIT, slot = blockIdx.y * KSPLIT + rank;
+        p.part_max[(size_t)r * np + slot] = best;
+        p.part_idx[(size_t)r * np + slot] = arg;
+      }
+    }
+  }
+  B200_STAMP(7);
+}
+
+template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
+  using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
+  static_assert(S::TOTAL <= 227 * 1024, "tile does not fit in shared memory");
+  auto kern = linear_kernel<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
+  // idempotent; set on every call so that it holds on every device of the process
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear: smem attribute: %s", cudaGetErrorString(e));
+  const dim3 grid(KSPLIT, a.N / (NW * 16));
+  e = launch_kernel(kern, grid, dim3(NW * 32), S::TOTAL, stream, KSPLIT, pdl, a);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT>
+int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
+  if (a.rows <= 16) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s);
+  if (a.rows <= 64) {
+    if constexpr (LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024)
+      return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>(a, pdl, s);
+    else
+      return fail(B200DEC_EINVAL, "linear: %d rows need a smaller K / ksplit than %d for this operand", a.rows, KSLICE);
+  }
+  if constexpr (LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 128>::TOTAL <= 227 * 1024)
+    return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 128>(a, pdl, s);
+  else
+    return fail(B200DEC_EINVAL, "linear: %d rows need a smaller K / ksplit than %d for this operand", a.rows, KSLICE);
+}
+
+// Does the (kind, operand, tile) combination fit shared memory for this many rows? (host-side query)
+template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT>
+bool fits(int rows) {
+  if (rows <= 16) return true;
+  if (rows <= 64) return LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024;
+  return LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 128>::TOTAL <= 227 * 1024;
+}
+
+// the (K / ksplit, ksplit) pairs with kernels: K = 1024 as 8 x 128, 4 x 256, 2 x 512; K = 4096 as 8 x 512
+#define B200_TILE_CASES(X) X(4, 128, 8) X(4, 256, 4) X(4, 512, 2) X(4, 512, 8) X(8, 128, 8) X(8, 256, 4) X(8, 512, 2) X(8, 512, 8)
+
+template <int WT, bool SPLIT, bool LN>
+int launch_shape(const LinArgs& a, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
+  const int kslice = k / ksplit;
+  constexpr int KPB = WTraits<WT>::KPB;
+#define B200_CASE(NW_, KS_, SP_)                                                                    \
+  if (warps == NW_ && kslice == KS_ && ksplit == SP_) {                                             \
+    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0)   \
+      return launch_mb<WT, SPLIT, LN, NW_, KS_, SP_>(a, pdl, s);                                    \
+  }
+  B200_TILE_CASES(B200_CASE)
+#undef B200_CASE
+  return fail(B200DEC_EINVAL, "linear: no kernel for warps=%d K=%d ksplit=%d (K = 1024: 8|4|2; K = 4096: 8)", warps, k,
+              ksplit);
+}
+
+template <int WT, bool SPLIT, bool LN>
+bool fits_shape(int warps, int k, int ksplit, int rows) {
+  const int kslice = k / ksplit;
+  constexpr int KPB = WTraits<WT>::KPB;
+#define B200_CASE(NW_, KS_, SP_)                                                                    \
+  if (warps == NW_ && kslice == KS_ && ksplit == SP_) {                                             \
+    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0)   \
+      return fits<WT, SPLIT, LN, NW_, KS_, SP_>(rows);                                              \
+  }
+  B200_TILE_CASES(B200_CASE)
+#undef B200_CASE
+  return false;
+}
+
+// one entry per weight kind, each defined in its own translation unit
+int launch_int8(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+int launch_bf16(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+int launch_24(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+bool fits_int8(bool split, bool ln, int warps, int k, int ksplit, int rows);
+bool fits_bf16(bool split, bool ln, int warps, int k, int ksplit, int rows);
+bool fits_24(bool split, bool ln, int warps, int k, int ksplit, int rows);
+
+}  // namespace b200dec_detail

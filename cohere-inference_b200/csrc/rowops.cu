@@ -112,8 +112,10 @@ __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
   }
   ln_row(v, p.ln0.w, p.ln0.b, p.ln0.eps, lane, o);
   store_row(o, p.x, B200DEC_OUT_F32, row, lane);
-  ln_row(o, p.ln1.w, p.ln1.b, p.ln1.eps, lane, v);
-  store_row(v, p.hn, p.hn_kind, row, lane);
+  if (p.hn) {  // optionally also the first layer's LayerNorm of the new row
+    ln_row(o, p.ln1.w, p.ln1.b, p.ln1.eps, lane, v);
+    store_row(v, p.hn, p.hn_kind, row, lane);
+  }
 }
 
 struct LnArgs {
@@ -300,7 +302,7 @@ namespace b200dec_detail {
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
                   void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
-  B200_REQUIRE(active && tok && pos && embed && pos_table && x && hn && status && ln0.w && ln0.b && ln1.w && ln1.b,
+  B200_REQUIRE(active && tok && pos && embed && pos_table && x && status && ln0.w && ln0.b && (!hn || (ln1.w && ln1.b)),
                "embed_ln: null pointer");
   B200_REQUIRE(rows >= 1, "embed_ln: rows %d", rows);
   EmbedArgs p{active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, hn, status,

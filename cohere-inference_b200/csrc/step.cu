@@ -1,18 +1,18 @@
 // One decoding step as a sequence of kernel launches on the caller's stream (capturable into a CUDA graph):
-// embed + 2 LayerNorms, then per layer  qkv -> self-attention -> o (+residual) -> LN -> cross q -> cross-attention ->
-// cross o (+residual) -> LN -> fc1 (+act) -> fc2 (+residual) -> LN, then the vocabulary projection with per-tile
-// argmax and the pick. The residual stream x stays fp32; projections add into it in their epilogue.
+// embed + embedding LayerNorm, then per layer  qkv (LN on load) -> self-attention -> o (+residual) -> cross q (LN on
+// load) -> cross-attention -> cross o (+residual) -> fc1 (LN on load, activation) -> fc2 (+residual), then the
+// vocabulary projection (final LN on load) with per-tile argmax and the pick: 3 + 8 L kernels. The residual stream x
+// stays fp32; projections add into it in their epilogue and normalise it while staging their operand.
 #include "common.cuh"
 
 namespace b200dec_detail {
-int linear_impl(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, void* out, int out_kind,
-                int ldo, int act, int pdl, void* stream);
-int head_impl(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, float* pmax, int* pidx,
-              float* logits, int pdl, void* stream);
+int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
+                int out_kind, int ldo, int act, int pdl, void* stream);
+int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
+              int* pidx, float* logits, int pdl, void* stream);
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
-                  const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
-                  void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
-int layer_norm_impl(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream);
+                  const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
+                  float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
               const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax, int pdl,
@@ -31,56 +31,66 @@ extern "C" {
 
 int b200dec_step_launches(const b200dec_plan* plan, int rows) {
   (void)rows;
-  return plan ? 3 + 11 * plan->layers : 0;
+  return plan ? 3 + 8 * plan->layers : 0;
 }
 
-int b200dec_step(const b200dec_plan* pl, int rows, void* stream) {
+// Rows [row0, row0 + rows) of the step's batch as one chain of kernels. Every scratch buffer is indexed by row, so
+// disjoint row ranges may run concurrently on different streams (the caller forks and joins them).
+int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) {
   B200_REQUIRE(pl && pl->layer && pl->layers >= 1, "step: null plan or no layers");
-  B200_REQUIRE(rows >= 1 && rows <= 128, "step: rows %d outside 1..128", rows);
+  B200_REQUIRE(rows >= 1 && row0 >= 0 && row0 + rows <= 128, "step: rows %d + %d outside 0..128", row0, rows);
   B200_REQUIRE(pl->heads * pl->head_dim == D_MODEL, "step: heads * head_dim must be %d", D_MODEL);
   B200_REQUIRE(pl->vocab == pl->head.n, "step: vocab %d vs head rows %d", pl->vocab, pl->head.n);
-  const int hd = pl->heads * pl->head_dim, pdl = pl->pdl;
-  const int ok_a = pl->a_kind == B200DEC_A_F16 ? B200DEC_OUT_F16 : B200DEC_OUT_F32;
-  const int ok_head = pl->head_a_kind == B200DEC_A_F16 ? B200DEC_OUT_F16 : B200DEC_OUT_F32;
+  const int hd = pl->heads * pl->head_dim;
+  // which launches carry the programmatic-dependent-launch attribute: bit 0 a projection (or the pick) that follows a
+  // projection, bit 1 the attention kernels, bit 2 a projection that follows an attention kernel
+  const int pdl = pl->pdl & 1, pdl_attn = (pl->pdl >> 1) & 1, pdl_after = (pl->pdl >> 2) & 1;
+  const bool a16 = pl->a_kind == B200DEC_A_F16;
+  const int ok_a = a16 ? B200DEC_OUT_F16 : B200DEC_OUT_F32;
   const float scale = 1.0f / sqrtf((float)pl->head_dim);
-  const int ffn = pl->layer[0].fc1.n;
+  const int ffn = pl->layer[0].fc1.n, partials = b200dec_head_partials(&pl->head);
+  // this row range's share of every buffer
+  const int32_t* active = pl->active + row0;
+  float* x = pl->x + (size_t)row0 * D_MODEL;
+  float* qkv = pl->qkv + (size_t)row0 * 3 * hd;
+  float* cq = pl->cq + (size_t)row0 * hd;
+  void* att = (char*)pl->att + (size_t)row0 * hd * (a16 ? 2 : 4);
+  void* mid = (char*)pl->mid + (size_t)row0 * ffn * (a16 ? 2 : 4);
+  float* attn_part = pl->attn_part ? pl->attn_part + b200dec_attention_scratch_floats(row0, pl->heads, pl->head_dim) : nullptr;
+  int32_t* attn_count = pl->attn_count ? pl->attn_count + (size_t)row0 * pl->heads : nullptr;
+  float* head_max = pl->head_max + (size_t)row0 * partials;
+  int32_t* head_idx = pl->head_idx + (size_t)row0 * partials;
+  float* logits = pl->logits ? pl->logits + (size_t)row0 * pl->vocab : nullptr;
 
-  B200_TRY(embed_ln_impl(pl->active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
-                         pl->emb_ln, pl->layer[0].ln1, pl->x, pl->hn, ok_a, rows, pl->status, pdl, stream));
+  B200_TRY(embed_ln_impl(active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
+                         pl->emb_ln, pl->layer[0].ln1, x, nullptr, B200DEC_OUT_F32, rows, pl->status, pdl, stream));
   for (int i = 0; i < pl->layers; ++i) {
     const b200dec_layer& ly = pl->layer[i];
-    const bool last = i + 1 == pl->layers;
-    B200_TRY(linear_impl(&ly.qkv, pl->hn, pl->a_kind, D_MODEL, rows, pl->qkv, B200DEC_OUT_F32, 3 * hd,
+    B200_TRY(linear_impl(&ly.qkv, x, pl->a_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream));
-    B200_TRY(b200dec_attention(1, pl->active, pl->qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
-                               pl->head_dim, pl->seq, scale, pl->att, ok_a, rows, pl->attn_part, pl->attn_count,
-                               pl->status, pdl, stream));
-    B200_TRY(linear_impl(&ly.o, pl->att, pl->a_kind, hd, rows, pl->x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
-                         pdl, stream));
-    B200_TRY(layer_norm_impl(pl->x, ly.ln2, pl->hn, ok_a, rows, pdl, stream));
-    B200_TRY(linear_impl(&ly.cq, pl->hn, pl->a_kind, D_MODEL, rows, pl->cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
+    B200_TRY(b200dec_attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
+                               pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
+                               pdl_attn, stream));
+    B200_TRY(linear_impl(&ly.o, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
+                         pdl_after, stream));
+    B200_TRY(linear_impl(&ly.cq, x, pl->a_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
                          stream));
-    B200_TRY(b200dec_attention(0, pl->active, pl->cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len,
-                               pl->slots, pl->heads, pl->head_dim, pl->frames, scale, pl->att, ok_a, rows,
-                               pl->attn_part, pl->attn_count, pl->status, pdl, stream));
-    B200_TRY(linear_impl(&ly.co, pl->att, pl->a_kind, hd, rows, pl->x, B200DEC_OUT_F32_ADD, D_MODEL,
+    B200_TRY(b200dec_attention(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len, pl->slots,
+                               pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows, attn_part, attn_count,
+                               pl->status, pdl_attn, stream));
+    B200_TRY(linear_impl(&ly.co, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
+                         pdl_after, stream));
+    B200_TRY(linear_impl(&ly.fc1, x, pl->a_kind, &ly.ln3, D_MODEL, rows, mid, ok_a, ffn, pl->act, pdl, stream));
+    B200_TRY(linear_impl(&ly.fc2, mid, pl->a_kind, nullptr, ffn, rows, x, B200DEC_OUT_F32_ADD, D_MODEL,
                          B200DEC_ACT_NONE, pdl, stream));
-    B200_TRY(layer_norm_impl(pl->x, ly.ln3, pl->hn, ok_a, rows, pdl, stream));
-    B200_TRY(linear_impl(&ly.fc1, pl->hn, pl->a_kind, D_MODEL, rows, pl->mid, ok_a, ffn, pl->act, pdl, stream));
-    B200_TRY(linear_impl(&ly.fc2, pl->mid, pl->a_kind, ffn, rows, pl->x, B200DEC_OUT_F32_ADD, D_MODEL,
-                         B200DEC_ACT_NONE, pdl, stream));
-    if (last)
-      B200_TRY(layer_norm_impl(pl->x, pl->final_ln, pl->hn_head, ok_head, rows, pdl, stream));
-    else
-      B200_TRY(layer_norm_impl(pl->x, pl->layer[i + 1].ln1, pl->hn, ok_a, rows, pdl, stream));
   }
-  const int partials = b200dec_head_partials(&pl->head);
-  B200_TRY(head_impl(&pl->head, pl->hn_head, pl->head_a_kind, D_MODEL, rows, pl->head_max, pl->head_idx, pl->logits,
-                     pdl, stream));
-  B200_TRY(pick_impl(pl->head_max, pl->head_idx, partials, pl->active, rows, pl->slots, pl->tok, pl->pos,
-                     pl->finished, pl->forced, pl->max_prompt, pl->plen, pl->limit, pl->out, pl->out_cols, pl->eos,
-                     pl->argmax, pdl, stream));
+  B200_TRY(head_impl(&pl->head, x, pl->head_a_kind, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pdl,
+                     stream));
+  B200_TRY(pick_impl(head_max, head_idx, partials, active, rows, pl->slots, pl->tok, pl->pos, pl->finished, pl->forced,
+                     pl->max_prompt, pl->plen, pl->limit, pl->out, pl->out_cols, pl->eos, pl->argmax, pdl, stream));
   return 0;
 }
+
+int b200dec_step(const b200dec_plan* pl, int rows, void* stream) { return b200dec_step_rows(pl, 0, rows, stream); }
 
 }  // extern "C"

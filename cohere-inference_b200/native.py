@@ -18,13 +18,13 @@ W_BF16, W_INT8, W_INT8_24 = 0, 1, 2
 A_F16, A_F32_SPLIT = 0, 1
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
-ST_TOKEN_RANGE, ST_POS_RANGE, ST_FRAMES_RANGE, ST_SLOT_RANGE = 1, 2, 4, 8
+ST_TOKEN_RANGE, ST_POS_RANGE, ST_FRAMES_RANGE, ST_SLOT_RANGE, ST_TIMEOUT = 1, 2, 4, 8, 16
 
 vp, i32, i64, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
 
 
 class Weight(C.Structure):
-    _fields_ = [("w", vp), ("meta", vp), ("scale", vp), ("bias", vp), ("n", i32), ("k", i32), ("kind", i32),
+    _fields_ = [("w", vp), ("meta", vp), ("scale", vp), ("bias", vp), ("ln_g", vp), ("ln_bias", vp), ("n", i32), ("k", i32), ("kind", i32),
                 ("warps", i32), ("ksplit", i32)]
 
 
@@ -47,7 +47,7 @@ class Plan(C.Structure):
                 ("head", Weight),
                 ("active", vp), ("tok", vp), ("pos", vp), ("plen", vp), ("limit", vp), ("cross_len", vp),
                 ("finished", vp), ("forced", vp), ("out", vp), ("status", vp),
-                ("x", vp), ("hn", vp), ("hn_head", vp), ("qkv", vp), ("cq", vp), ("att", vp), ("mid", vp),
+                ("x", vp), ("qkv", vp), ("cq", vp), ("att", vp), ("mid", vp),
                 ("attn_part", vp), ("attn_count", vp), ("head_max", vp), ("head_idx", vp),
                 ("logits", vp), ("argmax", vp)]
 
@@ -68,9 +68,11 @@ PROTOTYPES = {
     "b200dec_embed_ln": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, Norm, Norm, vp, vp, C.c_int, C.c_int, vp,
                                    C.c_int, vp]),
     "b200dec_layer_norm": (C.c_int, [vp, Norm, vp, C.c_int, C.c_int, C.c_int, vp]),
-    "b200dec_linear": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.c_int, C.c_int, vp, C.c_int, C.c_int, C.c_int,
-                                 C.c_int, vp]),
-    "b200dec_head_argmax": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
+    "b200dec_linear": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, C.c_int, C.c_int,
+                                 C.c_int, C.c_int, vp]),
+    "b200dec_linear_fits": (C.c_int, [C.c_int] * 7),
+    "b200dec_head_argmax": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, vp, vp,
+                                      C.c_int, vp]),
     "b200dec_head_partials": (C.c_int, [C.POINTER(Weight)]),
     "b200dec_pick": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp, vp, vp, C.c_int,
                                C.c_int, vp, C.c_int, vp]),
@@ -79,6 +81,7 @@ PROTOTYPES = {
     "b200dec_attention_scratch_floats": (i64, [C.c_int, C.c_int, C.c_int]),
     "b200dec_scatter_kv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_step": (C.c_int, [C.POINTER(Plan), C.c_int, vp]),
+    "b200dec_step_rows": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_int, vp]),
     "b200dec_step_launches": (C.c_int, [C.POINTER(Plan), C.c_int]),
 }
 

@@ -64,23 +64,28 @@ def compress_24(q: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
 # (N, K) -> (warps per CTA, CTAs per cluster along K) by weight kind: CTAs = N / (16 warps) * ksplit, K / ksplit in
 # {128, 256, 512}. Chosen so every projection spreads over about one CTA per SM (148) or two.
 TILE_CONFIG = {
-    (3072, 1024): (4, 4),
-    (1024, 1024): (4, 8),
-    (4096, 1024): (4, 4),
-    (1024, 4096): (4, 8),
-    (16384, 1024): (8, 2),
+    (3072, 1024): [(8, 8), (4, 8), (4, 4)],
+    (1024, 1024): [(4, 8), (4, 4)],
+    (4096, 1024): [(8, 8), (4, 8), (4, 4)],
+    (1024, 4096): [(4, 8)],
+    (16384, 1024): [(8, 8), (8, 4), (8, 2)],
 }
 
 
-def tile_config(n: int, k: int, kind: int, split_rows128: bool = False) -> tuple[int, int]:
-    warps, ksplit = TILE_CONFIG.get((n, k), (4, max(1, k // 256)))
-    if split_rows128 and k // ksplit > 256:  # a split fp32 operand of 128 rows fits shared memory up to 256 per CTA
-        ksplit = k // 256
-    while k // ksplit > 512:
-        ksplit *= 2
-    assert ksplit in (1, 2, 4, 8) and k // ksplit in (128, 256, 512), (n, k, ksplit)
-    assert (16 * warps) % (8 * ksplit) == 0
-    return warps, ksplit
+def tile_config(n: int, k: int, kind: int, a_kind: int = nv.A_F16, ln: bool = False, max_rows: int = 64
+                ) -> tuple[int, int]:
+    """The first preferred (warps, ksplit) of the shape whose shared-memory footprint fits `max_rows` rows in one
+    pass; if none does, the first valid one (the library then makes two passes of 64 rows)."""
+    fits = nv.lib().b200dec_linear_fits
+    prefs = TILE_CONFIG.get((n, k), []) + [(w, s) for s in (8, 4, 2, 1) for w in (4, 8)]
+    valid = [(w, s) for w, s in prefs if n % (16 * w) == 0 and (k, s) in ((1024, 8), (1024, 4), (1024, 2), (4096, 8))
+             and (16 * w) % (8 * s) == 0 and (k // s) % {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_INT8_24: 128}[kind] == 0
+             and (not ln or k == 1024)]
+    assert valid, f"no tile for a ({n}, {k}) projection"
+    for w, s in valid:
+        if fits(kind, a_kind, int(ln), w, s, k, max_rows):
+            return w, s
+    return valid[0]
 
 
 @dataclass
@@ -98,10 +103,13 @@ class PackedLinear:
     q: torch.Tensor | None = None
     kept: torch.Tensor | None = None
     words: torch.Tensor | None = None
+    # for a projection with a folded LayerNorm: sum_k gamma[k] W[n][k] and sum_k beta[k] W[n][k]
+    ln_g: torch.Tensor | None = None
+    ln_bias: torch.Tensor | None = None
 
     def struct(self) -> nv.Weight:
-        return nv.Weight(nv.ptr(self.tiled), nv.ptr(self.meta), nv.ptr(self.scale), nv.ptr(self.bias), self.n, self.k,
-                         self.kind, self.warps, self.ksplit)
+        return nv.Weight(nv.ptr(self.tiled), nv.ptr(self.meta), nv.ptr(self.scale), nv.ptr(self.bias),
+                         nv.ptr(self.ln_g), nv.ptr(self.ln_bias), self.n, self.k, self.kind, self.warps, self.ksplit)
 
     def stream_bytes(self) -> int:
         """Bytes a step reads for this projection: weights (+ selectors) + 4 B scale + bias per channel as stored."""
@@ -115,13 +123,25 @@ class PackedLinear:
         return b
 
 
-def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep_reference: bool = False,
-                split_rows128: bool = False) -> PackedLinear:
-    """One (N, K) projection into the streaming layout of the given kind (native.W_BF16 / W_INT8 / W_INT8_24)."""
+def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep_reference: bool = False, *,
+                a_kind: int | None = None, ln: tuple[torch.Tensor, torch.Tensor] | None = None,
+                max_rows: int = 64) -> PackedLinear:
+    """One (N, K) projection into the streaming layout of the given kind (native.W_BF16 / W_INT8 / W_INT8_24).
+    a_kind and max_rows describe how it will be called (operand precision, most rows): they only choose the CTA
+    tile. ln = (gamma, beta) of the LayerNorm this projection folds in: the two per-channel vectors of that fold are
+    computed here from the weights the kernel multiplies by."""
     w = _f32(weight)
     n, k = w.shape
     lib = nv.lib()
-    warps, ksplit = tile_config(n, k, kind, split_rows128)
+    if a_kind is None:
+        a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
+    warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
+    ln_g = ln_bias = None
+    if ln is not None:
+        wd = dequantized(w, kind).double()
+        ln_g = (wd @ ln[0].detach().double().to(w.device)).float().contiguous()
+        ln_bias = (wd @ ln[1].detach().double().to(w.device)).float().contiguous()
+        del wd
     b = None if bias is None else bias.detach().float().contiguous()
     dev = w.device
     tiled = torch.empty(lib.b200dec_tiled_bytes(kind, n, k), dtype=torch.uint8, device=dev)
@@ -142,7 +162,7 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     torch.cuda.current_stream().synchronize()  # the temporaries above may be freed once the tilers are done
     if not keep_reference:
         q = kept = words = None
-    return PackedLinear(kind, n, k, tiled, meta, scale, b, warps, ksplit, q, kept, words)
+    return PackedLinear(kind, n, k, tiled, meta, scale, b, warps, ksplit, q, kept, words, ln_g, ln_bias)
 
 
 def dequantized(weight: torch.Tensor, kind: int) -> torch.Tensor:

@@ -29,22 +29,23 @@ ACTS = {"relu": nv.ACT_RELU, "gelu": nv.ACT_GELU}
 class _Layer:
     """Packed projections and fp32 norms of one decoder layer (reference: _Layer, stream_decoder.py:51-62)."""
 
-    def __init__(self, layer, kind: int, ffn_kind: int, wide: bool, keep_reference: bool):
+    def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool):
         sa, ca = layer.self_attn, layer.encoder_attn
-        dev = sa.q_proj.weight.device
         f = lambda t: t.detach().float().contiguous()  # noqa: E731
         self.norms = [(f(m.weight), f(m.bias), float(m.eps)) for m in
                       (layer.input_layernorm, layer.post_attention_layernorm, layer.final_layernorm)]
         cat = lambda *p: torch.cat([f(x) for x in p]).contiguous()  # noqa: E731
-        pk = lambda w, b, k: pack_linear(w, b, k, keep_reference, wide)  # noqa: E731
+
+        def pk(w, b, k, ln=None):  # ln: the norm this projection folds in (it reads the fp32 residual stream)
+            return pack_linear(w, b, k, keep_reference, a_kind=a_kind, ln=ln and ln[:2], max_rows=max_rows)
+
         self.qkv = pk(cat(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight),
-                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), kind)
+                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), kind, self.norms[0])
         self.o = pk(sa.o_proj.weight, sa.o_proj.bias, kind)
-        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, kind)
+        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, kind, self.norms[1])
         self.co = pk(ca.o_proj.weight, ca.o_proj.bias, kind)
-        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, ffn_kind)
+        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, ffn_kind, self.norms[2])
         self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, ffn_kind)
-        assert dev.type == "cuda"
 
     def projections(self) -> list[PackedLinear]:
         return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
@@ -55,15 +56,18 @@ class StreamDecoder:
 
     def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
-                 eos: int | None = None, record: bool = False, pdl: bool = True, graphs: bool = True,
-                 head_split: bool = True, keep_reference: bool = False):
+                 eos: int | None = None, record: bool = False, pdl: bool | int = 1, graphs: bool = True,
+                 head_split: bool = True, keep_reference: bool = False, chains: int = 2):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
         magnitude-pruned 2:4 and stored compressed (needs int8). eos: overrides config.eos_token_id (-1: never end on
         a token). record: keep the last step's logits and every slot's un-forced argmax (teacher forcing, tests).
-        pdl: chain the step's kernels with programmatic dependent launch. graphs: capture one CUDA graph per bucket
-        (False: launch the kernels directly, for debugging)."""
+        pdl: which of the step's kernels launch programmatically after their predecessor (bits: 1 a projection after a
+        projection, 2 the attention kernels, 4 a projection after attention; True = 1, False = 0). graphs: capture one CUDA graph per bucket
+        (False: launch the kernels directly, for debugging). chains: a step's rows are split into up to this many
+        independent kernel chains that run concurrently (parallel branches of the graph), so that one chain's
+        attention overlaps the others' projections; results do not depend on it."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
         dec, cfg = model.model.decoder, model.config
@@ -84,7 +88,7 @@ class StreamDecoder:
         ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
         self.a_kind = nv.A_F16 if int8 else nv.A_F32_SPLIT
         self.head_a_kind = nv.A_F32_SPLIT if (head_split or not int8) else nv.A_F16
-        wide = max(self.buckets) > 64  # split fp32 operands of > 64 rows: at most 256 of K per CTA
+        bm = max(self.buckets)
         with torch.cuda.device(dev):
             f = lambda t: t.detach().float().contiguous()  # noqa: E731
             self.embed = dec.embed_tokens.weight.detach().to(torch.bfloat16).contiguous()
@@ -92,10 +96,9 @@ class StreamDecoder:
             self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
             ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
             self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
-            self.layers = [_Layer(layer, kind, ffn_kind, wide and self.a_kind == nv.A_F32_SPLIT, keep_reference)
-                           for layer in dec.layers]
+            self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference) for layer in dec.layers]
             self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, kind, keep_reference,
-                                    wide and self.head_a_kind == nv.A_F32_SPLIT)
+                                    a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
             # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection, kept as the
             # fp32 values the quantised (or bf16) weights stand for
             self.proj = (dequantized(dec.proj.weight, kind), f(dec.proj.bias))
@@ -124,15 +127,11 @@ class StreamDecoder:
             self.finished = torch.ones(S + 1, device=dev, dtype=torch.uint8)
             self.forced = torch.full((S + 1, max_prompt), self.pad, device=dev, dtype=torch.long)
             self.out = torch.full((S + 1, self.seq + 1), self.pad, device=dev, dtype=torch.long)
-            bm = max(self.buckets)
             self.active = torch.full((bm,), S, **i32)
             self.status = torch.zeros(1, **i32)
             adt = torch.float16 if self.a_kind == nv.A_F16 else torch.float32
-            hdt = torch.float16 if self.head_a_kind == nv.A_F16 else torch.float32
             f32 = dict(device=dev, dtype=torch.float32)
             self.x = torch.zeros(bm, self.width, **f32)
-            self.hn = torch.zeros(bm, self.width, device=dev, dtype=adt)
-            self.hn_head = torch.zeros(bm, self.width, device=dev, dtype=hdt)
             self.qkv = torch.zeros(bm, 3 * self.width, **f32)
             self.cq = torch.zeros(bm, self.width, **f32)
             self.att = torch.zeros(bm, self.width, device=dev, dtype=adt)
@@ -150,6 +149,8 @@ class StreamDecoder:
             self.flags = torch.ones(S + 1, dtype=torch.uint8).pin_memory()
             self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
+            self.chains = max(1, int(chains))
+            self.side_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(self.chains - 1)]
             self._build_plan()
             self.launches_per_step = lib.b200dec_step_launches(C.byref(self.plan), 1)
             self.weight_bytes = sum(p.stream_bytes() for ly in self.layers for p in ly.projections()) + \
@@ -182,15 +183,43 @@ class StreamDecoder:
         p.layer = C.cast(self._layer_structs, C.POINTER(nv.Layer))
         p.head = self.head.struct()
         for name in ("active", "tok", "pos", "plen", "limit", "cross_len", "finished", "forced", "out", "status", "x",
-                     "hn", "hn_head", "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
+                     "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
                      "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
         self.plan = p
 
     def _step(self, b: int) -> None:
         """Bucket b's kernels and the flags' copy on the current stream (reference: _step, stream_decoder.py:176-199)."""
-        nv.check(nv.lib().b200dec_step(C.byref(self.plan), b, nv.stream_ptr()))
+        ranges = self.row_ranges(b)
+        if len(ranges) == 1:
+            nv.check(nv.lib().b200dec_step(C.byref(self.plan), b, nv.stream_ptr()))
+        else:
+            # independent chains over disjoint rows on forked streams: one chain's attention (HBM-bound) overlaps the
+            # others' projections (latency-bound); the fork and the join are events, so a capture records them as
+            # parallel branches of the graph
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for (r0, n), side in zip(ranges, [main] + self.side_streams):
+                if side is not main:
+                    side.wait_event(fork)
+                nv.check(nv.lib().b200dec_step_rows(C.byref(self.plan), r0, n, side.cuda_stream))
+                if side is not main:
+                    done = torch.cuda.Event()
+                    done.record(side)
+                    main.wait_event(done)
         self.flags.copy_(self.finished, non_blocking=True)
+
+    def row_ranges(self, b: int) -> list[tuple[int, int]]:
+        """The (first row, rows) of the concurrent chains a step of b rows is split into: at most `chains` ranges of
+        whole 8-row tiles."""
+        c = max(1, min(self.chains, b // 8))
+        per = ((b + c - 1) // c + 7) // 8 * 8 if c > 1 else b
+        out, r0 = [], 0
+        while r0 < b:
+            out.append((r0, min(per, b - r0)))
+            r0 += per
+        return out
 
     @torch.no_grad()
     def _capture(self) -> None:
@@ -223,9 +252,12 @@ class StreamDecoder:
         self.stream.synchronize()
         st = int(self.status.item())
         if st:
-            names = [n for n, bit in (("token id", nv.ST_TOKEN_RANGE), ("position", nv.ST_POS_RANGE),
-                                      ("frame count", nv.ST_FRAMES_RANGE), ("slot", nv.ST_SLOT_RANGE)) if st & bit]
-            raise nv.NativeError("decoder kernels saw out-of-range " + ", ".join(names))
+            names = [n for n, bit in (("out-of-range token id", nv.ST_TOKEN_RANGE),
+                                      ("out-of-range position", nv.ST_POS_RANGE),
+                                      ("out-of-range frame count", nv.ST_FRAMES_RANGE),
+                                      ("out-of-range slot", nv.ST_SLOT_RANGE),
+                                      ("a bounded wait inside a kernel ran out", nv.ST_TIMEOUT)) if st & bit]
+            raise nv.NativeError("decoder kernels reported: " + ", ".join(names))
 
     # ---- host side -----------------------------------------------------------------------------------------------
 

@@ -26,7 +26,8 @@ enum { B200DEC_ACT_NONE = 0, B200DEC_ACT_RELU = 1, B200DEC_ACT_GELU = 2 };
 enum { B200DEC_OK = 0, B200DEC_EINVAL = 1, B200DEC_ECUDA = 2, B200DEC_EARCH = 3 };
 
 /* bits of the device status word (written by kernels, never cleared by them) */
-enum { B200DEC_ST_TOKEN_RANGE = 1, B200DEC_ST_POS_RANGE = 2, B200DEC_ST_FRAMES_RANGE = 4, B200DEC_ST_SLOT_RANGE = 8 };
+enum { B200DEC_ST_TOKEN_RANGE = 1, B200DEC_ST_POS_RANGE = 2, B200DEC_ST_FRAMES_RANGE = 4, B200DEC_ST_SLOT_RANGE = 8,
+       B200DEC_ST_TIMEOUT = 16 /* a bounded wait inside a kernel ran out; the kernel returned without its result */ };
 
 /* One projection y = a W^T (* scale) + bias in the tiled layout. */
 typedef struct b200dec_weight {
@@ -34,6 +35,8 @@ typedef struct b200dec_weight {
   const void* meta;    /* tiled 2:4 selectors, else NULL */
   const float* scale;  /* per output channel, int8 kinds; NULL for bf16 */
   const float* bias;   /* per output channel or NULL */
+  const float* ln_g;   /* for a projection called with a folded LayerNorm: g[n] = sum_k gamma[k] W[n][k] ... */
+  const float* ln_bias;/* ... and sum_k beta[k] W[n][k], of the dequantised weights W; else NULL */
   int32_t n, k;        /* logical shape */
   int32_t kind;        /* B200DEC_W_* */
   int32_t warps;       /* output tile of a CTA = 16 * warps channels (4 or 8) */
@@ -83,8 +86,6 @@ typedef struct b200dec_plan {
   int32_t* status;        /* one word, B200DEC_ST_* bits */
   /* scratch owned by the caller */
   float* x;       /* (max rows, 1024) residual stream */
-  void* hn;       /* (max rows, 1024) a16 or f32 by a_kind */
-  void* hn_head;  /* (max rows, 1024) a16 or f32 by head_a_kind */
   float* qkv;     /* (max rows, 3072) */
   float* cq;      /* (max rows, 1024) */
   void* att;      /* (max rows, 1024) a16 or f32 */
@@ -125,23 +126,31 @@ int b200dec_tile_24(const int8_t* kept, const int32_t* words, int n, int k, void
 
 /* ---- step kernels ------------------------------------------------------------------------------------------- */
 
-/* x = LN_emb(embed[tok[s]] + pos_table[pos[s]]), hn = LN_1(x), s = active[r] in 0..slots (slots = the dummy).
+/* x = LN_emb(embed[tok[s]] + pos_table[pos[s]]) and, when hn is not NULL, hn = LN_1(x); s = active[r] in 0..slots
+ * (slots = the dummy).
  * Replaces dec_embed (kernels/csrc/decoder_ops.cu:24-54, 208-219). */
 int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                      const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                      float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
 /* hn = LN(x) for an fp32 residual stream that the preceding projection already added into
- * (B200DEC_OUT_F32_ADD). Replaces dec_add_ln (kernels/csrc/decoder_ops.cu:56-83, 221-231). */
+ * (B200DEC_OUT_F32_ADD). Replaces dec_add_ln (kernels/csrc/decoder_ops.cu:56-83, 221-231). The step itself does not
+ * launch it: its projections normalise while staging their operand (the `ln` argument of b200dec_linear). */
 int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream);
-/* out = act(a W^T * scale + bias) for rows <= 128. Replaces dec_w8_linear (kernels/csrc/dec_w8.cu:46-234), the
- * Triton _linear (kernels/decoder_kernels.py:19-66) and the cuBLAS F.linear of kernels/stream_decoder.py:23-27. */
-int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, void* out, int out_kind,
-                   int ldo, int act, int pdl, void* stream);
+/* out = act(a' W^T * scale + bias) for rows <= 128, where a' = a, or LayerNorm(a) of the fp32 rows a when ln is not
+ * NULL (then K = 1024, a_kind only selects the operand precision, and w->ln_g / w->ln_bias must have been computed
+ * from ln's gamma and beta). Replaces dec_w8_linear
+ * (kernels/csrc/dec_w8.cu:46-234), the Triton _linear (kernels/decoder_kernels.py:19-66), the cuBLAS F.linear of
+ * kernels/stream_decoder.py:23-27 and, with ln, the dec_add_ln in front of it (kernels/csrc/decoder_ops.cu:56-83). */
+int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                   void* out, int out_kind, int ldo, int act, int pdl, void* stream);
+/* 1 when a projection with this tile (warps, ksplit) fits shared memory for `rows` rows in one pass (else the call
+ * makes two passes of up to 64 rows and reads the weights twice). Host-only query. */
+int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int k, int rows);
 /* Vocabulary projection fused with the per-tile argmax: writes, per row, b200dec_head_partials(w) (max, first index)
  * pairs; logits (rows, n) fp32 optional. Replaces the head projection + the scan of dec_pick
  * (kernels/stream_decoder.py:173-174, 197; kernels/csrc/decoder_ops.cu:106-147). */
-int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, int lda, int rows, float* part_max,
-                        int32_t* part_idx, float* logits, int pdl, void* stream);
+int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                        float* part_max, int32_t* part_idx, float* logits, int pdl, void* stream);
 int b200dec_head_partials(const b200dec_weight* w);
 /* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and
  * finished slots change nothing. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
@@ -164,6 +173,10 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
 /* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
  * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
 int b200dec_step(const b200dec_plan* plan, int rows, void* stream);
+/* The same for rows [row0, row0 + rows) of the step's batch only. Disjoint row ranges share no scratch, so a caller
+ * may run several ranges concurrently on forked streams to overlap one range's attention (bound by HBM) with another's
+ * projections (bound by latency). No counterpart in the reference, which runs the batch as one chain. */
+int b200dec_step_rows(const b200dec_plan* plan, int row0, int rows, void* stream);
 /* Kernels b200dec_step launches for `rows` rows (for launch accounting). */
 int b200dec_step_launches(const b200dec_plan* plan, int rows);
 

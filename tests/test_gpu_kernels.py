@@ -64,7 +64,7 @@ def test_compress_patterns_and_rejects_dense(pk, golden_dir):
 
 def test_tiled_layouts(nv, pk):
     rng = np.random.default_rng(3)
-    n, k = 64, 256
+    n, k = 64, 1024
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     # int8: byte [nt][kb][h][lane = 4 g + t][e] = q[16 nt + g + 8 h][64 kb + 16 t + e] + 128
     p = pk.pack_linear(cuda(w), None, nv.W_INT8, keep_reference=True)
@@ -109,29 +109,40 @@ def test_tiled_layouts(nv, pk):
 SHAPES = [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (16384, 1024)]
 
 
-def _linear_case(nv, pk, kind, a_kind, n, k, rows, act, out_kind, seed, bias=True):
+def _linear_case(nv, pk, kind, a_kind, n, k, rows, act, out_kind, seed, bias=True, ln=False, pdl=0):
     rng = np.random.default_rng(seed)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     b = (rng.standard_normal(n) * 0.1).astype(np.float32) if bias else None
     a = rng.standard_normal((rows, k)).astype(np.float32)
     x0 = rng.standard_normal((rows, n)).astype(np.float32)
-    p = pk.pack_linear(cuda(w), None if b is None else cuda(b), kind)
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    g_d, b_d = cuda(gam), cuda(bet)
+    p = pk.pack_linear(cuda(w), None if b is None else cuda(b), kind, a_kind=a_kind, ln=(g_d, b_d) if ln else None,
+                       max_rows=rows)
     wd = pk.dequantized(cuda(w), kind).cpu().numpy()
-    if a_kind == nv.A_F16:
+    norm = None
+    if ln:  # the operand is LayerNorm(a) of fp32 rows with their own offsets and spreads, folded into the epilogue
+        a = (a * (1 + rng.random((rows, 1))) + rng.standard_normal((rows, 1))).astype(np.float32)
+        norm = nv.norm(g_d, b_d, 1e-5)
+        a_dev = cuda(a)
+        a_ref = layer_norm(a, gam, bet, 1e-5)  # exact: the kernel's fp16 rounding of (a - c) * gamma is its error
+    elif a_kind == nv.A_F16:
         a_dev = cuda(a.astype(np.float16))
         a_ref = a.astype(np.float16).astype(np.float32)
     else:
         a_dev, a_ref = cuda(a), a
     y = a_ref.astype(np.float64) @ wd.astype(np.float64).T + (0 if b is None else b)
-    y = activation({nv.ACT_NONE: "none", nv.ACT_RELU: "relu", nv.ACT_GELU: "gelu"}[act], y.astype(np.float32)) \
-        if act != nv.ACT_NONE else y.astype(np.float32)
+    y = y.astype(np.float32)
+    if act != nv.ACT_NONE:
+        y = activation({nv.ACT_RELU: "relu", nv.ACT_GELU: "gelu"}[act], y)
     if out_kind == nv.OUT_F16:
         out = torch.zeros(rows, n, dtype=torch.float16, device="cuda")
     else:
         out = cuda(x0) if out_kind == nv.OUT_F32_ADD else torch.zeros(rows, n, device="cuda")
     ws = p.struct()
-    nv.check(nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a_dev), a_kind, k, rows, nv.ptr(out), out_kind, n, act, 0,
-                                     nv.stream_ptr()))
+    nv.check(nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a_dev), a_kind, C.byref(norm) if ln else None, k, rows,
+                                     nv.ptr(out), out_kind, n, act, pdl, nv.stream_ptr()))
     torch.cuda.synchronize()
     got = out.float().cpu().numpy()
     if out_kind == nv.OUT_F32_ADD:
@@ -157,6 +168,20 @@ def test_linear_kinds(nv, pk, kind, a_kind, n, k, rows):
     np.testing.assert_allclose(got, want, atol=3e-4, rtol=1e-5)
 
 
+@pytest.mark.parametrize("kind,a_kind", [("W_INT8", "A_F16"), ("W_INT8", "A_F32_SPLIT"), ("W_BF16", "A_F32_SPLIT"),
+                                         ("W_INT8_24", "A_F16")])
+@pytest.mark.parametrize("n", [1024, 3072, 4096])
+@pytest.mark.parametrize("rows", [2, 64, 128])
+def test_linear_layernorm_on_load(nv, pk, kind, a_kind, n, rows):
+    """The operand is LayerNorm(x) of fp32 rows, normalised while staging from statistics the cluster's CTAs exchange."""
+    got, want = _linear_case(nv, pk, getattr(nv, kind), getattr(nv, a_kind), n, 1024, rows, nv.ACT_NONE, nv.OUT_F32,
+                             seed=3 * n + rows, ln=True)
+    # fp16 operand: each of the 1024 terms carries a relative rounding error of up to 2^-11 (outputs are ~0.6 rms);
+    # the split operand keeps ~21 bits
+    tol = 4e-3 if a_kind == "A_F16" else 4e-4
+    np.testing.assert_allclose(got, want, atol=tol, rtol=1e-4)
+
+
 @pytest.mark.parametrize("act", ["ACT_RELU", "ACT_GELU"])
 @pytest.mark.parametrize("out_kind", ["OUT_F16", "OUT_F32_ADD"])
 def test_linear_epilogues(nv, pk, act, out_kind):
@@ -166,7 +191,7 @@ def test_linear_epilogues(nv, pk, act, out_kind):
 
 
 def test_linear_no_bias_and_pdl_flag(nv, pk):
-    got, want = _linear_case(nv, pk, nv.W_INT8, nv.A_F16, 1024, 1024, 5, nv.ACT_NONE, nv.OUT_F32, 5, bias=False)
+    got, want = _linear_case(nv, pk, nv.W_INT8, nv.A_F16, 1024, 1024, 5, nv.ACT_NONE, nv.OUT_F32, 5, bias=False, pdl=1)
     np.testing.assert_allclose(got, want, atol=2e-4, rtol=1e-5)
 
 
@@ -175,26 +200,34 @@ def test_linear_rejects_bad_arguments(nv, pk):
     ws = p.struct()
     a = torch.zeros(4, 1024, dtype=torch.float16, device="cuda")
     out = torch.zeros(4, 1024, device="cuda")
-    rc = nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, 1024, 129, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
+    rc = nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, None, 1024, 129, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
                                  nv.stream_ptr())
     assert rc == 1 and b"rows" in nv.lib().b200dec_last_error()
     ws.ksplit = 3
-    assert nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, 1024, 4, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
+    assert nv.lib().b200dec_linear(C.byref(ws), nv.ptr(a), nv.A_F16, None, 1024, 4, nv.ptr(out), nv.OUT_F32, 1024, 0, 0,
                                    nv.stream_ptr()) == 1
     torch.cuda.synchronize()
 
 
 @pytest.mark.parametrize("rows", [1, 7, 64, 128])
-@pytest.mark.parametrize("a_kind", ["A_F16", "A_F32_SPLIT"])
-def test_head_argmax(nv, pk, rows, a_kind):
+@pytest.mark.parametrize("a_kind,ln", [("A_F16", False), ("A_F32_SPLIT", False), ("A_F32_SPLIT", True)])
+def test_head_argmax(nv, pk, rows, a_kind, ln):
     rng = np.random.default_rng(rows)
     n, k = 16384, 1024
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     b = (rng.standard_normal(n) * 0.01).astype(np.float32)
     a = rng.standard_normal((rows, k)).astype(np.float32)
-    p = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8, split_rows128=rows > 64 and a_kind == "A_F32_SPLIT")
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    g_d, b_d = cuda(gam), cuda(bet)
+    p = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8, a_kind=getattr(nv, a_kind), ln=(g_d, b_d) if ln else None,
+                       max_rows=rows)
     wd = pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy()
-    if a_kind == "A_F16":
+    norm = None
+    if ln:
+        norm = nv.norm(g_d, b_d, 1e-5)
+        a_dev, a_ref = cuda(a), layer_norm(a, gam, bet, 1e-5)
+    elif a_kind == "A_F16":
         a_dev, a_ref = cuda(a.astype(np.float16)), a.astype(np.float16).astype(np.float32)
     else:
         a_dev, a_ref = cuda(a), a
@@ -203,12 +236,12 @@ def test_head_argmax(nv, pk, rows, a_kind):
     pm = torch.zeros(rows, np_, device="cuda")
     pi = torch.zeros(rows, np_, dtype=torch.int32, device="cuda")
     logits = torch.zeros(rows, n, device="cuda")
-    nv.check(nv.lib().b200dec_head_argmax(C.byref(ws), nv.ptr(a_dev), getattr(nv, a_kind), k, rows, nv.ptr(pm),
-                                          nv.ptr(pi), nv.ptr(logits), 0, nv.stream_ptr()))
+    nv.check(nv.lib().b200dec_head_argmax(C.byref(ws), nv.ptr(a_dev), getattr(nv, a_kind), C.byref(norm) if ln else None,
+                                          k, rows, nv.ptr(pm), nv.ptr(pi), nv.ptr(logits), 0, nv.stream_ptr()))
     torch.cuda.synchronize()
     want = (a_ref.astype(np.float64) @ wd.astype(np.float64).T + b).astype(np.float32)
     lg = logits.cpu().numpy()
-    np.testing.assert_allclose(lg, want, atol=3e-4, rtol=1e-5)
+    np.testing.assert_allclose(lg, want, atol=4e-4, rtol=1e-5)
     # the partials are exactly the first-index maxima of the kernel's own logits, tile by tile
     tile = n // np_
     t = lg.reshape(rows, np_, tile)
@@ -281,9 +314,10 @@ def _attention_ref(q, k, v, scale):
 @pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
 @pytest.mark.parametrize("rows", [1, 5, 64])
 @pytest.mark.parametrize("self_", [0, 1])
-def test_attention(nv, H, D, rows, self_):
-    rng = np.random.default_rng(rows * 10 + H + self_)
-    S, cap = max(rows, 4) + 2, 96
+@pytest.mark.parametrize("cap", [96, 300])  # one span of keys per row, and up to three (partials merged in order)
+def test_attention(nv, H, D, rows, self_, cap):
+    rng = np.random.default_rng(rows * 10 + H + self_ + cap)
+    S = max(rows, 4) + 2
     kc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
     vc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
     active = rng.permutation(S)[:rows].astype(np.int32)
@@ -291,6 +325,8 @@ def test_attention(nv, H, D, rows, self_):
     n[active[0]] = 0 if self_ else 1  # shortest case
     if rows > 1:
         n[active[1]] = cap - 1 if self_ else cap  # longest case
+    if rows >= 5 and cap > 130:
+        n[active[2]], n[active[3]], n[active[4]] = 128, 129, 256  # span boundaries
     ld = 3 * H * D if self_ else H * D
     q = rng.standard_normal((rows, ld)).astype(np.float32)
     kd, vd = cuda(kc).to(torch.bfloat16), cuda(vc).to(torch.bfloat16)

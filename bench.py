@@ -105,7 +105,7 @@ def run_ours(args) -> None:
     torch.cuda.set_device(dev)
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
-                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains)
+                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring)
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -181,6 +181,7 @@ def run_ours(args) -> None:
     # ---- the dominant kernel alone: cross-attention over all rows, cycling the layers so no launch finds its
     # cache in L2 (one layer's cross K/V is ~56 MB, the eight together ~450 MB > the 126 MB L2)
     lib, L = nv.lib(), len(dec.layers)
+    attn_fn = lib.b200dec_attention_ring if args.attn_ring else lib.b200dec_attention
     kv_bytes = sum(lens) * 2 * 1024 * 2
     reps = 10
     with torch.cuda.stream(dec.stream):
@@ -190,7 +191,7 @@ def run_ours(args) -> None:
                 ks.record(dec.stream)
             for i in range(reps * L):
                 ly = i % L
-                nv.check(lib.b200dec_attention(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
+                nv.check(attn_fn(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
                                                nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
                                                dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
                                                nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status), 0,
@@ -240,7 +241,7 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
                     "ms_per_step": round(e2e_ms / args.steps, 3)},
             "gpu_launches": dec.launches_per_step * len(dec.row_ranges(BATCH)) * steps_per_pass * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "attention_kernel<64,false> (cross-attention, 64 rows x 16 heads)",
+            "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention") + " kernel <64, cross> (64 rows x 16 heads)",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
                          "traffic": None,
@@ -266,7 +267,8 @@ def run_profile(args) -> None:
     torch.cuda.set_device(dev)
     B = args.profile_slots
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=B, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
-                        buckets=(B,), int8=True, eos=-1, graphs=False, ffn_sparse=args.sparse)
+                        buckets=(B,), int8=True, eos=-1, graphs=False, ffn_sparse=args.sparse, chains=args.chains,
+                        attn_ring=args.attn_ring)
     rng = np.random.default_rng(1000)
     lens = rng.integers(FRAMES[0], FRAMES[1] + 1, B).tolist()
     prompts = [torch.from_numpy(rng.integers(0, 16384, PROMPT).astype(np.int64)) for _ in range(B)]
@@ -337,7 +339,8 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
     ap.add_argument("--pdl", type=int, default=1, help="which launches are programmatic: 1 projection after projection, "
                     "2 attention, 4 projection after attention (sum them)")
-    ap.add_argument("--chains", type=int, default=2, help="concurrent kernel chains a step's rows are split into")
+    ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")
+    ap.add_argument("--chains", type=int, default=1, help="concurrent kernel chains a step's rows are split into")
     ap.add_argument("--profile", type=int, default=0, help="profiler mode: this many directly launched steps")
     ap.add_argument("--profile-slots", type=int, default=BATCH)
     ap.add_argument("--profile-pos", type=int, default=225)

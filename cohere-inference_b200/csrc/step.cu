@@ -62,20 +62,22 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   int32_t* head_idx = pl->head_idx + (size_t)row0 * partials;
   float* logits = pl->logits ? pl->logits + (size_t)row0 * pl->vocab : nullptr;
 
+  const auto attention = pl->attn_ring ? b200dec_attention_ring : b200dec_attention;
+
   B200_TRY(embed_ln_impl(active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
                          pl->emb_ln, pl->layer[0].ln1, x, nullptr, B200DEC_OUT_F32, rows, pl->status, pdl, stream));
   for (int i = 0; i < pl->layers; ++i) {
     const b200dec_layer& ly = pl->layer[i];
     B200_TRY(linear_impl(&ly.qkv, x, pl->a_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream));
-    B200_TRY(b200dec_attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
+    B200_TRY(attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
                                pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
                                pdl_attn, stream));
     B200_TRY(linear_impl(&ly.o, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
                          pdl_after, stream));
     B200_TRY(linear_impl(&ly.cq, x, pl->a_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
                          stream));
-    B200_TRY(b200dec_attention(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len, pl->slots,
+    B200_TRY(attention(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len, pl->slots,
                                pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows, attn_part, attn_count,
                                pl->status, pdl_attn, stream));
     B200_TRY(linear_impl(&ly.co, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,

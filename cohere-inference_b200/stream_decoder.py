@@ -57,7 +57,7 @@ class StreamDecoder:
     def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 1, graphs: bool = True,
-                 head_split: bool = True, keep_reference: bool = False, chains: int = 2):
+                 head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -67,7 +67,8 @@ class StreamDecoder:
         projection, 2 the attention kernels, 4 a projection after attention; True = 1, False = 0). graphs: capture one CUDA graph per bucket
         (False: launch the kernels directly, for debugging). chains: a step's rows are split into up to this many
         independent kernel chains that run concurrently (parallel branches of the graph), so that one chain's
-        attention overlaps the others' projections; results do not depend on it."""
+        attention overlaps the others' projections; results do not depend on it. attn_ring: use the persistent
+        bulk-copy attention kernel (csrc/attention_ring.cu) instead of the one-CTA-per-(row, head) kernel."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
         dec, cfg = model.model.decoder, model.config
@@ -83,6 +84,7 @@ class StreamDecoder:
         self.pad = cfg.pad_token_id
         self.scale = self.d ** -0.5
         self.int8, self.ffn_sparse, self.pdl, self.use_graphs = int8, ffn_sparse, pdl, graphs
+        self.attn_ring = bool(attn_ring)
         self.act = ACTS[cfg.hidden_act]
         kind = nv.W_INT8 if int8 else nv.W_BF16
         ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
@@ -178,6 +180,7 @@ class StreamDecoder:
         p.slots, p.seq, p.frames, p.vocab = self.slots, self.seq, self.frames, self.vocab
         p.max_prompt, p.out_cols, p.pad, p.eos = self.max_prompt, self.out.shape[1], self.pad, self.eos
         p.a_kind, p.max_pos, p.head_a_kind, p.pdl = self.a_kind, self.max_pos, self.head_a_kind, int(self.pdl)
+        p.attn_ring = int(self.attn_ring)
         p.embed, p.pos_table = nv.ptr(self.embed), nv.ptr(self.pos_table)
         p.emb_ln, p.final_ln = nv.norm(*self.emb_ln), nv.norm(*self.final_ln)
         p.layer = C.cast(self._layer_structs, C.POINTER(nv.Layer))

@@ -66,8 +66,10 @@ typedef struct b200dec_plan {
   int32_t slots, seq, frames, vocab;         /* dummy slot = slots; caches hold seq / frames positions */
   int32_t max_prompt, out_cols, pad, eos;    /* forced (slots+1, max_prompt), out (slots+1, out_cols) */
   int32_t a_kind, max_pos;                   /* B200DEC_A_*: operand precision of the layer projections */
-  int32_t head_a_kind, pdl;                  /* operand precision of the vocabulary projection; pdl != 0 chains
-                                                the kernels with programmatic dependent launch */
+  int32_t head_a_kind, pdl;                  /* operand precision of the vocabulary projection; pdl: which launches are
+                                                programmatic (1 projection after projection, 2 attention, 4 projection
+                                                after attention) */
+  int32_t attn_ring, _pad0;                  /* != 0: the attention kernels are b200dec_attention_ring */
   const void* embed;  /* bf16 (vocab, 1024) */
   const void* pos_table; /* bf16 (max_pos, 1024) */
   b200dec_norm emb_ln, final_ln;
@@ -165,6 +167,12 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
                       const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                       int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
 int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim);
+/* The same operation, arguments and workspace as b200dec_attention (rows <= 128) by a persistent kernel: two CTAs
+ * per SM, one producer lane streaming (row, head) caches through a shared-memory ring with cp.async.bulk and
+ * mbarriers, four consumer warps. Smaller footprint per SM; see csrc/attention_ring.cu. */
+int b200dec_attention_ring(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                           const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
+                           int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
 /* Packed cross keys/values kv (nrows, L * 2 * H * D) fp32, row i = frame frame_of[i] of slot slot_of[i], into the
  * bf16 slot caches (L, slots + 1, H, frames, D). Replaces dec_scatter_kv (kernels/csrc/decoder_ops.cu:163-173,
  * 316-327). */

@@ -314,8 +314,9 @@ def _attention_ref(q, k, v, scale):
 @pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
 @pytest.mark.parametrize("rows", [1, 5, 64])
 @pytest.mark.parametrize("self_", [0, 1])
-@pytest.mark.parametrize("cap", [96, 300])  # one span of keys per row, and up to three (partials merged in order)
-def test_attention(nv, H, D, rows, self_, cap):
+@pytest.mark.parametrize("cap", [96, 300])  # one span of keys per row, and several (partials merged in order)
+@pytest.mark.parametrize("ring", [False, True])  # the one-CTA-per-(row, head) kernel and the persistent ring kernel
+def test_attention(nv, H, D, rows, self_, cap, ring):
     rng = np.random.default_rng(rows * 10 + H + self_ + cap)
     S = max(rows, 4) + 2
     kc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
@@ -338,9 +339,9 @@ def test_attention(nv, H, D, rows, self_, cap):
     scale = D ** -0.5
     a_d, q_d, n_d = cuda(active), cuda(q), cuda(n)  # held until the synchronize
     for _ in range(2):  # twice: the split counters must have been reset
-        nv.check(lib.b200dec_attention(self_, nv.ptr(a_d), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd),
-                                       nv.ptr(n_d), S, H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, nv.ptr(part),
-                                       nv.ptr(count), nv.ptr(status), 0, nv.stream_ptr()))
+        fn = lib.b200dec_attention_ring if ring else lib.b200dec_attention
+        nv.check(fn(self_, nv.ptr(a_d), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), nv.ptr(n_d), S, H, D, cap, scale,
+                    nv.ptr(out), nv.OUT_F32, rows, nv.ptr(part), nv.ptr(count), nv.ptr(status), 0, nv.stream_ptr()))
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and int(count.abs().sum().item()) == 0
     got = out.cpu().numpy()

@@ -232,3 +232,51 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
 }
 
 }  // extern "C"
+
+// ---- the same attention for callers that cannot hand over scratch memory ---------------------------------------------
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: a serving loop whose
+// memory pool was sized and frozen at start-up, a plugin ABI that hands a kernel nothing but its inputs and outputs,
+// a foreign-language runtime (cgo, JNI) whose bookkeeping would never see a cudaMalloc made on its behalf. For them
+// the split workspace (partial outputs of a row's spans and the per-row arrival counters) lives in this file-scope
+// device array instead of in a caller's buffer. Every GPU that loads the library holds its 4.3 MB until the process
+// exits, which is why its capacity is kept modest: rows * heads <= 512, which covers the small batches whose rows the
+// kernel splits into spans to fill the GPU (a large batch gives every CTA a whole row and needs no workspace).
+namespace {
+constexpr int STATIC_MAX_ITEMS = 512;                                  // rows * heads
+constexpr size_t STATIC_PART_FLOATS = (size_t)STATIC_MAX_ITEMS * MAX_SPLITS * (128 + 2);  // head_dim up to 128
+static __device__ __align__(256) float g_static_scratch[STATIC_PART_FLOATS + STATIC_MAX_ITEMS];
+constexpr int MAX_DEVICES = 64;
+}  // namespace
+
+extern "C" int b200dec_attention_static(int self, const int32_t* active, const float* q, int ldq, void* kcache,
+                                        void* vcache, const int32_t* n, int slots, int heads, int head_dim, int cap,
+                                        float scale, void* out, int out_kind, int rows, int32_t* status, int pdl,
+                                        void* stream) {
+  B200_REQUIRE(rows >= 1 && heads >= 1 && (long long)rows * heads <= STATIC_MAX_ITEMS,
+               "attention_static: rows * heads = %lld exceeds the built-in workspace of %d (use b200dec_attention with "
+               "a caller-owned workspace)", (long long)rows * heads, STATIC_MAX_ITEMS);
+  B200_REQUIRE(head_dim == 64 || head_dim == 128, "attention_static: head_dim %d (64 or 128)", head_dim);
+  // The array's name is only a host-side handle; the device address comes from the runtime, once per device, with that
+  // device current. This first call per device is the set-up and should happen before any stream capture.
+  static float* base[MAX_DEVICES] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  B200_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "attention_static: device %d", dev);
+  float* scratch = __atomic_load_n(&base[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    e = cudaGetSymbolAddress((void**)&scratch, g_static_scratch);
+    if (e != cudaSuccess || !scratch)
+      return fail(B200DEC_ECUDA, "attention_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    __atomic_store_n(&base[dev], scratch, __ATOMIC_RELEASE);  // same value from every thread that races here
+  }
+  int32_t* count = reinterpret_cast<int32_t*>(scratch + STATIC_PART_FLOATS);
+  // The array keeps whatever the previous call left. The partials are fully rewritten before they are read; the
+  // arrival counters must start at zero (a call that was cut short could have left them otherwise), so clear them on
+  // the caller's stream first. A memset is not an allocation.
+  e = cudaMemsetAsync(count, 0, (size_t)rows * heads * sizeof(int32_t), (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention_static: clearing the counters: %s", cudaGetErrorString(e));
+  return b200dec_attention(self, active, q, ldq, kcache, vcache, n, slots, heads, head_dim, cap, scale, out, out_kind,
+                           rows, scratch, count, status, pdl, stream);
+}

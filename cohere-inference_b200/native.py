@@ -81,6 +81,8 @@ PROTOTYPES = {
     "b200dec_attention_scratch_floats": (i64, [C.c_int, C.c_int, C.c_int]),
     "b200dec_attention_ring": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
                                          vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
+    "b200dec_attention_static": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           f32, vp, C.c_int, C.c_int, vp, C.c_int, vp]),
     "b200dec_scatter_kv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_step": (C.c_int, [C.POINTER(Plan), C.c_int, vp]),
     "b200dec_step_rows": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_int, vp]),

@@ -173,6 +173,16 @@ int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim);
 int b200dec_attention_ring(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
                            const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                            int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
+/* b200dec_attention for a caller that cannot provide the split workspace because it must not allocate device memory
+ * where it calls this (a frozen memory pool, a plugin ABI that passes only inputs and outputs, a foreign runtime that
+ * would not see the allocation). No counterpart in the reference. The workspace is an array inside the library
+ * instead (4.3 MB per GPU, held until the process exits), good for rows * heads <= 512; larger calls are refused
+ * with an error. The first call on each device looks the array's address up and should come before any stream
+ * capture. All calls on a device share the array: two calls whose kernels overlap on the GPU (different streams)
+ * race on it. Allocates nothing, frees nothing. */
+int b200dec_attention_static(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                             const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
+                             int out_kind, int rows, int32_t* status, int pdl, void* stream);
 /* Packed cross keys/values kv (nrows, L * 2 * H * D) fp32, row i = frame frame_of[i] of slot slot_of[i], into the
  * bf16 slot caches (L, slots + 1, H, frames, D). Replaces dec_scatter_kv (kernels/csrc/decoder_ops.cu:163-173,
  * 316-327). */

@@ -337,7 +337,7 @@ def main() -> None:
     ap.add_argument("--cpu-steps", type=int, default=32, help="decoding steps of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
-    ap.add_argument("--pdl", type=int, default=1, help="which launches are programmatic: 1 projection after projection, "
+    ap.add_argument("--pdl", type=int, default=0, help="which launches are programmatic: 1 projection after projection, "
                     "2 attention, 4 projection after attention (sum them)")
     ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")
     ap.add_argument("--chains", type=int, default=1, help="concurrent kernel chains a step's rows are split into")

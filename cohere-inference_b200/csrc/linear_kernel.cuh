@@ -26,14 +26,14 @@ struct LinArgs {
   float ln_eps;
   int lda, ldo, rows, N, out_kind, act, head;
 #ifdef B200DEC_STAMPS
-  long long* stamps;  // per CTA 8 clock64() values at the phase boundaries (latency studies only)
+  long long* stamps;  // per CTA 12 clock64() values at the phase boundaries (latency studies only)
 #endif
 };
 
 #ifdef B200DEC_STAMPS
 #define B200_STAMP(i)                                                                                        \
   do {                                                                                                       \
-    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (i)] = clock64(); \
+    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (i)] = clock64(); \
   } while (0)
 #else
 #define B200_STAMP(i)
@@ -107,15 +107,13 @@ struct LinSmem {
   static constexpr int BN = NW * 16;
   static constexpr int A_BYTES = MB * RS * (SPLIT ? 2 : 1);
   static constexpr int RECV_BYTES = MB * BN * 4;       // [KSPLIT][MB][BN / KSPLIT] partial sums pushed by the cluster
-  static constexpr int RED_BYTES = MB * (BN + 4) * 4;  // this CTA's partial tile, transposed for the push
   // fp32 source rows are first copied asynchronously into shared memory (slices up to 256 wide; wider ones are
-  // converted straight from registers); the copy shares its bytes with the partial tile, which is written later
+  // converted straight from registers)
   static constexpr bool RAW_STAGE = (LN || SPLIT) && KSLICE <= 256;
   static constexpr int RAW_BYTES = RAW_STAGE ? MB * KSLICE * 4 : 0;
-  static constexpr int SCRATCH_BYTES = RAW_BYTES > RED_BYTES ? RAW_BYTES : RED_BYTES;
   static constexpr int STATS_BYTES = LN ? KSPLIT * MB * 8 : 0;  // [KSPLIT][MB] (sum, sum of squares) of each slice
-  static constexpr int OFF_A = 0, OFF_RECV = OFF_A + A_BYTES, OFF_RED = OFF_RECV + RECV_BYTES,
-                       OFF_STATS = OFF_RED + SCRATCH_BYTES, TOTAL = OFF_STATS + STATS_BYTES;
+  static constexpr int OFF_A = 0, OFF_RECV = OFF_A + A_BYTES, OFF_RAW = OFF_RECV + RECV_BYTES,
+                       OFF_STATS = OFF_RAW + RAW_BYTES, TOTAL = OFF_STATS + STATS_BYTES;
 };
 
 // WT: weight storage. SPLIT: the activation operand is two 16-bit halves (hi + lo) of an fp32 value, else one fp16.
@@ -129,7 +127,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   using T = WTraits<WT>;
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
-  constexpr int RS = S::RS, LDR = BN + 4, CPR = BN / KSPLIT, GPR = CPR / 4, NB = MB / 8, NBG = NB < 8 ? NB : 8;
+  constexpr int RS = S::RS, CPR = BN / KSPLIT, GPR = CPR / 4, NB = MB / 8, NBG = NB < 8 ? NB : 8;
   constexpr bool BF = WT == B200DEC_W_BF16;
   constexpr bool F32SRC = LN || SPLIT;  // the source rows are fp32
   static_assert(CPR % 8 == 0, "each CTA finishes a multiple of 8 channels");
@@ -138,7 +136,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   unsigned char* a_hi = smem + S::OFF_A;
   unsigned char* a_lo = a_hi + MB * RS;
   float* recv = reinterpret_cast<float*>(smem + S::OFF_RECV);
-  float* red = reinterpret_cast<float*>(smem + S::OFF_RED);
+  float* raw = reinterpret_cast<float*>(smem + S::OFF_RAW);  // the async copy of the fp32 rows (RAW_STAGE)
   float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -205,7 +203,6 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
     constexpr int RPG = (MB + NT / 8 - 1) / (NT / 8);  // rows per 8-lane group
     const float* A = reinterpret_cast<const float*>(p.a);
     const int l8 = tid & 7;
-    float* raw = red;  // the async copy of the fp32 rows (RAW_STAGE)
     float shift[RPG];
     if constexpr (S::RAW_STAGE) {
       constexpr int CH = KSLICE / 4;
@@ -225,49 +222,57 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
         }
       }
     }
+    float4 gam[LN ? J : 1];  // this lane's gammas, the same for every row
+    if constexpr (LN) {
+#pragma unroll
+      for (int j = 0; j < J; ++j) gam[j] = __ldg(reinterpret_cast<const float4*>(p.ln_w + k0 + (j * 8 + l8) * 4));
+    }
+    B200_STAMP(8);
     if constexpr (S::RAW_STAGE) {
       cp_async_wait_all();
       __syncthreads();
     }
+    B200_STAMP(9);
+    float s1[RPG], s2[RPG];
 #pragma unroll
-    for (int it = 0; it < RPG; ++it) {
+    for (int it = 0; it < RPG; ++it) {  // no early exit: the iterations are independent and interleave
       const int r = (tid >> 3) + it * (NT / 8);
-      if (r >= rows8) break;  // whole warps leave together (rows8 % 8 == 0, 4 groups per warp)
       const bool live = r < p.rows;
-      float4 v[J];
-      const float c = LN ? shift[it] : 0.f;
-      if (live) {
+      s1[it] = 0.f, s2[it] = 0.f;
+      if (r < rows8) {  // whole warps agree (rows8 % 8 == 0, 4 row groups per warp)
+        const float c = LN ? shift[it] : 0.f;
 #pragma unroll
         for (int j = 0; j < J; ++j) {
-          if constexpr (S::RAW_STAGE) v[j] = *reinterpret_cast<const float4*>(raw + r * KSLICE + (j * 8 + l8) * 4);
-          else v[j] = ld_cg_f4(A + (size_t)r * p.lda + k0 + (j * 8 + l8) * 4);
-        }
-      }
-      float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-      for (int j = 0; j < J; ++j) {
-        uint2 hi = make_uint2(0, 0), lo = make_uint2(0, 0);
-        if (live) {
-          float4 x = v[j];
-          if constexpr (LN) {
-            const float4 gm = *reinterpret_cast<const float4*>(p.ln_w + k0 + (j * 8 + l8) * 4);
-            x.x -= c, x.y -= c, x.z -= c, x.w -= c;
-            s1 += (x.x + x.y) + (x.z + x.w);
-            s2 += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
-            x.x *= gm.x, x.y *= gm.y, x.z *= gm.z, x.w *= gm.w;
+          uint2 hi = make_uint2(0, 0), lo = make_uint2(0, 0);
+          if (live) {
+            float4 x;
+            if constexpr (S::RAW_STAGE) x = *reinterpret_cast<const float4*>(raw + r * KSLICE + (j * 8 + l8) * 4);
+            else x = ld_cg_f4(A + (size_t)r * p.lda + k0 + (j * 8 + l8) * 4);
+            if constexpr (LN) {
+              x.x -= c, x.y -= c, x.z -= c, x.w -= c;
+              s1[it] += (x.x + x.y) + (x.z + x.w);
+              s2[it] += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
+              x.x *= gam[j].x, x.y *= gam[j].y, x.z *= gam[j].z, x.w *= gam[j].w;
+            }
+            to_operand<BF, SPLIT>(x, hi, lo);
           }
-          to_operand<BF, SPLIT>(x, hi, lo);
+          *reinterpret_cast<uint2*>(a_hi + r * RS + (j * 8 + l8) * 8) = hi;
+          if constexpr (SPLIT) *reinterpret_cast<uint2*>(a_lo + r * RS + (j * 8 + l8) * 8) = lo;
         }
-        *reinterpret_cast<uint2*>(a_hi + r * RS + (j * 8 + l8) * 8) = hi;
-        if constexpr (SPLIT) *reinterpret_cast<uint2*>(a_lo + r * RS + (j * 8 + l8) * 8) = lo;
       }
-      if constexpr (LN) {
+    }
+    if constexpr (LN) {
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-          s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-          s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+      for (int o = 1; o < 8; o <<= 1)
+#pragma unroll
+        for (int it = 0; it < RPG; ++it) {
+          s1[it] += __shfl_xor_sync(0xffffffffu, s1[it], o);
+          s2[it] += __shfl_xor_sync(0xffffffffu, s2[it], o);
         }
-        if (live && l8 < KSPLIT) cluster.map_shared_rank(stats, l8)[rank * MB + r] = make_float2(s1, s2);
+#pragma unroll
+      for (int it = 0; it < RPG; ++it) {
+        const int r = (tid >> 3) + it * (NT / 8);
+        if (r < p.rows && l8 < KSPLIT) cluster.map_shared_rank(stats, l8)[rank * MB + r] = make_float2(s1[it], s2[it]);
       }
     }
   }
@@ -352,22 +357,20 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   B200_STAMP(4);
 
   // ---- partial tile -> the CTAs that own its channels (distributed shared memory), one cluster barrier ------------
+  // Straight from the accumulators: a warp's store instruction covers 8 consecutive channels (32 bytes) of 4 rows,
+  // all owned by one CTA of the cluster.
+  {
+    const int ch0 = warp * 16 + g, ch1 = ch0 + 8;
+    float* dst0 = cluster.map_shared_rank(recv, ch0 / CPR) + rank * MB * CPR + ch0 % CPR;
+    float* dst1 = cluster.map_shared_rank(recv, ch1 / CPR) + rank * MB * CPR + ch1 % CPR;
 #pragma unroll
-  for (int nb = 0; nb < NB; ++nb) {
-    if (nb < ntiles) {
-      const int r = nb * 8 + 2 * t, c = warp * 16 + g;
-      red[r * LDR + c] = acc[nb][0];
-      red[(r + 1) * LDR + c] = acc[nb][1];
-      red[r * LDR + c + 8] = acc[nb][2];
-      red[(r + 1) * LDR + c + 8] = acc[nb][3];
+    for (int nb = 0; nb < NB; ++nb) {
+      if (nb < ntiles) {
+        const int r = nb * 8 + 2 * t;
+        if (r < p.rows) dst0[r * CPR] = acc[nb][0], dst1[r * CPR] = acc[nb][2];
+        if (r + 1 < p.rows) dst0[(r + 1) * CPR] = acc[nb][1], dst1[(r + 1) * CPR] = acc[nb][3];
+      }
     }
-  }
-  __syncthreads();
-  for (int it = tid; it < p.rows * (BN / 4); it += NT) {
-    const int r = it / (BN / 4), ch = (it % (BN / 4)) * 4;
-    const float4 v = *reinterpret_cast<const float4*>(red + r * LDR + ch);
-    float* dst = cluster.map_shared_rank(recv, ch / CPR) + (rank * MB + r) * CPR + (ch % CPR);
-    *reinterpret_cast<float4*>(dst) = v;
   }
   // this thread's share of the finished tile: row r, channels n .. n+3; the residual it adds to is fetched now so
   // that its latency overlaps the barrier

@@ -56,7 +56,7 @@ class StreamDecoder:
 
     def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
-                 eos: int | None = None, record: bool = False, pdl: bool | int = 1, graphs: bool = True,
+                 eos: int | None = None, record: bool = False, pdl: bool | int = 0, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32

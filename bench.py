@@ -244,7 +244,9 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention") + " kernel <64, cross> (64 rows x 16 heads)",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
-                         "traffic": None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu capture summarised in
+                         # profiles/attention_kernel_config3.md (55.72 MB + 0.36 MB for 55.44 MB of K/V), scaled by bytes
+                         "traffic": int(kv_bytes * ATTN_TRAFFIC_PER_BYTE), "traffic_source": "ncu, profiles/attention_kernel_config3.md",
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
                                   "frac_of_8TBs": round(step_gbs / 8000, 4)}},
@@ -256,6 +258,9 @@ def run_ours(args) -> None:
         print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
+
+
+ATTN_TRAFFIC_PER_BYTE = (55.72 + 0.36) / 55.44   # measured DRAM traffic / algorithmic K/V bytes, cross-attention launch
 
 
 def run_profile(args) -> None:

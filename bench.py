@@ -105,7 +105,8 @@ def run_ours(args) -> None:
     torch.cuda.set_device(dev)
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
-                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring)
+                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
+                        head_split=not args.no_head_split)
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -184,20 +185,27 @@ def run_ours(args) -> None:
     attn_fn = lib.b200dec_attention_ring if args.attn_ring else lib.b200dec_attention
     kv_bytes = sum(lens) * 2 * 1024 * 2
     reps = 10
+
+    def attn_launches():
+        for i in range(reps * L):
+            ly = i % L
+            nv.check(attn_fn(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
+                             nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
+                             dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
+                             nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status),
+                             1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
+
+    # launched from a CUDA graph, as in the step (from Python the loop would be bound by the host's launch rate)
+    attn_graph = torch.cuda.CUDAGraph()
+    ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(dec.stream):
-        ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for timed in (False, True):
-            if timed:
-                ks.record(dec.stream)
-            for i in range(reps * L):
-                ly = i % L
-                nv.check(attn_fn(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
-                                               nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
-                                               dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
-                                               nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status), 0,
-                                               nv.stream_ptr(dec.stream)))
-            if timed:
-                ke.record(dec.stream)
+        attn_launches()
+        with torch.cuda.graph(attn_graph, stream=dec.stream):
+            attn_launches()
+        attn_graph.replay()
+        ks.record(dec.stream)
+        attn_graph.replay()
+        ke.record(dec.stream)
     dec.stream.synchronize()
     attn_us = ks.elapsed_time(ke) * 1e3 / (reps * L)
     attn_gbs = kv_bytes / (attn_us / 1e6) / 1e9
@@ -344,6 +352,7 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
     ap.add_argument("--pdl", type=int, default=0, help="which launches are programmatic: 1 projection after projection, "
                     "2 attention, 4 projection after attention (sum them)")
+    ap.add_argument("--no-head-split", action="store_true", help="vocabulary projection on a single fp16 operand")
     ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")
     ap.add_argument("--chains", type=int, default=1, help="concurrent kernel chains a step's rows are split into")
     ap.add_argument("--profile", type=int, default=0, help="profiler mode: this many directly launched steps")

@@ -10,9 +10,12 @@
 // projection) are rounded to bf16 into the cache at position n[slot] and attended from registers.
 //
 // Cache layout (slots + 1, H, cap, D): all keys of one (slot, head) are one contiguous run, the unit a CTA streams.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 using namespace b200dec_detail;
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -37,32 +40,30 @@ struct AttnArgs {
   int* status;
   int ldq, H, cap, slots, out_kind, rows, splits;
   float scale_log2;  // head_dim^-0.5 * log2(e)
+#ifdef B200DEC_STAMPS
+  long long* stamps;  // per CTA 12 timer values (latency studies only)
+#endif
 };
 
+#ifdef B200DEC_STAMPS
+#define ATTN_STAMP(i)                                                                                               \
+  do {                                                                                                              \
+    if (p.stamps && threadIdx.x == 0)                                                                               \
+      p.stamps[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 12 + (i)] = stamp_clock();         \
+  } while (0)
+#else
+#define ATTN_STAMP(i)
+#endif
+
+// One CTA's pass over keys [start, end) of (slot s, head h) for the query of row r, plus (with_new) the row's new key:
+// on return threads tid < D hold the pass's running maximum M, sum L and un-normalised output O for dim tid.
 template <int D, bool SELF>
-__global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
+DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start, int end, bool with_new,
+                       float* s_m, float* s_l, float (*s_acc)[D + 4], float& M, float& L, float& O) {
   constexpr int LPK = D / 8;           // lanes per key
   constexpr int NG = NTHREADS / LPK;   // key groups per CTA
   constexpr int U = 4;                 // keys in flight per group
-  __shared__ float s_m[NG], s_l[NG];
-  __shared__ float s_acc[NG][D + 4];
-  __shared__ int s_last;
-
-  const int h = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, nsp = p.splits;
   const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
-  pdl_trigger();
-  pdl_wait();
-
-  int s = p.active[r];
-  if (s < 0 || s > p.slots) {
-    if (tid == 0) atomicOr(p.status, B200DEC_ST_SLOT_RANGE);
-    s = p.slots;
-  }
-  int n = p.n[s];
-  if (SELF ? (n < 0 || n >= p.cap) : (n < 1 || n > p.cap)) {
-    if (tid == 0) atomicOr(p.status, SELF ? B200DEC_ST_POS_RANGE : B200DEC_ST_FRAMES_RANGE);
-    n = SELF ? max(0, min(n, p.cap - 1)) : max(1, min(n, p.cap));
-  }
 
   // the query, pre-scaled so that scores are in log2 units
   float q[8];
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
     m = mn;
   };
 
-  if (SELF && sp == 0 && tid < 32) {
+  if (SELF && with_new && tid < 32) {
     // The new key and value: rounded to bf16 into the cache at position n, and attended as stored. `attend` shuffles
     // across the warp, so all of warp 0 goes through it with only group 0 (lanes 0 .. LPK-1) valid.
     const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 8;
@@ -109,8 +110,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
     attend(kk, vv, grp == 0);
   }
 
-  // cached keys [start, end) of this split, group g taking start + g, + NG, ...
-  const int chunk = (n + nsp - 1) / nsp, start = sp * chunk, end = min(n, start + chunk);
+  // cached keys [start, end), group g taking start + g, + NG, ...
   const __nv_bfloat16* kb = p.k + base;
   const __nv_bfloat16* vb = p.v + base;
   // whole-warp trip count: every lane runs the same number of iterations (shuffles), invalid keys are masked
@@ -130,13 +130,14 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
       if (j0 + u * NG < end) attend(kk[u], vv[u], j + u * NG < end);  // warp-uniform condition
     }
   }
-
+  ATTN_STAMP(3);
   // merge the groups
+  __syncthreads();  // the arrays may still be read by a previous pass
   if (gl == 0) s_m[grp] = m, s_l[grp] = l;
 #pragma unroll
   for (int i = 0; i < 8; ++i) s_acc[grp][gl * 8 + i] = acc[i];
   __syncthreads();
-  float M = -1e30f, L = 0.f, O = 0.f;
+  M = -1e30f, L = 0.f, O = 0.f;
   if (tid < D) {
 #pragma unroll
     for (int gi = 0; gi < NG; ++gi) M = fmaxf(M, s_m[gi]);
@@ -147,15 +148,54 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
       O += w * s_acc[gi][tid];
     }
   }
-  auto store = [&](float val) {
-    const size_t o = (size_t)r * p.H * D + h * D + tid;
-    if (p.out_kind == B200DEC_OUT_F16)
-      reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(clamp_h(val));
-    else
-      reinterpret_cast<float*>(p.out)[o] = val;
-  };
+}
+
+template <int D>
+DEVI void store_out(const AttnArgs& p, int r, int h, float val) {
+  const size_t o = (size_t)r * p.H * D + h * D + threadIdx.x;
+  if (p.out_kind == B200DEC_OUT_F16)
+    reinterpret_cast<__half*>(p.out)[o] = __float2half_rn(clamp_h(val));
+  else
+    reinterpret_cast<float*>(p.out)[o] = val;
+}
+
+// slot and length of row r, clamped into range (a bad value is reported through the status word)
+template <bool SELF>
+DEVI void row_state(const AttnArgs& p, int r, bool report, int& s, int& n) {
+  s = p.active[r];
+  if (s < 0 || s > p.slots) {
+    if (report) atomicOr(p.status, B200DEC_ST_SLOT_RANGE);
+    s = p.slots;
+  }
+  n = p.n[s];
+  if (SELF ? (n < 0 || n >= p.cap) : (n < 1 || n > p.cap)) {
+    if (report) atomicOr(p.status, SELF ? B200DEC_ST_POS_RANGE : B200DEC_ST_FRAMES_RANGE);
+    n = SELF ? max(0, min(n, p.cap - 1)) : max(1, min(n, p.cap));
+  }
+}
+
+template <int D, bool SELF>
+__global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (D / 8);
+  __shared__ float s_m[NG], s_l[NG];
+  __shared__ float s_acc[NG][D + 4];
+  __shared__ int s_last;
+
+  const int h = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, nsp = p.splits;
+  const int tid = threadIdx.x;
+  ATTN_STAMP(0);
+  pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
+  pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
+
+  int s, n;
+  row_state<SELF>(p, r, tid == 0, s, n);
+  ATTN_STAMP(2);
+  const int chunk = (n + nsp - 1) / nsp, start = sp * chunk, end = min(n, start + chunk);
+  float M, L, O;
+  attend_range<D, SELF>(p, r, s, h, n, start, end, sp == 0, s_m, s_l, s_acc, M, L, O);
   if (nsp == 1) {
-    if (tid < D) store(O / L);
+    if (tid < D) store_out<D>(p, r, h, O / L);
+    ATTN_STAMP(7);
     return;
   }
   // split: partial to the workspace, the last CTA of this (row, head) merges
@@ -179,9 +219,87 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
       LL += w * __ldcg(pb + i * (D + 2) + D + 1);
       OO += w * __ldcg(pb + i * (D + 2) + tid);
     }
-    store(OO / LL);
+    store_out<D>(p, r, h, OO / LL);
   }
   if (tid == 0) p.count[item] = 0;
+}
+
+// ---- large batches: rows paired long with short --------------------------------------------------------------------
+//
+// With a thousand (row, head) items every SM holds several CTAs and the stream runs at memory speed while all of them
+// are busy, but a row's CTA can only keep so many bytes in flight, so the longest rows decide when the kernel ends.
+// Here the rows are ranked by length inside the kernel and the i-th longest is paired with the i-th shortest in a
+// cluster of two CTAs: CTA 0 takes the head of the long row, CTA 1 the short row and then the tail of the long one, cut
+// so that both read the same number of keys. CTA 1 hands its partial (max, sum, output) of the long row to CTA 0
+// through distributed shared memory; one cluster barrier, no global workspace. Rows of (nearly) equal length skip the
+// exchange.
+constexpr int PAIR_MAX_ROWS = 256;
+
+template <int D, bool SELF>
+__global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (D / 8);
+  __shared__ float s_m[NG], s_l[NG];
+  __shared__ float s_acc[NG][D + 4];
+  __shared__ float s_peer[D + 2];  // CTA 0: the partial its peer computed for the long row
+  __shared__ int t_slot[PAIR_MAX_ROWS], t_n[PAIR_MAX_ROWS];
+  __shared__ int s_pair[2];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int role = blockIdx.x, h = blockIdx.y, i = blockIdx.z, rows = p.rows;
+  const int tid = threadIdx.x;
+  ATTN_STAMP(0);
+  pdl_wait();
+  pdl_trigger();
+
+  for (int r = tid; r < rows; r += NTHREADS) {
+    int s, n;
+    row_state<SELF>(p, r, blockIdx.x + blockIdx.y + blockIdx.z == 0, s, n);
+    t_slot[r] = s, t_n[r] = n;
+  }
+  __syncthreads();
+  for (int r = tid; r < rows; r += NTHREADS) {  // rank by decreasing length, ties by row
+    const int n = t_n[r];
+    int rank = 0;
+    for (int j = 0; j < rows; ++j) rank += (t_n[j] > n) || (t_n[j] == n && j < r);
+    if (rank == i) s_pair[0] = r;
+    if (rank == rows - 1 - i) s_pair[1] = r;
+  }
+  __syncthreads();
+  ATTN_STAMP(2);
+  const int r_long = s_pair[0], r_short = s_pair[1];
+  const int n_long = t_n[r_long], n_short = t_n[r_short];
+  const bool solo = r_long == r_short;  // the middle row of an odd count
+  // keys [cut, n_long) of the long row go to CTA 1 (a multiple of 16 keeps both CTAs' loads aligned to whole groups)
+  int cut = n_long;
+  if (!solo && n_long - n_short >= 32) cut = min(n_long, ((n_long + n_short) / 2 + 15) & ~15);
+  const bool helped = cut < n_long;
+
+  float M, L, O;
+  if (role == 0) {
+    attend_range<D, SELF>(p, r_long, t_slot[r_long], h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
+    if (helped) {
+      cluster.sync();  // the peer's partial has landed
+      if (tid < D) {
+        const float pm = s_peer[D], pl = s_peer[D + 1], po = s_peer[tid];
+        const float mm = fmaxf(M, pm), w0 = ex2(M - mm), w1 = ex2(pm - mm);
+        L = w0 * L + w1 * pl, O = w0 * O + w1 * po;
+      }
+    }
+    if (tid < D) store_out<D>(p, r_long, h, O / L);
+  } else {
+    if (!solo) {
+      attend_range<D, SELF>(p, r_short, t_slot[r_short], h, n_short, 0, n_short, true, s_m, s_l, s_acc, M, L, O);
+      if (tid < D) store_out<D>(p, r_short, h, O / L);
+    }
+    if (helped) {
+      attend_range<D, SELF>(p, r_long, t_slot[r_long], h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
+      float* peer = cluster.map_shared_rank(s_peer, 0);
+      if (tid < D) peer[tid] = O;
+      if (tid == 0) peer[D] = M, peer[D + 1] = L;
+      cluster.sync();
+    }
+  }
+  ATTN_STAMP(7);
 }
 
 int pick_splits(int rows, int heads, int cap) {
@@ -218,9 +336,27 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
   p.ldq = ldq, p.H = heads, p.cap = cap, p.slots = slots, p.out_kind = out_kind, p.rows = rows;
   p.splits = (part && count) ? pick_splits(rows, heads, cap) : 1;
   p.scale_log2 = scale * 1.4426950408889634f;
-  const dim3 grid(heads, rows, p.splits);
   cudaStream_t s = (cudaStream_t)stream;
   cudaError_t e;
+  if (p.splits == 1 && rows * heads >= 512 && rows <= PAIR_MAX_ROWS) {
+    // a large batch: rows paired long with short, two CTAs per pair and head
+    const dim3 grid(2, heads, (rows + 1) / 2);
+#ifdef B200DEC_TIMELINE
+    p.stamps = timeline_next(2 * heads * ((rows + 1) / 2), self ? 3000000 : 4000000);
+#endif
+    if (head_dim == 64)
+      e = self ? launch_kernel(attention_pair_kernel<64, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+               : launch_kernel(attention_pair_kernel<64, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+    else
+      e = self ? launch_kernel(attention_pair_kernel<128, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+               : launch_kernel(attention_pair_kernel<128, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+    if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention launch: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  const dim3 grid(heads, rows, p.splits);
+#ifdef B200DEC_TIMELINE
+  p.stamps = timeline_next(heads * rows * p.splits, self ? 3000000 : 4000000);
+#endif
   if (head_dim == 64)
     e = self ? launch_kernel(attention_kernel<64, true>, grid, dim3(NTHREADS), 0, s, 0, pdl, p)
              : launch_kernel(attention_kernel<64, false>, grid, dim3(NTHREADS), 0, s, 0, pdl, p);

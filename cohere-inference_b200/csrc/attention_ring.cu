@@ -156,8 +156,8 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
     for (int i = 0; i < NSTAGE; ++i) mbar_init(&full[i], 1), mbar_init(&empty[i], NCW);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
+  pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
   if (tid < p.rows) {  // the rows' slots and lengths, validated once
     int s = p.active[tid];
     if (s < 0 || s > p.slots) {

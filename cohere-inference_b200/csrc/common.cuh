@@ -60,6 +60,23 @@ inline cudaError_t launch_kernel(Kern kern, dim3 grid, dim3 block, size_t smem, 
   return cudaLaunchKernelEx(&cfg, kern, args);
 }
 
+// ---- timeline study builds (-DB200DEC_TIMELINE): every launch gets the next slice of a device buffer, 12 slots per
+// CTA, and its CTAs store the global nanosecond timer there at their phase boundaries -------------------------------
+#ifdef B200DEC_TIMELINE
+#define B200DEC_STAMPS 1
+namespace b200dec_detail {
+long long* timeline_next(int ctas, int kind);  // host side, rowops.cu; nullptr when no buffer is set
+}
+using b200dec_detail::timeline_next;
+DEVI long long stamp_clock() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#else
+DEVI long long stamp_clock() { return clock64(); }
+#endif
+
 // ---- loads --------------------------------------------------------------------------------------------------------
 // Read-once streams (weights, KV cache): no L1 allocation.
 DEVI uint4 ld_stream16(const void* p) {

@@ -33,7 +33,7 @@ struct LinArgs {
 #ifdef B200DEC_STAMPS
 #define B200_STAMP(i)                                                                                        \
   do {                                                                                                       \
-    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (i)] = clock64(); \
+    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (i)] = stamp_clock(); \
   } while (0)
 #else
 #define B200_STAMP(i)
@@ -470,7 +470,13 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear: smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid(KSPLIT, a.N / (NW * 16));
+#ifdef B200DEC_TIMELINE
+  LinArgs b = a;
+  b.stamps = timeline_next(grid.x * grid.y, (LN ? 2000000 : 1000000) + a.N / 16 * 1000 + KSLICE * KSPLIT / 16);
+  e = launch_kernel(kern, grid, dim3(NW * 32), S::TOTAL, stream, KSPLIT, pdl, b);
+#else
   e = launch_kernel(kern, grid, dim3(NW * 32), S::TOTAL, stream, KSPLIT, pdl, a);
+#endif
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear launch: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -25,7 +25,31 @@ int check_launch(const char* what) {
   return 0;
 }
 
+#ifdef B200DEC_TIMELINE
+static long long* g_tl_base = nullptr;
+static long long g_tl_cap = 0, g_tl_used = 0;
+static int g_tl_n = 0, g_tl_kind[4096], g_tl_ctas[4096];
+static long long g_tl_off[4096];
+long long* timeline_next(int ctas, int kind) {
+  if (!g_tl_base || g_tl_n >= 4096 || g_tl_used + (long long)ctas * 12 > g_tl_cap) return nullptr;
+  long long* at = g_tl_base + g_tl_used;
+  g_tl_kind[g_tl_n] = kind, g_tl_ctas[g_tl_n] = ctas, g_tl_off[g_tl_n] = g_tl_used, ++g_tl_n;
+  g_tl_used += (long long)ctas * 12;
+  return at;
+}
+#endif
 }  // namespace b200dec_detail
+
+#ifdef B200DEC_TIMELINE
+extern "C" void b200dec_timeline_set(long long* base, long long capacity) {
+  g_tl_base = base, g_tl_cap = capacity, g_tl_used = 0, g_tl_n = 0;
+}
+extern "C" int b200dec_timeline_get(int* kinds, int* ctas, long long* offsets, int max) {
+  const int n = g_tl_n < max ? g_tl_n : max;
+  for (int i = 0; i < n; ++i) kinds[i] = g_tl_kind[i], ctas[i] = g_tl_ctas[i], offsets[i] = g_tl_off[i];
+  return n;
+}
+#endif
 
 namespace {
 
@@ -83,8 +107,8 @@ struct EmbedArgs {
 
 __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
+  pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
   if (row >= p.rows) return;
   int s = p.active[row];
   if (s < 0 || s > p.slots) {
@@ -127,8 +151,8 @@ struct LnArgs {
 
 __global__ void __launch_bounds__(128) layer_norm_kernel(const LnArgs p) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
+  pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
   if (row >= p.rows) return;
   float v[32], o[32];
 #pragma unroll
@@ -158,8 +182,8 @@ struct PickArgs {
 // one warp per row: first index of the maximum over the row's partials, then dec_pick's bookkeeping
 __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  pdl_trigger();
-  pdl_wait();
+  pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
+  pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
   if (row >= p.rows) return;
   const int s = p.active[row];
   if (s < 0 || s >= p.dummy) return;  // the dummy slot (and anything outside the table) never advances

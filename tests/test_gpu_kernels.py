@@ -312,7 +312,7 @@ def _attention_ref(q, k, v, scale):
 
 
 @pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
-@pytest.mark.parametrize("rows", [1, 5, 64])
+@pytest.mark.parametrize("rows", [1, 5, 41, 64])  # 41 and 64 rows x 16 heads: the long-with-short paired kernel (odd, even)
 @pytest.mark.parametrize("self_", [0, 1])
 @pytest.mark.parametrize("cap", [96, 300])  # one span of keys per row, and several (partials merged in order)
 @pytest.mark.parametrize("ring", [False, True])  # the one-CTA-per-(row, head) kernel and the persistent ring kernel
@@ -328,6 +328,8 @@ def test_attention(nv, H, D, rows, self_, cap, ring):
         n[active[1]] = cap - 1 if self_ else cap  # longest case
     if rows >= 5 and cap > 130:
         n[active[2]], n[active[3]], n[active[4]] = 128, 129, 256  # span boundaries
+    if rows == 41:
+        n[active[5:20]] = 77  # many equal lengths: pairs that skip the exchange, ties in the ranking
     ld = 3 * H * D if self_ else H * D
     q = rng.standard_normal((rows, ld)).astype(np.float32)
     kd, vd = cuda(kc).to(torch.bfloat16), cuda(vc).to(torch.bfloat16)

@@ -34,6 +34,7 @@ struct AttnArgs {
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   const int* n;
+  const int* sched;  // paired kernel: (rows, 4) = {row, slot, length, 0} by decreasing length, or null
   void* out;
   float* part;
   int* count;
@@ -235,13 +236,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
 // exchange.
 constexpr int PAIR_MAX_ROWS = 256;
 
-template <int D, bool SELF>
+template <int D, bool SELF, bool TABLE>
 __global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs p) {
   constexpr int NG = NTHREADS / (D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ float s_peer[D + 2];  // CTA 0: the partial its peer computed for the long row
-  __shared__ int t_slot[PAIR_MAX_ROWS], t_n[PAIR_MAX_ROWS];
+  __shared__ int t_slot[TABLE ? 1 : PAIR_MAX_ROWS], t_n[TABLE ? 1 : PAIR_MAX_ROWS];
   __shared__ int s_pair[2];
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -251,23 +252,31 @@ __global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs
   pdl_wait();
   pdl_trigger();
 
-  for (int r = tid; r < rows; r += NTHREADS) {
-    int s, n;
-    row_state<SELF>(p, r, blockIdx.x + blockIdx.y + blockIdx.z == 0, s, n);
-    t_slot[r] = s, t_n[r] = n;
+  int r_long, r_short, s_long, s_short, n_long, n_short;
+  if constexpr (TABLE) {
+    // the step's schedule (built beside the embedding): two entries, no dependent loads
+    const int4 a = __ldcg(reinterpret_cast<const int4*>(p.sched) + i);
+    const int4 b = __ldcg(reinterpret_cast<const int4*>(p.sched) + (rows - 1 - i));
+    r_long = a.x, s_long = a.y, n_long = a.z, r_short = b.x, s_short = b.y, n_short = b.z;
+  } else {
+    for (int r = tid; r < rows; r += NTHREADS) {
+      int s, n;
+      row_state<SELF>(p, r, blockIdx.x + blockIdx.y + blockIdx.z == 0, s, n);
+      t_slot[r] = s, t_n[r] = n;
+    }
+    __syncthreads();
+    for (int r = tid; r < rows; r += NTHREADS) {  // rank by decreasing length, ties by row
+      const int n = t_n[r];
+      int rank = 0;
+      for (int j = 0; j < rows; ++j) rank += (t_n[j] > n) || (t_n[j] == n && j < r);
+      if (rank == i) s_pair[0] = r;
+      if (rank == rows - 1 - i) s_pair[1] = r;
+    }
+    __syncthreads();
+    r_long = s_pair[0], r_short = s_pair[1];
+    s_long = t_slot[r_long], s_short = t_slot[r_short], n_long = t_n[r_long], n_short = t_n[r_short];
   }
-  __syncthreads();
-  for (int r = tid; r < rows; r += NTHREADS) {  // rank by decreasing length, ties by row
-    const int n = t_n[r];
-    int rank = 0;
-    for (int j = 0; j < rows; ++j) rank += (t_n[j] > n) || (t_n[j] == n && j < r);
-    if (rank == i) s_pair[0] = r;
-    if (rank == rows - 1 - i) s_pair[1] = r;
-  }
-  __syncthreads();
   ATTN_STAMP(2);
-  const int r_long = s_pair[0], r_short = s_pair[1];
-  const int n_long = t_n[r_long], n_short = t_n[r_short];
   const bool solo = r_long == r_short;  // the middle row of an odd count
   // keys [cut, n_long) of the long row go to CTA 1 (a multiple of 16 keeps both CTAs' loads aligned to whole groups)
   int cut = n_long;
@@ -276,7 +285,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs
 
   float M, L, O;
   if (role == 0) {
-    attend_range<D, SELF>(p, r_long, t_slot[r_long], h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
+    attend_range<D, SELF>(p, r_long, s_long, h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
     if (helped) {
       cluster.sync();  // the peer's partial has landed
       if (tid < D) {
@@ -288,11 +297,11 @@ __global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs
     if (tid < D) store_out<D>(p, r_long, h, O / L);
   } else {
     if (!solo) {
-      attend_range<D, SELF>(p, r_short, t_slot[r_short], h, n_short, 0, n_short, true, s_m, s_l, s_acc, M, L, O);
+      attend_range<D, SELF>(p, r_short, s_short, h, n_short, 0, n_short, true, s_m, s_l, s_acc, M, L, O);
       if (tid < D) store_out<D>(p, r_short, h, O / L);
     }
     if (helped) {
-      attend_range<D, SELF>(p, r_long, t_slot[r_long], h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
+      attend_range<D, SELF>(p, r_long, s_long, h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
       float* peer = cluster.map_shared_rank(s_peer, 0);
       if (tid < D) peer[tid] = O;
       if (tid == 0) peer[D] = M, peer[D + 1] = L;
@@ -345,11 +354,11 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
     p.stamps = timeline_next(2 * heads * ((rows + 1) / 2), self ? 3000000 : 4000000);
 #endif
     if (head_dim == 64)
-      e = self ? launch_kernel(attention_pair_kernel<64, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-               : launch_kernel(attention_pair_kernel<64, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+      e = self ? launch_kernel(attention_pair_kernel<64, true, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+               : launch_kernel(attention_pair_kernel<64, false, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
     else
-      e = self ? launch_kernel(attention_pair_kernel<128, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-               : launch_kernel(attention_pair_kernel<128, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+      e = self ? launch_kernel(attention_pair_kernel<128, true, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+               : launch_kernel(attention_pair_kernel<128, false, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention launch: %s", cudaGetErrorString(e));
     return 0;
   }
@@ -368,6 +377,36 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
 }
 
 }  // extern "C"
+
+extern "C" int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache,
+                                        void* vcache, int heads, int head_dim, int cap, float scale, void* out,
+                                        int out_kind, int rows, int pdl, void* stream) {
+  B200_REQUIRE(sched && q && kcache && vcache && out, "attention_paired: null pointer");
+  B200_REQUIRE(head_dim == 64 || head_dim == 128, "attention_paired: head_dim %d (64 or 128)", head_dim);
+  B200_REQUIRE(rows >= 1 && rows <= PAIR_MAX_ROWS && heads >= 1 && cap >= 1, "attention_paired: rows %d heads %d cap %d",
+               rows, heads, cap);
+  B200_REQUIRE(ldq % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
+                   ((uintptr_t)vcache & 15) == 0 && ((uintptr_t)sched & 15) == 0, "attention_paired: alignment");
+  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "attention_paired: out_kind");
+  AttnArgs p{};
+  p.sched = sched, p.q = q, p.k = (__nv_bfloat16*)kcache, p.v = (__nv_bfloat16*)vcache, p.out = out;
+  p.ldq = ldq, p.H = heads, p.cap = cap, p.out_kind = out_kind, p.rows = rows, p.splits = 1;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const dim3 grid(2, heads, (rows + 1) / 2);
+#ifdef B200DEC_TIMELINE
+  p.stamps = timeline_next(2 * heads * ((rows + 1) / 2), self ? 3000000 : 4000000);
+#endif
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
+  if (head_dim == 64)
+    e = self ? launch_kernel(attention_pair_kernel<64, true, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+             : launch_kernel(attention_pair_kernel<64, false, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+  else
+    e = self ? launch_kernel(attention_pair_kernel<128, true, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
+             : launch_kernel(attention_pair_kernel<128, false, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention_paired launch: %s", cudaGetErrorString(e));
+  return 0;
+}
 
 // ---- the same attention for callers that cannot hand over scratch memory ---------------------------------------------
 //

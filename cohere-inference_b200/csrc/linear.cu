@@ -163,7 +163,10 @@ int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, cons
   return head_impl(w, a, a_kind, ln, lda, rows, part_max, part_idx, logits, pdl, stream);
 }
 
-int b200dec_head_partials(const b200dec_weight* w) { return w ? (w->n / (16 * w->warps)) * w->ksplit : 0; }
+int b200dec_head_partials(const b200dec_weight* w) {
+  if (!w) return 0;
+  return w->kind == B200DEC_W_INT8_UMMA ? w->n / 128 : (w->n / (16 * w->warps)) * w->ksplit;
+}
 
 int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int k, int rows) {
   if (ksplit < 1 || k % ksplit) return 0;
@@ -171,7 +174,7 @@ int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int
 }
 
 int64_t b200dec_tiled_bytes(int kind, int n, int k) {
-  if (kind == B200DEC_W_INT8) return (int64_t)n * k;
+  if (kind == B200DEC_W_INT8 || kind == B200DEC_W_INT8_UMMA) return (int64_t)n * k;
   if (kind == B200DEC_W_BF16) return (int64_t)n * k * 2;
   if (kind == B200DEC_W_INT8_24) return (int64_t)n * k / 2;
   return -1;

@@ -92,7 +92,60 @@ DEVI void store_row(const float (&o)[32], void* dst, int kind, size_t row, int l
   }
 }
 
+// ---- row schedule: the step's rows ranked by decreasing length, once per step -------------------------------------
+// The paired attention kernel gives the i-th longest row and the i-th shortest to one cluster; the ranking is the same
+// for all layers of a step, so one CTA computes it at the start of the step (beside the embedding) and the sixteen
+// attention launches read two table entries each. Entry i = {row, slot, length, 0} of the row of rank i.
+constexpr int SCHED_MAX_ROWS = 256;
+struct SchedArgs {
+  const int* active;
+  const int* pos;        // per slot: keys in the self cache (the new token's position)
+  const int* cross_len;  // per slot: encoder frames
+  int* sched_self;       // (rows, 4) or null
+  int* sched_cross;
+  int* status;
+  int slots, seq, frames, rows;
+};
+
+DEVI void rank_rows(const SchedArgs& p, const int* len, bool self, int* out, int* t_s, int* t_n) {
+  const int cap = self ? p.seq : p.frames;
+  for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+    int s = p.active[r];
+    if (s < 0 || s > p.slots) {
+      atomicOr(p.status, B200DEC_ST_SLOT_RANGE);
+      s = p.slots;
+    }
+    int n = len[s];
+    if (self ? (n < 0 || n >= cap) : (n < 1 || n > cap)) {
+      atomicOr(p.status, self ? B200DEC_ST_POS_RANGE : B200DEC_ST_FRAMES_RANGE);
+      n = self ? max(0, min(n, cap - 1)) : max(1, min(n, cap));
+    }
+    t_s[r] = s, t_n[r] = n;
+  }
+  __syncthreads();
+  for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+    const int n = t_n[r];
+    int rank = 0;
+    for (int j = 0; j < p.rows; ++j) rank += (t_n[j] > n) || (t_n[j] == n && j < r);  // ties by row
+    *reinterpret_cast<int4*>(out + 4 * rank) = make_int4(r, t_s[r], n, 0);
+  }
+  __syncthreads();
+}
+
+DEVI void build_schedules(const SchedArgs& p) {
+  __shared__ int t_s[SCHED_MAX_ROWS], t_n[SCHED_MAX_ROWS];
+  if (p.sched_self) rank_rows(p, p.pos, true, p.sched_self, t_s, t_n);
+  if (p.sched_cross) rank_rows(p, p.cross_len, false, p.sched_cross, t_s, t_n);
+}
+
+__global__ void __launch_bounds__(128) row_schedule_kernel(const SchedArgs p) {
+  pdl_wait();
+  pdl_trigger();
+  build_schedules(p);
+}
+
 struct EmbedArgs {
+  SchedArgs sched;  // sched.rows == 0: no schedule; else the grid's last CTA builds it
   const int* active;
   const int64_t* tok;
   const int* pos;
@@ -109,6 +162,10 @@ __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   pdl_wait();     // a dependent grid may start only after this one has seen its predecessor complete, so what a
   pdl_trigger();  // kernel reads before its own wait was written at least two kernels earlier
+  if (p.sched.rows > 0 && blockIdx.x == gridDim.x - 1) {  // the extra CTA
+    build_schedules(p.sched);
+    return;
+  }
   if (row >= p.rows) return;
   int s = p.active[row];
   if (s < 0 || s > p.slots) {
@@ -325,14 +382,18 @@ namespace b200dec_detail {
 
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
-                  void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
+                  void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream, const int32_t* cross_len,
+                  int seq, int frames, int32_t* sched_self, int32_t* sched_cross) {
   B200_REQUIRE(active && tok && pos && embed && pos_table && x && status && ln0.w && ln0.b && (!hn || (ln1.w && ln1.b)),
                "embed_ln: null pointer");
   B200_REQUIRE(rows >= 1, "embed_ln: rows %d", rows);
-  EmbedArgs p{active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, hn, status,
+  const bool sched = (sched_self || sched_cross) && rows <= SCHED_MAX_ROWS;
+  B200_REQUIRE(!sched || !sched_cross || cross_len, "embed_ln: a cross schedule needs the frame counts");
+  EmbedArgs p{SchedArgs{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, sched ? rows : 0},
+              active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, hn, status,
               vocab, max_pos, slots, hn_kind, rows};
-  const cudaError_t e = launch_kernel(embed_ln_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, 0,
-                                      pdl, p);
+  const cudaError_t e = launch_kernel(embed_ln_kernel, dim3((rows + 3) / 4 + (sched ? 1 : 0)), dim3(128), 0,
+                                      (cudaStream_t)stream, 0, pdl, p);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "embed_ln launch: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -371,7 +432,19 @@ int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* p
                      const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                      float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
   return embed_ln_impl(active, tok, pos, embed, pos_table, vocab, max_pos, slots, ln0, ln1, x, hn, hn_kind, rows, status,
-                       pdl, stream);
+                       pdl, stream, nullptr, 0, 0, nullptr, nullptr);
+}
+
+int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_t* cross_len, int slots, int seq,
+                         int frames, int rows, int32_t* sched_self, int32_t* sched_cross, int32_t* status,
+                         void* stream) {
+  B200_REQUIRE(active && status && (sched_self || sched_cross), "row_schedule: null pointer");
+  B200_REQUIRE((!sched_self || pos) && (!sched_cross || cross_len), "row_schedule: a table without its lengths");
+  B200_REQUIRE(rows >= 1 && rows <= SCHED_MAX_ROWS, "row_schedule: rows %d (1..%d)", rows, SCHED_MAX_ROWS);
+  SchedArgs p{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, rows};
+  const cudaError_t e = launch_kernel(row_schedule_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 0, 0, p);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "row_schedule launch: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, int rows, int pdl, void* stream) {

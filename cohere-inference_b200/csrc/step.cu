@@ -10,9 +10,12 @@ int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200de
                 int out_kind, int ldo, int act, int pdl, void* stream);
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
               int* pidx, float* logits, int pdl, void* stream);
+int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows, float* part_max,
+                   int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream);
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
-                  float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream);
+                  float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream,
+                  const int32_t* cross_len, int seq, int frames, int32_t* sched_self, int32_t* sched_cross);
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
               const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax, int pdl,
@@ -63,31 +66,49 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   float* logits = pl->logits ? pl->logits + (size_t)row0 * pl->vocab : nullptr;
 
   const auto attention = pl->attn_ring ? b200dec_attention_ring : b200dec_attention;
+  // a large batch: the rows are ranked by length once (an extra CTA of the embedding kernel) and the attention
+  // kernels pair long rows with short ones from the two tables
+  const bool paired = !pl->attn_ring && pl->sched_self && pl->sched_cross && rows * pl->heads >= 512 && rows <= 256;
+  int32_t* sched_self = paired ? pl->sched_self + 4 * row0 : nullptr;
+  int32_t* sched_cross = paired ? pl->sched_cross + 4 * row0 : nullptr;
 
   B200_TRY(embed_ln_impl(active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
-                         pl->emb_ln, pl->layer[0].ln1, x, nullptr, B200DEC_OUT_F32, rows, pl->status, pdl, stream));
+                         pl->emb_ln, pl->layer[0].ln1, x, nullptr, B200DEC_OUT_F32, rows, pl->status, pdl, stream,
+                         pl->cross_len, pl->seq, pl->frames, sched_self, sched_cross));
   for (int i = 0; i < pl->layers; ++i) {
     const b200dec_layer& ly = pl->layer[i];
     B200_TRY(linear_impl(&ly.qkv, x, pl->a_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream));
-    B200_TRY(attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
-                               pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
-                               pdl_attn, stream));
+    if (paired)
+      B200_TRY(b200dec_attention_paired(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, pl->heads, pl->head_dim,
+                                        pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
+    else
+      B200_TRY(attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
+                                 pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
+                                 pdl_attn, stream));
     B200_TRY(linear_impl(&ly.o, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
                          pdl_after, stream));
     B200_TRY(linear_impl(&ly.cq, x, pl->a_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
                          stream));
-    B200_TRY(attention(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len, pl->slots,
-                               pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows, attn_part, attn_count,
-                               pl->status, pdl_attn, stream));
+    if (paired)
+      B200_TRY(b200dec_attention_paired(0, sched_cross, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->heads,
+                                        pl->head_dim, pl->frames, scale, att, ok_a, rows, pdl_attn, stream));
+    else
+      B200_TRY(attention(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->cross_len, pl->slots,
+                                 pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows, attn_part, attn_count,
+                                 pl->status, pdl_attn, stream));
     B200_TRY(linear_impl(&ly.co, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
                          pdl_after, stream));
     B200_TRY(linear_impl(&ly.fc1, x, pl->a_kind, &ly.ln3, D_MODEL, rows, mid, ok_a, ffn, pl->act, pdl, stream));
     B200_TRY(linear_impl(&ly.fc2, mid, pl->a_kind, nullptr, ffn, rows, x, B200DEC_OUT_F32_ADD, D_MODEL,
                          B200DEC_ACT_NONE, pdl, stream));
   }
-  B200_TRY(head_impl(&pl->head, x, pl->head_a_kind, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pdl,
-                     stream));
+  if (pl->head.kind == B200DEC_W_INT8_UMMA)
+    B200_TRY(head_umma_impl(&pl->head, x, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pl->status, pdl,
+                            stream));
+  else
+    B200_TRY(head_impl(&pl->head, x, pl->head_a_kind, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pdl,
+                       stream));
   B200_TRY(pick_impl(head_max, head_idx, partials, active, rows, pl->slots, pl->tok, pl->pos, pl->finished, pl->forced,
                      pl->max_prompt, pl->plen, pl->limit, pl->out, pl->out_cols, pl->eos, pl->argmax, pdl, stream));
   return 0;

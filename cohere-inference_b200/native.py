@@ -14,7 +14,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200dec.so")
 
-W_BF16, W_INT8, W_INT8_24 = 0, 1, 2
+W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA = 0, 1, 2, 3
 A_F16, A_F32_SPLIT = 0, 1
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
@@ -49,7 +49,7 @@ class Plan(C.Structure):
                 ("finished", vp), ("forced", vp), ("out", vp), ("status", vp),
                 ("x", vp), ("qkv", vp), ("cq", vp), ("att", vp), ("mid", vp),
                 ("attn_part", vp), ("attn_count", vp), ("head_max", vp), ("head_idx", vp),
-                ("logits", vp), ("argmax", vp)]
+                ("sched_self", vp), ("sched_cross", vp), ("logits", vp), ("argmax", vp)]
 
 
 # name -> (restype, argtypes); every symbol include/b200dec.h declares
@@ -74,11 +74,16 @@ PROTOTYPES = {
     "b200dec_head_argmax": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, vp, vp,
                                       C.c_int, vp]),
     "b200dec_head_partials": (C.c_int, [C.POINTER(Weight)]),
+    "b200dec_head_umma": (C.c_int, [C.POINTER(Weight), vp, C.POINTER(Norm), C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp]),
+    "b200dec_tile_int8_umma": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_pick": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp, vp, vp, C.c_int,
                                C.c_int, vp, C.c_int, vp]),
     "b200dec_attention": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
                                     vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
     "b200dec_attention_scratch_floats": (i64, [C.c_int, C.c_int, C.c_int]),
+    "b200dec_row_schedule": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]),
+    "b200dec_attention_paired": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, f32, vp,
+                                           C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_attention_ring": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
                                          vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
     "b200dec_attention_static": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -141,7 +141,10 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
+    if kind == nv.W_INT8_UMMA:  # the tcgen05 vocabulary projection: one CTA per 128 channels, LayerNorm done in-kernel
+        warps, ksplit, ln = 4, 1, None
+    else:
+        warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
     ln_g = ln_bias = None
     if ln is not None:
         wd = dequantized(w, kind).double()
@@ -158,6 +161,9 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     elif kind == nv.W_INT8:
         q, scale = quantize_rows(w)
         nv.check(lib.b200dec_tile_int8(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
+    elif kind == nv.W_INT8_UMMA:
+        q, scale = quantize_rows(w)
+        nv.check(lib.b200dec_tile_int8_umma(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
     elif kind == nv.W_INT8_24:
         q, scale = quantize_rows(prune_24_magnitude(w))
         kept, words = compress_24(q)

@@ -16,6 +16,7 @@ projections), `ffn_sparse=True` additionally stores fc1/fc2 2:4; the residual st
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.nn.functional as F
@@ -57,7 +58,8 @@ class StreamDecoder:
     def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 0, graphs: bool = True,
-                 head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False):
+                 head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
+                 head_umma: bool = True):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -99,7 +101,8 @@ class StreamDecoder:
             ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
             self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
             self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference) for layer in dec.layers]
-            self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, kind, keep_reference,
+            head_kind = nv.W_INT8_UMMA if (head_umma and int8 and self.vocab % 128 == 0) else kind
+            self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
                                     a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
             # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection, kept as the
             # fp32 values the quantised (or bf16) weights stand for
@@ -145,6 +148,9 @@ class StreamDecoder:
             self.head_partials = lib.b200dec_head_partials(C.byref(self.head.struct()))
             self.head_max = torch.zeros(bm, self.head_partials, **f32)
             self.head_idx = torch.zeros(bm, self.head_partials, **i32)
+            # the step's rows ranked by length (self / cross), rebuilt by every step for the paired attention kernel
+            self.sched_self = torch.zeros(bm, 4, **i32)
+            self.sched_cross = torch.zeros(bm, 4, **i32)
             self.logits = torch.zeros(bm, self.vocab, **f32) if record else None
             self.argmax = torch.zeros(S + 1, device=dev, dtype=torch.long) if record else None
             # host side: the end flags after each step (pinned, copied by the step itself)
@@ -187,8 +193,10 @@ class StreamDecoder:
         p.head = self.head.struct()
         for name in ("active", "tok", "pos", "plen", "limit", "cross_len", "finished", "forced", "out", "status", "x",
                      "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
-                     "logits", "argmax"):
+                     "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
+        if os.environ.get("B200DEC_NO_SCHED"):  # tuning runs: rank the rows inside every attention launch instead
+            p.sched_self = p.sched_cross = None
         self.plan = p
 
     def _step(self, b: int) -> None:

@@ -19,7 +19,8 @@
 extern "C" {
 #endif
 
-enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2 };   /* weight storage of one projection */
+enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* weight storage of one projection */
+       B200DEC_W_INT8_UMMA = 3 };  /* int8 in the block layout of the tcgen05 vocabulary projection (b200dec_head_umma) */
 enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1 };                       /* activation operand of a projection */
 enum { B200DEC_OUT_F16 = 0, B200DEC_OUT_F32 = 1, B200DEC_OUT_F32_ADD = 2 };/* store, or add into an fp32 residual */
 enum { B200DEC_ACT_NONE = 0, B200DEC_ACT_RELU = 1, B200DEC_ACT_GELU = 2 };
@@ -96,6 +97,8 @@ typedef struct b200dec_plan {
   int32_t* attn_count; /* rows * heads counters, zero on entry and on exit */
   float* head_max;     /* (max rows, b200dec_head_partials()) */
   int32_t* head_idx;
+  int32_t* sched_self;  /* (max rows, 4) row schedules for b200dec_attention_paired, 16-byte aligned; both NULL: */
+  int32_t* sched_cross; /* the step uses b200dec_attention for every batch size */
   /* optional recording (tests, teacher forcing); NULL in production */
   float* logits;       /* (rows, vocab) */
   int64_t* argmax;     /* (slots + 1): the un-forced greedy choice of each slot's last step */
@@ -154,6 +157,15 @@ int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int
 int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                         float* part_max, int32_t* part_idx, float* logits, int pdl, void* stream);
 int b200dec_head_partials(const b200dec_weight* w);
+/* The same vocabulary projection on the fifth-generation tensor cores (tcgen05.mma, accumulator in tensor memory):
+ * x (rows, lda) fp32 is normalised by ln inside the kernel (ln is required), w->kind must be B200DEC_W_INT8_UMMA
+ * (w->w from b200dec_tile_int8_umma, K = 1024, N a multiple of 128; w->warps, ksplit, ln_g, ln_bias unused) and the
+ * partials are one per 128 channels (b200dec_head_partials() = N / 128). rows <= 128, 64 per pass. Replaces the same
+ * reference code as b200dec_head_argmax. status receives B200DEC_ST_TIMEOUT if a bounded wait ran out. */
+int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,
+                      float* part_max, int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream);
+/* q (n, k) int8 row-major (b200dec_quantize_rows) -> the 8 KB block layout of b200dec_head_umma, n*k bytes. */
+int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* stream);
 /* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and
  * finished slots change nothing. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
 int b200dec_pick(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows,
@@ -167,6 +179,22 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
                       const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                       int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
 int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim);
+/* The step's rows ranked by decreasing length, for b200dec_attention_paired: sched_self from pos[slot] (keys in the
+ * self cache), sched_cross from cross_len[slot] (encoder frames); either table may be NULL. Entry i of a table is
+ * int32 {row, slot, length, 0} of the row of rank i (ties by row), lengths clamped into 0..seq-1 / 1..frames and slots
+ * into 0..slots with the status bits of b200dec_attention. rows <= 256. b200dec_step builds both tables with an extra
+ * CTA of its embedding kernel; this entry point is for hosts that launch the kernels themselves. No counterpart in the
+ * reference (its attention takes rows in batch order, kernels/csrc/dec_attn.cuh:84-188). */
+int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_t* cross_len, int slots, int seq,
+                         int frames, int rows, int32_t* sched_self, int32_t* sched_cross, int32_t* status,
+                         void* stream);
+/* b200dec_attention for a large batch (rows * heads >= 512 is where it pays), reading the rows from a schedule: the
+ * i-th longest row and the i-th shortest share a cluster of two CTAs that read the same number of keys; the partial
+ * of the long row's tail crosses distributed shared memory. Same results as b200dec_attention up to the order of the
+ * softmax merge. sched: (rows, 4) int32 from b200dec_row_schedule, 16-byte aligned. */
+int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
+                             int heads, int head_dim, int cap, float scale, void* out, int out_kind, int rows,
+                             int pdl, void* stream);
 /* The same operation, arguments and workspace as b200dec_attention (rows <= 128) by a persistent kernel: two CTAs
  * per SM, one producer lane streaming (row, head) caches through a shared-memory ring with cp.async.bulk and
  * mbarriers, four consumer warps. Smaller footprint per SM; see csrc/attention_ring.cu. */

@@ -249,6 +249,43 @@ def test_head_argmax(nv, pk, rows, a_kind, ln):
     assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * tile)
 
 
+@pytest.mark.parametrize("rows", [1, 33, 64, 100])
+@pytest.mark.parametrize("n", [256, 16384])
+def test_head_umma(nv, pk, rows, n):
+    """The tcgen05 vocabulary projection: logits vs fp64 on the dequantised weights (operand fp16, so the tolerance of
+    the other fp16-operand projections), partials = first-index maxima of its own logits per 128 channels; twice in a
+    row (tensor memory and barriers are set up per launch)."""
+    rng = np.random.default_rng(rows + n)
+    k = 1024
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.01).astype(np.float32)
+    a = (rng.standard_normal((rows, k)) * 1.5 + 0.3).astype(np.float32)
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    g_d, b_d, a_d = cuda(gam), cuda(bet), cuda(a)
+    p = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA)
+    wd = pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy()
+    norm, ws = nv.norm(g_d, b_d, 1e-5), p.struct()
+    np_ = nv.lib().b200dec_head_partials(C.byref(ws))
+    assert np_ == n // 128
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        pm = torch.full((rows, np_), -7.0, device="cuda")
+        pi = torch.full((rows, np_), -7, dtype=torch.int32, device="cuda")
+        logits = torch.zeros(rows, n, device="cuda")
+        nv.check(nv.lib().b200dec_head_umma(C.byref(ws), nv.ptr(a_d), C.byref(norm), k, rows, nv.ptr(pm), nv.ptr(pi),
+                                            nv.ptr(logits), nv.ptr(status), 0, nv.stream_ptr()))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        a_ref = layer_norm(a, gam, bet, 1e-5).astype(np.float16).astype(np.float64)
+        want = (a_ref @ wd.astype(np.float64).T + b).astype(np.float32)
+        lg = logits.cpu().numpy()
+        np.testing.assert_allclose(lg, want, atol=4e-4, rtol=1e-5)
+        t = lg.reshape(rows, np_, 128)
+        assert np.array_equal(pm.cpu().numpy(), t.max(-1))
+        assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * 128)
+
+
 # ---- row kernels ---------------------------------------------------------------------------------------------------------
 
 def test_embed_ln_and_layer_norm(nv):
@@ -361,6 +398,74 @@ def test_attention(nv, H, D, rows, self_, cap, ring):
             else:
                 K, V = kc[s, h, :n[s]], vc[s, h, :n[s]]
             np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=2e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
+@pytest.mark.parametrize("rows", [2, 41, 64])
+@pytest.mark.parametrize("self_", [0, 1])
+def test_row_schedule_and_paired_attention(nv, H, D, rows, self_):
+    """The schedule is the rows by decreasing length (ties by row) with their slots; the paired kernel driven by it
+    equals the reference attention and appends the new keys, twice in a row."""
+    cap = 300
+    rng = np.random.default_rng(rows + H + self_)
+    S = rows + 3
+    kc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
+    vc = bf16_round(rng.standard_normal((S + 1, H, cap, D)).astype(np.float32))
+    active = rng.permutation(S)[:rows].astype(np.int32)
+    n = rng.integers(0 if self_ else 1, cap - 1, S + 1).astype(np.int32)
+    n[active[0]] = 0 if self_ else 1
+    n[active[1]] = cap - 1 if self_ else cap
+    if rows > 20:
+        n[active[5:20]] = 77                       # ties, and pairs of equal length (no exchange)
+        n[active[20]], n[active[21]] = 100, 131    # a difference just under / over the exchange threshold
+    ld = 3 * H * D if self_ else H * D
+    q = rng.standard_normal((rows, ld)).astype(np.float32)
+    kd, vd = cuda(kc).to(torch.bfloat16), cuda(vc).to(torch.bfloat16)
+    lib = nv.lib()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sched = torch.full((rows, 4), -1, dtype=torch.int32, device="cuda")
+    out = torch.zeros(rows, H * D, device="cuda")
+    a_d, q_d, n_d = cuda(active), cuda(q), cuda(n)
+    scale = D ** -0.5
+    for _ in range(2):
+        nv.check(lib.b200dec_row_schedule(nv.ptr(a_d), nv.ptr(n_d) if self_ else None, None if self_ else nv.ptr(n_d), S,
+                                          cap, cap, rows, nv.ptr(sched) if self_ else None,
+                                          None if self_ else nv.ptr(sched), nv.ptr(status), nv.stream_ptr()))
+        nv.check(lib.b200dec_attention_paired(self_, nv.ptr(sched), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), H, D, cap,
+                                              scale, nv.ptr(out), nv.OUT_F32, rows, 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    lens = n[active]
+    order = sorted(range(rows), key=lambda r: (-int(lens[r]), r))
+    want = np.array([[r, active[r], lens[r], 0] for r in order], np.int32)
+    np.testing.assert_array_equal(sched.cpu().numpy(), want)
+    got, k_after = out.cpu().numpy(), kd.float().cpu().numpy()
+    for r in range(rows):
+        s = active[r]
+        for h in range(H):
+            qq = q[r, h * D:(h + 1) * D]
+            if self_:
+                kn = bf16_round(q[r, (H + h) * D:(H + h + 1) * D])
+                vn = bf16_round(q[r, (2 * H + h) * D:(2 * H + h + 1) * D])
+                assert np.array_equal(k_after[s, h, n[s]], kn)
+                K = np.concatenate([kc[s, h, :n[s]], kn[None]])
+                V = np.concatenate([vc[s, h, :n[s]], vn[None]])
+            else:
+                K, V = kc[s, h, :n[s]], vc[s, h, :n[s]]
+            np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=2e-5, rtol=1e-4)
+
+
+def test_row_schedule_reports_bad_state(nv):
+    lib = nv.lib()
+    active = cuda(np.array([0, 9, 1], np.int32))          # slot 9 does not exist (slots = 3)
+    lens = cuda(np.array([5, 400, 7, 1], np.int32))        # 400 frames > the capacity of 100
+    sched = torch.zeros(3, 4, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nv.check(lib.b200dec_row_schedule(nv.ptr(active), None, nv.ptr(lens), 3, 100, 100, 3, None, nv.ptr(sched),
+                                      nv.ptr(status), nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == nv.ST_SLOT_RANGE | nv.ST_FRAMES_RANGE
+    np.testing.assert_array_equal(sched.cpu().numpy(), [[2, 1, 100, 0], [0, 0, 5, 0], [1, 3, 1, 0]])
 
 
 def test_pick_semantics(nv):

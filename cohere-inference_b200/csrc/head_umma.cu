@@ -7,9 +7,9 @@
 //     fp32) and writes them as fp16 into sixteen K-major tiles of 64 rows x 64 k with the 128-byte swizzle.
 //   * A operand: the weights stream from HBM as 8 KB blocks (128 channels x 64 k, uint8 = q + 128, laid out by
 //     b200dec_tile_int8_umma so that a thread's 16-byte pieces are conflict-free) through a ring filled by one
-//     producer lane with cp.async.bulk; four converter warps widen each block to fp16 (exact) into a second ring of
+//     producer lane with cp.async.bulk; eight converter warps widen each block to fp16 (exact) into a second ring of
 //     swizzled K-major tiles; one lane issues the MMAs of a block and `tcgen05.commit`s the tile's release.
-//   * Epilogue: `tcgen05.ld` (thread = channel, 64 rows in registers), scale and bias, transposed through shared memory
+//   * Epilogue: `tcgen05.ld` (thread = channel, 32 of the rows in registers), scale and bias, transposed through shared memory
 //     for the per-row argmax over the CTA's channels (first index of the maximum, NaN never wins) and the optional
 //     logits store.
 // Every mbarrier wait is bounded; a wait that runs out sets B200DEC_ST_TIMEOUT and the roles fall through to the end
@@ -24,7 +24,7 @@ constexpr int UM = 128;                 // channels per CTA (MMA M)
 constexpr int UN = 64;                  // rows (MMA N)
 constexpr int KB = 64;                  // k per block: one 128-byte row of fp16
 constexpr int NKB = D_MODEL / KB;       // 16 blocks
-constexpr int RAW_STAGES = 4, A_STAGES = 3;
+constexpr int RAW_STAGES = 8, A_STAGES = 2;  // 64 KB of weights in flight per SM: what HBM latency asks for
 constexpr int RAW_BYTES = UM * KB;      // 8 KB of uint8
 constexpr int A_BYTES = UM * KB * 2;    // 16 KB of fp16
 constexpr int XB_BYTES = UN * KB * 2;   // 8 KB: one k-block of the activations
@@ -33,7 +33,7 @@ constexpr int OFF_A = X_BYTES, OFF_RAW = OFF_A + A_STAGES * A_BYTES, SMEM_USED =
 constexpr int SMEM_BYTES = SMEM_USED + 1024;  // slack to align the base to a swizzle atom
 constexpr int OUT_LD = UM + 4;                // epilogue tile (64 rows x 128 channels fp32) row pitch, reuses the rings
 static_assert(UN * OUT_LD * 4 <= SMEM_USED - OFF_A, "epilogue tile fits in the rings");
-constexpr int NWORK = 4;                      // converter / epilogue warps
+constexpr int NWORK = 8;                      // staging / converter / epilogue warps
 constexpr int NTHREADS = (NWORK + 2) * 32;    // + the MMA warp and the producer warp
 constexpr int TMEM_COLS = 64;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -51,7 +51,20 @@ struct HeadArgs {
   int* status;
   float ln_eps;
   int lda, rows, N;
+#ifdef B200DEC_STAMPS
+  long long* stamps;  // per CTA 12 timer values (latency studies only)
+#endif
 };
+
+#ifdef B200DEC_STAMPS
+#define HEAD_STAMP(i)                                                                   \
+  do {                                                                                  \
+    if (p.stamps && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == ((i) == 6 ? NWORK : 0)) \
+      p.stamps[blockIdx.x * 12 + (i)] = stamp_clock();                                  \
+  } while (0)
+#else
+#define HEAD_STAMP(i)
+#endif
 
 DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 DEVI void mbar_init(uint64_t* bar, int count) {
@@ -138,6 +151,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;  // channels [128 tile, +128)
+  HEAD_STAMP(0);
   const uint8_t* wsrc = p.w + (size_t)tile * NKB * RAW_BYTES;
 
   if (tid == 0) {
@@ -160,6 +174,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = tmem_base;
+  HEAD_STAMP(1);
 
   if (warp == NWORK + 1) {
     // ---- producer: the tile's sixteen weight blocks through the raw ring (independent of the previous kernel) -------
@@ -191,119 +206,135 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
       }
       if (!ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
       umma_commit(&d_full);  // arrives when everything issued so far has completed (also after a time-out)
+      HEAD_STAMP(6);
     }
   } else {
     // ---- workers: normalise the rows into the B tiles, then widen weight blocks, then the epilogue ------------------
     pdl_wait();
     pdl_trigger();
-    for (int r = warp; r < UN; r += NWORK) {
-      float v[32];
-      const bool live = r < p.rows;
+    HEAD_STAMP(2);
+    // two rows per warp in flight (the loads of a row are one L2 round trip; a warp has 64 / 8 rows to do)
+    for (int r0 = warp; r0 < UN; r0 += 2 * NWORK) {
+      float v[2][32];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 f = live ? ld_cg_f4(p.x + (size_t)r * p.lda + i * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-        v[4 * i] = f.x, v[4 * i + 1] = f.y, v[4 * i + 2] = f.z, v[4 * i + 3] = f.w;
+      for (int u = 0; u < 2; ++u) {
+        const int r = (r0 + u * NWORK + tile) & (UN - 1);  // rotated by the tile index: at any moment the CTAs
+        const bool live = r < p.rows;                       // of the grid ask L2 for different rows
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 f = live ? ld_cg_f4(p.x + (size_t)r * p.lda + i * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[u][4 * i] = f.x, v[u][4 * i + 1] = f.y, v[u][4 * i + 2] = f.z, v[u][4 * i + 3] = f.w;
+        }
       }
-      float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s += v[i];
-      const float mean = warp_sum(s) * (1.f / D_MODEL);
-      float q = 0.f;
+      for (int u = 0; u < 2; ++u) {
+        const int r = (r0 + u * NWORK + tile) & (UN - 1);
+        const bool live = r < p.rows;
+        float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) q += (v[i] - mean) * (v[i] - mean);
-      const float rstd = rsqrtf(warp_sum(q) * (1.f / D_MODEL) + p.ln_eps);
+        for (int i = 0; i < 32; ++i) s += v[u][i];
+        const float mean = warp_sum(s) * (1.f / D_MODEL);
+        float q = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int c = i * 128 + lane * 4;  // columns c .. c+3: half a 16-byte chunk of k-block c / 64
-        const float4 g = __ldg(reinterpret_cast<const float4*>(p.ln_w + c));
-        const float4 b = __ldg(reinterpret_cast<const float4*>(p.ln_b + c));
-        uint2 h = make_uint2(0, 0);
-        if (live)
-          h = make_uint2(pack_f16((v[4 * i] - mean) * rstd * g.x + b.x, (v[4 * i + 1] - mean) * rstd * g.y + b.y),
-                         pack_f16((v[4 * i + 2] - mean) * rstd * g.z + b.z, (v[4 * i + 3] - mean) * rstd * g.w + b.w));
-        const int kb = c >> 6, chunk = (c & 63) >> 3;
-        *reinterpret_cast<uint2*>(xs + kb * XB_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4) +
-                                  (c & 7) * 2) = h;
+        for (int i = 0; i < 32; ++i) q += (v[u][i] - mean) * (v[u][i] - mean);
+        const float rstd = rsqrtf(warp_sum(q) * (1.f / D_MODEL) + p.ln_eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int c = i * 128 + lane * 4;  // columns c .. c+3: half a 16-byte chunk of k-block c / 64
+          const float4 g = __ldg(reinterpret_cast<const float4*>(p.ln_w + c));
+          const float4 b = __ldg(reinterpret_cast<const float4*>(p.ln_b + c));
+          uint2 h = make_uint2(0, 0);
+          if (live)
+            h = make_uint2(pack_f16((v[u][4 * i] - mean) * rstd * g.x + b.x, (v[u][4 * i + 1] - mean) * rstd * g.y + b.y),
+                           pack_f16((v[u][4 * i + 2] - mean) * rstd * g.z + b.z,
+                                    (v[u][4 * i + 3] - mean) * rstd * g.w + b.w));
+          const int kb = c >> 6, chunk = (c & 63) >> 3;
+          *reinterpret_cast<uint2*>(xs + kb * XB_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4) +
+                                    (c & 7) * 2) = h;
+        }
       }
     }
     fence_async_shared();  // the MMA reads these tiles through the async proxy
     __syncwarp();
     if (lane == 0) mbar_arrive(&x_full);
+    HEAD_STAMP(3);
 
     bool ok = true;
-    const int ch = tid;  // this thread's channel of the tile
+    const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile (= its tensor-memory lane)
+    const int hf = warp >> 2;               // and its half: 16-k pieces 2 hf, 2 hf + 1 of a block, rows 32 hf .. + 31
     for (int kb = 0; kb < NKB; ++kb) {
       if (!ok) break;
       const int rs = kb % RAW_STAGES, st = kb % A_STAGES;
       ok = mbar_wait(&raw_full[rs], (kb / RAW_STAGES) & 1);
       if (!ok) break;
-      uint4 r[4];
+      uint4 r[2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) r[j] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + j * 2048 + ch * 16);
+      for (int j = 0; j < 2; ++j)
+        r[j] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + (2 * hf + j) * 2048 + ch * 16);
       __syncwarp();
       if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the block's bytes are in registers
       ok = mbar_wait(&a_empty[st], ((kb / A_STAGES) & 1) ^ 1);
       if (!ok) break;
       unsigned char* row = as + st * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {  // k = 16 j .. 16 j + 15: chunks 2j and 2j + 1 of the row
+      for (int j = 0; j < 2; ++j) {  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
+        const int pj = 2 * hf + j;
         uint4 lo, hi;
         widen16(r[j], lo, hi);
-        *reinterpret_cast<uint4*>(row + (((2 * j) ^ (ch & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(row + (((2 * j + 1) ^ (ch & 7)) << 4)) = hi;
+        *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
       }
       fence_async_shared();
       __syncwarp();
       if (lane == 0) mbar_arrive(&a_full[st]);
     }
     if (!ok && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+    HEAD_STAMP(4);
 
     // ---- epilogue ---------------------------------------------------------------------------------------------------
     const bool got = mbar_wait(&d_full, 0);
     if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+    HEAD_STAMP(5);
     tc_fence_after();
     float* outs = reinterpret_cast<float*>(as);  // (64 rows, OUT_LD): the rings are idle once d_full has fired
     {
-      uint32_t d[UN];
-      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+      uint32_t d[32];
+      const uint32_t taddr = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(hf * 32);
       asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
           "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-          "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-          "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
           : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
             "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]),
             "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]), "=r"(d[24]),
-            "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31]), "=r"(d[32]),
-            "=r"(d[33]), "=r"(d[34]), "=r"(d[35]), "=r"(d[36]), "=r"(d[37]), "=r"(d[38]), "=r"(d[39]), "=r"(d[40]),
-            "=r"(d[41]), "=r"(d[42]), "=r"(d[43]), "=r"(d[44]), "=r"(d[45]), "=r"(d[46]), "=r"(d[47]), "=r"(d[48]),
-            "=r"(d[49]), "=r"(d[50]), "=r"(d[51]), "=r"(d[52]), "=r"(d[53]), "=r"(d[54]), "=r"(d[55]), "=r"(d[56]),
-            "=r"(d[57]), "=r"(d[58]), "=r"(d[59]), "=r"(d[60]), "=r"(d[61]), "=r"(d[62]), "=r"(d[63])
+            "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
           : "r"(taddr)
           : "memory");
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const float sc = s_scale[ch], bi = s_bias[ch];
 #pragma unroll
-      for (int r = 0; r < UN; ++r) outs[r * OUT_LD + ch] = __uint_as_float(d[r]) * sc + bi;
+      for (int r = 0; r < 32; ++r) outs[(hf * 32 + r) * OUT_LD + ch] = __uint_as_float(d[r]) * sc + bi;
     }
     tc_fence_before();
     asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the workers only
     {
-      // per-row argmax over the tile's channels: two threads per row, 64 channels each, lowest index wins ties
-      const int r = tid >> 1, half = tid & 1;
+      // per-row argmax over the tile's channels: four threads per row, 32 channels each, lowest index wins ties
+      const int r = tid >> 2, qt = tid & 3;
       float best = -INFINITY;
       int arg = 0x7fffffff;
-      const float* rowp = outs + r * OUT_LD + half * 64;
+      const float* rowp = outs + r * OUT_LD + qt * 32;
 #pragma unroll 8
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         const float v = rowp[c];
-        if (v > best) best = v, arg = tile * UM + half * 64 + c;
+        if (v > best) best = v, arg = tile * UM + qt * 32 + c;
       }
-      const float ob = __shfl_xor_sync(0xffffffffu, best, 1);
-      const int oa = __shfl_xor_sync(0xffffffffu, arg, 1);
-      if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
-      if (half == 0 && r < p.rows) {
+#pragma unroll
+      for (int o = 1; o < 4; o <<= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+      }
+      if (qt == 0 && r < p.rows) {
         const int np = p.N / UM;
         p.part_max[(size_t)r * np + tile] = best;
         p.part_idx[(size_t)r * np + tile] = arg;
@@ -315,6 +346,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
       }
     }
   }
+  HEAD_STAMP(7);
   // ---- release the tensor memory: after every warp is done with it ----------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -357,6 +389,9 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* 
     a.part_max = part_max + (size_t)r0 * np, a.part_idx = part_idx + (size_t)r0 * np;
     a.logits = logits ? logits + (size_t)r0 * w->n : nullptr;
     a.status = status, a.lda = lda, a.rows = rows - r0 < UN ? rows - r0 : UN, a.N = w->n;
+#ifdef B200DEC_TIMELINE
+    a.stamps = timeline_next(np, 5000000);
+#endif
     e = launch_kernel(head_umma_kernel, dim3(np), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream, 0, pdl, a);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma launch: %s", cudaGetErrorString(e));
   }

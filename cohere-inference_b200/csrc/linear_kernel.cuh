@@ -380,6 +380,19 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   if (one_item && tid < items && !p.head && p.out_kind == B200DEC_OUT_F32_ADD)
     resid = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + (size_t)(tid / GPR) * p.ldo +
                                                    blockIdx.y * BN + rank * CPR + (tid % GPR) * 4));
+  // likewise the per-channel vectors of the epilogue (the same four channels for every item of this thread)
+  const int n_mine = blockIdx.y * BN + rank * CPR + (tid % GPR) * 4;
+  const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f), zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool pre = NT % GPR == 0;  // then `it % GPR` is the same for all of a thread's items
+  const float4 sc_pre = (pre && p.scale) ? __ldg(reinterpret_cast<const float4*>(p.scale + n_mine)) : one4;
+  const float4 bb_pre = (pre && p.bias) ? __ldg(reinterpret_cast<const float4*>(p.bias + n_mine)) : zero4;
+  float4 gg_pre = zero4, lb_pre = zero4;
+  if constexpr (LN) {
+    if (pre) {
+      gg_pre = __ldg(reinterpret_cast<const float4*>(p.ln_g + n_mine));
+      lb_pre = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
+    }
+  }
   B200_STAMP(5);
   cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this
   B200_STAMP(6);
@@ -397,7 +410,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
         s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
       }
       if (p.scale) {
-        const float4 sc = *reinterpret_cast<const float4*>(p.scale + n);
+        const float4 sc = pre ? sc_pre : *reinterpret_cast<const float4*>(p.scale + n);
         s.x *= sc.x, s.y *= sc.y, s.z *= sc.z, s.w *= sc.w;
       }
       if constexpr (LN) {
@@ -409,13 +422,13 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
         }
         const float dm = s1 * (1.f / K);  // mean - shift
         const float rstd = rsqrtf(fmaxf(s2 * (1.f / K) - dm * dm, 0.f) + p.ln_eps);
-        const float4 gg = *reinterpret_cast<const float4*>(p.ln_g + n);
-        const float4 lb = *reinterpret_cast<const float4*>(p.ln_bias + n);
+        const float4 gg = pre ? gg_pre : *reinterpret_cast<const float4*>(p.ln_g + n);
+        const float4 lb = pre ? lb_pre : *reinterpret_cast<const float4*>(p.ln_bias + n);
         s.x = rstd * (s.x - dm * gg.x) + lb.x, s.y = rstd * (s.y - dm * gg.y) + lb.y;
         s.z = rstd * (s.z - dm * gg.z) + lb.z, s.w = rstd * (s.w - dm * gg.w) + lb.w;
       }
       if (p.bias) {
-        const float4 bb = *reinterpret_cast<const float4*>(p.bias + n);
+        const float4 bb = pre ? bb_pre : *reinterpret_cast<const float4*>(p.bias + n);
         s.x += bb.x, s.y += bb.y, s.z += bb.z, s.w += bb.w;
       }
       s.x = act_fn(s.x, p.act), s.y = act_fn(s.y, p.act), s.z = act_fn(s.z, p.act), s.w = act_fn(s.w, p.act);

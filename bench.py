@@ -249,11 +249,11 @@ def run_ours(args) -> None:
                     "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
                     "ms_per_step": round(e2e_ms / args.steps, 3)},
             "gpu_launches": dec.launches_per_step * len(dec.row_ranges(BATCH)) * steps_per_pass * args.steps,
-            "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention") + " kernel <64, cross> (64 rows x 16 heads)",
+            "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention_pair") + " kernel <64, cross> (64 rows x 16 heads), replayed from a CUDA graph",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
                          # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu capture summarised in
-                         # profiles/attention_kernel_config3.md (55.72 MB + 0.36 MB for 55.44 MB of K/V), scaled by bytes
+                         # profiles/attention_kernel_config3.md (55.73 MB + 0.20 MB for 55.44 MB of K/V), scaled by bytes
                          "traffic": int(kv_bytes * ATTN_TRAFFIC_PER_BYTE), "traffic_source": "ncu, profiles/attention_kernel_config3.md",
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
@@ -268,7 +268,7 @@ def run_ours(args) -> None:
         torch.distributed.destroy_process_group()
 
 
-ATTN_TRAFFIC_PER_BYTE = (55.72 + 0.36) / 55.44   # measured DRAM traffic / algorithmic K/V bytes, cross-attention launch
+ATTN_TRAFFIC_PER_BYTE = (55.73 + 0.20) / 55.44   # measured DRAM traffic / algorithmic K/V bytes, cross-attention launch
 
 
 def run_profile(args) -> None:
@@ -306,6 +306,69 @@ def run_profile(args) -> None:
     print(json.dumps({"profile_steps": args.profile, "rows": B, "pos": args.profile_pos + 3, "sum_frames": sum(lens),
                       "cross_kv_bytes_per_launch": kv, "self_kv_bytes_per_launch": B * (args.profile_pos + 4) * 4096,
                       "weight_bytes": dec.weight_bytes, "launches_per_step": dec.launches_per_step}))
+
+
+def run_stream(args) -> None:
+    """BASELINE configs 4 / 5 (not the headline line): continuous batching, 128 slots per GPU, 2:4 int8 feed-forward
+    weights, a seeded Poisson stream of `--requests` requests dealt round-robin over the ranks, admitted and evicted
+    between graph replays by DecodeScheduler. Prints one JSON line: delivered new tokens / device time of the whole
+    run (max over ranks), occupancy, and the run's algorithmic bytes against the measured HBM peak."""
+    from cohere_inference_b200 import DecodeScheduler, StreamDecoder, synthetic_model, synthetic_requests
+    from cohere_inference_b200 import dataparallel as dp
+    rank, local, world = dp.init()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    SLOTS = 128
+    dec = StreamDecoder(synthetic_model(0).to(dev), slots=SLOTS, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
+                        int8=True, ffn_sparse=True, eos=-1, pdl=args.pdl, attn_ring=args.attn_ring,
+                        head_umma=not args.no_head_umma)
+    mine = dp.partition(synthetic_requests(args.requests, seed=0, slots=SLOTS * world), rank, world)
+
+    def memory_of(req):
+        g = torch.Generator(device=dev).manual_seed(req.mem_seed)
+        return torch.randn(req.frames, 1024, device=dev, generator=g)
+
+    sched = DecodeScheduler(dec, memory_of, account_bytes=True)
+    clocks = ClockSampler(local).__enter__()
+    dp.barrier(dev)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(dec.stream)
+    out = sched.run(mine)
+    e1.record(dec.stream)
+    torch.cuda.synchronize()
+    dp.barrier(dev)
+    wall = time.perf_counter() - t0
+    clocks.__exit__()
+    dec.check_status()
+    st = sched.stats
+    ms = dp.max_over_ranks(e0.elapsed_time(e1), dev)
+    stats = dp.gather_stats(dict(steps=st.steps, row_steps=st.row_steps, padded_row_steps=st.padded_row_steps,
+                                 slot_steps=st.slot_steps, admitted=st.admitted, evicted=st.evicted,
+                                 new_tokens=st.new_tokens, delivered_tokens=st.delivered_tokens, bytes=st.bytes,
+                                 gpu_us=int(e0.elapsed_time(e1) * 1e3)), dev)
+    assert all(o is not None for o in out) and st.evicted == len(mine)
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        tokens = sum(s["new_tokens"] for s in stats)
+        gbs = sum(s["bytes"] for s in stats) / world / (ms / 1e3) / 1e9
+        print(json.dumps({
+            "metric": "decoded tokens/s, continuous batching, 128 slots per GPU, 2:4 int8 feed-forward", "impl": "ours",
+            "value": round(tokens / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "higher_is_better": True,
+            "scaling": "strong", "data": "synthetic",
+            "config": {"workload": f"BASELINE config {'4' if world == 1 else '5'}: {args.requests} requests, encoder "
+                                   "lengths U[50,375], targets U[16,448], Poisson arrivals for ~95 % full slots, "
+                                   "admission and eviction between graph replays", "slots_per_gpu": SLOTS},
+            "steps": [s["steps"] for s in stats], "ms_per_step": round(ms / max(s["steps"] for s in stats), 4),
+            "occupancy": round(sum(s["row_steps"] for s in stats) / max(1, sum(s["slot_steps"] for s in stats)), 4),
+            "padding": round(sum(s["padded_row_steps"] for s in stats) / max(1, sum(s["row_steps"] for s in stats)), 4),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "what": "whole run, per GPU"},
+            "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in stats],
+            "clocks": clocks.summary(), "wall_s": round(wall, 2)}), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
 
 
 def run_reference(args) -> None:
@@ -360,12 +423,17 @@ def main() -> None:
     ap.add_argument("--profile-slots", type=int, default=BATCH)
     ap.add_argument("--profile-pos", type=int, default=225)
     ap.add_argument("--sparse", action="store_true", help="profiler mode: 2:4 feed-forward weights")
+    ap.add_argument("--workload", default="batch64", choices=["batch64", "stream"],
+                    help="batch64: BASELINE config 3 (the headline line); stream: configs 4 / 5, continuous batching")
+    ap.add_argument("--requests", type=int, default=2000, help="stream workload: requests in the whole stream")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.profile:
         run_profile(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "stream":
+        run_stream(args)
     else:
         run_ours(args)
 

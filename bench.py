@@ -189,11 +189,17 @@ def run_ours(args) -> None:
     def attn_launches():
         for i in range(reps * L):
             ly = i % L
-            nv.check(attn_fn(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
-                             nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
-                             dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
-                             nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status),
-                             1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
+            if args.attn_ring:
+                nv.check(attn_fn(0, nv.ptr(dec.active), nv.ptr(dec.cq), 1024, nv.ptr(dec.cross_k[ly]),
+                                 nv.ptr(dec.cross_v[ly]), nv.ptr(dec.cross_len), dec.slots, dec.h, dec.d,
+                                 dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
+                                 nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status),
+                                 1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
+            else:  # what the step launches at this batch size: the paired kernel on the step's own row schedule
+                nv.check(lib.b200dec_attention_paired(0, nv.ptr(dec.sched_cross), nv.ptr(dec.cq), 1024,
+                                                      nv.ptr(dec.cross_k[ly]), nv.ptr(dec.cross_v[ly]), dec.h, dec.d,
+                                                      dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
+                                                      1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
 
     # launched from a CUDA graph, as in the step (from Python the loop would be bound by the host's launch rate)
     attn_graph = torch.cuda.CUDAGraph()

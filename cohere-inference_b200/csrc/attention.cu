@@ -176,7 +176,7 @@ DEVI void row_state(const AttnArgs& p, int r, bool report, int& s, int& n) {
 }
 
 template <int D, bool SELF>
-__global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
+__global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p) {
   constexpr int NG = NTHREADS / (D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_kernel(const AttnArgs p) {
 constexpr int PAIR_MAX_ROWS = 256;
 
 template <int D, bool SELF, bool TABLE>
-__global__ void __launch_bounds__(NTHREADS) attention_pair_kernel(const AttnArgs p) {
+__global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnArgs p) {
   constexpr int NG = NTHREADS / (D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];

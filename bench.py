@@ -106,7 +106,7 @@ def run_ours(args) -> None:
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
-                        head_split=not args.no_head_split, head_umma=not args.no_head_umma)
+                        head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8)
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -183,7 +183,7 @@ def run_ours(args) -> None:
     # cache in L2 (one layer's cross K/V is ~56 MB, the eight together ~450 MB > the 126 MB L2)
     lib, L = nv.lib(), len(dec.layers)
     attn_fn = lib.b200dec_attention_ring if args.attn_ring else lib.b200dec_attention
-    kv_bytes = sum(lens) * 2 * 1024 * 2
+    kv_bytes = int(sum(lens) * 2 * 1024 * ((1 + 4 / dec.d) if args.kv_int8 else 2))
     reps = 10
 
     def attn_launches():
@@ -195,6 +195,12 @@ def run_ours(args) -> None:
                                  dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16, BATCH,
                                  nv.ptr(dec.attn_part), nv.ptr(dec.attn_count), nv.ptr(dec.status),
                                  1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
+            elif args.kv_int8:
+                nv.check(lib.b200dec_attention_paired_q8(0, nv.ptr(dec.sched_cross), nv.ptr(dec.cq), 1024,
+                                                         nv.ptr(dec.cross_k[ly]), nv.ptr(dec.cross_v[ly]),
+                                                         nv.ptr(dec.cross_ks[ly]), nv.ptr(dec.cross_vs[ly]), dec.h,
+                                                         dec.d, dec.frames, dec.scale, nv.ptr(dec.att), nv.OUT_F16,
+                                                         BATCH, 1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
             else:  # what the step launches at this batch size: the paired kernel on the step's own row schedule
                 nv.check(lib.b200dec_attention_paired(0, nv.ptr(dec.sched_cross), nv.ptr(dec.cq), 1024,
                                                       nv.ptr(dec.cross_k[ly]), nv.ptr(dec.cross_v[ly]), dec.h, dec.d,
@@ -239,14 +245,14 @@ def run_ours(args) -> None:
                "sample": r["sample"], "ms_per_step": round(r["ms_per_step"], 2)}
     if rank == 0:
         line = {
-            "metric": "decoded tokens/s at batch 64, weight-only int8", "value": round(value, 1), "unit": "tokens/s",
+            "metric": "decoded tokens/s at batch 64, weight-only int8" + (", int8 KV caches" if args.kv_int8 else ""), "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights x fp16, fp32 accumulate",
             "data": "synthetic",
             "config": {"workload": "BASELINE config 3: 8 layers x 1024, 16 heads x 64, GELU, vocab 16384; batch 64 per GPU, "
                                    "encoder lengths U[50,375], 10-token prompts + 448 new tokens, one CUDA graph per "
                                    "decoding step; a bench step = one pass = 457 replays",
-                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "bf16", "parallelism": f"dp{world} replicas", "chains_per_step": len(dec.row_ranges(BATCH)),
+                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "int8 + fp32 scale per head vector" if args.kv_int8 else "bf16", "parallelism": f"dp{world} replicas", "chains_per_step": len(dec.row_ranges(BATCH)),
                        "l2": "inputs larger than L2: each replay streams ~0.2-1.9 GB of KV cache and weights",
                        "weights": "seed-0 random init N(0, 0.02)"},
             "p50_step_ms": round(p50, 4),
@@ -260,7 +266,8 @@ def run_ours(args) -> None:
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
                          # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu capture summarised in
                          # profiles/attention_kernel_config3.md (55.73 MB + 0.20 MB for 55.44 MB of K/V), scaled by bytes
-                         "traffic": int(kv_bytes * ATTN_TRAFFIC_PER_BYTE), "traffic_source": "ncu, profiles/attention_kernel_config3.md",
+                         "traffic": None if args.kv_int8 else int(kv_bytes * ATTN_TRAFFIC_PER_BYTE),
+                         "traffic_source": "ncu, profiles/attention_kernel_config3.md",
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
                                   "frac_of_8TBs": round(step_gbs / 8000, 4)}},
@@ -423,6 +430,8 @@ def main() -> None:
                     "2 attention, 4 projection after attention (sum them)")
     ap.add_argument("--no-head-umma", action="store_true", help="vocabulary projection on mma.sync instead of tcgen05")
     ap.add_argument("--no-head-split", action="store_true", help="vocabulary projection on a single fp16 operand")
+    ap.add_argument("--kv-int8", action="store_true", help="int8 KV caches with per-vector scales (the reference's int8 "
+                    "mode); a separate row, the headline keeps bf16 caches")
     ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")
     ap.add_argument("--chains", type=int, default=1, help="concurrent kernel chains a step's rows are split into")
     ap.add_argument("--profile", type=int, default=0, help="profiler mode: this many directly launched steps")

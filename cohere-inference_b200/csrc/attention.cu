@@ -34,6 +34,8 @@ struct AttnArgs {
   __nv_bfloat16* k;
   __nv_bfloat16* v;
   const int* n;
+  float* ks;         // int8 caches: one fp32 scale per cached key vector / value vector, (slots + 1, H, cap)
+  float* vs;
   const int* sched;  // paired kernel: (rows, 4) = {row, slot, length, 0} by decreasing length, or null
   void* out;
   float* part;
@@ -151,6 +153,148 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
   }
 }
 
+// ---- int8 caches: one fp32 scale per head vector (the format of the reference's int8 mode) ---------------------------
+// vector -> scale = absmax / 127 (1 when the vector is zero), q = rint(clamp(x * (1 / scale), +-127)); x ~ q * scale.
+// int8 byte j of a word as an exact float: the byte (biased by 128) becomes the low mantissa bits of 1.5 * 2^23.
+DEVI float q8_float(uint32_t biased_word, int j) {
+  return __uint_as_float(__byte_perm(biased_word, 0x4B400000u, 0x7650 | j)) - 12583040.f;
+}
+
+// The same pass as attend_range over int8 caches: a key (or value) of D int8 is read by D / 16 lanes with one 16-byte
+// load each. The row's new key and value are rounded to bf16, quantised into the cache, and attended in that step as
+// the bf16 values (the quantised copy serves the later steps), as the reference does.
+template <int D, bool SELF>
+DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int start, int end, bool with_new,
+                          float* s_m, float* s_l, float (*s_acc)[D + 4], float& M, float& L, float& O) {
+  constexpr int LPK = D / 16;          // lanes per key
+  constexpr int NG = NTHREADS / LPK;   // key groups per CTA
+  constexpr int U = 4;                 // keys in flight per group
+  const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
+  const int8_t* k8 = reinterpret_cast<const int8_t*>(p.k);
+  const int8_t* v8 = reinterpret_cast<const int8_t*>(p.v);
+
+  float q[16];
+  {
+    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * 16;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = ld_cg_f4(qp + 4 * i);
+      q[4 * i] = a.x * p.scale_log2, q[4 * i + 1] = a.y * p.scale_log2;
+      q[4 * i + 2] = a.z * p.scale_log2, q[4 * i + 3] = a.w * p.scale_log2;
+    }
+  }
+  const size_t vec0 = ((size_t)s * p.H + h) * p.cap;  // index of key 0: scales, and * D the vectors
+  float m = -1e30f, l = 0.f, acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+
+  // kf, vf: the lane's 16 dims of a key and a value as floats still to be multiplied by ksc, vsc
+  auto attend = [&](const float (&kf)[16], float ksc, const float (&vf)[16], float vsc, bool valid) {
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) d0 += q[i] * kf[i], d1 += q[i + 1] * kf[i + 1];
+    float d = d0 + d1;
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    const float sc = valid ? d * ksc : -INFINITY;
+    const float mn = fmaxf(m, sc), a = ex2(m - mn), e0 = ex2(sc - mn), e = e0 * vsc;
+    l = l * a + e0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = acc[i] * a + e * vf[i];
+    m = mn;
+  };
+  auto widen = [&](const uint4& w, float (&f)[16]) {
+    const uint32_t b[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) f[i] = q8_float(b[i >> 2], i & 3);
+  };
+
+  if (SELF && with_new && tid < 32) {
+    // warp 0: group 0 (lanes 0 .. LPK-1) holds the new key and value; all lanes go through the shuffles
+    const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 16;
+    const float* vp = kp + p.H * D;
+    float kn[16], vn[16];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = ld_cg_f4(kp + 4 * i), b = ld_cg_f4(vp + 4 * i);
+      const uint32_t k01 = pack_bf16(a.x, a.y), k23 = pack_bf16(a.z, a.w), v01 = pack_bf16(b.x, b.y), v23 = pack_bf16(b.z, b.w);
+      kn[4 * i] = bf16_lo(k01), kn[4 * i + 1] = bf16_hi(k01), kn[4 * i + 2] = bf16_lo(k23), kn[4 * i + 3] = bf16_hi(k23);
+      vn[4 * i] = bf16_lo(v01), vn[4 * i + 1] = bf16_hi(v01), vn[4 * i + 2] = bf16_lo(v23), vn[4 * i + 3] = bf16_hi(v23);
+    }
+    auto quantise = [&](const float (&f)[16], int8_t* dst, float* scale) {
+      float mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(f[i]));
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float sc = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f, inv = __fdiv_rn(1.f, sc);
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int qi = __float2int_rn(fminf(fmaxf(__fmul_rn(f[i], inv), -127.f), 127.f));
+        w[i >> 2] |= (uint32_t)(qi & 0xff) << ((i & 3) * 8);
+      }
+      if (grp == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        if (gl == 0) *scale = sc;
+      }
+    };
+    quantise(kn, const_cast<int8_t*>(k8) + (vec0 + n) * D + gl * 16, p.ks + vec0 + n);
+    quantise(vn, const_cast<int8_t*>(v8) + (vec0 + n) * D + gl * 16, p.vs + vec0 + n);
+    attend(kn, 1.f, vn, 1.f, grp == 0);
+  }
+
+  const int8_t* kb = k8 + vec0 * D + gl * 16;
+  const int8_t* vb = v8 + vec0 * D + gl * 16;
+  const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
+  for (int j0 = first; j0 < end; j0 += NG * U) {
+    const int j = j0 + (grp % (32 / LPK));
+    uint4 kk[U], vv[U];
+    float ksc[U], vsc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int jj = j + u * NG;
+      const bool ok = jj < end;
+      kk[u] = ok ? ld_stream16(kb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+      vv[u] = ok ? ld_stream16(vb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+      ksc[u] = ok ? __uint_as_float(ld_stream4(p.ks + vec0 + jj)) : 1.f;
+      vsc[u] = ok ? __uint_as_float(ld_stream4(p.vs + vec0 + jj)) : 1.f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (j0 + u * NG < end) {  // warp-uniform condition
+        float kf[16], vf[16];
+        widen(kk[u], kf), widen(vv[u], vf);
+        attend(kf, ksc[u], vf, vsc[u], j + u * NG < end);
+      }
+    }
+  }
+  ATTN_STAMP(3);
+  __syncthreads();  // the arrays may still be read by a previous pass
+  if (gl == 0) s_m[grp] = m, s_l[grp] = l;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s_acc[grp][gl * 16 + i] = acc[i];
+  __syncthreads();
+  M = -1e30f, L = 0.f, O = 0.f;
+  if (tid < D) {
+#pragma unroll 8
+    for (int gi = 0; gi < NG; ++gi) M = fmaxf(M, s_m[gi]);
+#pragma unroll 8
+    for (int gi = 0; gi < NG; ++gi) {
+      const float w = ex2(s_m[gi] - M);
+      L += w * s_l[gi];
+      O += w * s_acc[gi][tid];
+    }
+  }
+}
+
+template <int D, bool SELF, bool Q8>
+DEVI void attend_pass(const AttnArgs& p, int r, int s, int h, int n, int start, int end, bool with_new, float* s_m,
+                      float* s_l, float (*s_acc)[D + 4], float& M, float& L, float& O) {
+  if constexpr (Q8) attend_range_q8<D, SELF>(p, r, s, h, n, start, end, with_new, s_m, s_l, s_acc, M, L, O);
+  else attend_range<D, SELF>(p, r, s, h, n, start, end, with_new, s_m, s_l, s_acc, M, L, O);
+}
+
 template <int D>
 DEVI void store_out(const AttnArgs& p, int r, int h, float val) {
   const size_t o = (size_t)r * p.H * D + h * D + threadIdx.x;
@@ -175,9 +319,9 @@ DEVI void row_state(const AttnArgs& p, int r, bool report, int& s, int& n) {
   }
 }
 
-template <int D, bool SELF>
-__global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (D / 8);
+template <int D, bool SELF, bool Q8>
+__global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (Q8 ? D / 16 : D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ int s_last;
@@ -193,7 +337,7 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p
   ATTN_STAMP(2);
   const int chunk = (n + nsp - 1) / nsp, start = sp * chunk, end = min(n, start + chunk);
   float M, L, O;
-  attend_range<D, SELF>(p, r, s, h, n, start, end, sp == 0, s_m, s_l, s_acc, M, L, O);
+  attend_pass<D, SELF, Q8>(p, r, s, h, n, start, end, sp == 0, s_m, s_l, s_acc, M, L, O);
   if (nsp == 1) {
     if (tid < D) store_out<D>(p, r, h, O / L);
     ATTN_STAMP(7);
@@ -236,9 +380,9 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p
 // exchange.
 constexpr int PAIR_MAX_ROWS = 256;
 
-template <int D, bool SELF, bool TABLE>
-__global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (D / 8);
+template <int D, bool SELF, bool TABLE, bool Q8>
+__global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_pair_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (Q8 ? D / 16 : D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ float s_peer[D + 2];  // CTA 0: the partial its peer computed for the long row
@@ -285,7 +429,7 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
 
   float M, L, O;
   if (role == 0) {
-    attend_range<D, SELF>(p, r_long, s_long, h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
+    attend_pass<D, SELF, Q8>(p, r_long, s_long, h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
     if (helped) {
       cluster.sync();  // the peer's partial has landed
       if (tid < D) {
@@ -297,11 +441,11 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
     if (tid < D) store_out<D>(p, r_long, h, O / L);
   } else {
     if (!solo) {
-      attend_range<D, SELF>(p, r_short, s_short, h, n_short, 0, n_short, true, s_m, s_l, s_acc, M, L, O);
+      attend_pass<D, SELF, Q8>(p, r_short, s_short, h, n_short, 0, n_short, true, s_m, s_l, s_acc, M, L, O);
       if (tid < D) store_out<D>(p, r_short, h, O / L);
     }
     if (helped) {
-      attend_range<D, SELF>(p, r_long, s_long, h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
+      attend_pass<D, SELF, Q8>(p, r_long, s_long, h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
       float* peer = cluster.map_shared_rank(s_peer, 0);
       if (tid < D) peer[tid] = O;
       if (tid == 0) peer[D] = M, peer[D + 1] = L;
@@ -323,6 +467,63 @@ int pick_splits(int rows, int heads, int cap) {
 
 }  // namespace
 
+namespace {
+
+template <bool Q8>
+cudaError_t launch_attention(bool pair, bool table, int head_dim, int self, dim3 grid, cudaStream_t s, int pdl,
+                             const AttnArgs& p) {
+  const dim3 block(NTHREADS);
+#define B200_ATTN_CASE(D_, SELF_)                                                                                  \
+  if (head_dim == D_ && (self != 0) == SELF_) {                                                                    \
+    if (!pair) return launch_kernel(attention_kernel<D_, SELF_, Q8>, grid, block, 0, s, 0, pdl, p);                \
+    return table ? launch_kernel(attention_pair_kernel<D_, SELF_, true, Q8>, grid, block, 0, s, 2, pdl, p)         \
+                 : launch_kernel(attention_pair_kernel<D_, SELF_, false, Q8>, grid, block, 0, s, 2, pdl, p);       \
+  }
+  B200_ATTN_CASE(64, true)
+  B200_ATTN_CASE(64, false)
+  B200_ATTN_CASE(128, true)
+  B200_ATTN_CASE(128, false)
+#undef B200_ATTN_CASE
+  return cudaErrorInvalidValue;
+}
+
+// Shared by the entry points. sched != null: the paired kernel on a row schedule; else the paired kernel with its own
+// ranking for a large batch, or one CTA per (row, head, split). ks != null: int8 caches with per-vector scales.
+int run_attention(const char* what, int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                  float* ks, float* vs, const int32_t* n, const int32_t* sched, int slots, int heads, int head_dim,
+                  int cap, float scale, void* out, int out_kind, int rows, float* part, int32_t* count, int32_t* status,
+                  int pdl, void* stream) {
+  B200_REQUIRE(q && kcache && vcache && out && (sched || (active && n && status)), "%s: null pointer", what);
+  B200_REQUIRE((ks == nullptr) == (vs == nullptr), "%s: key and value scales go together", what);
+  B200_REQUIRE(head_dim == 64 || head_dim == 128, "%s: head_dim %d (64 or 128)", what, head_dim);
+  B200_REQUIRE(rows >= 1 && rows <= 65535 && heads >= 1 && cap >= 1, "%s: rows %d heads %d cap %d", what, rows, heads,
+               cap);
+  B200_REQUIRE(!sched || (rows <= PAIR_MAX_ROWS && ((uintptr_t)sched & 15) == 0),
+               "%s: schedule (rows <= %d, 16-byte aligned)", what, PAIR_MAX_ROWS);
+  B200_REQUIRE(ldq % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
+                   ((uintptr_t)vcache & 15) == 0, "%s: alignment", what);
+  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "%s: out_kind", what);
+  AttnArgs p{};
+  p.active = active, p.q = q, p.k = (__nv_bfloat16*)kcache, p.v = (__nv_bfloat16*)vcache, p.ks = ks, p.vs = vs;
+  p.n = n, p.sched = sched, p.out = out, p.part = part, p.count = count, p.status = status;
+  p.ldq = ldq, p.H = heads, p.cap = cap, p.slots = slots, p.out_kind = out_kind, p.rows = rows;
+  p.splits = (!sched && part && count) ? pick_splits(rows, heads, cap) : 1;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  // a large batch: rows paired long with short, two CTAs per pair and head
+  const bool pair = sched || (p.splits == 1 && rows * heads >= 512 && rows <= PAIR_MAX_ROWS);
+  const dim3 grid = pair ? dim3(2, heads, (rows + 1) / 2) : dim3(heads, rows, p.splits);
+#ifdef B200DEC_TIMELINE
+  p.stamps = timeline_next(grid.x * grid.y * grid.z, self ? 3000000 : 4000000);
+#endif
+  const cudaStream_t st = (cudaStream_t)stream;
+  const cudaError_t e = ks ? launch_attention<true>(pair, sched != nullptr, head_dim, self, grid, st, pdl, p)
+                           : launch_attention<false>(pair, sched != nullptr, head_dim, self, grid, st, pdl, p);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "%s launch: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
 extern "C" {
 
 int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim) {
@@ -332,81 +533,36 @@ int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim) {
 int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
                       const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                       int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream) {
-  B200_REQUIRE(active && q && kcache && vcache && n && out && status, "attention: null pointer");
-  B200_REQUIRE(head_dim == 64 || head_dim == 128, "attention: head_dim %d (64 or 128)", head_dim);
-  B200_REQUIRE(rows >= 1 && rows <= 65535 && heads >= 1 && cap >= 1, "attention: rows %d heads %d cap %d", rows,
-               heads, cap);
-  B200_REQUIRE(ldq % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
-                   ((uintptr_t)vcache & 15) == 0, "attention: alignment");
-  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "attention: out_kind");
-  AttnArgs p{};
-  p.active = active, p.q = q, p.k = (__nv_bfloat16*)kcache, p.v = (__nv_bfloat16*)vcache, p.n = n, p.out = out;
-  p.part = part, p.count = count, p.status = status;
-  p.ldq = ldq, p.H = heads, p.cap = cap, p.slots = slots, p.out_kind = out_kind, p.rows = rows;
-  p.splits = (part && count) ? pick_splits(rows, heads, cap) : 1;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t e;
-  if (p.splits == 1 && rows * heads >= 512 && rows <= PAIR_MAX_ROWS) {
-    // a large batch: rows paired long with short, two CTAs per pair and head
-    const dim3 grid(2, heads, (rows + 1) / 2);
-#ifdef B200DEC_TIMELINE
-    p.stamps = timeline_next(2 * heads * ((rows + 1) / 2), self ? 3000000 : 4000000);
-#endif
-    if (head_dim == 64)
-      e = self ? launch_kernel(attention_pair_kernel<64, true, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-               : launch_kernel(attention_pair_kernel<64, false, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
-    else
-      e = self ? launch_kernel(attention_pair_kernel<128, true, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-               : launch_kernel(attention_pair_kernel<128, false, false>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
-    if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention launch: %s", cudaGetErrorString(e));
-    return 0;
-  }
-  const dim3 grid(heads, rows, p.splits);
-#ifdef B200DEC_TIMELINE
-  p.stamps = timeline_next(heads * rows * p.splits, self ? 3000000 : 4000000);
-#endif
-  if (head_dim == 64)
-    e = self ? launch_kernel(attention_kernel<64, true>, grid, dim3(NTHREADS), 0, s, 0, pdl, p)
-             : launch_kernel(attention_kernel<64, false>, grid, dim3(NTHREADS), 0, s, 0, pdl, p);
-  else
-    e = self ? launch_kernel(attention_kernel<128, true>, grid, dim3(NTHREADS), 0, s, 0, pdl, p)
-             : launch_kernel(attention_kernel<128, false>, grid, dim3(NTHREADS), 0, s, 0, pdl, p);
-  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention launch: %s", cudaGetErrorString(e));
-  return 0;
+  return run_attention("attention", self, active, q, ldq, kcache, vcache, nullptr, nullptr, n, nullptr, slots, heads,
+                       head_dim, cap, scale, out, out_kind, rows, part, count, status, pdl, stream);
+}
+
+int b200dec_attention_q8(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                         float* kscale, float* vscale, const int32_t* n, int slots, int heads, int head_dim, int cap,
+                         float scale, void* out, int out_kind, int rows, float* part, int32_t* count, int32_t* status,
+                         int pdl, void* stream) {
+  B200_REQUIRE(kscale && vscale, "attention_q8: null scales");
+  return run_attention("attention_q8", self, active, q, ldq, kcache, vcache, kscale, vscale, n, nullptr, slots, heads,
+                       head_dim, cap, scale, out, out_kind, rows, part, count, status, pdl, stream);
+}
+
+int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
+                             int heads, int head_dim, int cap, float scale, void* out, int out_kind, int rows, int pdl,
+                             void* stream) {
+  B200_REQUIRE(sched, "attention_paired: null schedule");
+  return run_attention("attention_paired", self, nullptr, q, ldq, kcache, vcache, nullptr, nullptr, nullptr, sched, 0,
+                       heads, head_dim, cap, scale, out, out_kind, rows, nullptr, nullptr, nullptr, pdl, stream);
+}
+
+int b200dec_attention_paired_q8(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
+                                float* kscale, float* vscale, int heads, int head_dim, int cap, float scale, void* out,
+                                int out_kind, int rows, int pdl, void* stream) {
+  B200_REQUIRE(sched && kscale && vscale, "attention_paired_q8: null schedule or scales");
+  return run_attention("attention_paired_q8", self, nullptr, q, ldq, kcache, vcache, kscale, vscale, nullptr, sched, 0,
+                       heads, head_dim, cap, scale, out, out_kind, rows, nullptr, nullptr, nullptr, pdl, stream);
 }
 
 }  // extern "C"
-
-extern "C" int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache,
-                                        void* vcache, int heads, int head_dim, int cap, float scale, void* out,
-                                        int out_kind, int rows, int pdl, void* stream) {
-  B200_REQUIRE(sched && q && kcache && vcache && out, "attention_paired: null pointer");
-  B200_REQUIRE(head_dim == 64 || head_dim == 128, "attention_paired: head_dim %d (64 or 128)", head_dim);
-  B200_REQUIRE(rows >= 1 && rows <= PAIR_MAX_ROWS && heads >= 1 && cap >= 1, "attention_paired: rows %d heads %d cap %d",
-               rows, heads, cap);
-  B200_REQUIRE(ldq % 4 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
-                   ((uintptr_t)vcache & 15) == 0 && ((uintptr_t)sched & 15) == 0, "attention_paired: alignment");
-  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "attention_paired: out_kind");
-  AttnArgs p{};
-  p.sched = sched, p.q = q, p.k = (__nv_bfloat16*)kcache, p.v = (__nv_bfloat16*)vcache, p.out = out;
-  p.ldq = ldq, p.H = heads, p.cap = cap, p.out_kind = out_kind, p.rows = rows, p.splits = 1;
-  p.scale_log2 = scale * 1.4426950408889634f;
-  const dim3 grid(2, heads, (rows + 1) / 2);
-#ifdef B200DEC_TIMELINE
-  p.stamps = timeline_next(2 * heads * ((rows + 1) / 2), self ? 3000000 : 4000000);
-#endif
-  cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t e;
-  if (head_dim == 64)
-    e = self ? launch_kernel(attention_pair_kernel<64, true, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-             : launch_kernel(attention_pair_kernel<64, false, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
-  else
-    e = self ? launch_kernel(attention_pair_kernel<128, true, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p)
-             : launch_kernel(attention_pair_kernel<128, false, true>, grid, dim3(NTHREADS), 0, s, 2, pdl, p);
-  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention_paired launch: %s", cudaGetErrorString(e));
-  return 0;
-}
 
 // ---- the same attention for callers that cannot hand over scratch memory ---------------------------------------------
 //

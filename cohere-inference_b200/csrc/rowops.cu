@@ -288,6 +288,44 @@ __global__ void scatter_kv_kernel(const float* __restrict__ kv, const int* __res
       make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
 }
 
+// The same into int8 caches with one fp32 scale per head vector (the reference's int8 mode, kernels/csrc/
+// decoder_ops.cu:176-204): the values are rounded to bf16 first (what the bf16 cache would hold), then
+// scale = absmax / 127 (1 for a zero vector), q = rint(clamp(x * (1 / scale), +-127)). D / 8 threads per vector.
+__global__ void scatter_kv_q8_kernel(const float* __restrict__ kv, const int* __restrict__ slot_of,
+                                     const int* __restrict__ frame_of, int8_t* ck, int8_t* cv, float* cks, float* cvs,
+                                     int nrows, int L, int S1, int H, int D, int T) {
+  const int d8n = D / 8, chunks = L * 2 * H * d8n;  // d8n = 8 or 16 threads per vector, aligned inside a warp
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = idx < (size_t)nrows * chunks;
+  const int row = live ? idx / chunks : 0, c = live ? idx % chunks : 0;
+  const int d8 = c % d8n, h = (c / d8n) % H, kvi = (c / (d8n * H)) % 2, l = c / (d8n * H * 2);
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (live) {
+    const float* src = kv + (size_t)row * chunks * 8 + (size_t)c * 8;
+    const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+    const uint32_t w[4] = {pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[2 * i] = bf16_lo(w[i]), f[2 * i + 1] = bf16_hi(w[i]);
+  }
+  float mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
+  for (int o = 1; o < d8n; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (!live) return;
+  const int slot = slot_of[row], frame = frame_of[row];
+  if (slot < 0 || slot >= S1 || frame < 0 || frame >= T) return;
+  const float sc = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f, inv = __fdiv_rn(1.f, sc);
+  uint32_t w[2] = {0, 0};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int q = __float2int_rn(fminf(fmaxf(__fmul_rn(f[i], inv), -127.f), 127.f));
+    w[i >> 2] |= (uint32_t)(q & 0xff) << ((i & 3) * 8);
+  }
+  const size_t vec = (((size_t)l * S1 + slot) * H + h) * T + frame;
+  *reinterpret_cast<uint2*>((kvi ? cv : ck) + vec * D + d8 * 8) = make_uint2(w[0], w[1]);
+  if (d8 == 0) (kvi ? cvs : cks)[vec] = sc;
+}
+
 // ---- packers -------------------------------------------------------------------------------------------------------
 
 __constant__ int c_w8_perm[16] = {0, 1, 8, 9, 2, 3, 10, 11, 4, 5, 12, 13, 6, 7, 14, 15};
@@ -469,6 +507,19 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
       kv, slot_of, frame_of, (__nv_bfloat16*)ck, (__nv_bfloat16*)cv, nrows, layers, slots_plus_1, heads, head_dim,
       frames);
   return check_launch("scatter_kv");
+}
+
+int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
+                          float* ck_scale, float* cv_scale, int nrows, int layers, int slots_plus_1, int heads,
+                          int head_dim, int frames, void* stream) {
+  B200_REQUIRE(kv && slot_of && frame_of && ck && cv && ck_scale && cv_scale, "scatter_kv_q8: null pointer");
+  B200_REQUIRE((head_dim == 64 || head_dim == 128) && nrows >= 0, "scatter_kv_q8: head_dim %d (64 or 128)", head_dim);
+  if (nrows == 0) return 0;
+  const size_t total = (size_t)nrows * layers * 2 * heads * (head_dim / 8);  // a multiple of 8 or 16: whole vectors
+  scatter_kv_q8_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      kv, slot_of, frame_of, (int8_t*)ck, (int8_t*)cv, ck_scale, cv_scale, nrows, layers, slots_plus_1, heads, head_dim,
+      frames);
+  return check_launch("scatter_kv_q8");
 }
 
 int b200dec_quantize_rows(const float* w, int n, int k, int8_t* q, float* scale, void* stream) {

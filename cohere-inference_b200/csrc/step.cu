@@ -44,6 +44,7 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   B200_REQUIRE(rows >= 1 && row0 >= 0 && row0 + rows <= 128, "step: rows %d + %d outside 0..128", row0, rows);
   B200_REQUIRE(pl->heads * pl->head_dim == D_MODEL, "step: heads * head_dim must be %d", D_MODEL);
   B200_REQUIRE(pl->vocab == pl->head.n, "step: vocab %d vs head rows %d", pl->vocab, pl->head.n);
+  B200_REQUIRE(!(pl->kv_int8 && pl->attn_ring), "step: the ring attention kernel reads bf16 caches only");
   const int hd = pl->heads * pl->head_dim;
   // which launches carry the programmatic-dependent-launch attribute: bit 0 a projection (or the pick) that follows a
   // projection, bit 1 the attention kernels, bit 2 a projection that follows an attention kernel
@@ -79,7 +80,14 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     const b200dec_layer& ly = pl->layer[i];
     B200_TRY(linear_impl(&ly.qkv, x, pl->a_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream));
-    if (paired)
+    if (pl->kv_int8 && paired)
+      B200_TRY(b200dec_attention_paired_q8(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, ly.self_ks, ly.self_vs,
+                                           pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
+    else if (pl->kv_int8)
+      B200_TRY(b200dec_attention_q8(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, ly.self_ks, ly.self_vs, pl->pos,
+                                    pl->slots, pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part,
+                                    attn_count, pl->status, pdl_attn, stream));
+    else if (paired)
       B200_TRY(b200dec_attention_paired(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, pl->heads, pl->head_dim,
                                         pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
     else
@@ -90,7 +98,15 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
                          pdl_after, stream));
     B200_TRY(linear_impl(&ly.cq, x, pl->a_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
                          stream));
-    if (paired)
+    if (pl->kv_int8 && paired)
+      B200_TRY(b200dec_attention_paired_q8(0, sched_cross, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, ly.cross_ks,
+                                           ly.cross_vs, pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows,
+                                           pdl_attn, stream));
+    else if (pl->kv_int8)
+      B200_TRY(b200dec_attention_q8(0, active, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, ly.cross_ks, ly.cross_vs,
+                                    pl->cross_len, pl->slots, pl->heads, pl->head_dim, pl->frames, scale, att, ok_a,
+                                    rows, attn_part, attn_count, pl->status, pdl_attn, stream));
+    else if (paired)
       B200_TRY(b200dec_attention_paired(0, sched_cross, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, pl->heads,
                                         pl->head_dim, pl->frames, scale, att, ok_a, rows, pdl_attn, stream));
     else

@@ -35,14 +35,14 @@ class Norm(C.Structure):
 class Layer(C.Structure):
     _fields_ = [("ln1", Norm), ("ln2", Norm), ("ln3", Norm), ("qkv", Weight), ("o", Weight), ("cq", Weight),
                 ("co", Weight), ("fc1", Weight), ("fc2", Weight), ("self_k", vp), ("self_v", vp), ("cross_k", vp),
-                ("cross_v", vp)]
+                ("cross_v", vp), ("self_ks", vp), ("self_vs", vp), ("cross_ks", vp), ("cross_vs", vp)]
 
 
 class Plan(C.Structure):
     _fields_ = [("layers", i32), ("heads", i32), ("head_dim", i32), ("act", i32),
                 ("slots", i32), ("seq", i32), ("frames", i32), ("vocab", i32),
                 ("max_prompt", i32), ("out_cols", i32), ("pad", i32), ("eos", i32),
-                ("a_kind", i32), ("max_pos", i32), ("head_a_kind", i32), ("pdl", i32), ("attn_ring", i32), ("_pad0", i32),
+                ("a_kind", i32), ("max_pos", i32), ("head_a_kind", i32), ("pdl", i32), ("attn_ring", i32), ("kv_int8", i32),
                 ("embed", vp), ("pos_table", vp), ("emb_ln", Norm), ("final_ln", Norm), ("layer", C.POINTER(Layer)),
                 ("head", Weight),
                 ("active", vp), ("tok", vp), ("pos", vp), ("plen", vp), ("limit", vp), ("cross_len", vp),
@@ -81,6 +81,12 @@ PROTOTYPES = {
     "b200dec_attention": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
                                     vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
     "b200dec_attention_scratch_floats": (i64, [C.c_int, C.c_int, C.c_int]),
+    "b200dec_attention_q8": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       f32, vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
+    "b200dec_attention_paired_q8": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, f32, vp,
+                                              C.c_int, C.c_int, C.c_int, vp]),
+    "b200dec_scatter_kv_q8": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                        vp]),
     "b200dec_row_schedule": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]),
     "b200dec_attention_paired": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, f32, vp,
                                            C.c_int, C.c_int, C.c_int, vp]),

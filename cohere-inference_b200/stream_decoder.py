@@ -59,7 +59,7 @@ class StreamDecoder:
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 0, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
-                 head_umma: bool = True):
+                 head_umma: bool = True, kv_int8: bool = False):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -118,11 +118,21 @@ class StreamDecoder:
             assert self.seq <= self.max_pos, "positions exceed the learned position table"
             self.frames = int(model.model.encoder._get_subsampling_output_length(
                 torch.tensor([int(max_audio_s * 100) + 1])).item())
-            bf = dict(device=dev, dtype=torch.bfloat16)
+            # kv_int8: keys and values as int8 with one fp32 scale per head vector, the format of the reference's int8
+            # mode (stream_decoder.py:102-115); otherwise bf16
+            self.kv_int8 = bool(kv_int8)
+            assert not (self.kv_int8 and attn_ring), "the ring attention kernel reads bf16 caches only"
+            bf = dict(device=dev, dtype=torch.int8 if self.kv_int8 else torch.bfloat16)
             self.self_k = torch.zeros(L, S + 1, self.h, self.seq, self.d, **bf)
             self.self_v = torch.zeros_like(self.self_k)
             self.cross_k = torch.zeros(L, S + 1, self.h, self.frames, self.d, **bf)
             self.cross_v = torch.zeros_like(self.cross_k)
+            self.self_ks = self.self_vs = self.cross_ks = self.cross_vs = None
+            if self.kv_int8:
+                self.self_ks = torch.ones(L, S + 1, self.h, self.seq, device=dev)
+                self.self_vs = torch.ones_like(self.self_ks)
+                self.cross_ks = torch.ones(L, S + 1, self.h, self.frames, device=dev)
+                self.cross_vs = torch.ones_like(self.cross_ks)
             i32 = dict(device=dev, dtype=torch.int32)
             self.cross_len = torch.ones(S + 1, **i32)
             self.tok = torch.full((S + 1,), self.pad, device=dev, dtype=torch.long)
@@ -181,12 +191,15 @@ class StreamDecoder:
             s.fc1, s.fc2 = ly.fc1.struct(), ly.fc2.struct()
             s.self_k, s.self_v = nv.ptr(self.self_k[i]), nv.ptr(self.self_v[i])
             s.cross_k, s.cross_v = nv.ptr(self.cross_k[i]), nv.ptr(self.cross_v[i])
+            if self.kv_int8:
+                s.self_ks, s.self_vs = nv.ptr(self.self_ks[i]), nv.ptr(self.self_vs[i])
+                s.cross_ks, s.cross_vs = nv.ptr(self.cross_ks[i]), nv.ptr(self.cross_vs[i])
         p = nv.Plan()
         p.layers, p.heads, p.head_dim, p.act = L, self.h, self.d, self.act
         p.slots, p.seq, p.frames, p.vocab = self.slots, self.seq, self.frames, self.vocab
         p.max_prompt, p.out_cols, p.pad, p.eos = self.max_prompt, self.out.shape[1], self.pad, self.eos
         p.a_kind, p.max_pos, p.head_a_kind, p.pdl = self.a_kind, self.max_pos, self.head_a_kind, int(self.pdl)
-        p.attn_ring = int(self.attn_ring)
+        p.attn_ring, p.kv_int8 = int(self.attn_ring), int(self.kv_int8)
         p.embed, p.pos_table = nv.ptr(self.embed), nv.ptr(self.pos_table)
         p.emb_ln, p.final_ln = nv.norm(*self.emb_ln), nv.norm(*self.final_ln)
         p.layer = C.cast(self._layer_structs, C.POINTER(nv.Layer))
@@ -286,9 +299,15 @@ class StreamDecoder:
         slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lengths))
         frame_of = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths])
         slot_of, frame_of = slot_of.to(self.device, non_blocking=True), frame_of.to(self.device, non_blocking=True)
-        nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
-                                             nv.ptr(self.cross_v), kv.shape[0], len(self.layers), self.slots + 1,
-                                             self.h, self.d, self.frames, nv.stream_ptr()))
+        if self.kv_int8:
+            nv.check(nv.lib().b200dec_scatter_kv_q8(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
+                                                    nv.ptr(self.cross_v), nv.ptr(self.cross_ks), nv.ptr(self.cross_vs),
+                                                    kv.shape[0], len(self.layers), self.slots + 1, self.h, self.d,
+                                                    self.frames, nv.stream_ptr()))
+        else:
+            nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
+                                                 nv.ptr(self.cross_v), kv.shape[0], len(self.layers), self.slots + 1,
+                                                 self.h, self.d, self.frames, nv.stream_ptr()))
         kv.record_stream(torch.cuda.current_stream())
 
     def admit(self, slots: list[int], prompts: list[torch.Tensor], frames: list[int],
@@ -346,4 +365,6 @@ class StreamDecoder:
         pad = (rows or len(positions)) - len(positions)
         kv = sum((int(p) + 1) + int(t) for p, t in zip(positions, frames)) + pad * 2
         n = len(positions) + pad
-        return self.weight_bytes + L * 2 * d * 2 * kv + n * L * 2 * d * 2 + n * 2 * d * 2
+        # bytes per cached or appended vector element: 2 (bf16), or 1 + 4 / D (int8 and its share of the vector's scale)
+        b_kv = 1 + 4 / self.d if self.kv_int8 else 2
+        return int(self.weight_bytes + L * 2 * d * b_kv * kv + n * L * 2 * d * b_kv + n * 2 * d * 2)

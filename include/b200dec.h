@@ -54,10 +54,14 @@ typedef struct b200dec_norm {
 typedef struct b200dec_layer {
   b200dec_norm ln1, ln2, ln3;
   b200dec_weight qkv, o, cq, co, fc1, fc2;
-  void* self_k;   /* bf16 (slots + 1, H, seq, D) */
+  void* self_k;   /* bf16, or int8 when the plan's kv_int8 is set, (slots + 1, H, seq, D) */
   void* self_v;
-  const void* cross_k; /* bf16 (slots + 1, H, frames, D) */
+  const void* cross_k; /* bf16 or int8 (slots + 1, H, frames, D) */
   const void* cross_v;
+  float* self_ks;      /* kv_int8: one fp32 scale per cached vector, (slots + 1, H, seq); else NULL */
+  float* self_vs;
+  float* cross_ks;     /* (slots + 1, H, frames) */
+  float* cross_vs;
 } b200dec_layer;
 
 /* Everything one decoding step touches. Replaces the argument lists of StreamDecoder._step
@@ -70,7 +74,9 @@ typedef struct b200dec_plan {
   int32_t head_a_kind, pdl;                  /* operand precision of the vocabulary projection; pdl: which launches are
                                                 programmatic (1 projection after projection, 2 attention, 4 projection
                                                 after attention) */
-  int32_t attn_ring, _pad0;                  /* != 0: the attention kernels are b200dec_attention_ring */
+  int32_t attn_ring, kv_int8;                /* attn_ring != 0: the attention kernels are b200dec_attention_ring;
+                                                kv_int8 != 0: int8 caches with per-vector scales (the layers'
+                                                self_ks .. cross_vs), attention by the *_q8 entry points */
   const void* embed;  /* bf16 (vocab, 1024) */
   const void* pos_table; /* bf16 (max_pos, 1024) */
   b200dec_norm emb_ln, final_ln;
@@ -179,6 +185,15 @@ int b200dec_attention(int self, const int32_t* active, const float* q, int ldq, 
                       const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                       int out_kind, int rows, float* part, int32_t* count, int32_t* status, int pdl, void* stream);
 int64_t b200dec_attention_scratch_floats(int rows, int heads, int head_dim);
+/* b200dec_attention over int8 caches (slots + 1, H, cap, D) with one fp32 scale per cached key vector and value
+ * vector (slots + 1, H, cap): x ~ q * scale, scale = absmax / 127 (1 for a zero vector), q = rint(clamp(x / scale)).
+ * self != 0 rounds the row's new key and value to bf16, writes their int8 form and scales at n[s], and attends them
+ * in this step as the bf16 values. Replaces dec_attention_q8 (kernels/csrc/decoder_ops.cu:263-290;
+ * dec_attn.cuh:38-63, 100-106, 116-152). */
+int b200dec_attention_q8(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
+                         float* kscale, float* vscale, const int32_t* n, int slots, int heads, int head_dim, int cap,
+                         float scale, void* out, int out_kind, int rows, float* part, int32_t* count, int32_t* status,
+                         int pdl, void* stream);
 /* The step's rows ranked by decreasing length, for b200dec_attention_paired: sched_self from pos[slot] (keys in the
  * self cache), sched_cross from cross_len[slot] (encoder frames); either table may be NULL. Entry i of a table is
  * int32 {row, slot, length, 0} of the row of rank i (ties by row), lengths clamped into 0..seq-1 / 1..frames and slots
@@ -195,6 +210,10 @@ int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_
 int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
                              int heads, int head_dim, int cap, float scale, void* out, int out_kind, int rows,
                              int pdl, void* stream);
+/* The same over int8 caches (see b200dec_attention_q8). */
+int b200dec_attention_paired_q8(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
+                                float* kscale, float* vscale, int heads, int head_dim, int cap, float scale, void* out,
+                                int out_kind, int rows, int pdl, void* stream);
 /* The same operation, arguments and workspace as b200dec_attention (rows <= 128) by a persistent kernel: two CTAs
  * per SM, one producer lane streaming (row, head) caches through a shared-memory ring with cp.async.bulk and
  * mbarriers, four consumer warps. Smaller footprint per SM; see csrc/attention_ring.cu. */
@@ -216,6 +235,11 @@ int b200dec_attention_static(int self, const int32_t* active, const float* q, in
  * 316-327). */
 int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
                        int nrows, int layers, int slots_plus_1, int heads, int head_dim, int frames, void* stream);
+/* The same into int8 caches with fp32 scales (L, slots + 1, H, frames): every head vector is rounded to bf16, then
+ * quantised as in b200dec_attention_q8. Replaces dec_scatter_kv_q8 (kernels/csrc/decoder_ops.cu:175-204). */
+int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
+                          float* ck_scale, float* cv_scale, int nrows, int layers, int slots_plus_1, int heads,
+                          int head_dim, int frames, void* stream);
 /* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
  * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
 int b200dec_step(const b200dec_plan* plan, int rows, void* stream);

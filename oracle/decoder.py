@@ -111,9 +111,29 @@ class OracleConfig:
                    getattr(cfg, "layer_norm_eps", 1e-5), cfg.pad_token_id, cfg.eos_token_id)
 
 
+def kv_int8(a: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """The reference's int8 cache format (kernels/csrc/dec_attn.cuh:46-63, decoder_ops.cu:190-203): per vector along
+    the last axis scale = absmax / 127 (1 for a zero vector), q = rint(clamp(x * (1 / scale), +-127)), all in fp32,
+    rint = half to even. Returns (q int8, scale fp32 with the last axis kept at length 1)."""
+    a = np.asarray(a, dtype=F32)
+    mx = np.abs(a).max(-1, keepdims=True).astype(F32)
+    sc = np.where(mx > 0, (mx / F32(127)).astype(F32), F32(1)).astype(F32)
+    inv = (F32(1) / sc).astype(F32)
+    q = np.rint(np.clip((a * inv).astype(F32), F32(-127), F32(127)))
+    return q.astype(np.int8), sc
+
+
+def kv_int8_round(a: np.ndarray) -> np.ndarray:
+    """What an int8 cache gives back for a vector that was rounded to bf16 and then quantised: q * scale in fp32."""
+    q, sc = kv_int8(bf16_round(a))
+    return (q.astype(F32) * sc).astype(F32)
+
+
 class OracleDecoder:
     """One decoding step over explicit per-sequence caches. kv_round: "bf16" rounds keys and values to bf16 when they
-    enter a cache (what a bf16 KV cache holds); None keeps fp32."""
+    enter a cache (what a bf16 KV cache holds); "int8" stores the int8 form of the bf16-rounded vector (kv_int8) and,
+    as the reference does, attends a row's new key and value in the step that appends them as the bf16 values; None
+    keeps fp32."""
 
     def __init__(self, weights: dict, cfg: OracleConfig, kv_round: str | None = None):
         self.w, self.cfg, self.kv_round = weights, cfg, kv_round
@@ -129,6 +149,8 @@ class OracleDecoder:
         return layer_norm(x, self.w[prefix + ".weight"], self.w[prefix + ".bias"], self.cfg.eps)
 
     def _store(self, a):
+        if self.kv_round == "int8":
+            return kv_int8_round(a)
         return bf16_round(a) if self.kv_round == "bf16" else a.astype(F32)
 
     def cross_kv(self, memory: np.ndarray) -> list[tuple[np.ndarray, np.ndarray]]:
@@ -168,9 +190,15 @@ class OracleDecoder:
             for r in range(B):
                 ks, vs = self_caches[r][i]
                 assert len(ks) == pos[r], "self cache length must equal the position being fed"
-                ks.append(self._store(k[r].reshape(c.heads, c.head_dim)))
-                vs.append(self._store(v[r].reshape(c.heads, c.head_dim)))
-                a[r] = self._attend(q[r].reshape(c.heads, c.head_dim), np.stack(ks, 1), np.stack(vs, 1))
+                kn, vn = k[r].reshape(c.heads, c.head_dim), v[r].reshape(c.heads, c.head_dim)
+                ks.append(self._store(kn))
+                vs.append(self._store(vn))
+                if self.kv_round == "int8":  # this step sees the new pair before quantisation
+                    kk = np.stack(ks[:-1] + [bf16_round(kn)], 1)
+                    vv = np.stack(vs[:-1] + [bf16_round(vn)], 1)
+                else:
+                    kk, vv = np.stack(ks, 1), np.stack(vs, 1)
+                a[r] = self._attend(q[r].reshape(c.heads, c.head_dim), kk, vv)
             x = x + self._lin(a, p + ".self_attn.o_proj")
             h = self._ln(x, p + ".post_attention_layernorm")
             q = self._lin(h, p + ".encoder_attn.q_proj")

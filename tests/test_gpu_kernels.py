@@ -468,6 +468,109 @@ def test_row_schedule_reports_bad_state(nv):
     np.testing.assert_array_equal(sched.cpu().numpy(), [[2, 1, 100, 0], [0, 0, 5, 0], [1, 3, 1, 0]])
 
 
+def _kv8(a):
+    from oracle.decoder import kv_int8
+    return kv_int8(bf16_round(a))
+
+
+@pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
+def test_scatter_kv_q8_bit_exact(nv, H, D):
+    """int8 cross caches and their scales equal the quantiser of the reference's int8 mode applied to the bf16-rounded
+    vectors, bit for bit (incl. an all-zero vector: scale 1)."""
+    rng = np.random.default_rng(D)
+    L, S1, T, rows = 3, 4, 7, 9
+    kv = (rng.standard_normal((rows, L * 2 * H * D)) * rng.uniform(0.01, 30, (rows, 1))).astype(np.float32)
+    kv[2, :D] = 0.0
+    slot_of = rng.integers(0, S1, rows).astype(np.int32)
+    frame_of = np.arange(rows, dtype=np.int32) % T
+    (slot_of[7], frame_of[7]), (slot_of[8], frame_of[8]) = (1, 0), (2, 0)  # distinct (slot, frame) pairs
+    pairs = set()
+    for i in range(rows):
+        while (slot_of[i], frame_of[i]) in pairs:
+            frame_of[i] = (frame_of[i] + 1) % T
+        pairs.add((slot_of[i], frame_of[i]))
+    ck = torch.zeros(L, S1, H, T, D, dtype=torch.int8, device="cuda")
+    cv = torch.zeros_like(ck)
+    cks = torch.full((L, S1, H, T), -1.0, device="cuda")
+    cvs = torch.full_like(cks, -1.0)
+    kv_d, so_d, fo_d = cuda(kv), cuda(slot_of), cuda(frame_of)
+    nv.check(nv.lib().b200dec_scatter_kv_q8(nv.ptr(kv_d), nv.ptr(so_d), nv.ptr(fo_d), nv.ptr(ck), nv.ptr(cv), nv.ptr(cks),
+                                            nv.ptr(cvs), rows, L, S1, H, D, T, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    x = kv.reshape(rows, L, 2, H, D)
+    for i in range(rows):
+        for which, (c, cs) in enumerate(((ck, cks), (cv, cvs))):
+            q, sc = _kv8(x[i, :, which])  # (L, H, D), (L, H, 1)
+            assert np.array_equal(c[:, slot_of[i], :, frame_of[i]].cpu().numpy(), q)
+            assert np.array_equal(cs[:, slot_of[i], :, frame_of[i]].cpu().numpy(), sc[..., 0])
+
+
+@pytest.mark.parametrize("H,D", [(16, 64), (8, 128)])
+@pytest.mark.parametrize("rows", [3, 41])   # one CTA per (row, head, split); rows paired in clusters
+@pytest.mark.parametrize("self_", [0, 1])
+@pytest.mark.parametrize("paired", [False, True])
+def test_attention_q8(nv, H, D, rows, self_, paired):
+    """Attention over int8 caches vs fp64 on the dequantised caches; the appended key and value are stored in the
+    reference's int8 form (bit-exact) and attended in this step as their bf16 values."""
+    if paired and rows < 41:
+        pytest.skip("the schedule-driven kernel is for large batches")
+    cap = 200
+    rng = np.random.default_rng(rows + H + self_)
+    S = rows + 2
+    kq = rng.integers(-127, 128, (S + 1, H, cap, D)).astype(np.int8)
+    vq = rng.integers(-127, 128, (S + 1, H, cap, D)).astype(np.int8)
+    ksc = rng.uniform(0.002, 0.03, (S + 1, H, cap)).astype(np.float32)
+    vsc = rng.uniform(0.002, 0.03, (S + 1, H, cap)).astype(np.float32)
+    active = rng.permutation(S)[:rows].astype(np.int32)
+    n = rng.integers(0 if self_ else 1, cap - 1, S + 1).astype(np.int32)
+    n[active[0]] = 0 if self_ else 1
+    n[active[1]] = cap - 1 if self_ else cap
+    ld = 3 * H * D if self_ else H * D
+    q = rng.standard_normal((rows, ld)).astype(np.float32)
+    kd, vd, ksd, vsd = cuda(kq), cuda(vq), cuda(ksc), cuda(vsc)
+    lib = nv.lib()
+    part = torch.zeros(lib.b200dec_attention_scratch_floats(rows, H, D), device="cuda")
+    count = torch.zeros(rows * H, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sched = torch.zeros(rows, 4, dtype=torch.int32, device="cuda")
+    out = torch.zeros(rows, H * D, device="cuda")
+    scale = D ** -0.5
+    a_d, q_d, n_d = cuda(active), cuda(q), cuda(n)
+    if paired:
+        nv.check(lib.b200dec_row_schedule(nv.ptr(a_d), nv.ptr(n_d) if self_ else None, None if self_ else nv.ptr(n_d), S,
+                                          cap, cap, rows, nv.ptr(sched) if self_ else None,
+                                          None if self_ else nv.ptr(sched), nv.ptr(status), nv.stream_ptr()))
+        nv.check(lib.b200dec_attention_paired_q8(self_, nv.ptr(sched), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), nv.ptr(ksd),
+                                                 nv.ptr(vsd), H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, 0,
+                                                 nv.stream_ptr()))
+    else:
+        nv.check(lib.b200dec_attention_q8(self_, nv.ptr(a_d), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), nv.ptr(ksd),
+                                          nv.ptr(vsd), nv.ptr(n_d), S, H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows,
+                                          nv.ptr(part), nv.ptr(count), nv.ptr(status), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(count.abs().sum().item()) == 0
+    got = out.cpu().numpy()
+    k_after, ks_after = kd.cpu().numpy(), ksd.cpu().numpy()
+    v_after, vs_after = vd.cpu().numpy(), vsd.cpu().numpy()
+    kf = kq.astype(np.float32) * ksc[..., None]
+    vf = vq.astype(np.float32) * vsc[..., None]
+    for r in range(rows):
+        s = active[r]
+        for h in range(H):
+            qq = q[r, h * D:(h + 1) * D]
+            if self_:
+                kn = bf16_round(q[r, (H + h) * D:(H + h + 1) * D])
+                vn = bf16_round(q[r, (2 * H + h) * D:(2 * H + h + 1) * D])
+                (kq8, ks8), (vq8, vs8) = _kv8(kn), _kv8(vn)
+                assert np.array_equal(k_after[s, h, n[s]], kq8) and ks_after[s, h, n[s]] == ks8[0]
+                assert np.array_equal(v_after[s, h, n[s]], vq8) and vs_after[s, h, n[s]] == vs8[0]
+                K = np.concatenate([kf[s, h, :n[s]], kn[None]])
+                V = np.concatenate([vf[s, h, :n[s]], vn[None]])
+            else:
+                K, V = kf[s, h, :n[s]], vf[s, h, :n[s]]
+            np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=3e-5, rtol=1e-4)
+
+
 def test_pick_semantics(nv):
     """dec_pick's bookkeeping: forced prompt tokens, greedy after it, end at eos or the limit, dummy and finished rows
     untouched, ties to the lowest index."""

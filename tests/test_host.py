@@ -36,7 +36,7 @@ def test_library_exports_every_declared_symbol():
 def test_structs_match_header_sizes():
     from cohere_inference_b200 import native
     assert ctypes.sizeof(native.Weight) == 72 and ctypes.sizeof(native.Norm) == 24  # 6 pointers + 5 ints, padded
-    assert ctypes.sizeof(native.Layer) == 3 * 24 + 6 * 72 + 4 * 8
+    assert ctypes.sizeof(native.Layer) == 3 * 24 + 6 * 72 + 8 * 8
 
 
 def test_missing_library_fails_loudly(monkeypatch):

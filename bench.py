@@ -89,6 +89,16 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+_RESULT_OUT = None
+
+
+def emit(text: str, flush: bool = True) -> None:
+    """The result line, on the process's original stdout (see main: everything else is sent to stderr)."""
+    out = _RESULT_OUT or sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
 def make_inputs(seed: int):
     rng = np.random.default_rng(seed)
     lens = rng.integers(FRAMES[0], FRAMES[1] + 1, BATCH).tolist()
@@ -257,6 +267,8 @@ def run_ours(args) -> None:
                        "weights": "seed-0 random init N(0, 0.02)"},
             "p50_step_ms": round(p50, 4),
             "tokens_per_s_per_gpu": round(value / world, 1),
+            # every row advances one position per replay, the 9 prompt-feeding steps of a sequence included
+            "row_steps_per_s": round(world * BATCH * steps_per_pass * args.steps / (ms / 1e3), 1),
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(memory_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
                     "ms_per_step": round(e2e_ms / args.steps, 3)},
@@ -276,7 +288,7 @@ def run_ours(args) -> None:
             "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in all_stats],
             "wall_s": round(t_wall, 3),
         }
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
 
@@ -316,7 +328,7 @@ def run_profile(args) -> None:
     torch.cuda.profiler.stop()
     dec.check_status()
     kv = sum(lens) * 2 * 1024 * 2
-    print(json.dumps({"profile_steps": args.profile, "rows": B, "pos": args.profile_pos + 3, "sum_frames": sum(lens),
+    emit(json.dumps({"profile_steps": args.profile, "rows": B, "pos": args.profile_pos + 3, "sum_frames": sum(lens),
                       "cross_kv_bytes_per_launch": kv, "self_kv_bytes_per_launch": B * (args.profile_pos + 4) * 4096,
                       "weight_bytes": dec.weight_bytes, "launches_per_step": dec.launches_per_step}))
 
@@ -366,7 +378,7 @@ def run_stream(args) -> None:
         peak, peak_kind = measured_peak()
         tokens = sum(s["new_tokens"] for s in stats)
         gbs = sum(s["bytes"] for s in stats) / world / (ms / 1e3) / 1e9
-        print(json.dumps({
+        emit(json.dumps({
             "metric": "decoded tokens/s, continuous batching, 128 slots per GPU, 2:4 int8 feed-forward", "impl": "ours",
             "value": round(tokens / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "higher_is_better": True,
             "scaling": "strong", "data": "synthetic",
@@ -414,7 +426,7 @@ def run_reference(args) -> None:
                              "sample": r["sample"]},
             "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line), flush=True)
 
 
 def main() -> None:
@@ -442,6 +454,12 @@ def main() -> None:
                     help="batch64: BASELINE config 3 (the headline line); stream: configs 4 / 5, continuous batching")
     ap.add_argument("--requests", type=int, default=2000, help="stream workload: requests in the whole stream")
     args = ap.parse_args()
+    # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 themselves (NCCL's
+    # version banner, for one) are pointed at stderr, the result goes to a copy of the original descriptor
+    global _RESULT_OUT
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.profile:
         run_profile(args)

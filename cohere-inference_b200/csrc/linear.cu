@@ -78,7 +78,7 @@ __global__ void tile_24_kernel(const int8_t* __restrict__ kept, const uint32_t* 
   }
 }
 
-bool fits_any(int kind, bool split, bool ln, int warps, int k, int ksplit, int rows) {
+bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int rows) {
   switch (kind) {
     case B200DEC_W_INT8: return fits_int8(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_BF16: return fits_bf16(split, ln, warps, k, ksplit, rows);
@@ -88,7 +88,8 @@ bool fits_any(int kind, bool split, bool ln, int warps, int k, int ksplit, int r
 }
 
 int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
-               int out_kind, int ldo, int act, float* pmax, int* pidx, float* logits, int head, int pdl, void* stream) {
+               int out_kind, int ldo, int act, float* pmax, int* pidx, float* logits, int head, int pdl, void* stream,
+               const b200dec_ln_link* link = nullptr) {
   B200_REQUIRE(w && w->w && a, "linear: null pointer");
   B200_REQUIRE(rows >= 1 && rows <= 128, "linear: rows %d outside 1..128", rows);
   B200_REQUIRE(w->warps == 4 || w->warps == 8, "linear: warps must be 4 or 8");
@@ -98,8 +99,19 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   B200_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w->w & 15) == 0, "linear: operands must be 16-byte aligned");
   B200_REQUIRE(lda % 8 == 0 && lda >= w->k, "linear: lda %d", lda);
   B200_REQUIRE((w->kind == B200DEC_W_BF16) == (w->scale == nullptr), "linear: scale present iff int8");
-  const bool split = a_kind == B200DEC_A_F32_SPLIT, lnorm = ln != nullptr;
-  B200_REQUIRE(split || a_kind == B200DEC_A_F16, "linear: a_kind %d", a_kind);
+  const bool split = a_kind == B200DEC_A_F32_SPLIT;
+  B200_REQUIRE(split || a_kind == B200DEC_A_F16 || a_kind == B200DEC_A_F16_ROWS16, "linear: a_kind %d", a_kind);
+  // 0: no LayerNorm; 1: folded, the rows are fp32; 2: folded, the rows are fp16 copies of the LayerNorm's input
+  int lnorm = ln == nullptr ? 0 : a_kind == B200DEC_A_F16_ROWS16 ? 2 : 1;
+  if (lnorm == 2 && !fits_any(w->kind, false, 2, w->warps, w->k, w->ksplit, rows < 64 ? rows : 64))
+    return fail(B200DEC_EINVAL, "linear: fp16 LayerNorm rows need int8 weights and a K slice of at most 256");
+  const b200dec_ln_link none{};
+  const b200dec_ln_link lk = link ? *link : none;
+  B200_REQUIRE(!lk.out16 || (out_kind == B200DEC_OUT_F32_ADD && ((uintptr_t)lk.out16 & 7) == 0 && lk.next_gamma &&
+                             lk.stats_out && ((uintptr_t)lk.next_gamma & 15) == 0),
+               "linear: the fp16 operand for the next LayerNorm goes with OUT_F32_ADD, its gamma and the sums");
+  B200_REQUIRE(lnorm != 2 || (lk.stats_in && lk.stats_slots >= 1 && lk.stats_slots <= 128 && ((uintptr_t)lk.stats_in & 7) == 0),
+               "linear: fp16 LayerNorm rows come with their partial sums (link->stats_in, stats_slots)");
   if (lnorm)
     B200_REQUIRE(ln->w && w->ln_g && w->ln_bias && w->k == D_MODEL,
                  "linear: the folded LayerNorm needs gamma, the weight's ln_g / ln_bias vectors and K = %d", D_MODEL);
@@ -114,18 +126,25 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
       fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, 64)) {
     // this operand does not fit shared memory for 128 rows at this K slice: two passes of up to 64 rows (the weights
     // are read twice; projections sized with b200dec_linear_fits avoid this)
-    const size_t asz = (split || lnorm) ? 4 : 2, osz = out_kind == B200DEC_OUT_F16 ? 2 : 4;
+    const size_t asz = (split || lnorm == 1) ? 4 : 2, osz = out_kind == B200DEC_OUT_F16 ? 2 : 4;
     const int np = head ? (w->n / (16 * w->warps)) * w->ksplit : 0;
-    const int rc = run_linear(w, a, a_kind, ln, lda, 64, out, out_kind, ldo, act, pmax, pidx, logits, head, pdl, stream);
+    const int rc = run_linear(w, a, a_kind, ln, lda, 64, out, out_kind, ldo, act, pmax, pidx, logits, head, pdl, stream,
+                              link);
     if (rc) return rc;
+    b200dec_ln_link up = lk;  // the second pass: the same link 64 rows further
+    if (up.out16) up.out16 = (char*)up.out16 + (size_t)64 * ldo * 2;
+    if (up.stats_out) up.stats_out += (size_t)64 * 2 * b200dec_linear_stat_slots(w);
+    if (up.stats_in) up.stats_in += (size_t)64 * 2 * up.stats_slots;
     return run_linear(w, (const char*)a + (size_t)64 * lda * asz, a_kind, ln, lda, rows - 64,
                       out ? (char*)out + (size_t)64 * ldo * osz : nullptr, out_kind, ldo, act,
                       pmax ? pmax + (size_t)64 * np : nullptr, pidx ? pidx + (size_t)64 * np : nullptr,
-                      logits ? logits + (size_t)64 * w->n : nullptr, head, pdl, stream);
+                      logits ? logits + (size_t)64 * w->n : nullptr, head, pdl, stream, link ? &up : nullptr);
   }
   LinArgs p{};
   p.w = (const uint8_t*)w->w, p.meta = (const uint32_t*)w->meta, p.scale = w->scale, p.bias = w->bias;
   p.a = a, p.out = out, p.part_max = pmax, p.part_idx = pidx, p.logits = logits;
+  p.next_gamma = lk.next_gamma, p.out16 = (__half*)lk.out16, p.stats_out = lk.stats_out;
+  p.stats_in = lk.stats_in, p.stats_slots = lk.stats_slots;
   if (lnorm) p.ln_w = ln->w, p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
   p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.out_kind = out_kind, p.act = act, p.head = head;
   cudaStream_t s = (cudaStream_t)stream;
@@ -141,8 +160,9 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
 
 namespace b200dec_detail {
 int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
-                int out_kind, int ldo, int act, int pdl, void* stream) {
-  return run_linear(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, nullptr, nullptr, nullptr, 0, pdl, stream);
+                int out_kind, int ldo, int act, int pdl, void* stream, const b200dec_ln_link* link) {
+  return run_linear(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, nullptr, nullptr, nullptr, 0, pdl, stream,
+                    link);
 }
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
               int* pidx, float* logits, int pdl, void* stream) {
@@ -155,13 +175,21 @@ extern "C" {
 
 int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                    void* out, int out_kind, int ldo, int act, int pdl, void* stream) {
-  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream);
+  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, nullptr);
+}
+
+int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                          void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,
+                          void* stream) {
+  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, link);
 }
 
 int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                         float* part_max, int32_t* part_idx, float* logits, int pdl, void* stream) {
   return head_impl(w, a, a_kind, ln, lda, rows, part_max, part_idx, logits, pdl, stream);
 }
+
+int b200dec_linear_stat_slots(const b200dec_weight* w) { return w ? (w->n / (16 * w->warps)) * w->ksplit : 0; }
 
 int b200dec_head_partials(const b200dec_weight* w) {
   if (!w) return 0;
@@ -170,7 +198,8 @@ int b200dec_head_partials(const b200dec_weight* w) {
 
 int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int k, int rows) {
   if (ksplit < 1 || k % ksplit) return 0;
-  return fits_any(kind, a_kind == B200DEC_A_F32_SPLIT, ln != 0, warps, k, ksplit, rows) ? 1 : 0;
+  const int mode = ln == 0 ? 0 : a_kind == B200DEC_A_F16_ROWS16 ? 2 : 1;
+  return fits_any(kind, a_kind == B200DEC_A_F32_SPLIT, mode, warps, k, ksplit, rows) ? 1 : 0;
 }
 
 int64_t b200dec_tiled_bytes(int kind, int n, int k) {

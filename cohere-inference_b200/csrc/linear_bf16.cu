@@ -4,15 +4,21 @@
 
 namespace b200dec_detail {
 
-int launch_bf16(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
-  if (!split) return fail(B200DEC_EINVAL, "linear: bf16 weights take the split fp32 operand");
-  return ln ? launch_shape<B200DEC_W_BF16, true, true>(a, warps, k, ksplit, pdl, s)
-            : launch_shape<B200DEC_W_BF16, true, false>(a, warps, k, ksplit, pdl, s);
+int launch_bf16(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
+  if (split) {
+    if (ln == 2) return fail(B200DEC_EINVAL, "linear: fp16 LayerNorm rows go with the single fp16 operand");
+    return ln ? launch_shape<B200DEC_W_BF16, true, 1>(a, warps, k, ksplit, pdl, s)
+              : launch_shape<B200DEC_W_BF16, true, 0>(a, warps, k, ksplit, pdl, s);
+  }
+  if (ln == 2) return fail(B200DEC_EINVAL, "linear: fp16 LayerNorm rows are for int8 weights");
+  return ln ? launch_shape<B200DEC_W_BF16, false, 1>(a, warps, k, ksplit, pdl, s)
+            : launch_shape<B200DEC_W_BF16, false, 0>(a, warps, k, ksplit, pdl, s);
 }
 
-bool fits_bf16(bool split, bool ln, int warps, int k, int ksplit, int rows) {
-  if (!split) return false;
-  return ln ? fits_shape<B200DEC_W_BF16, true, true>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_BF16, true, false>(warps, k, ksplit, rows);
+bool fits_bf16(bool split, int ln, int warps, int k, int ksplit, int rows) {
+  if (split) return ln == 2 ? false : ln ? fits_shape<B200DEC_W_BF16, true, 1>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_BF16, true, 0>(warps, k, ksplit, rows);
+  if (ln == 2) return false;
+  return ln ? fits_shape<B200DEC_W_BF16, false, 1>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_BF16, false, 0>(warps, k, ksplit, rows);
 }
 
 }  // namespace b200dec_detail

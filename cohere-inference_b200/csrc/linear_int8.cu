@@ -4,16 +4,21 @@
 
 namespace b200dec_detail {
 
-int launch_int8(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
-  if (split) return ln ? launch_shape<B200DEC_W_INT8, true, true>(a, warps, k, ksplit, pdl, s)
-                       : launch_shape<B200DEC_W_INT8, true, false>(a, warps, k, ksplit, pdl, s);
-  return ln ? launch_shape<B200DEC_W_INT8, false, true>(a, warps, k, ksplit, pdl, s)
-            : launch_shape<B200DEC_W_INT8, false, false>(a, warps, k, ksplit, pdl, s);
+int launch_int8(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
+  if (split) {
+    if (ln == 2) return fail(B200DEC_EINVAL, "linear: fp16 LayerNorm rows go with the single fp16 operand");
+    return ln ? launch_shape<B200DEC_W_INT8, true, 1>(a, warps, k, ksplit, pdl, s)
+              : launch_shape<B200DEC_W_INT8, true, 0>(a, warps, k, ksplit, pdl, s);
+  }
+  if (ln == 2) return launch_shape<B200DEC_W_INT8, false, 2>(a, warps, k, ksplit, pdl, s);
+  return ln ? launch_shape<B200DEC_W_INT8, false, 1>(a, warps, k, ksplit, pdl, s)
+            : launch_shape<B200DEC_W_INT8, false, 0>(a, warps, k, ksplit, pdl, s);
 }
 
-bool fits_int8(bool split, bool ln, int warps, int k, int ksplit, int rows) {
-  if (split) return ln ? fits_shape<B200DEC_W_INT8, true, true>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_INT8, true, false>(warps, k, ksplit, rows);
-  return ln ? fits_shape<B200DEC_W_INT8, false, true>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_INT8, false, false>(warps, k, ksplit, rows);
+bool fits_int8(bool split, int ln, int warps, int k, int ksplit, int rows) {
+  if (split) return ln == 2 ? false : ln ? fits_shape<B200DEC_W_INT8, true, 1>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_INT8, true, 0>(warps, k, ksplit, rows);
+  if (ln == 2) return fits_shape<B200DEC_W_INT8, false, 2>(warps, k, ksplit, rows);
+  return ln ? fits_shape<B200DEC_W_INT8, false, 1>(warps, k, ksplit, rows) : fits_shape<B200DEC_W_INT8, false, 0>(warps, k, ksplit, rows);
 }
 
 }  // namespace b200dec_detail

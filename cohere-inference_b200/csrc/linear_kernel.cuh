@@ -20,6 +20,15 @@ struct LinArgs {
   const float* ln_g;     // ... g[n] = sum_k gamma[k] W[n][k] ...
   const float* ln_bias;  // ... and sum_k beta[k] W[n][k], both of the dequantised weights
   void* out;
+  // Link to the LayerNorm-folding projection that reads the rows an OUT_F32_ADD call updates (all null: none): the
+  // rows times that LayerNorm's gamma as fp16 (its operand), and per finishing CTA the rows' sum and sum of squares
+  // over its channels, stats_out (rows, gridDim.y * KSPLIT, 2).
+  const float* next_gamma;
+  __half* out16;
+  float* stats_out;
+  // The reading side (LN == 2): those partial sums, (rows, stats_slots, 2).
+  const float* stats_in;
+  int stats_slots;
   float* part_max;
   int* part_idx;
   float* logits;
@@ -101,7 +110,7 @@ DEVI void to_operand(float4 v, uint2& hi, uint2& lo) {
   }
 }
 
-template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 struct LinSmem {
   static constexpr int RS = KSLICE * 2 + WTraits<WT>::PAD;  // bytes per staged activation row
   static constexpr int BN = NW * 16;
@@ -109,9 +118,9 @@ struct LinSmem {
   static constexpr int RECV_BYTES = MB * BN * 4;       // [KSPLIT][MB][BN / KSPLIT] partial sums pushed by the cluster
   // fp32 source rows are first copied asynchronously into shared memory (slices up to 256 wide; wider ones are
   // converted straight from registers)
-  static constexpr bool RAW_STAGE = (LN || SPLIT) && KSLICE <= 256;
+  static constexpr bool RAW_STAGE = (LN == 1 || SPLIT) && KSLICE <= 256;
   static constexpr int RAW_BYTES = RAW_STAGE ? MB * KSLICE * 4 : 0;
-  static constexpr int STATS_BYTES = LN ? KSPLIT * MB * 8 : 0;  // [KSPLIT][MB] (sum, sum of squares) of each slice
+  static constexpr int STATS_BYTES = LN == 1 ? KSPLIT * MB * 8 : LN == 2 ? MB * 8 : 0;  // per slice / totals  // [KSPLIT][MB] (sum, sum of squares) of each slice
   static constexpr int OFF_A = 0, OFF_RECV = OFF_A + A_BYTES, OFF_RAW = OFF_RECV + RECV_BYTES,
                        OFF_STATS = OFF_RAW + RAW_BYTES, TOTAL = OFF_STATS + STATS_BYTES;
 };
@@ -122,14 +131,15 @@ struct LinSmem {
 // slice's (a - c) and (a - c)^2, and the finishing CTA applies  y = rstd * (acc * scale - (mean - c) * g) + bias',
 // which equals LayerNorm(a) W^T + bias exactly (g and bias' are precomputed per output channel). NW warps = 16 NW
 // channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
-template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   using T = WTraits<WT>;
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
   constexpr int RS = S::RS, CPR = BN / KSPLIT, GPR = CPR / 4, NB = MB / 8, NBG = NB < 8 ? NB : 8;
   constexpr bool BF = WT == B200DEC_W_BF16;
-  constexpr bool F32SRC = LN || SPLIT;  // the source rows are fp32
+  constexpr bool F32SRC = LN == 1 || SPLIT;  // the source rows are fp32
+  static_assert(LN != 2 || (!SPLIT && KSLICE <= 256), "fp16 source rows: one fp16 operand, a row's chunks within a warp");
   static_assert(CPR % 8 == 0, "each CTA finishes a multiple of 8 channels");
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ uint32_t lut[32];
@@ -195,7 +205,31 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
       else
         *reinterpret_cast<uint4*>(a_hi + r * RS + c * 16) = make_uint4(0, 0, 0, 0);
     }
+    if constexpr (LN == 2) {
+      // The rows are already this projection's operand (x * gamma as fp16, written by the projection that updated x):
+      // nothing to convert. Their statistics come as one partial (sum, sum of squares) per row and finishing CTA of
+      // that projection; the cluster shares the adding up: this CTA takes rows rank, rank + KSPLIT, ... (a warp per
+      // row, lanes over the partials, fixed order) and hands each total to every CTA of the cluster.
+      constexpr int RPW = (MB + KSPLIT * NW - 1) / (KSPLIT * NW);  // rows per warp, all their loads issued at once
+      float2 v[RPW][4];                                              // up to 128 partials per row: 4 per lane
+#pragma unroll
+      for (int j = 0; j < RPW; ++j) {
+        const int r = rank + KSPLIT * (warp + NW * j);
+        const float2* part = reinterpret_cast<const float2*>(p.stats_in) + (size_t)r * p.stats_slots;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          v[j][i] = (r < p.rows && lane + 32 * i < p.stats_slots) ? __ldcg(part + lane + 32 * i) : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < RPW; ++j) {
+        const int r = rank + KSPLIT * (warp + NW * j);
+        float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
+        s1 = warp_sum(s1), s2 = warp_sum(s2);
+        if (r < p.rows && lane < KSPLIT) cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
+      }
+    }
     cp_async_wait_all();
+
   } else {
     // fp32 rows: 8 lanes per row, each with KSLICE / 32 independent 16-byte loads in flight; converted (and, for the
     // folded LayerNorm, shifted, scaled by gamma and summed) on the way to shared memory
@@ -415,10 +449,15 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
       }
       if constexpr (LN) {
         float s1 = 0.f, s2 = 0.f;
+        if constexpr (LN == 2) {
+          const float2 st = stats[r];
+          s1 = st.x, s2 = st.y;
+        } else {
 #pragma unroll
-        for (int q = 0; q < KSPLIT; ++q) {
-          const float2 st = stats[q * MB + r];
-          s1 += st.x, s2 += st.y;
+          for (int q = 0; q < KSPLIT; ++q) {
+            const float2 st = stats[q * MB + r];
+            s1 += st.x, s2 += st.y;
+          }
         }
         const float dm = s1 * (1.f / K);  // mean - shift
         const float rstd = rsqrtf(fmaxf(s2 * (1.f / K) - dm * dm, 0.f) + p.ln_eps);
@@ -441,12 +480,29 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
           if (p.out_kind == B200DEC_OUT_F32_ADD) {
             const float4 x = one_item ? resid : __ldcg(o);
             s.x += x.x, s.y += x.y, s.z += x.z, s.w += x.w;
+            if (p.out16) {
+              const float4 gn = *reinterpret_cast<const float4*>(p.next_gamma + n);
+              *reinterpret_cast<uint2*>(p.out16 + (size_t)r * p.ldo + n) =
+                  make_uint2(pack_f16(s.x * gn.x, s.y * gn.y), pack_f16(s.z * gn.z, s.w * gn.w));
+            }
           }
           *o = s;
         }
       } else if (p.logits) {
         *reinterpret_cast<float4*>(p.logits + (size_t)r * p.N + n) = s;
       }
+    }
+    if (p.stats_out) {  // warp-uniform; the row's GPR consecutive lanes add up their channels, one of them publishes
+      float p1 = live ? (s.x + s.y) + (s.z + s.w) : 0.f;
+      float p2 = live ? (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w) : 0.f;
+#pragma unroll
+      for (int o = 1; o < GPR && o < 32; o <<= 1) {
+        p1 += __shfl_xor_sync(0xffffffffu, p1, o);
+        p2 += __shfl_xor_sync(0xffffffffu, p2, o);
+      }
+      if (live && c4 == 0)
+        reinterpret_cast<float2*>(p.stats_out)[(size_t)r * (gridDim.y * KSPLIT) + blockIdx.y * KSPLIT + rank] =
+            make_float2(p1, p2);
     }
     if (p.head) {
       // first index of the maximum over this CTA's channels of row r (NaN never wins): GPR consecutive lanes
@@ -474,7 +530,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
   B200_STAMP(7);
 }
 
-template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT, int MB>
+template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   static_assert(S::TOTAL <= 227 * 1024, "tile does not fit in shared memory");
@@ -494,7 +550,7 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
   return 0;
 }
 
-template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT>
+template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT>
 int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
   if (a.rows <= 16) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s);
   if (a.rows <= 64) {
@@ -510,7 +566,7 @@ int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
 }
 
 // Does the (kind, operand, tile) combination fit shared memory for this many rows? (host-side query)
-template <int WT, bool SPLIT, bool LN, int NW, int KSLICE, int KSPLIT>
+template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT>
 bool fits(int rows) {
   if (rows <= 16) return true;
   if (rows <= 64) return LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024;
@@ -520,13 +576,14 @@ bool fits(int rows) {
 // the (K / ksplit, ksplit) pairs with kernels: K = 1024 as 8 x 128, 4 x 256, 2 x 512; K = 4096 as 8 x 512
 #define B200_TILE_CASES(X) X(4, 128, 8) X(4, 256, 4) X(4, 512, 2) X(4, 512, 8) X(8, 128, 8) X(8, 256, 4) X(8, 512, 2) X(8, 512, 8)
 
-template <int WT, bool SPLIT, bool LN>
+template <int WT, bool SPLIT, int LN>
 int launch_shape(const LinArgs& a, int warps, int k, int ksplit, bool pdl, cudaStream_t s) {
   const int kslice = k / ksplit;
   constexpr int KPB = WTraits<WT>::KPB;
 #define B200_CASE(NW_, KS_, SP_)                                                                    \
   if (warps == NW_ && kslice == KS_ && ksplit == SP_) {                                             \
-    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0)   \
+    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0 && \
+                  (LN != 2 || (!SPLIT && KS_ <= 256)))                                              \
       return launch_mb<WT, SPLIT, LN, NW_, KS_, SP_>(a, pdl, s);                                    \
   }
   B200_TILE_CASES(B200_CASE)
@@ -535,13 +592,14 @@ int launch_shape(const LinArgs& a, int warps, int k, int ksplit, bool pdl, cudaS
               ksplit);
 }
 
-template <int WT, bool SPLIT, bool LN>
+template <int WT, bool SPLIT, int LN>
 bool fits_shape(int warps, int k, int ksplit, int rows) {
   const int kslice = k / ksplit;
   constexpr int KPB = WTraits<WT>::KPB;
 #define B200_CASE(NW_, KS_, SP_)                                                                    \
   if (warps == NW_ && kslice == KS_ && ksplit == SP_) {                                             \
-    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0)   \
+    if constexpr (KS_ % KPB == 0 && (!LN || KS_ * SP_ == D_MODEL) && (NW_ * 16) % (8 * SP_) == 0 && \
+                  (LN != 2 || (!SPLIT && KS_ <= 256)))                                              \
       return fits<WT, SPLIT, LN, NW_, KS_, SP_>(rows);                                              \
   }
   B200_TILE_CASES(B200_CASE)
@@ -550,11 +608,11 @@ bool fits_shape(int warps, int k, int ksplit, int rows) {
 }
 
 // one entry per weight kind, each defined in its own translation unit
-int launch_int8(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
-int launch_bf16(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
-int launch_24(const LinArgs& a, bool split, bool ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
-bool fits_int8(bool split, bool ln, int warps, int k, int ksplit, int rows);
-bool fits_bf16(bool split, bool ln, int warps, int k, int ksplit, int rows);
-bool fits_24(bool split, bool ln, int warps, int k, int ksplit, int rows);
+int launch_int8(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+int launch_bf16(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+int launch_24(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+bool fits_int8(bool split, int ln, int warps, int k, int ksplit, int rows);
+bool fits_bf16(bool split, int ln, int warps, int k, int ksplit, int rows);
+bool fits_24(bool split, int ln, int warps, int k, int ksplit, int rows);
 
 }  // namespace b200dec_detail

@@ -144,6 +144,23 @@ __global__ void __launch_bounds__(128) row_schedule_kernel(const SchedArgs p) {
   build_schedules(p);
 }
 
+// o (a row in registers) -> fp16(o * gamma) and the row's (sum, sum of squares): the ready operand of a
+// LayerNorm-folding projection and the statistics that go with it (one slot per row)
+DEVI void ln_operand_row(const float (&o)[32], const float* gamma, void* dst, float* stats, size_t row, int lane) {
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = i * 128 + lane * 4;
+    const float4 g = *reinterpret_cast<const float4*>(gamma + c);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(dst) + row * D_MODEL + c) =
+        make_uint2(pack_f16(o[4 * i] * g.x, o[4 * i + 1] * g.y), pack_f16(o[4 * i + 2] * g.z, o[4 * i + 3] * g.w));
+    s1 += (o[4 * i] + o[4 * i + 1]) + (o[4 * i + 2] + o[4 * i + 3]);
+    s2 += (o[4 * i] * o[4 * i] + o[4 * i + 1] * o[4 * i + 1]) + (o[4 * i + 2] * o[4 * i + 2] + o[4 * i + 3] * o[4 * i + 3]);
+  }
+  s1 = warp_sum(s1), s2 = warp_sum(s2);
+  if (lane == 0) reinterpret_cast<float2*>(stats)[row] = make_float2(s1, s2);
+}
+
 struct EmbedArgs {
   SchedArgs sched;  // sched.rows == 0: no schedule; else the grid's last CTA builds it
   const int* active;
@@ -153,6 +170,9 @@ struct EmbedArgs {
   const __nv_bfloat16* ptab;
   b200dec_norm ln0, ln1;
   float* x;
+  void* x16;  // null, or (rows, 1024) fp16 = x * next_gamma with the rows' (sum, sum of squares) in stats (rows, 2):
+  const float* next_gamma;  // the ready operand of the first LayerNorm-folding projection
+  float* stats;
   void* hn;
   int* status;
   int vocab, max_pos, slots, hn_kind, rows;
@@ -193,6 +213,7 @@ __global__ void __launch_bounds__(128) embed_ln_kernel(const EmbedArgs p) {
   }
   ln_row(v, p.ln0.w, p.ln0.b, p.ln0.eps, lane, o);
   store_row(o, p.x, B200DEC_OUT_F32, row, lane);
+  if (p.x16) ln_operand_row(o, p.next_gamma, p.x16, p.stats, row, lane);  // what the first projection stages
   if (p.hn) {  // optionally also the first layer's LayerNorm of the new row
     ln_row(o, p.ln1.w, p.ln1.b, p.ln1.eps, lane, v);
     store_row(v, p.hn, p.hn_kind, row, lane);
@@ -219,6 +240,19 @@ __global__ void __launch_bounds__(128) layer_norm_kernel(const LnArgs p) {
   }
   ln_row(v, p.ln.w, p.ln.b, p.ln.eps, lane, o);
   store_row(o, p.hn, p.hn_kind, row, lane);
+}
+
+__global__ void __launch_bounds__(128) ln_rows16_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                        int rows, void* out16, float* stats) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 a = ld_cg_f4(x + (size_t)row * D_MODEL + i * 128 + lane * 4);
+    v[4 * i] = a.x, v[4 * i + 1] = a.y, v[4 * i + 2] = a.z, v[4 * i + 3] = a.w;
+  }
+  ln_operand_row(v, gamma, out16, stats, row, lane);
 }
 
 struct PickArgs {
@@ -421,15 +455,17 @@ namespace b200dec_detail {
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
                   void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream, const int32_t* cross_len,
-                  int seq, int frames, int32_t* sched_self, int32_t* sched_cross) {
+                  int seq, int frames, int32_t* sched_self, int32_t* sched_cross, void* x16, const float* next_gamma,
+                  float* stats) {
   B200_REQUIRE(active && tok && pos && embed && pos_table && x && status && ln0.w && ln0.b && (!hn || (ln1.w && ln1.b)),
                "embed_ln: null pointer");
   B200_REQUIRE(rows >= 1, "embed_ln: rows %d", rows);
+  B200_REQUIRE(!x16 || (next_gamma && stats), "embed_ln: the fp16 operand needs the next gamma and a place for the sums");
   const bool sched = (sched_self || sched_cross) && rows <= SCHED_MAX_ROWS;
   B200_REQUIRE(!sched || !sched_cross || cross_len, "embed_ln: a cross schedule needs the frame counts");
   EmbedArgs p{SchedArgs{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, sched ? rows : 0},
-              active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, hn, status,
-              vocab, max_pos, slots, hn_kind, rows};
+              active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, x16, next_gamma,
+              stats, hn, status, vocab, max_pos, slots, hn_kind, rows};
   const cudaError_t e = launch_kernel(embed_ln_kernel, dim3((rows + 3) / 4 + (sched ? 1 : 0)), dim3(128), 0,
                                       (cudaStream_t)stream, 0, pdl, p);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "embed_ln launch: %s", cudaGetErrorString(e));
@@ -470,7 +506,14 @@ int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* p
                      const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                      float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
   return embed_ln_impl(active, tok, pos, embed, pos_table, vocab, max_pos, slots, ln0, ln1, x, hn, hn_kind, rows, status,
-                       pdl, stream, nullptr, 0, 0, nullptr, nullptr);
+                       pdl, stream, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr);
+}
+
+int b200dec_ln_rows16(const float* x, const float* gamma, int rows, void* out16, float* stats, void* stream) {
+  B200_REQUIRE(x && gamma && out16 && stats && rows >= 1 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out16 & 7) == 0,
+               "ln_rows16: bad arguments");
+  ln_rows16_kernel<<<(rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(x, gamma, rows, out16, stats);
+  return check_launch("ln_rows16");
 }
 
 int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_t* cross_len, int slots, int seq,

@@ -7,7 +7,7 @@
 
 namespace b200dec_detail {
 int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
-                int out_kind, int ldo, int act, int pdl, void* stream);
+                int out_kind, int ldo, int act, int pdl, void* stream, const b200dec_ln_link* link);
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
               int* pidx, float* logits, int pdl, void* stream);
 int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows, float* part_max,
@@ -15,7 +15,8 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* 
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                   float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream,
-                  const int32_t* cross_len, int seq, int frames, int32_t* sched_self, int32_t* sched_cross);
+                  const int32_t* cross_len, int seq, int frames, int32_t* sched_self, int32_t* sched_cross, void* x16,
+                  const float* next_gamma, float* stats);
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
               const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax, int pdl,
@@ -66,6 +67,39 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   int32_t* head_idx = pl->head_idx + (size_t)row0 * partials;
   float* logits = pl->logits ? pl->logits + (size_t)row0 * pl->vocab : nullptr;
 
+  // The LayerNorm-folding projections stage an fp16 copy of the residual stream when the plan has one and the layer
+  // projections are the kind that can (single fp16 operand, int8 or 2:4 weights, K slice <= 256); the projections that
+  // update the stream (and the embedding) write that copy.
+  void* xh = nullptr;
+  if (pl->xh && pl->ln_stats && a16 && pl->layer[0].qkv.kind != B200DEC_W_BF16 &&
+      b200dec_linear_fits(pl->layer[0].qkv.kind, B200DEC_A_F16_ROWS16, 1, pl->layer[0].qkv.warps, pl->layer[0].qkv.ksplit,
+                          D_MODEL, rows) &&
+      b200dec_linear_fits(pl->layer[0].cq.kind, B200DEC_A_F16_ROWS16, 1, pl->layer[0].cq.warps, pl->layer[0].cq.ksplit,
+                          D_MODEL, rows) &&
+      b200dec_linear_fits(pl->layer[0].fc1.kind, B200DEC_A_F16_ROWS16, 1, pl->layer[0].fc1.warps, pl->layer[0].fc1.ksplit,
+                          D_MODEL, rows))
+    xh = (char*)pl->xh + (size_t)row0 * D_MODEL * 2;
+  const void* ln_src = xh ? xh : (const void*)x;
+  const int ln_kind = xh ? B200DEC_A_F16_ROWS16 : pl->a_kind;
+  // The statistics travel as partial sums, one slot per row and finishing CTA of the producer (the embedding: one).
+  constexpr int STAT_SLOTS = 128;
+  float* stats = xh ? pl->ln_stats + (size_t)row0 * STAT_SLOTS * 2 : nullptr;
+  if (xh) {
+    const b200dec_layer& l0 = pl->layer[0];
+    B200_REQUIRE(b200dec_linear_stat_slots(&l0.o) <= STAT_SLOTS && b200dec_linear_stat_slots(&l0.co) <= STAT_SLOTS &&
+                     b200dec_linear_stat_slots(&l0.fc2) <= STAT_SLOTS, "step: more finishing CTAs than statistic slots");
+  }
+  auto producer = [&](const float* gamma) {
+    b200dec_ln_link l{};
+    if (xh && gamma) l.next_gamma = gamma, l.out16 = xh, l.stats_out = stats;
+    return l;
+  };
+  auto reader = [&](int slots) {
+    b200dec_ln_link l{};
+    if (xh) l.stats_in = stats, l.stats_slots = slots;
+    return l;
+  };
+
   const auto attention = pl->attn_ring ? b200dec_attention_ring : b200dec_attention;
   // a large batch: the rows are ranked by length once (an extra CTA of the embedding kernel) and the attention
   // kernels pair long rows with short ones from the two tables
@@ -75,11 +109,17 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
 
   B200_TRY(embed_ln_impl(active, pl->tok, pl->pos, pl->embed, pl->pos_table, pl->vocab, pl->max_pos, pl->slots,
                          pl->emb_ln, pl->layer[0].ln1, x, nullptr, B200DEC_OUT_F32, rows, pl->status, pdl, stream,
-                         pl->cross_len, pl->seq, pl->frames, sched_self, sched_cross));
+                         pl->cross_len, pl->seq, pl->frames, sched_self, sched_cross, xh, pl->layer[0].ln1.w, stats));
   for (int i = 0; i < pl->layers; ++i) {
     const b200dec_layer& ly = pl->layer[i];
-    B200_TRY(linear_impl(&ly.qkv, x, pl->a_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
-                         B200DEC_ACT_NONE, pdl, stream));
+    // who wrote the operand and statistics each LayerNorm-folding projection reads: qkv <- embedding (1 slot) or the
+    // previous layer's fc2; cross-q <- o; fc1 <- cross-o
+    const b200dec_ln_link r1 = reader(i == 0 ? 1 : b200dec_linear_stat_slots(&pl->layer[i - 1].fc2)),
+                          p2 = producer(ly.ln2.w), r2 = reader(b200dec_linear_stat_slots(&ly.o)),
+                          p3 = producer(ly.ln3.w), r3 = reader(b200dec_linear_stat_slots(&ly.co)),
+                          p1 = producer(i + 1 < pl->layers ? pl->layer[i + 1].ln1.w : nullptr);
+    B200_TRY(linear_impl(&ly.qkv, ln_src, ln_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
+                         B200DEC_ACT_NONE, pdl, stream, &r1));
     if (pl->kv_int8 && paired)
       B200_TRY(b200dec_attention_paired_q8(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, ly.self_ks, ly.self_vs,
                                            pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
@@ -95,9 +135,9 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
                                  pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
                                  pdl_attn, stream));
     B200_TRY(linear_impl(&ly.o, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
-                         pdl_after, stream));
-    B200_TRY(linear_impl(&ly.cq, x, pl->a_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
-                         stream));
+                         pdl_after, stream, &p2));
+    B200_TRY(linear_impl(&ly.cq, ln_src, ln_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,
+                         stream, &r2));
     if (pl->kv_int8 && paired)
       B200_TRY(b200dec_attention_paired_q8(0, sched_cross, cq, hd, (void*)ly.cross_k, (void*)ly.cross_v, ly.cross_ks,
                                            ly.cross_vs, pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows,
@@ -114,10 +154,11 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
                                  pl->heads, pl->head_dim, pl->frames, scale, att, ok_a, rows, attn_part, attn_count,
                                  pl->status, pdl_attn, stream));
     B200_TRY(linear_impl(&ly.co, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
-                         pdl_after, stream));
-    B200_TRY(linear_impl(&ly.fc1, x, pl->a_kind, &ly.ln3, D_MODEL, rows, mid, ok_a, ffn, pl->act, pdl, stream));
+                         pdl_after, stream, &p3));
+    B200_TRY(linear_impl(&ly.fc1, ln_src, ln_kind, &ly.ln3, D_MODEL, rows, mid, ok_a, ffn, pl->act, pdl, stream, &r3));
+    // the last layer's fc2 feeds the vocabulary projection, which reads the fp32 rows: no link
     B200_TRY(linear_impl(&ly.fc2, mid, pl->a_kind, nullptr, ffn, rows, x, B200DEC_OUT_F32_ADD, D_MODEL,
-                         B200DEC_ACT_NONE, pdl, stream));
+                         B200DEC_ACT_NONE, pdl, stream, &p1));
   }
   if (pl->head.kind == B200DEC_W_INT8_UMMA)
     B200_TRY(head_umma_impl(&pl->head, x, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pl->status, pdl,

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200dec.so")
 
 W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA = 0, 1, 2, 3
-A_F16, A_F32_SPLIT = 0, 1
+A_F16, A_F32_SPLIT, A_F16_ROWS16 = 0, 1, 2
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
 ST_TOKEN_RANGE, ST_POS_RANGE, ST_FRAMES_RANGE, ST_SLOT_RANGE, ST_TIMEOUT = 1, 2, 4, 8, 16
@@ -30,6 +30,10 @@ class Weight(C.Structure):
 
 class Norm(C.Structure):
     _fields_ = [("w", vp), ("b", vp), ("eps", f32), ("_pad", i32)]
+
+
+class LnLink(C.Structure):
+    _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32), ("_pad", i32)]
 
 
 class Layer(C.Structure):
@@ -49,7 +53,7 @@ class Plan(C.Structure):
                 ("finished", vp), ("forced", vp), ("out", vp), ("status", vp),
                 ("x", vp), ("qkv", vp), ("cq", vp), ("att", vp), ("mid", vp),
                 ("attn_part", vp), ("attn_count", vp), ("head_max", vp), ("head_idx", vp),
-                ("sched_self", vp), ("sched_cross", vp), ("logits", vp), ("argmax", vp)]
+                ("xh", vp), ("ln_stats", vp), ("sched_self", vp), ("sched_cross", vp), ("logits", vp), ("argmax", vp)]
 
 
 # name -> (restype, argtypes); every symbol include/b200dec.h declares
@@ -70,6 +74,10 @@ PROTOTYPES = {
     "b200dec_layer_norm": (C.c_int, [vp, Norm, vp, C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_linear": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, C.c_int, C.c_int,
                                  C.c_int, C.c_int, vp]),
+    "b200dec_linear_linked": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, C.c_int,
+                                        C.c_int, C.c_int, C.POINTER(LnLink), C.c_int, vp]),
+    "b200dec_linear_stat_slots": (C.c_int, [C.POINTER(Weight)]),
+    "b200dec_ln_rows16": (C.c_int, [vp, vp, C.c_int, vp, vp, vp]),
     "b200dec_linear_fits": (C.c_int, [C.c_int] * 7),
     "b200dec_head_argmax": (C.c_int, [C.POINTER(Weight), vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, vp, vp,
                                       C.c_int, vp]),

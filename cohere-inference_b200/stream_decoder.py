@@ -159,6 +159,10 @@ class StreamDecoder:
             self.head_max = torch.zeros(bm, self.head_partials, **f32)
             self.head_idx = torch.zeros(bm, self.head_partials, **i32)
             # the step's rows ranked by length (self / cross), rebuilt by every step for the paired attention kernel
+            # the residual stream times the next LayerNorm's gamma as fp16, and the rows' partial sums (one slot per
+            # finishing CTA of the producer): what the LayerNorm-folding projections stage (int8 / 2:4 weights)
+            self.xh = torch.zeros(bm, self.width, device=dev, dtype=torch.float16) if int8 else None
+            self.ln_stats = torch.zeros(bm, 128, 2, device=dev) if int8 else None
             self.sched_self = torch.zeros(bm, 4, **i32)
             self.sched_cross = torch.zeros(bm, 4, **i32)
             self.logits = torch.zeros(bm, self.vocab, **f32) if record else None
@@ -206,8 +210,10 @@ class StreamDecoder:
         p.head = self.head.struct()
         for name in ("active", "tok", "pos", "plen", "limit", "cross_len", "finished", "forced", "out", "status", "x",
                      "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
-                     "sched_self", "sched_cross", "logits", "argmax"):
+                     "xh", "ln_stats", "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
+        if os.environ.get("B200DEC_NO_XH"):  # tuning runs: the projections convert the fp32 rows themselves
+            p.xh = None
         if os.environ.get("B200DEC_NO_SCHED"):  # tuning runs: rank the rows inside every attention launch instead
             p.sched_self = p.sched_cross = None
         self.plan = p

@@ -21,7 +21,9 @@ extern "C" {
 
 enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* weight storage of one projection */
        B200DEC_W_INT8_UMMA = 3 };  /* int8 in the block layout of the tcgen05 vocabulary projection (b200dec_head_umma) */
-enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1 };                       /* activation operand of a projection */
+enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1,  /* activation operand of a projection: one fp16, or hi + lo */
+       B200DEC_A_F16_ROWS16 = 2 };  /* one fp16, and with a LayerNorm the rows handed in are its ready fp16 operand
+                                      (see b200dec_ln_link) */
 enum { B200DEC_OUT_F16 = 0, B200DEC_OUT_F32 = 1, B200DEC_OUT_F32_ADD = 2 };/* store, or add into an fp32 residual */
 enum { B200DEC_ACT_NONE = 0, B200DEC_ACT_RELU = 1, B200DEC_ACT_GELU = 2 };
 enum { B200DEC_OK = 0, B200DEC_EINVAL = 1, B200DEC_ECUDA = 2, B200DEC_EARCH = 3 };
@@ -103,6 +105,9 @@ typedef struct b200dec_plan {
   int32_t* attn_count; /* rows * heads counters, zero on entry and on exit */
   float* head_max;     /* (max rows, b200dec_head_partials()) */
   int32_t* head_idx;
+  void* xh;             /* (max rows, 1024) fp16: the residual stream times the next LayerNorm's gamma, the operand of
+                           the LayerNorm-folding projections (a_kind F16 only); NULL: they convert the fp32 rows */
+  float* ln_stats;      /* (max rows, 128, 2) partial row sums that go with xh (see b200dec_ln_link) */
   int32_t* sched_self;  /* (max rows, 4) row schedules for b200dec_attention_paired, 16-byte aligned; both NULL: */
   int32_t* sched_cross; /* the step uses b200dec_attention for every batch size */
   /* optional recording (tests, teacher forcing); NULL in production */
@@ -154,6 +159,27 @@ int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, i
  * kernels/stream_decoder.py:23-27 and, with ln, the dec_add_ln in front of it (kernels/csrc/decoder_ops.cu:56-83). */
 int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                    void* out, int out_kind, int ldo, int act, int pdl, void* stream);
+/* Links between a projection that updates the residual stream (B200DEC_OUT_F32_ADD) and the LayerNorm-folding
+ * projection that reads it next, so that the reader stages a ready fp16 operand with asynchronous copies instead of
+ * converting fp32 rows. The producer (next_gamma, out16, stats_out set) also writes out16 (rows, ldo) = updated row *
+ * next_gamma as fp16 and, per row, one partial (sum, sum of squares) for each of its b200dec_linear_stat_slots(w)
+ * finishing CTAs: stats_out (rows, slots, 2) fp32. The reader (ln != NULL, a_kind = B200DEC_A_F16_ROWS16, a = that
+ * out16, int8 or 2:4 weights with a K slice <= 256) adds up stats_in (rows, stats_slots, 2) in a fixed order.
+ * b200dec_ln_rows16 starts a chain from fp32 rows: out16 = x * gamma and one slot of sums per row. Same reference
+ * counterparts as b200dec_linear and b200dec_layer_norm. */
+typedef struct b200dec_ln_link {
+  const float* next_gamma;
+  void* out16;
+  float* stats_out;
+  const float* stats_in;
+  int32_t stats_slots;
+  int32_t _pad;
+} b200dec_ln_link;
+int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                          void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,
+                          void* stream);
+int b200dec_linear_stat_slots(const b200dec_weight* w);
+int b200dec_ln_rows16(const float* x, const float* gamma, int rows, void* out16, float* stats, void* stream);
 /* 1 when a projection with this tile (warps, ksplit) fits shared memory for `rows` rows in one pass (else the call
  * makes two passes of up to 64 rows and reads the weights twice). Host-only query. */
 int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int k, int rows);

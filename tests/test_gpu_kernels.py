@@ -182,6 +182,68 @@ def test_linear_layernorm_on_load(nv, pk, kind, a_kind, n, rows):
     np.testing.assert_allclose(got, want, atol=tol, rtol=1e-4)
 
 
+def _row_sums(x):
+    """(rows, 2) float64: sum and sum of squares of every row."""
+    return np.stack([x.astype(np.float64).sum(1), (x.astype(np.float64) ** 2).sum(1)], 1)
+
+
+@pytest.mark.parametrize("kind", ["W_INT8", "W_INT8_24"])
+@pytest.mark.parametrize("n", [1024, 3072, 4096])
+@pytest.mark.parametrize("rows", [2, 13, 64, 128])
+def test_linear_linked_layernorm(nv, pk, kind, n, rows):
+    """A projection that updates the residual rows also leaves the next LayerNorm's operand (row * gamma, fp16) and the
+    rows' partial sums (one slot per finishing CTA); the LayerNorm-folding projection that stages them equals
+    LayerNorm(rows) W^T + b. b200dec_ln_rows16 makes the same pair from fp32 rows."""
+    rng = np.random.default_rng(n + rows)
+    k = 1024
+    wk = getattr(nv, kind)
+    lib = nv.lib()
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    g_d, b_d = cuda(gam), cuda(bet)
+    # producer: x += mid @ Wp^T (a 1024 x 1024 projection)
+    wp = (rng.standard_normal((k, k)) * 0.02).astype(np.float32)
+    mid = rng.standard_normal((rows, k)).astype(np.float16)
+    x0 = (rng.standard_normal((rows, k)) * (1 + rng.random((rows, 1))) + rng.standard_normal((rows, 1))).astype(np.float32)
+    pp = pk.pack_linear(cuda(wp), None, nv.W_INT8, max_rows=rows)
+    x = cuda(x0)
+    x16 = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    mid_d, ps = cuda(mid), pp.struct()
+    slots = lib.b200dec_linear_stat_slots(C.byref(ps))
+    sums = torch.full((rows, slots, 2), float("nan"), device="cuda")
+    link = nv.LnLink(nv.ptr(g_d), nv.ptr(x16), nv.ptr(sums), None, 0, 0)
+    nv.check(lib.b200dec_linear_linked(C.byref(ps), nv.ptr(mid_d), nv.A_F16, None, k, rows, nv.ptr(x), nv.OUT_F32_ADD, k,
+                                       nv.ACT_NONE, C.byref(link), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    xn = x.cpu().numpy()
+    xw = mid.astype(np.float64) @ pk.dequantized(cuda(wp), nv.W_INT8).cpu().numpy().astype(np.float64).T + x0
+    np.testing.assert_allclose(xn, xw.astype(np.float32), atol=2e-4, rtol=1e-5)
+    assert np.array_equal(x16.cpu().numpy(), (xn * gam).astype(np.float16)), "the operand is fp16(row * gamma)"
+    np.testing.assert_allclose(sums.cpu().numpy().astype(np.float64).sum(1), _row_sums(xn), rtol=1e-5, atol=1e-3)
+    # the same pair from fp32 rows: one slot per row
+    x16b = torch.zeros_like(x16)
+    sums_b = torch.zeros(rows, 2, device="cuda")
+    nv.check(lib.b200dec_ln_rows16(nv.ptr(x), nv.ptr(g_d), rows, nv.ptr(x16b), nv.ptr(sums_b), nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(x16b, x16)
+    np.testing.assert_allclose(sums_b.cpu().numpy().astype(np.float64), _row_sums(xn), rtol=1e-5, atol=1e-3)
+    # reader: LayerNorm folded, operand and sums as left by the producer
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    pc = pk.pack_linear(cuda(w), cuda(b), wk, a_kind=nv.A_F16, ln=(g_d, b_d), max_rows=rows)
+    norm, cs = nv.norm(g_d, b_d, 1e-5), pc.struct()
+    out = torch.zeros(rows, n, device="cuda")
+    for stats, nslots in ((sums, slots), (sums_b, 1)):  # many partials per row, or one
+        out.zero_()
+        rlink = nv.LnLink(None, None, None, nv.ptr(stats), nslots, 0)
+        nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(x16), nv.A_F16_ROWS16, C.byref(norm), k, rows, nv.ptr(out),
+                                           nv.OUT_F32, n, nv.ACT_NONE, C.byref(rlink), 0, nv.stream_ptr()))
+        torch.cuda.synchronize()
+        want = (layer_norm(xn, gam, bet, 1e-5).astype(np.float64) @
+                pk.dequantized(cuda(w), wk).cpu().numpy().astype(np.float64).T + b)
+        np.testing.assert_allclose(out.cpu().numpy(), want.astype(np.float32), atol=4e-3, rtol=1e-4)
+
+
 @pytest.mark.parametrize("act", ["ACT_RELU", "ACT_GELU"])
 @pytest.mark.parametrize("out_kind", ["OUT_F16", "OUT_F32_ADD"])
 def test_linear_epilogues(nv, pk, act, out_kind):

@@ -438,7 +438,7 @@ def main() -> None:
     ap.add_argument("--cpu-steps", type=int, default=32, help="decoding steps of the bounded CPU sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
-    ap.add_argument("--pdl", type=int, default=5, help="which launches are programmatic: 1 projection after projection, "
+    ap.add_argument("--pdl", type=int, default=7, help="which launches are programmatic: 1 projection after projection, "
                     "2 attention, 4 projection after attention (sum them)")
     ap.add_argument("--no-head-umma", action="store_true", help="vocabulary projection on mma.sync instead of tcgen05")
     ap.add_argument("--no-head-split", action="store_true", help="vocabulary projection on a single fp16 operand")

@@ -396,15 +396,16 @@ __global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_pair_kernel(co
   const int role = blockIdx.x, h = blockIdx.y, i = blockIdx.z, rows = p.rows;
   const int tid = threadIdx.x;
   ATTN_STAMP(0);
-  pdl_wait();
-
   int r_long, r_short, s_long, s_short, n_long, n_short;
   if constexpr (TABLE) {
-    // the step's schedule (built beside the embedding): two entries, no dependent loads
+    // the step's schedule (built beside the embedding, at least two kernels ago: readable before the wait): two
+    // entries, no dependent loads
     const int4 a = __ldcg(reinterpret_cast<const int4*>(p.sched) + i);
     const int4 b = __ldcg(reinterpret_cast<const int4*>(p.sched) + (rows - 1 - i));
     r_long = a.x, s_long = a.y, n_long = a.z, r_short = b.x, s_short = b.y, n_short = b.z;
+    pdl_wait();
   } else {
+    pdl_wait();
     for (int r = tid; r < rows; r += NTHREADS) {
       int s, n;
       row_state<SELF>(p, r, blockIdx.x + blockIdx.y + blockIdx.z == 0, s, n);

@@ -57,7 +57,7 @@ class StreamDecoder:
 
     def __init__(self, model, slots: int = 128, max_new_tokens: int = 448, max_prompt: int = 16,
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
-                 eos: int | None = None, record: bool = False, pdl: bool | int = 5, graphs: bool = True,
+                 eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
                  head_umma: bool = True, kv_int8: bool = False):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).

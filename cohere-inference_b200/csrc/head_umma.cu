@@ -24,7 +24,7 @@ constexpr int UM = 128;                 // channels per CTA (MMA M)
 constexpr int UN = 64;                  // rows (MMA N)
 constexpr int KB = 64;                  // k per block: one 128-byte row of fp16
 constexpr int NKB = D_MODEL / KB;       // 16 blocks
-constexpr int RAW_STAGES = 8, A_STAGES = 2;  // 64 KB of weights in flight per SM: what HBM latency asks for
+constexpr int RAW_STAGES = 7, A_STAGES = 2;  // 56 KB of weights in flight per SM (what fits beside the activations)
 constexpr int RAW_BYTES = UM * KB;      // 8 KB of uint8
 constexpr int A_BYTES = UM * KB * 2;    // 16 KB of fp16
 constexpr int XB_BYTES = UN * KB * 2;   // 8 KB: one k-block of the activations
@@ -42,7 +42,12 @@ struct HeadArgs {
   const uint8_t* w;      // tiled weights
   const float* scale;
   const float* bias;     // may be null
-  const float* x;        // (rows, lda) fp32
+  const float* x;        // (rows, lda) fp32, normalised in the kernel; or null:
+  const __half* xg;      // (rows, lda) fp16 = row * gamma written by the projection that produced the rows, with
+  const float* stats;    // (rows, stats_slots, 2) partial (sum, sum of squares); the LayerNorm is then folded into
+  const float* ln_g;     // the epilogue: y = rstd * (acc * scale - mean * ln_g) + ln_bias + bias
+  const float* ln_bias;
+  int stats_slots;
   const float* ln_w;
   const float* ln_b;
   float* part_max;
@@ -147,7 +152,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
   __shared__ __align__(8) uint64_t raw_full[RAW_STAGES], raw_empty[RAW_STAGES], a_full[A_STAGES], a_empty[A_STAGES];
   __shared__ __align__(8) uint64_t x_full, d_full;
   __shared__ uint32_t tmem_base;
-  __shared__ float s_scale[UM], s_bias[UM];
+  __shared__ float s_scale[UM], s_bias[UM], s_g[UM];
+  __shared__ float s_mean[UN], s_rstd[UN];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;  // channels [128 tile, +128)
@@ -168,7 +174,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
   }
   if (tid < UM) {
     s_scale[tid] = p.scale[tile * UM + tid];
-    s_bias[tid] = p.bias ? p.bias[tile * UM + tid] : 0.f;
+    s_bias[tid] = (p.bias ? p.bias[tile * UM + tid] : 0.f) + (p.xg ? p.ln_bias[tile * UM + tid] : 0.f);
+    s_g[tid] = p.xg ? p.ln_g[tile * UM + tid] : 0.f;
   }
   tc_fence_before();
   __syncthreads();
@@ -213,6 +220,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
     pdl_wait();
     pdl_trigger();
     HEAD_STAMP(2);
+    if (p.xg) {
+      // The operand exists already (row * gamma as fp16): 16-byte asynchronous copies straight into the swizzled
+      // tiles, and the rows' statistics from the partial sums (four threads per row, fixed order).
+      const int wt = tid;  // 0 .. 255
+      for (int i = wt; i < UN * (D_MODEL / 8); i += NWORK * 32) {
+        const int r = i >> 7, c = i & 127, kb = c >> 3, chunk = c & 7;  // row, 16-byte chunk of the row
+        unsigned char* dst = xs + kb * XB_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
+        if (r < p.rows) cp_async16(dst, p.xg + (size_t)r * p.lda + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      {
+        const int r = wt >> 2, part = wt & 3;
+        float s1 = 0.f, s2 = 0.f;
+        if (r < p.rows) {
+          const float2* ps = reinterpret_cast<const float2*>(p.stats) + (size_t)r * p.stats_slots;
+          for (int i = part; i < p.stats_slots; i += 4) {
+            const float2 v = __ldcg(ps + i);
+            s1 += v.x, s2 += v.y;
+          }
+        }
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 2), s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+        if (part == 0) {
+          const float mean = s1 * (1.f / D_MODEL);
+          s_mean[r] = mean;
+          s_rstd[r] = rsqrtf(fmaxf(s2 * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
+        }
+      }
+      cp_async_wait_all();
+      asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the statistics are read by other warps later
+    } else
     // two rows per warp in flight (the loads of a row are one L2 round trip; a warp has 64 / 8 rows to do)
     for (int r0 = warp; r0 < UN; r0 += 2 * NWORK) {
       float v[2][32];
@@ -311,9 +349,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
           : "r"(taddr)
           : "memory");
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      const float sc = s_scale[ch], bi = s_bias[ch];
+      const float sc = s_scale[ch], bi = s_bias[ch], gch = s_g[ch];
+      if (p.xg) {
 #pragma unroll
-      for (int r = 0; r < 32; ++r) outs[(hf * 32 + r) * OUT_LD + ch] = __uint_as_float(d[r]) * sc + bi;
+        for (int r = 0; r < 32; ++r)
+          outs[(hf * 32 + r) * OUT_LD + ch] =
+              s_rstd[hf * 32 + r] * (__uint_as_float(d[r]) * sc - s_mean[hf * 32 + r] * gch) + bi;
+      } else {
+#pragma unroll
+        for (int r = 0; r < 32; ++r) outs[(hf * 32 + r) * OUT_LD + ch] = __uint_as_float(d[r]) * sc + bi;
+      }
     }
     tc_fence_before();
     asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the workers only
@@ -371,20 +416,30 @@ __global__ void tile_int8_umma_kernel(const int8_t* __restrict__ q, int n, int k
 
 namespace b200dec_detail {
 
-int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows, float* part_max,
-                   int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream) {
-  B200_REQUIRE(w && w->w && w->scale && x && ln && ln->w && ln->b && part_max && part_idx && status,
+// x: fp32 rows normalised by the kernel (xg null), or xg: the ready fp16 operand (row * gamma) with its partial sums
+// (x null; w->ln_g / ln_bias fold the LayerNorm into the epilogue).
+int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, const float* stats, int stats_slots,
+                   const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx, float* logits,
+                   int32_t* status, int pdl, void* stream) {
+  B200_REQUIRE(w && w->w && w->scale && (x || xg) && ln && ln->w && ln->b && part_max && part_idx && status,
                "head_umma: null pointer");
+  B200_REQUIRE(!xg || (stats && stats_slots >= 1 && w->ln_g && w->ln_bias && ((uintptr_t)xg & 15) == 0 && lda % 8 == 0),
+               "head_umma: the fp16 operand comes with its partial sums and the weight's ln_g / ln_bias");
   B200_REQUIRE(w->kind == B200DEC_W_INT8_UMMA && w->k == D_MODEL && w->n % UM == 0, "head_umma: weight kind %d (%d, %d)",
                w->kind, w->n, w->k);
   B200_REQUIRE(rows >= 1 && rows <= 128 && lda % 4 == 0 && ((uintptr_t)x & 15) == 0, "head_umma: rows %d lda %d", rows,
                lda);
+  if (xg) x = nullptr;
   cudaError_t e = cudaFuncSetAttribute(head_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma: smem attribute: %s", cudaGetErrorString(e));
   const int np = w->n / UM;
   for (int r0 = 0; r0 < rows; r0 += UN) {  // 64 rows per pass (the weights stream once per pass)
     HeadArgs a{};
-    a.w = (const uint8_t*)w->w, a.scale = w->scale, a.bias = w->bias, a.x = x + (size_t)r0 * lda;
+    a.w = (const uint8_t*)w->w, a.scale = w->scale, a.bias = w->bias, a.x = x ? x + (size_t)r0 * lda : nullptr;
+    if (xg) {
+      a.xg = (const __half*)xg + (size_t)r0 * lda, a.stats = stats + (size_t)r0 * stats_slots * 2;
+      a.stats_slots = stats_slots, a.ln_g = w->ln_g, a.ln_bias = w->ln_bias;
+    }
     a.ln_w = ln->w, a.ln_b = ln->b, a.ln_eps = ln->eps;
     a.part_max = part_max + (size_t)r0 * np, a.part_idx = part_idx + (size_t)r0 * np;
     a.logits = logits ? logits + (size_t)r0 * w->n : nullptr;
@@ -412,7 +467,15 @@ int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* str
 
 int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,
                       float* part_max, int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream) {
-  return head_umma_impl(w, x, ln, lda, rows, part_max, part_idx, logits, status, pdl, stream);
+  return head_umma_impl(w, x, nullptr, nullptr, 0, ln, lda, rows, part_max, part_idx, logits, status, pdl, stream);
+}
+
+int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const float* stats, int stats_slots,
+                             const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx,
+                             float* logits, int32_t* status, int pdl, void* stream) {
+  B200_REQUIRE(xg, "head_umma_linked: null operand");
+  return head_umma_impl(w, nullptr, xg, stats, stats_slots, ln, lda, rows, part_max, part_idx, logits, status, pdl,
+                        stream);
 }
 
 }  // extern "C"

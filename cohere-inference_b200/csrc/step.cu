@@ -10,8 +10,9 @@ int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200de
                 int out_kind, int ldo, int act, int pdl, void* stream, const b200dec_ln_link* link);
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
               int* pidx, float* logits, int pdl, void* stream);
-int head_umma_impl(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows, float* part_max,
-                   int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream);
+int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, const float* stats, int stats_slots,
+                   const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx, float* logits,
+                   int32_t* status, int pdl, void* stream);
 int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos, const void* embed,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                   float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream,
@@ -89,6 +90,8 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     B200_REQUIRE(b200dec_linear_stat_slots(&l0.o) <= STAT_SLOTS && b200dec_linear_stat_slots(&l0.co) <= STAT_SLOTS &&
                      b200dec_linear_stat_slots(&l0.fc2) <= STAT_SLOTS, "step: more finishing CTAs than statistic slots");
   }
+  // the tcgen05 vocabulary projection takes the last fc2's rows the same way when its weight carries the folded vectors
+  const bool head_linked = xh && pl->head.kind == B200DEC_W_INT8_UMMA && pl->head.ln_g && pl->head.ln_bias;
   auto producer = [&](const float* gamma) {
     b200dec_ln_link l{};
     if (xh && gamma) l.next_gamma = gamma, l.out16 = xh, l.stats_out = stats;
@@ -117,7 +120,7 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     const b200dec_ln_link r1 = reader(i == 0 ? 1 : b200dec_linear_stat_slots(&pl->layer[i - 1].fc2)),
                           p2 = producer(ly.ln2.w), r2 = reader(b200dec_linear_stat_slots(&ly.o)),
                           p3 = producer(ly.ln3.w), r3 = reader(b200dec_linear_stat_slots(&ly.co)),
-                          p1 = producer(i + 1 < pl->layers ? pl->layer[i + 1].ln1.w : nullptr);
+                          p1 = producer(i + 1 < pl->layers ? pl->layer[i + 1].ln1.w : head_linked ? pl->final_ln.w : nullptr);
     B200_TRY(linear_impl(&ly.qkv, ln_src, ln_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream, &r1));
     if (pl->kv_int8 && paired)
@@ -156,13 +159,14 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     B200_TRY(linear_impl(&ly.co, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
                          pdl_after, stream, &p3));
     B200_TRY(linear_impl(&ly.fc1, ln_src, ln_kind, &ly.ln3, D_MODEL, rows, mid, ok_a, ffn, pl->act, pdl, stream, &r3));
-    // the last layer's fc2 feeds the vocabulary projection, which reads the fp32 rows: no link
+    // the last layer's fc2 feeds the vocabulary projection
     B200_TRY(linear_impl(&ly.fc2, mid, pl->a_kind, nullptr, ffn, rows, x, B200DEC_OUT_F32_ADD, D_MODEL,
                          B200DEC_ACT_NONE, pdl, stream, &p1));
   }
   if (pl->head.kind == B200DEC_W_INT8_UMMA)
-    B200_TRY(head_umma_impl(&pl->head, x, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pl->status, pdl,
-                            stream));
+    B200_TRY(head_umma_impl(&pl->head, head_linked ? nullptr : x, head_linked ? xh : nullptr, stats,
+                            b200dec_linear_stat_slots(&pl->layer[pl->layers - 1].fc2), &pl->final_ln, D_MODEL, rows,
+                            head_max, head_idx, logits, pl->status, pdl, stream));
   else
     B200_TRY(head_impl(&pl->head, x, pl->head_a_kind, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pdl,
                        stream));

@@ -83,6 +83,8 @@ PROTOTYPES = {
                                       C.c_int, vp]),
     "b200dec_head_partials": (C.c_int, [C.POINTER(Weight)]),
     "b200dec_head_umma": (C.c_int, [C.POINTER(Weight), vp, C.POINTER(Norm), C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp]),
+    "b200dec_head_umma_linked": (C.c_int, [C.POINTER(Weight), vp, vp, C.c_int, C.POINTER(Norm), C.c_int, C.c_int, vp, vp,
+                                           vp, vp, C.c_int, vp]),
     "b200dec_tile_int8_umma": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_pick": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp, vp, vp, C.c_int,
                                C.c_int, vp, C.c_int, vp]),

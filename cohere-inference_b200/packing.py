@@ -141,8 +141,8 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    if kind == nv.W_INT8_UMMA:  # the tcgen05 vocabulary projection: one CTA per 128 channels, LayerNorm done in-kernel
-        warps, ksplit, ln = 4, 1, None
+    if kind == nv.W_INT8_UMMA:  # the tcgen05 vocabulary projection: one CTA per 128 channels, no tile choice
+        warps, ksplit = 4, 1
     else:
         warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
     ln_g = ln_bias = None

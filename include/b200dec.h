@@ -196,6 +196,12 @@ int b200dec_head_partials(const b200dec_weight* w);
  * reference code as b200dec_head_argmax. status receives B200DEC_ST_TIMEOUT if a bounded wait ran out. */
 int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,
                       float* part_max, int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream);
+/* The same with the LayerNorm's input handed over as in b200dec_ln_link: xg (rows, lda) fp16 = row * gamma (the out16
+ * of the projection that produced the rows, or of b200dec_ln_rows16) and its partial sums stats (rows, stats_slots,
+ * 2); the normalisation is folded into the epilogue with w->ln_g / w->ln_bias (ln supplies eps). */
+int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const float* stats, int stats_slots,
+                             const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx,
+                             float* logits, int32_t* status, int pdl, void* stream);
 /* q (n, k) int8 row-major (b200dec_quantize_rows) -> the 8 KB block layout of b200dec_head_umma, n*k bytes. */
 int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* stream);
 /* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and

@@ -346,6 +346,26 @@ def test_head_umma(nv, pk, rows, n):
         t = lg.reshape(rows, np_, 128)
         assert np.array_equal(pm.cpu().numpy(), t.max(-1))
         assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * 128)
+    # the same rows handed over as the ready fp16 operand (row * gamma) with their sums: LayerNorm folded into the epilogue
+    pl = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA, ln=(g_d, b_d))
+    wl = pl.struct()
+    xg = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    sums = torch.zeros(rows, 2, device="cuda")
+    nv.check(nv.lib().b200dec_ln_rows16(nv.ptr(a_d), nv.ptr(g_d), rows, nv.ptr(xg), nv.ptr(sums), nv.stream_ptr()))
+    pm = torch.full((rows, np_), -7.0, device="cuda")
+    pi = torch.full((rows, np_), -7, dtype=torch.int32, device="cuda")
+    logits = torch.zeros(rows, n, device="cuda")
+    nv.check(nv.lib().b200dec_head_umma_linked(C.byref(wl), nv.ptr(xg), nv.ptr(sums), 1, C.byref(norm), k, rows,
+                                               nv.ptr(pm), nv.ptr(pi), nv.ptr(logits), nv.ptr(status), 0,
+                                               nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    want = (layer_norm(a, gam, bet, 1e-5).astype(np.float64) @ wd.astype(np.float64).T + b).astype(np.float32)
+    lg = logits.cpu().numpy()
+    np.testing.assert_allclose(lg, want, atol=4e-3, rtol=1e-4)
+    t = lg.reshape(rows, np_, 128)
+    assert np.array_equal(pm.cpu().numpy(), t.max(-1))
+    assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * 128)
 
 
 # ---- row kernels ---------------------------------------------------------------------------------------------------------

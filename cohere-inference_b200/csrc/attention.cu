@@ -160,110 +160,106 @@ DEVI float q8_float(uint32_t biased_word, int j) {
   return __uint_as_float(__byte_perm(biased_word, 0x4B400000u, 0x7650 | j)) - 12583040.f;
 }
 
-// The same pass as attend_range over int8 caches: a key (or value) of D int8 is read by D / 16 lanes with one 16-byte
-// load each. The row's new key and value are rounded to bf16, quantised into the cache, and attended in that step as
-// the bf16 values (the quantised copy serves the later steps), as the reference does.
+// The same pass as attend_range over int8 caches, with the same lane layout: a key (or value) of D int8 is read by
+// D / 8 lanes with one 8-byte load each, its scale by every lane of the group. The row's new key and value are rounded
+// to bf16, quantised into the cache, and attended in that step as the bf16 values (the quantised copy serves the later
+// steps), as the reference does.
 template <int D, bool SELF>
 DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int start, int end, bool with_new,
                           float* s_m, float* s_l, float (*s_acc)[D + 4], float& M, float& L, float& O) {
-  constexpr int LPK = D / 16;          // lanes per key
+  constexpr int LPK = D / 8;           // lanes per key
   constexpr int NG = NTHREADS / LPK;   // key groups per CTA
   constexpr int U = 4;                 // keys in flight per group
   const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
   const int8_t* k8 = reinterpret_cast<const int8_t*>(p.k);
   const int8_t* v8 = reinterpret_cast<const int8_t*>(p.v);
 
-  float q[16];
+  float q[8];
   {
-    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * 16;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float4 a = ld_cg_f4(qp + 4 * i);
-      q[4 * i] = a.x * p.scale_log2, q[4 * i + 1] = a.y * p.scale_log2;
-      q[4 * i + 2] = a.z * p.scale_log2, q[4 * i + 3] = a.w * p.scale_log2;
-    }
+    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * 8;
+    const float4 a = ld_cg_f4(qp), b = ld_cg_f4(qp + 4);
+    q[0] = a.x * p.scale_log2, q[1] = a.y * p.scale_log2, q[2] = a.z * p.scale_log2, q[3] = a.w * p.scale_log2;
+    q[4] = b.x * p.scale_log2, q[5] = b.y * p.scale_log2, q[6] = b.z * p.scale_log2, q[7] = b.w * p.scale_log2;
   }
   const size_t vec0 = ((size_t)s * p.H + h) * p.cap;  // index of key 0: scales, and * D the vectors
-  float m = -1e30f, l = 0.f, acc[16];
+  float m = -1e30f, l = 0.f, acc[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
-  // kf, vf: the lane's 16 dims of a key and a value as floats still to be multiplied by ksc, vsc
-  auto attend = [&](const float (&kf)[16], float ksc, const float (&vf)[16], float vsc, bool valid) {
-    float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; i += 2) d0 += q[i] * kf[i], d1 += q[i + 1] * kf[i + 1];
-    float d = d0 + d1;
+  // kf, vf: the lane's 8 dims of a key and a value as floats still to be multiplied by ksc, vsc
+  auto attend = [&](const float (&kf)[8], float ksc, const float (&vf)[8], float vsc, bool valid) {
+    float d = (q[0] * kf[0] + q[1] * kf[1]) + (q[2] * kf[2] + q[3] * kf[3]) + (q[4] * kf[4] + q[5] * kf[5]) +
+              (q[6] * kf[6] + q[7] * kf[7]);
 #pragma unroll
     for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
     const float sc = valid ? d * ksc : -INFINITY;
     const float mn = fmaxf(m, sc), a = ex2(m - mn), e0 = ex2(sc - mn), e = e0 * vsc;
     l = l * a + e0;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) acc[i] = acc[i] * a + e * vf[i];
+    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * a + e * vf[i];
     m = mn;
   };
-  auto widen = [&](const uint4& w, float (&f)[16]) {
-    const uint32_t b[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+  auto widen = [&](const uint2& w, float (&f)[8]) {
+    const uint32_t b0 = w.x ^ 0x80808080u, b1 = w.y ^ 0x80808080u;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) f[i] = q8_float(b[i >> 2], i & 3);
+    for (int i = 0; i < 4; ++i) f[i] = q8_float(b0, i), f[4 + i] = q8_float(b1, i);
   };
 
   if (SELF && with_new && tid < 32) {
     // warp 0: group 0 (lanes 0 .. LPK-1) holds the new key and value; all lanes go through the shuffles
-    const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 16;
+    const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 8;
     const float* vp = kp + p.H * D;
-    float kn[16], vn[16];
+    float kn[8], vn[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       const float4 a = ld_cg_f4(kp + 4 * i), b = ld_cg_f4(vp + 4 * i);
       const uint32_t k01 = pack_bf16(a.x, a.y), k23 = pack_bf16(a.z, a.w), v01 = pack_bf16(b.x, b.y), v23 = pack_bf16(b.z, b.w);
       kn[4 * i] = bf16_lo(k01), kn[4 * i + 1] = bf16_hi(k01), kn[4 * i + 2] = bf16_lo(k23), kn[4 * i + 3] = bf16_hi(k23);
       vn[4 * i] = bf16_lo(v01), vn[4 * i + 1] = bf16_hi(v01), vn[4 * i + 2] = bf16_lo(v23), vn[4 * i + 3] = bf16_hi(v23);
     }
-    auto quantise = [&](const float (&f)[16], int8_t* dst, float* scale) {
+    auto quantise = [&](const float (&f)[8], int8_t* dst, float* scale) {
       float mx = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(f[i]));
+      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
 #pragma unroll
       for (int o = 1; o < LPK; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float sc = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f, inv = __fdiv_rn(1.f, sc);
-      uint32_t w[4] = {0, 0, 0, 0};
+      uint32_t w[2] = {0, 0};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int i = 0; i < 8; ++i) {
         const int qi = __float2int_rn(fminf(fmaxf(__fmul_rn(f[i], inv), -127.f), 127.f));
         w[i >> 2] |= (uint32_t)(qi & 0xff) << ((i & 3) * 8);
       }
       if (grp == 0) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
         if (gl == 0) *scale = sc;
       }
     };
-    quantise(kn, const_cast<int8_t*>(k8) + (vec0 + n) * D + gl * 16, p.ks + vec0 + n);
-    quantise(vn, const_cast<int8_t*>(v8) + (vec0 + n) * D + gl * 16, p.vs + vec0 + n);
+    quantise(kn, const_cast<int8_t*>(k8) + (vec0 + n) * D + gl * 8, p.ks + vec0 + n);
+    quantise(vn, const_cast<int8_t*>(v8) + (vec0 + n) * D + gl * 8, p.vs + vec0 + n);
     attend(kn, 1.f, vn, 1.f, grp == 0);
   }
 
-  const int8_t* kb = k8 + vec0 * D + gl * 16;
-  const int8_t* vb = v8 + vec0 * D + gl * 16;
+  const int8_t* kb = k8 + vec0 * D + gl * 8;
+  const int8_t* vb = v8 + vec0 * D + gl * 8;
   const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
   for (int j0 = first; j0 < end; j0 += NG * U) {
     const int j = j0 + (grp % (32 / LPK));
-    uint4 kk[U], vv[U];
+    uint2 kk[U], vv[U];
     float ksc[U], vsc[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int jj = j + u * NG;
       const bool ok = jj < end;
-      kk[u] = ok ? ld_stream16(kb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
-      vv[u] = ok ? ld_stream16(vb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+      kk[u] = ok ? ld_stream8(kb + (size_t)jj * D) : make_uint2(0, 0);
+      vv[u] = ok ? ld_stream8(vb + (size_t)jj * D) : make_uint2(0, 0);
       ksc[u] = ok ? __uint_as_float(ld_stream4(p.ks + vec0 + jj)) : 1.f;
       vsc[u] = ok ? __uint_as_float(ld_stream4(p.vs + vec0 + jj)) : 1.f;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (j0 + u * NG < end) {  // warp-uniform condition
-        float kf[16], vf[16];
+        float kf[8], vf[8];
         widen(kk[u], kf), widen(vv[u], vf);
         attend(kf, ksc[u], vf, vsc[u], j + u * NG < end);
       }
@@ -273,13 +269,13 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
   __syncthreads();  // the arrays may still be read by a previous pass
   if (gl == 0) s_m[grp] = m, s_l[grp] = l;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) s_acc[grp][gl * 16 + i] = acc[i];
+  for (int i = 0; i < 8; ++i) s_acc[grp][gl * 8 + i] = acc[i];
   __syncthreads();
   M = -1e30f, L = 0.f, O = 0.f;
   if (tid < D) {
-#pragma unroll 8
+#pragma unroll
     for (int gi = 0; gi < NG; ++gi) M = fmaxf(M, s_m[gi]);
-#pragma unroll 8
+#pragma unroll
     for (int gi = 0; gi < NG; ++gi) {
       const float w = ex2(s_m[gi] - M);
       L += w * s_l[gi];
@@ -320,8 +316,8 @@ DEVI void row_state(const AttnArgs& p, int r, bool report, int& s, int& n) {
 }
 
 template <int D, bool SELF, bool Q8>
-__global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (Q8 ? D / 16 : D / 8);
+__global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ int s_last;
@@ -384,8 +380,8 @@ __global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_kernel(const A
 constexpr int PAIR_MAX_ROWS = 256;
 
 template <int D, bool SELF, bool TABLE, bool Q8>
-__global__ void __launch_bounds__(NTHREADS, Q8 ? 5 : 7) attention_pair_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (Q8 ? D / 16 : D / 8);
+__global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnArgs p) {
+  constexpr int NG = NTHREADS / (D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ float s_peer[D + 2];  // CTA 0: the partial its peer computed for the long row

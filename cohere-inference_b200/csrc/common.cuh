@@ -86,6 +86,11 @@ DEVI uint4 ld_stream16(const void* p) {
                : "l"(p));
   return v;
 }
+DEVI uint2 ld_stream8(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
 DEVI uint32_t ld_stream4(const void* p) {
   uint32_t v;
   asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));

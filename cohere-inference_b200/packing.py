@@ -89,7 +89,10 @@ def tile_config(n: int, k: int, kind: int, a_kind: int = nv.A_F16, ln: bool = Fa
              and (not ln or k == 1024)]
     assert valid, f"no tile for a ({n}, {k}) projection"
     for w, s in valid:
-        if fits(kind, a_kind, int(ln), w, s, k, max_rows):
+        # a LayerNorm-folding projection of an fp16-operand decoder stages the ready fp16 rows its producer left
+        # (B200DEC_A_F16_ROWS16): half the shared memory of converting fp32 rows, so larger tiles fit
+        q_kind = nv.A_F16_ROWS16 if (ln and a_kind == nv.A_F16 and kind != nv.W_BF16 and k // s <= 256) else a_kind
+        if fits(kind, q_kind, int(ln), w, s, k, max_rows):
             return w, s
     return valid[0]
 

@@ -32,6 +32,8 @@
 // In step s of a block a lane holds 4 consecutive k of its two channels: (k, k+1) is fragment slot (2t, 2t+1) and
 // (k+2, k+3) slot (2t+8, 2t+9); the activation fragment of the same lane takes the same 4 k, so the permutation of K
 // inside a 16-step never has to be undone.
+#include <cstdlib>
+
 #include "linear_kernel.cuh"
 
 using namespace b200dec_detail;
@@ -122,7 +124,11 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   } else {
     B200_REQUIRE(pmax && pidx, "head: null partials");
   }
-  if (rows > 64 && !fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, rows) &&
+  static const bool split_wide = getenv("B200DEC_FC2_ONE_PASS") == nullptr;
+  // K = 4096 at more than 64 rows: its 128-row tile takes a whole SM's shared memory, and clusters of eight such CTAs
+  // could not all be placed at once (some started 9 us late); two passes of 64 rows are faster
+  const bool two_pass_wide = split_wide && rows > 64 && w->k == 4096;
+  if (rows > 64 && (two_pass_wide || !fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, rows)) &&
       fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, 64)) {
     // this operand does not fit shared memory for 128 rows at this K slice: two passes of up to 64 rows (the weights
     // are read twice; projections sized with b200dec_linear_fits avoid this)

@@ -85,15 +85,29 @@ bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int ro
     case B200DEC_W_INT8: return fits_int8(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_BF16: return fits_bf16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_24: return fits_24(split, ln, warps, k, ksplit, rows);
+    case B200DEC_W_INT8_UMMA: return !split && ln == 2 && k == D_MODEL && rows <= 128;
   }
   return false;
 }
+
+}  // namespace
+namespace b200dec_detail {
+int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                     void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
+                     void* stream);
+}
+namespace {
 
 int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
                int out_kind, int ldo, int act, float* pmax, int* pidx, float* logits, int head, int pdl, void* stream,
                const b200dec_ln_link* link = nullptr) {
   B200_REQUIRE(w && w->w && a, "linear: null pointer");
   B200_REQUIRE(rows >= 1 && rows <= 128, "linear: rows %d outside 1..128", rows);
+  if (w->kind == B200DEC_W_INT8_UMMA) {  // the tcgen05 kernel of linear_umma.cu
+    B200_REQUIRE(!head && link && link->status, "linear: a tcgen05 projection goes through b200dec_linear_linked with a "
+                 "status word");
+    return linear_umma_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, link, link->status, pdl, stream);
+  }
   B200_REQUIRE(w->warps == 4 || w->warps == 8, "linear: warps must be 4 or 8");
   B200_REQUIRE(w->ksplit == 1 || w->ksplit == 2 || w->ksplit == 4 || w->ksplit == 8, "linear: ksplit %d", w->ksplit);
   B200_REQUIRE(w->n % (16 * w->warps) == 0 && w->k % w->ksplit == 0, "linear: shape (%d, %d) vs tile", w->n, w->k);

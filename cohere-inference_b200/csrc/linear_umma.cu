@@ -1,0 +1,318 @@
+// LayerNorm-folding projections (qkv, fc1) on the fifth-generation tensor cores, for dense int8 weights:
+// out(rows, N) = act(LayerNorm(x) W^T * scale + bias), rows <= 128, K = 1024, N a multiple of 128.
+//
+// Same decomposition as the mma.sync kernel of linear_kernel.cuh with 128 channels per CTA and K split over a cluster
+// of four (256 k each), but the multiply is 16 `tcgen05.mma` (M = 128 channels, N = 64 or 128 rows, K = 16) into
+// tensor memory instead of 128-256 `mma.sync` per warp:
+//   * weights: the CTA's four 8 KB blocks (b200dec_tile_int8_umma layout) go to registers before the dependency wait,
+//     are widened to fp16 (exact) and written as K-major 128-byte-swizzled tiles;
+//   * activations: the ready operand of the LayerNorm (row * gamma as fp16, see b200dec_ln_link) is copied with
+//     cp.async straight into swizzled tiles; the rows' statistics are added up by the cluster from the producer's
+//     partial sums, as in the mma.sync kernel;
+//   * D(128 x rows) comes back with tcgen05.ld (thread = channel), each warp pushes its 32 channels to the CTA of the
+//     cluster that owns them (128-byte rows through distributed shared memory), one cluster barrier, then the same
+//     epilogue: y = rstd * (acc * scale - mean * g) + ln_bias + bias, activation, fp16 or fp32 store.
+// The wait for the MMAs is bounded (B200DEC_ST_TIMEOUT); tensor memory is released on every path.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+using namespace b200dec_detail;
+namespace cg = cooperative_groups;
+
+namespace {
+
+constexpr int UM = 128;             // channels per CTA (MMA M)
+constexpr int KSPLIT = 4;           // CTAs per cluster
+constexpr int KSLICE = D_MODEL / KSPLIT;  // 256
+constexpr int KB = 64;              // k per block: one 128-byte row of fp16
+constexpr int NKB = KSLICE / KB;    // 4 blocks per CTA
+constexpr int RAW_BYTES = UM * KB;  // 8 KB of uint8 per block
+constexpr int A_BYTES = UM * KB * 2;
+constexpr int CPR = UM / KSPLIT;    // 32 channels finished by each CTA
+constexpr int GPR = CPR / 4;        // threads per row in the epilogue
+constexpr int NTHREADS = 256;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct UArgs {
+  const uint8_t* w;
+  const float* scale;
+  const float* bias;     // may be null
+  const __half* xg;      // (rows, lda) fp16 = row * gamma
+  const float* stats;    // (rows, stats_slots, 2)
+  const float* ln_g;
+  const float* ln_bias;
+  void* out;
+  int* status;
+  float ln_eps;
+  int lda, ldo, rows, N, out_kind, act, stats_slots;
+};
+
+template <int MB>
+struct USmem {
+  static constexpr int XB_BYTES = MB * KB * 2;  // one k-block of the activations
+  static constexpr int OFF_A = 0, OFF_X = NKB * A_BYTES, OFF_RECV = OFF_X + NKB * XB_BYTES,
+                       OFF_STATS = OFF_RECV + KSPLIT * MB * CPR * 4, USED = OFF_STATS + MB * 8;
+  static constexpr int BYTES = USED + 1024;  // slack to align the base to a swizzle atom
+};
+
+DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+DEVI void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+DEVI void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+DEVI void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+DEVI bool mbar_wait(uint64_t* bar, uint32_t parity) {  // bounded; false when the limit ran out
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// K-major tile with the 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart
+DEVI uint64_t umma_desc(uint32_t saddr) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+template <int N>
+DEVI void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  // fp16 x fp16 -> fp32, both operands K-major, M = 128
+  constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+DEVI void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// 16 values of uint8 = q + 128 -> 16 exact fp16 q
+DEVI void widen16(const uint4& r, uint4& lo, uint4& hi) {
+  const uint32_t in[4] = {r.x, r.y, r.z, r.w};
+  uint32_t out[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t a = __byte_perm(in[i], 0x64646464u, 0x4140), b = __byte_perm(in[i], 0x64646464u, 0x4342);
+    const __half2 off = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+    const __half2 ha = __hsub2(*reinterpret_cast<const __half2*>(&a), off);
+    const __half2 hb = __hsub2(*reinterpret_cast<const __half2*>(&b), off);
+    out[2 * i] = *reinterpret_cast<const uint32_t*>(&ha), out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&hb);
+  }
+  lo = make_uint4(out[0], out[1], out[2], out[3]), hi = make_uint4(out[4], out[5], out[6], out[7]);
+}
+DEVI float act_fn(float v, int act) {
+  if (act == B200DEC_ACT_RELU) return fmaxf(v, 0.f);
+  if (act == B200DEC_ACT_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  return v;
+}
+// 32 consecutive columns of this warp's 32 tensor-memory lanes
+DEVI void tmem_ld32(uint32_t taddr, uint32_t (&d)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
+        "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]),
+        "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]), "=r"(d[24]),
+        "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int MB>
+__global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p) {
+  using S = USmem<MB>;
+  extern __shared__ unsigned char dyn_smem[];
+  unsigned char* smem = dyn_smem + ((1024 - (smem_u32(dyn_smem) & 1023)) & 1023);
+  unsigned char* as = smem + S::OFF_A;
+  unsigned char* xs = smem + S::OFF_X;
+  float* recv = reinterpret_cast<float*>(smem + S::OFF_RECV);  // [KSPLIT][MB][CPR]
+  float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
+  __shared__ __align__(8) uint64_t d_full;
+  __shared__ uint32_t tmem_base;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = blockIdx.x, tile = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile = its tensor-memory lane
+  const int hf = warp >> 2;               // its half: 16-k pieces 2 hf, 2 hf + 1 of a block; rows hf * MB / 2 ..
+
+  // ---- prologue: the CTA's four weight blocks into registers (independent of the previous kernel) -----------------
+  uint4 wr[NKB][2];
+  {
+    const uint8_t* wsrc = p.w + ((size_t)tile * (D_MODEL / KB) + rank * NKB) * RAW_BYTES + ch * 16;
+#pragma unroll
+    for (int b = 0; b < NKB; ++b)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) wr[b][j] = ld_stream16(wsrc + (size_t)b * RAW_BYTES + (2 * hf + j) * 2048);
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&d_full)));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "n"(MB)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_wait();
+
+  // ---- stage this K slice of the operand into swizzled tiles; the cluster adds up the rows' statistics -------------
+  const int k0 = rank * KSLICE;
+  for (int i = tid; i < MB * (KSLICE / 8); i += NTHREADS) {
+    const int r = i >> 5, c = i & 31, kb = c >> 3, chunk = c & 7;
+    unsigned char* dst = xs + kb * S::XB_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
+    if (r < p.rows) cp_async16(dst, p.xg + (size_t)r * p.lda + k0 + c * 8);
+    else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+  }
+  {
+    constexpr int RPW = (MB + KSPLIT * 8 - 1) / (KSPLIT * 8);  // rows per warp, all their loads issued at once
+    float2 v[RPW][4];
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {
+      const int r = rank + KSPLIT * (warp + 8 * j);
+      const float2* part = reinterpret_cast<const float2*>(p.stats) + (size_t)r * p.stats_slots;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        v[j][i] = (r < p.rows && lane + 32 * i < p.stats_slots) ? __ldcg(part + lane + 32 * i) : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {
+      const int r = rank + KSPLIT * (warp + 8 * j);
+      float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
+      s1 = warp_sum(s1), s2 = warp_sum(s2);
+      if (r < p.rows && lane < KSPLIT) cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
+    }
+  }
+  // ---- widen the weights into the A tiles ---------------------------------------------------------------------------
+#pragma unroll
+  for (int b = 0; b < NKB; ++b) {
+    unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int pj = 2 * hf + j;  // k = 16 pj .. 16 pj + 15 of the block: chunks 2 pj and 2 pj + 1 of the row
+      uint4 lo, hi;
+      widen16(wr[b][j], lo, hi);
+      *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+    }
+  }
+  cp_async_wait_all();
+  fence_async_shared();  // the MMA reads both operands through the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  pdl_trigger();
+  const uint32_t tmem_d = tmem_base;
+
+  // ---- multiply: one lane, 16 instructions, completion through an mbarrier -------------------------------------------
+  if (tid == 0) {
+#pragma unroll
+    for (int b = 0; b < NKB; ++b) {
+      const uint32_t a0 = smem_u32(as + b * A_BYTES), b0 = smem_u32(xs + b * S::XB_BYTES);
+#pragma unroll
+      for (int k = 0; k < KB / 16; ++k) umma_f16<MB>(tmem_d, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), (b | k) != 0);
+    }
+    umma_commit(&d_full);
+  }
+  const bool got = mbar_wait(&d_full, 0);
+  if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+  tc_fence_after();
+
+  // ---- partial tile -> the CTAs that own its channels: this warp's 32 channels all belong to CTA (warp & 3) -----------
+  {
+    float* dst = cluster.map_shared_rank(recv, warp & 3) + (size_t)rank * MB * CPR + lane;
+#pragma unroll
+    for (int c0 = 0; c0 < MB / 2; c0 += 32) {
+      uint32_t d[32];
+      tmem_ld32(tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(hf * (MB / 2) + c0), d);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int r = hf * (MB / 2) + c0 + i;
+        if (r < p.rows) dst[r * CPR] = __uint_as_float(d[i]);
+      }
+    }
+  }
+  // the per-channel vectors of the epilogue, fetched before the barrier
+  const int items = p.rows * GPR;
+  const int n_mine = tile * UM + rank * CPR + (tid % GPR) * 4;
+  const float4 sc = __ldg(reinterpret_cast<const float4*>(p.scale + n_mine));
+  const float4 gg = __ldg(reinterpret_cast<const float4*>(p.ln_g + n_mine));
+  const float4 lb = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
+  const float4 bb = p.bias ? __ldg(reinterpret_cast<const float4*>(p.bias + n_mine)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  tc_fence_before();
+  cluster.sync();  // all partials and statistics have landed; nobody touches remote shared memory after this
+
+  for (int it = tid; it < items; it += NTHREADS) {  // NTHREADS % GPR == 0: a thread keeps its four channels
+    const int r = it / GPR, c4 = it % GPR;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < KSPLIT; ++q) {  // fixed rank order
+      const float4 v = *reinterpret_cast<const float4*>(recv + (q * MB + r) * CPR + c4 * 4);
+      s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+    }
+    const float2 st = stats[r];
+    const float mean = st.x * (1.f / D_MODEL);
+    const float rstd = rsqrtf(fmaxf(st.y * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
+    s.x = rstd * (s.x * sc.x - mean * gg.x) + lb.x + bb.x, s.y = rstd * (s.y * sc.y - mean * gg.y) + lb.y + bb.y;
+    s.z = rstd * (s.z * sc.z - mean * gg.z) + lb.z + bb.z, s.w = rstd * (s.w * sc.w - mean * gg.w) + lb.w + bb.w;
+    s.x = act_fn(s.x, p.act), s.y = act_fn(s.y, p.act), s.z = act_fn(s.z, p.act), s.w = act_fn(s.w, p.act);
+    const int n = tile * UM + rank * CPR + c4 * 4;
+    if (p.out_kind == B200DEC_OUT_F16)
+      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)r * p.ldo + n) =
+          make_uint2(pack_f16(s.x, s.y), pack_f16(s.z, s.w));
+    else
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)r * p.ldo + n) = s;
+  }
+  // ---- release the tensor memory ----------------------------------------------------------------------------------------
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(MB) : "memory");
+  }
+}
+
+template <int MB>
+int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
+  auto kern = linear_umma_kernel<MB>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, USmem<MB>::BYTES);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
+  e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), USmem<MB>::BYTES, stream, KSPLIT, pdl, a);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma launch: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace
+
+namespace b200dec_detail {
+
+// A LayerNorm-folding projection whose weight is of kind B200DEC_W_INT8_UMMA: the rows come as in b200dec_ln_link.
+int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
+                     void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
+                     void* stream) {
+  B200_REQUIRE(w && w->w && w->scale && w->ln_g && w->ln_bias && a && ln && out && status, "linear_umma: null pointer");
+  B200_REQUIRE(w->k == D_MODEL && w->n % UM == 0, "linear_umma: shape (%d, %d)", w->n, w->k);
+  B200_REQUIRE(a_kind == B200DEC_A_F16_ROWS16 && link && link->stats_in && link->stats_slots >= 1 &&
+                   link->stats_slots <= 128, "linear_umma: the rows come as a ready fp16 operand with partial sums");
+  B200_REQUIRE(rows >= 1 && rows <= 128 && lda % 8 == 0 && ldo % 4 == 0 && ((uintptr_t)a & 15) == 0 &&
+                   ((uintptr_t)out & 15) == 0, "linear_umma: rows %d lda %d ldo %d", rows, lda, ldo);
+  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "linear_umma: out_kind %d", out_kind);
+  UArgs p{};
+  p.w = (const uint8_t*)w->w, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a;
+  p.stats = link->stats_in, p.stats_slots = link->stats_slots, p.ln_g = w->ln_g, p.ln_bias = w->ln_bias;
+  p.out = out, p.status = status, p.ln_eps = ln->eps;
+  p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.out_kind = out_kind, p.act = act;
+  return rows <= 64 ? launch_umma<64>(p, pdl, (cudaStream_t)stream) : launch_umma<128>(p, pdl, (cudaStream_t)stream);
+}
+
+}  // namespace b200dec_detail

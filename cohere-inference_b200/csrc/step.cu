@@ -99,7 +99,7 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   };
   auto reader = [&](int slots) {
     b200dec_ln_link l{};
-    if (xh) l.stats_in = stats, l.stats_slots = slots;
+    if (xh) l.stats_in = stats, l.stats_slots = slots, l.status = pl->status;
     return l;
   };
 

@@ -33,7 +33,8 @@ class Norm(C.Structure):
 
 
 class LnLink(C.Structure):
-    _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32), ("_pad", i32)]
+    _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32), ("_pad", i32),
+                ("status", vp)]
 
 
 class Layer(C.Structure):

@@ -30,7 +30,8 @@ ACTS = {"relu": nv.ACT_RELU, "gelu": nv.ACT_GELU}
 class _Layer:
     """Packed projections and fp32 norms of one decoder layer (reference: _Layer, stream_decoder.py:51-62)."""
 
-    def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool):
+    def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool,
+                 umma_kind: int | None = None):
         sa, ca = layer.self_attn, layer.encoder_attn
         f = lambda t: t.detach().float().contiguous()  # noqa: E731
         self.norms = [(f(m.weight), f(m.bias), float(m.eps)) for m in
@@ -41,11 +42,12 @@ class _Layer:
             return pack_linear(w, b, k, keep_reference, a_kind=a_kind, ln=ln and ln[:2], max_rows=max_rows)
 
         self.qkv = pk(cat(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight),
-                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), kind, self.norms[0])
+                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), umma_kind or kind, self.norms[0])
         self.o = pk(sa.o_proj.weight, sa.o_proj.bias, kind)
         self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, kind, self.norms[1])
         self.co = pk(ca.o_proj.weight, ca.o_proj.bias, kind)
-        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, ffn_kind, self.norms[2])
+        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias,
+                      umma_kind if (umma_kind is not None and ffn_kind == nv.W_INT8) else ffn_kind, self.norms[2])
         self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, ffn_kind)
 
     def projections(self) -> list[PackedLinear]:
@@ -59,7 +61,7 @@ class StreamDecoder:
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
-                 head_umma: bool = True, kv_int8: bool = False):
+                 head_umma: bool = True, kv_int8: bool = False, proj_umma: bool = True):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -100,7 +102,9 @@ class StreamDecoder:
             self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
             ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
             self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
-            self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference) for layer in dec.layers]
+            # proj_umma: the qkv and (dense) fc1 projections on the tcgen05 kernel of csrc/linear_umma.cu
+            umma = nv.W_INT8_UMMA if (proj_umma and int8) else None
+            self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma) for layer in dec.layers]
             head_kind = nv.W_INT8_UMMA if (head_umma and int8 and self.vocab % 128 == 0) else kind
             self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
                                     a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)

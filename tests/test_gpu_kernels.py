@@ -244,6 +244,43 @@ def test_linear_linked_layernorm(nv, pk, kind, n, rows):
         np.testing.assert_allclose(out.cpu().numpy(), want.astype(np.float32), atol=4e-3, rtol=1e-4)
 
 
+@pytest.mark.parametrize("n,act,out_kind", [(3072, "ACT_NONE", "OUT_F32"), (4096, "ACT_GELU", "OUT_F16"),
+                                            (1024, "ACT_RELU", "OUT_F32")])
+@pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])
+def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
+    """The tcgen05 projection (weight kind W_INT8_UMMA): LayerNorm folded, rows handed over as the ready fp16 operand
+    with partial sums; equals act(LayerNorm(rows) W^T + b) on the dequantised weights. Twice in a row (tensor memory
+    and the barrier are set up per launch)."""
+    rng = np.random.default_rng(n + rows)
+    k = 1024
+    lib = nv.lib()
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    x = (rng.standard_normal((rows, k)) * (1 + rng.random((rows, 1))) + 0.3 * rng.standard_normal((rows, 1))).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    g_d, b_d, x_d = cuda(gam), cuda(bet), cuda(x)
+    pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA, ln=(g_d, b_d))
+    norm, cs = nv.norm(g_d, b_d, 1e-5), pc.struct()
+    xg = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    sums = torch.zeros(rows, 2, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nv.check(lib.b200dec_ln_rows16(nv.ptr(x_d), nv.ptr(g_d), rows, nv.ptr(xg), nv.ptr(sums), nv.stream_ptr()))
+    ok, ak = getattr(nv, out_kind), getattr(nv, act)
+    want = layer_norm(x, gam, bet, 1e-5).astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy().astype(np.float64).T + b
+    want = want.astype(np.float32)
+    if ak != nv.ACT_NONE:
+        want = activation({nv.ACT_RELU: "relu", nv.ACT_GELU: "gelu"}[ak], want)
+    link = nv.LnLink(None, None, None, nv.ptr(sums), 1, 0, nv.ptr(status))
+    for _ in range(2):
+        out = torch.zeros(rows, n, dtype=torch.float16 if ok == nv.OUT_F16 else torch.float32, device="cuda")
+        nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(xg), nv.A_F16_ROWS16, C.byref(norm), k, rows, nv.ptr(out), ok,
+                                           n, ak, C.byref(link), 0, nv.stream_ptr()))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=5e-3, rtol=2e-3 if ok == nv.OUT_F16 else 1e-4)
+
+
 @pytest.mark.parametrize("act", ["ACT_RELU", "ACT_GELU"])
 @pytest.mark.parametrize("out_kind", ["OUT_F16", "OUT_F32_ADD"])
 def test_linear_epilogues(nv, pk, act, out_kind):

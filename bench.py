@@ -116,7 +116,7 @@ def run_ours(args) -> None:
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
-                        head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8, proj_umma=not args.no_proj_umma)
+                        head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8, proj_umma=False if args.no_proj_umma else (args.proj_umma or True))
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -440,7 +440,8 @@ def main() -> None:
     ap.add_argument("--no-pdl", action="store_true", help="launch the step's kernels without programmatic dependent launch")
     ap.add_argument("--pdl", type=int, default=7, help="which launches are programmatic: 1 projection after projection, "
                     "2 attention, 4 projection after attention (sum them)")
-    ap.add_argument("--no-proj-umma", action="store_true", help="qkv and fc1 on mma.sync instead of tcgen05")
+    ap.add_argument("--no-proj-umma", action="store_true", help="the layer projections on mma.sync instead of tcgen05")
+    ap.add_argument("--proj-umma", default="", help="all, or a subset of qkv,o,cq,co,fc1,fc2 on tcgen05 (default: qkv,fc1)")
     ap.add_argument("--no-head-umma", action="store_true", help="vocabulary projection on mma.sync instead of tcgen05")
     ap.add_argument("--no-head-split", action="store_true", help="vocabulary projection on a single fp16 operand")
     ap.add_argument("--kv-int8", action="store_true", help="int8 KV caches with per-vector scales (the reference's int8 "

@@ -85,7 +85,9 @@ bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int ro
     case B200DEC_W_INT8: return fits_int8(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_BF16: return fits_bf16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_24: return fits_24(split, ln, warps, k, ksplit, rows);
-    case B200DEC_W_INT8_UMMA: return !split && ln == 2 && k == D_MODEL && rows <= 128;
+    case B200DEC_W_INT8_UMMA:  // linear_umma.cu: fp16 rows, plain or as a LayerNorm's ready operand
+      return !split && rows <= 128 && ln != 1 &&
+             ((k == D_MODEL && (ksplit == 4 || ksplit == 8)) || (k == 4 * D_MODEL && ksplit == 8 && ln == 0));
   }
   return false;
 }
@@ -209,7 +211,10 @@ int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, cons
   return head_impl(w, a, a_kind, ln, lda, rows, part_max, part_idx, logits, pdl, stream);
 }
 
-int b200dec_linear_stat_slots(const b200dec_weight* w) { return w ? (w->n / (16 * w->warps)) * w->ksplit : 0; }
+int b200dec_linear_stat_slots(const b200dec_weight* w) {
+  if (!w) return 0;
+  return w->kind == B200DEC_W_INT8_UMMA ? (w->n / 128) * w->ksplit : (w->n / (16 * w->warps)) * w->ksplit;
+}
 
 int b200dec_head_partials(const b200dec_weight* w) {
   if (!w) return 0;

@@ -1,9 +1,10 @@
-// LayerNorm-folding projections (qkv, fc1) on the fifth-generation tensor cores, for dense int8 weights:
-// out(rows, N) = act(LayerNorm(x) W^T * scale + bias), rows <= 128, K = 1024, N a multiple of 128.
+// The layer projections on the fifth-generation tensor cores, for dense int8 weights:
+// out(rows, N) = act(a' W^T * scale + bias) [+ out], a' = the fp16 rows a or LayerNorm of the rows behind a ready
+// fp16 operand; rows <= 128, K = 1024 (split 4 or 8 ways) or 4096 (8 ways, 64 rows per pass), N a multiple of 128.
 //
-// Same decomposition as the mma.sync kernel of linear_kernel.cuh with 128 channels per CTA and K split over a cluster
-// of four (256 k each), but the multiply is 16 `tcgen05.mma` (M = 128 channels, N = 64 or 128 rows, K = 16) into
-// tensor memory instead of 128-256 `mma.sync` per warp:
+// Same decomposition as the mma.sync kernel of linear_kernel.cuh with 128 channels per CTA and K split over a
+// cluster, but the multiply is 8-32 `tcgen05.mma` (M = 128 channels, N = 64 or 128 rows, K = 16) into tensor memory
+// instead of 64-256 `mma.sync` per warp:
 //   * weights: the CTA's four 8 KB blocks (b200dec_tile_int8_umma layout) go to registers before the dependency wait,
 //     are widened to fp16 (exact) and written as K-major 128-byte-swizzled tiles;
 //   * activations: the ready operand of the LayerNorm (row * gamma as fp16, see b200dec_ln_link) is copied with
@@ -11,7 +12,9 @@
 //     partial sums, as in the mma.sync kernel;
 //   * D(128 x rows) comes back with tcgen05.ld (thread = channel), each warp pushes its 32 channels to the CTA of the
 //     cluster that owns them (128-byte rows through distributed shared memory), one cluster barrier, then the same
-//     epilogue: y = rstd * (acc * scale - mean * g) + ln_bias + bias, activation, fp16 or fp32 store.
+//     epilogue: y = rstd * (acc * scale - mean * g) + ln_bias + bias (or acc * scale + bias), activation, fp16 or fp32
+//     store or add into the residual stream, and for a projection that updates the stream the next LayerNorm's
+//     operand and partial sums (b200dec_ln_link).
 // The wait for the MMAs is bounded (B200DEC_ST_TIMEOUT); tensor memory is released on every path.
 #include <cooperative_groups.h>
 
@@ -23,14 +26,9 @@ namespace cg = cooperative_groups;
 namespace {
 
 constexpr int UM = 128;             // channels per CTA (MMA M)
-constexpr int KSPLIT = 4;           // CTAs per cluster
-constexpr int KSLICE = D_MODEL / KSPLIT;  // 256
 constexpr int KB = 64;              // k per block: one 128-byte row of fp16
-constexpr int NKB = KSLICE / KB;    // 4 blocks per CTA
 constexpr int RAW_BYTES = UM * KB;  // 8 KB of uint8 per block
 constexpr int A_BYTES = UM * KB * 2;
-constexpr int CPR = UM / KSPLIT;    // 32 channels finished by each CTA
-constexpr int GPR = CPR / 4;        // threads per row in the epilogue
 constexpr int NTHREADS = 256;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -38,18 +36,24 @@ struct UArgs {
   const uint8_t* w;
   const float* scale;
   const float* bias;     // may be null
-  const __half* xg;      // (rows, lda) fp16 = row * gamma
-  const float* stats;    // (rows, stats_slots, 2)
+  const __half* xg;      // (rows, lda) fp16: the operand rows (with a LayerNorm: row * gamma)
+  const float* stats;    // LayerNorm: (rows, stats_slots, 2) partial sums of the rows
   const float* ln_g;
   const float* ln_bias;
   void* out;
+  // a projection that updates the residual stream: the next LayerNorm's operand and partial sums (or null)
+  const float* next_gamma;
+  __half* out16;
+  float* stats_out;
   int* status;
   float ln_eps;
-  int lda, ldo, rows, N, out_kind, act, stats_slots;
+  int lda, ldo, rows, N, K, out_kind, act, stats_slots;
 };
 
-template <int MB>
+// MB: row capacity (MMA N); KSPLIT: CTAs per cluster; NKB: 64-k blocks per CTA
+template <int MB, int KSPLIT, int NKB>
 struct USmem {
+  static constexpr int CPR = UM / KSPLIT;       // channels finished by each CTA
   static constexpr int XB_BYTES = MB * KB * 2;  // one k-block of the activations
   static constexpr int OFF_A = 0, OFF_X = NKB * A_BYTES, OFF_RECV = OFF_X + NKB * XB_BYTES,
                        OFF_STATS = OFF_RECV + KSPLIT * MB * CPR * 4, USED = OFF_STATS + MB * 8;
@@ -129,9 +133,10 @@ DEVI void tmem_ld32(uint32_t taddr, uint32_t (&d)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int MB>
+template <int MB, int KSPLIT, int NKB, bool LN>
 __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p) {
-  using S = USmem<MB>;
+  using S = USmem<MB, KSPLIT, NKB>;
+  constexpr int CPR = S::CPR, GPR = CPR / 4, KSLICE = NKB * KB;
   extern __shared__ unsigned char dyn_smem[];
   unsigned char* smem = dyn_smem + ((1024 - (smem_u32(dyn_smem) & 1023)) & 1023);
   unsigned char* as = smem + S::OFF_A;
@@ -147,10 +152,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile = its tensor-memory lane
   const int hf = warp >> 2;               // its half: 16-k pieces 2 hf, 2 hf + 1 of a block; rows hf * MB / 2 ..
 
-  // ---- prologue: the CTA's four weight blocks into registers (independent of the previous kernel) -----------------
+  // ---- prologue: the CTA's weight blocks into registers (independent of the previous kernel) ----------------------
   uint4 wr[NKB][2];
   {
-    const uint8_t* wsrc = p.w + ((size_t)tile * (D_MODEL / KB) + rank * NKB) * RAW_BYTES + ch * 16;
+    const uint8_t* wsrc = p.w + ((size_t)tile * (p.K / KB) + rank * NKB) * RAW_BYTES + ch * 16;
 #pragma unroll
     for (int b = 0; b < NKB; ++b)
 #pragma unroll
@@ -169,13 +174,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
 
   // ---- stage this K slice of the operand into swizzled tiles; the cluster adds up the rows' statistics -------------
   const int k0 = rank * KSLICE;
-  for (int i = tid; i < MB * (KSLICE / 8); i += NTHREADS) {
-    const int r = i >> 5, c = i & 31, kb = c >> 3, chunk = c & 7;
+  constexpr int CH = KSLICE / 8;  // 16-byte chunks per row
+  for (int i = tid; i < MB * CH; i += NTHREADS) {
+    const int r = i / CH, c = i % CH, kb = c >> 3, chunk = c & 7;
     unsigned char* dst = xs + kb * S::XB_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
     if (r < p.rows) cp_async16(dst, p.xg + (size_t)r * p.lda + k0 + c * 8);
     else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
   }
-  {
+  if constexpr (LN) {
     constexpr int RPW = (MB + KSPLIT * 8 - 1) / (KSPLIT * 8);  // rows per warp, all their loads issued at once
     float2 v[RPW][4];
 #pragma unroll
@@ -215,7 +221,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   pdl_trigger();
   const uint32_t tmem_d = tmem_base;
 
-  // ---- multiply: one lane, 16 instructions, completion through an mbarrier -------------------------------------------
+  // ---- multiply: one lane, 4 instructions per block, completion through an mbarrier ---------------------------------
   if (tid == 0) {
 #pragma unroll
     for (int b = 0; b < NKB; ++b) {
@@ -229,9 +235,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
   tc_fence_after();
 
-  // ---- partial tile -> the CTAs that own its channels: this warp's 32 channels all belong to CTA (warp & 3) -----------
+  // ---- partial tile -> the CTAs that own its channels (CPR consecutive channels each) ---------------------------------
   {
-    float* dst = cluster.map_shared_rank(recv, warp & 3) + (size_t)rank * MB * CPR + lane;
+    float* dst = cluster.map_shared_rank(recv, ch / CPR) + (size_t)rank * MB * CPR + ch % CPR;
 #pragma unroll
     for (int c0 = 0; c0 < MB / 2; c0 += 32) {
       uint32_t d[32];
@@ -243,36 +249,70 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
       }
     }
   }
-  // the per-channel vectors of the epilogue, fetched before the barrier
+  // the per-channel vectors of the epilogue (and the residual, for one item per thread), fetched before the barrier
   const int items = p.rows * GPR;
   const int n_mine = tile * UM + rank * CPR + (tid % GPR) * 4;
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f), one4 = make_float4(1.f, 1.f, 1.f, 1.f);
   const float4 sc = __ldg(reinterpret_cast<const float4*>(p.scale + n_mine));
-  const float4 gg = __ldg(reinterpret_cast<const float4*>(p.ln_g + n_mine));
-  const float4 lb = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
-  const float4 bb = p.bias ? __ldg(reinterpret_cast<const float4*>(p.bias + n_mine)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4 gg = LN ? __ldg(reinterpret_cast<const float4*>(p.ln_g + n_mine)) : zero4;
+  const float4 lb = LN ? __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine)) : zero4;
+  const float4 bb = p.bias ? __ldg(reinterpret_cast<const float4*>(p.bias + n_mine)) : zero4;
+  const float4 gn = p.out16 ? __ldg(reinterpret_cast<const float4*>(p.next_gamma + n_mine)) : one4;
+  const bool add = p.out_kind == B200DEC_OUT_F32_ADD;
+  float4 resid = zero4;
+  if (add && tid < items)
+    resid = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + (size_t)(tid / GPR) * p.ldo + n_mine));
   tc_fence_before();
   cluster.sync();  // all partials and statistics have landed; nobody touches remote shared memory after this
 
-  for (int it = tid; it < items; it += NTHREADS) {  // NTHREADS % GPR == 0: a thread keeps its four channels
-    const int r = it / GPR, c4 = it % GPR;
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int q = 0; q < KSPLIT; ++q) {  // fixed rank order
-      const float4 v = *reinterpret_cast<const float4*>(recv + (q * MB + r) * CPR + c4 * 4);
-      s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
-    }
-    const float2 st = stats[r];
-    const float mean = st.x * (1.f / D_MODEL);
-    const float rstd = rsqrtf(fmaxf(st.y * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
-    s.x = rstd * (s.x * sc.x - mean * gg.x) + lb.x + bb.x, s.y = rstd * (s.y * sc.y - mean * gg.y) + lb.y + bb.y;
-    s.z = rstd * (s.z * sc.z - mean * gg.z) + lb.z + bb.z, s.w = rstd * (s.w * sc.w - mean * gg.w) + lb.w + bb.w;
-    s.x = act_fn(s.x, p.act), s.y = act_fn(s.y, p.act), s.z = act_fn(s.z, p.act), s.w = act_fn(s.w, p.act);
+  const int padded = (items + 31) & ~31;
+  for (int it = tid; it < padded; it += NTHREADS) {  // NTHREADS % GPR == 0: a thread keeps its four channels
+    const bool live = it < items;
+    const int r = live ? it / GPR : 0, c4 = it % GPR;
     const int n = tile * UM + rank * CPR + c4 * 4;
-    if (p.out_kind == B200DEC_OUT_F16)
-      *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)r * p.ldo + n) =
-          make_uint2(pack_f16(s.x, s.y), pack_f16(s.z, s.w));
-    else
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)r * p.ldo + n) = s;
+    float4 s = zero4;
+    if (live) {
+#pragma unroll
+      for (int q = 0; q < KSPLIT; ++q) {  // fixed rank order
+        const float4 v = *reinterpret_cast<const float4*>(recv + (q * MB + r) * CPR + c4 * 4);
+        s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+      }
+      s.x *= sc.x, s.y *= sc.y, s.z *= sc.z, s.w *= sc.w;
+      if constexpr (LN) {
+        const float2 st = stats[r];
+        const float mean = st.x * (1.f / D_MODEL);
+        const float rstd = rsqrtf(fmaxf(st.y * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
+        s.x = rstd * (s.x - mean * gg.x) + lb.x, s.y = rstd * (s.y - mean * gg.y) + lb.y;
+        s.z = rstd * (s.z - mean * gg.z) + lb.z, s.w = rstd * (s.w - mean * gg.w) + lb.w;
+      }
+      s.x += bb.x, s.y += bb.y, s.z += bb.z, s.w += bb.w;
+      s.x = act_fn(s.x, p.act), s.y = act_fn(s.y, p.act), s.z = act_fn(s.z, p.act), s.w = act_fn(s.w, p.act);
+      if (p.out_kind == B200DEC_OUT_F16) {
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + (size_t)r * p.ldo + n) =
+            make_uint2(pack_f16(s.x, s.y), pack_f16(s.z, s.w));
+      } else {
+        float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)r * p.ldo + n);
+        if (add) {
+          const float4 x = it == tid ? resid : __ldcg(o);
+          s.x += x.x, s.y += x.y, s.z += x.z, s.w += x.w;
+          if (p.out16)
+            *reinterpret_cast<uint2*>(p.out16 + (size_t)r * p.ldo + n) =
+                make_uint2(pack_f16(s.x * gn.x, s.y * gn.y), pack_f16(s.z * gn.z, s.w * gn.w));
+        }
+        *o = s;
+      }
+    }
+    if (p.stats_out) {  // warp-uniform; the row's GPR consecutive lanes add up their channels, one of them publishes
+      float p1 = live ? (s.x + s.y) + (s.z + s.w) : 0.f;
+      float p2 = live ? (s.x * s.x + s.y * s.y) + (s.z * s.z + s.w * s.w) : 0.f;
+#pragma unroll
+      for (int o = 1; o < GPR; o <<= 1) {
+        p1 += __shfl_xor_sync(0xffffffffu, p1, o);
+        p2 += __shfl_xor_sync(0xffffffffu, p2, o);
+      }
+      if (live && c4 == 0)
+        reinterpret_cast<float2*>(p.stats_out)[(size_t)r * (gridDim.y * KSPLIT) + tile * KSPLIT + rank] = make_float2(p1, p2);
+    }
   }
   // ---- release the tensor memory ----------------------------------------------------------------------------------------
   __syncthreads();
@@ -282,37 +322,79 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   }
 }
 
-template <int MB>
+template <int MB, int KSPLIT, int NKB, bool LN>
 int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
-  auto kern = linear_umma_kernel<MB>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, USmem<MB>::BYTES);
-  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
-  e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), USmem<MB>::BYTES, stream, KSPLIT, pdl, a);
-  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma launch: %s", cudaGetErrorString(e));
-  return 0;
+  using S = USmem<MB, KSPLIT, NKB>;
+  if constexpr (S::BYTES > 227 * 1024 - 512) {
+    return fail(B200DEC_EINVAL, "linear_umma: %d rows of K / %d do not fit shared memory", MB, KSPLIT);
+  } else {
+    auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES);
+    if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
+    e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), S::BYTES, stream, KSPLIT, pdl, a);
+    if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma launch: %s", cudaGetErrorString(e));
+    return 0;
+  }
+}
+
+template <int KSPLIT, int NKB>
+int launch_rows(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
+  if (a.rows <= 64) return ln ? launch_umma<64, KSPLIT, NKB, true>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false>(a, pdl, s);
+  return ln ? launch_umma<128, KSPLIT, NKB, true>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false>(a, pdl, s);
 }
 
 }  // namespace
 
 namespace b200dec_detail {
 
-// A LayerNorm-folding projection whose weight is of kind B200DEC_W_INT8_UMMA: the rows come as in b200dec_ln_link.
+// A projection whose weight is of kind B200DEC_W_INT8_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
+// operand and link->stats_in its partial sums (b200dec_ln_link). w->ksplit: CTAs per cluster (K = 1024: 4 or 8;
+// K = 4096: 8, 64 rows per pass).
 int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                      void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
                      void* stream) {
-  B200_REQUIRE(w && w->w && w->scale && w->ln_g && w->ln_bias && a && ln && out && status, "linear_umma: null pointer");
-  B200_REQUIRE(w->k == D_MODEL && w->n % UM == 0, "linear_umma: shape (%d, %d)", w->n, w->k);
-  B200_REQUIRE(a_kind == B200DEC_A_F16_ROWS16 && link && link->stats_in && link->stats_slots >= 1 &&
-                   link->stats_slots <= 128, "linear_umma: the rows come as a ready fp16 operand with partial sums");
-  B200_REQUIRE(rows >= 1 && rows <= 128 && lda % 8 == 0 && ldo % 4 == 0 && ((uintptr_t)a & 15) == 0 &&
+  B200_REQUIRE(w && w->w && w->scale && a && out && status, "linear_umma: null pointer");
+  B200_REQUIRE((w->k == D_MODEL && (w->ksplit == 4 || w->ksplit == 8)) || (w->k == 4 * D_MODEL && w->ksplit == 8),
+               "linear_umma: K %d split %d ways", w->k, w->ksplit);
+  B200_REQUIRE(w->n % UM == 0, "linear_umma: N %d", w->n);
+  const b200dec_ln_link none{};
+  const b200dec_ln_link lk = link ? *link : none;
+  if (ln)
+    B200_REQUIRE(a_kind == B200DEC_A_F16_ROWS16 && w->k == D_MODEL && w->ln_g && w->ln_bias && lk.stats_in &&
+                     lk.stats_slots >= 1 && lk.stats_slots <= 128,
+                 "linear_umma: LayerNorm rows come as a ready fp16 operand with partial sums");
+  else
+    B200_REQUIRE(a_kind == B200DEC_A_F16 || a_kind == B200DEC_A_F16_ROWS16, "linear_umma: fp16 rows only");
+  B200_REQUIRE(rows >= 1 && rows <= 128 && lda % 8 == 0 && lda >= w->k && ldo % 4 == 0 && ((uintptr_t)a & 15) == 0 &&
                    ((uintptr_t)out & 15) == 0, "linear_umma: rows %d lda %d ldo %d", rows, lda, ldo);
-  B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "linear_umma: out_kind %d", out_kind);
-  UArgs p{};
-  p.w = (const uint8_t*)w->w, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a;
-  p.stats = link->stats_in, p.stats_slots = link->stats_slots, p.ln_g = w->ln_g, p.ln_bias = w->ln_bias;
-  p.out = out, p.status = status, p.ln_eps = ln->eps;
-  p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.out_kind = out_kind, p.act = act;
-  return rows <= 64 ? launch_umma<64>(p, pdl, (cudaStream_t)stream) : launch_umma<128>(p, pdl, (cudaStream_t)stream);
+  B200_REQUIRE(out_kind >= 0 && out_kind <= 2, "linear_umma: out_kind %d", out_kind);
+  B200_REQUIRE(!lk.out16 || (out_kind == B200DEC_OUT_F32_ADD && lk.next_gamma && lk.stats_out),
+               "linear_umma: the next LayerNorm's operand goes with OUT_F32_ADD, its gamma and the sums");
+  const int slots = (w->n / UM) * w->ksplit;
+  const int pass = w->k == D_MODEL ? 128 : 64;  // K = 4096: the operands of 128 rows do not fit shared memory
+  for (int r0 = 0; r0 < rows; r0 += pass) {
+    UArgs p{};
+    p.w = (const uint8_t*)w->w, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a + (size_t)r0 * lda;
+    if (ln) {
+      p.stats = lk.stats_in + (size_t)r0 * lk.stats_slots * 2, p.stats_slots = lk.stats_slots;
+      p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
+    }
+    const size_t osz = out_kind == B200DEC_OUT_F16 ? 2 : 4;
+    p.out = (char*)out + (size_t)r0 * ldo * osz, p.status = status;
+    if (lk.out16) {
+      p.next_gamma = lk.next_gamma, p.out16 = (__half*)lk.out16 + (size_t)r0 * ldo;
+      p.stats_out = lk.stats_out + (size_t)r0 * slots * 2;
+    }
+    p.lda = lda, p.ldo = ldo, p.rows = rows - r0 < pass ? rows - r0 : pass, p.N = w->n, p.K = w->k;
+    p.out_kind = out_kind, p.act = act;
+    cudaStream_t s = (cudaStream_t)stream;
+    int rc;
+    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, ln != nullptr, pdl, s);
+    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, ln != nullptr, pdl, s);
+    else rc = launch_rows<8, 8>(p, false, pdl, s);
+    if (rc) return rc;
+  }
+  return 0;
 }
 
 }  // namespace b200dec_detail

@@ -144,8 +144,8 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    if kind == nv.W_INT8_UMMA:  # the tcgen05 vocabulary projection: one CTA per 128 channels, no tile choice
-        warps, ksplit = 4, 1
+    if kind == nv.W_INT8_UMMA:  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
+        warps, ksplit = 8, (4 if (k == 1024 and n >= 3072) else 8)  # 96, 128 or 64 CTAs (the head ignores the split)
     else:
         warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
     ln_g = ln_bias = None

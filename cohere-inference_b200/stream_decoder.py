@@ -31,7 +31,7 @@ class _Layer:
     """Packed projections and fp32 norms of one decoder layer (reference: _Layer, stream_decoder.py:51-62)."""
 
     def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool,
-                 umma_kind: int | None = None):
+                 umma: frozenset = frozenset()):
         sa, ca = layer.self_attn, layer.encoder_attn
         f = lambda t: t.detach().float().contiguous()  # noqa: E731
         self.norms = [(f(m.weight), f(m.bias), float(m.eps)) for m in
@@ -41,14 +41,16 @@ class _Layer:
         def pk(w, b, k, ln=None):  # ln: the norm this projection folds in (it reads the fp32 residual stream)
             return pack_linear(w, b, k, keep_reference, a_kind=a_kind, ln=ln and ln[:2], max_rows=max_rows)
 
+        # umma: the projections that run on the tcgen05 kernel (dense int8 only)
+        uk = lambda name, k: nv.W_INT8_UMMA if (name in umma and k == nv.W_INT8) else k  # noqa: E731
+
         self.qkv = pk(cat(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight),
-                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), umma_kind or kind, self.norms[0])
-        self.o = pk(sa.o_proj.weight, sa.o_proj.bias, kind)
-        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, kind, self.norms[1])
-        self.co = pk(ca.o_proj.weight, ca.o_proj.bias, kind)
-        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias,
-                      umma_kind if (umma_kind is not None and ffn_kind == nv.W_INT8) else ffn_kind, self.norms[2])
-        self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, ffn_kind)
+                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), uk("qkv", kind), self.norms[0])
+        self.o = pk(sa.o_proj.weight, sa.o_proj.bias, uk("o", kind))
+        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, uk("cq", kind), self.norms[1])
+        self.co = pk(ca.o_proj.weight, ca.o_proj.bias, uk("co", kind))
+        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, uk("fc1", ffn_kind), self.norms[2])
+        self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, uk("fc2", ffn_kind))
 
     def projections(self) -> list[PackedLinear]:
         return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
@@ -61,7 +63,7 @@ class StreamDecoder:
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
-                 head_umma: bool = True, kv_int8: bool = False, proj_umma: bool = True):
+                 head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -102,8 +104,11 @@ class StreamDecoder:
             self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
             ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
             self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
-            # proj_umma: the qkv and (dense) fc1 projections on the tcgen05 kernel of csrc/linear_umma.cu
-            umma = nv.W_INT8_UMMA if (proj_umma and int8) else None
+            # proj_umma: the dense int8 projections that run on the tcgen05 kernel of csrc/linear_umma.cu: True = qkv and
+            # fc1 (the two with enough multiply per CTA to gain; the narrow ones and fc2 measured 1-2 % slower there
+            # than on mma.sync), "all", or a comma-separated subset of qkv,o,cq,co,fc1,fc2
+            names = "qkv,fc1" if proj_umma is True else "qkv,o,cq,co,fc1,fc2" if proj_umma == "all" else (proj_umma or "")
+            umma = frozenset(n for n in names.split(",") if n) if int8 else frozenset()
             self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma) for layer in dec.layers]
             head_kind = nv.W_INT8_UMMA if (head_umma and int8 and self.vocab % 128 == 0) else kind
             self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,

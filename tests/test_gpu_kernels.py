@@ -281,6 +281,51 @@ def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
         np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=5e-3, rtol=2e-3 if ok == nv.OUT_F16 else 1e-4)
 
 
+@pytest.mark.parametrize("n,k", [(1024, 1024), (1024, 4096), (3072, 1024)])
+@pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])
+def test_linear_umma_plain_and_stream_update(nv, pk, n, k, rows):
+    """The tcgen05 projection without a LayerNorm (the o, cross-o and fc2 shapes: K split 4 or 8 ways, K = 4096 in
+    passes of 64 rows): a plain fp32 store, then the residual update that also leaves the next LayerNorm's fp16
+    operand and partial sums."""
+    rng = np.random.default_rng(n + k + rows)
+    lib = nv.lib()
+    a = (rng.standard_normal((rows, k)) * 0.5).astype(np.float16)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA)
+    cs = pc.struct()
+    a_d = cuda(a)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    prod = a.astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy().astype(np.float64).T + b
+    out = torch.zeros(rows, n, device="cuda")
+    link = nv.LnLink(None, None, None, None, 0, 0, nv.ptr(status))
+    nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(a_d), nv.A_F16, None, k, rows, nv.ptr(out), nv.OUT_F32, n,
+                                       nv.ACT_NONE, C.byref(link), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    np.testing.assert_allclose(out.cpu().numpy(), prod.astype(np.float32), atol=2e-3, rtol=1e-4)
+    if n != 1024:
+        return
+    x0 = rng.standard_normal((rows, n)).astype(np.float32)
+    gam = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    g_d = cuda(gam)
+    slots = lib.b200dec_linear_stat_slots(C.byref(cs))
+    assert slots == (n // 128) * pc.ksplit
+    for _ in range(2):
+        x = cuda(x0.copy())
+        x16 = torch.zeros(rows, n, dtype=torch.float16, device="cuda")
+        sums = torch.full((rows, slots, 2), float("nan"), device="cuda")
+        plink = nv.LnLink(nv.ptr(g_d), nv.ptr(x16), nv.ptr(sums), None, 0, 0, nv.ptr(status))
+        nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(a_d), nv.A_F16, None, k, rows, nv.ptr(x), nv.OUT_F32_ADD, n,
+                                           nv.ACT_NONE, C.byref(plink), 0, nv.stream_ptr()))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        xn = x.cpu().numpy()
+        np.testing.assert_allclose(xn, (x0 + prod).astype(np.float32), atol=2e-3, rtol=1e-4)
+        assert torch.equal(x16, (x * g_d).to(torch.float16))
+        np.testing.assert_allclose(sums.sum(1).cpu().numpy().astype(np.float64), _row_sums(xn), rtol=1e-5, atol=1e-3)
+
+
 @pytest.mark.parametrize("act", ["ACT_RELU", "ACT_GELU"])
 @pytest.mark.parametrize("out_kind", ["OUT_F16", "OUT_F32_ADD"])
 def test_linear_epilogues(nv, pk, act, out_kind):

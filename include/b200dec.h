@@ -21,9 +21,10 @@ extern "C" {
 
 enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* weight storage of one projection */
        B200DEC_W_INT8_UMMA = 3 };  /* int8 in the block layout of the tcgen05 kernels (b200dec_tile_int8_umma): the
-                                      vocabulary projection (b200dec_head_umma) and, through b200dec_linear_linked with
-                                      a_kind B200DEC_A_F16_ROWS16, LayerNorm-folding projections with K = 1024 and N a
-                                      multiple of 128 */
+                                      vocabulary projection (b200dec_head_umma) and, through b200dec_linear_linked,
+                                      layer projections on fp16 rows (a_kind B200DEC_A_F16, or B200DEC_A_F16_ROWS16
+                                      with a LayerNorm): N a multiple of 128, K = 1024 with w->ksplit 4 or 8, or
+                                      K = 4096 with w->ksplit 8 and no LayerNorm */
 enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1,  /* activation operand of a projection: one fp16, or hi + lo */
        B200DEC_A_F16_ROWS16 = 2 };  /* one fp16, and with a LayerNorm the rows handed in are its ready fp16 operand
                                       (see b200dec_ln_link) */
@@ -177,7 +178,8 @@ typedef struct b200dec_ln_link {
   const float* stats_in;
   int32_t stats_slots;
   int32_t _pad;
-  int32_t* status;  /* reader with a B200DEC_W_INT8_UMMA weight: the status word for a bounded wait that ran out */
+  int32_t* status;  /* required with a B200DEC_W_INT8_UMMA weight (reader, producer or neither): the status word
+                       that receives B200DEC_ST_TIMEOUT if the bounded wait for the MMAs ran out */
 } b200dec_ln_link;
 int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                           void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,

@@ -19,7 +19,6 @@ import ctypes as C
 import os
 
 import torch
-import torch.nn.functional as F
 
 from . import native as nv
 from .packing import PackedLinear, dequantized, pack_linear
@@ -54,6 +53,38 @@ class _Layer:
 
     def projections(self) -> list[PackedLinear]:
         return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
+
+
+class _PrefillLinear:
+    """y = x W^T + b for the cross-K/V prefill (fill_cross; reference: the two F.linear of stream_decoder.py:232), as
+    ONE bf16 tensor-core GEMM (library GEMM, fp32 accumulate and output) that keeps fp32-level accuracy: with
+    x = xh + xl and W = Wh + Wl (bf16 pairs), x W^T = xh Wh^T + xl Wh^T + xh Wl^T up to 2^-17 relative, written as a
+    single product of [xh | xl | xh | 1 1 0..] with [Wh | Wh | Wl | bh bl 0..] (the bias rides in two extra columns)."""
+
+    def __init__(self, w: torch.Tensor, b: torch.Tensor):
+        n, k = w.shape
+        self.n, self.k, self.ka = n, k, 3 * k + 8
+        bf = torch.bfloat16
+        wh = w.to(bf)
+        wa = torch.zeros(n, self.ka, dtype=bf, device=w.device)
+        wa[:, :k] = wh
+        wa[:, k:2 * k] = wh
+        wa[:, 2 * k:3 * k] = (w - wh.float()).to(bf)
+        bh = b.to(bf)
+        wa[:, 3 * k] = bh
+        wa[:, 3 * k + 1] = (b - bh.float()).to(bf)
+        self.wa = wa
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        k = self.k
+        xa = torch.empty(x.shape[0], self.ka, dtype=torch.bfloat16, device=x.device)
+        xh = x.to(torch.bfloat16)
+        xa[:, :k] = xh
+        xa[:, k:2 * k] = x - xh.float()
+        xa[:, 2 * k:3 * k] = xh
+        xa[:, 3 * k:] = 0
+        xa[:, 3 * k:3 * k + 2] = 1
+        return torch.mm(xa, self.wa.t(), out_dtype=torch.float32)
 
 
 class StreamDecoder:
@@ -115,11 +146,12 @@ class StreamDecoder:
                                     a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
             # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection, kept as the
             # fp32 values the quantised (or bf16) weights stand for
-            self.proj = (dequantized(dec.proj.weight, kind), f(dec.proj.bias))
-            self.cross_w = torch.cat([dequantized(w, kind) for layer in dec.layers
-                                      for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)])
-            self.cross_b = torch.cat([f(b) for layer in dec.layers
-                                      for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)])
+            self.proj = _PrefillLinear(dequantized(dec.proj.weight, kind), f(dec.proj.bias))
+            self.cross = _PrefillLinear(
+                torch.cat([dequantized(w, kind) for layer in dec.layers
+                           for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)]),
+                torch.cat([f(b) for layer in dec.layers
+                           for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)]))
             L, S = len(self.layers), slots
             self.slots, self.dummy = S, S
             self.max_prompt = max_prompt
@@ -310,7 +342,7 @@ class StreamDecoder:
         assert hidden.shape[0] == sum(lengths) and len(lengths) == len(slots)
         assert all(1 <= n <= self.frames for n in lengths), "frames per piece outside 1..%d" % self.frames
         assert all(0 <= s < self.slots for s in slots)
-        kv = F.linear(F.linear(hidden.float(), *self.proj), self.cross_w, self.cross_b).contiguous()
+        kv = self.cross(self.proj(hidden.float()))
         slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lengths))
         frame_of = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths])
         slot_of, frame_of = slot_of.to(self.device, non_blocking=True), frame_of.to(self.device, non_blocking=True)

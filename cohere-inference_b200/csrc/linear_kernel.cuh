@@ -132,7 +132,16 @@ struct LinSmem {
 // which equals LayerNorm(a) W^T + bias exactly (g and bias' are precomputed per output channel). NW warps = 16 NW
 // channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
-__global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p) {
+__global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) {
+  LinArgs p = p_in;
+  if constexpr (MB == 32) {  // the rows are dealt over blockIdx.z, 32 each (plain fp16 operand only)
+    const int row0 = blockIdx.z * 32;
+    p.a = reinterpret_cast<const char*>(p.a) + (size_t)row0 * p.lda * 2;
+    p.out = reinterpret_cast<char*>(p.out) + (size_t)row0 * p.ldo * (p.out_kind == B200DEC_OUT_F16 ? 2 : 4);
+    if (p.out16) p.out16 += (size_t)row0 * p.ldo;
+    if (p.stats_out) p.stats_out += (size_t)row0 * (gridDim.y * KSPLIT) * 2;
+    p.rows = p.rows - row0 < 32 ? p.rows - row0 : 32;
+  }
   using T = WTraits<WT>;
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
@@ -539,7 +548,7 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
   // idempotent; set on every call so that it holds on every device of the process
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear: smem attribute: %s", cudaGetErrorString(e));
-  const dim3 grid(KSPLIT, a.N / (NW * 16));
+  const dim3 grid(KSPLIT, a.N / (NW * 16), MB == 32 ? (a.rows + 31) / 32 : 1);
 #ifdef B200DEC_TIMELINE
   LinArgs b = a;
   b.stamps = timeline_next(grid.x * grid.y, (LN ? 2000000 : 1000000) + a.N / 16 * 1000 + KSLICE * KSPLIT / 16);
@@ -554,6 +563,12 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT>
 int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
   if (a.rows <= 16) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s);
+  // fc2 (K = 4096 in slices of 512, 64 channels per CTA): 33-64 rows as two CTAs of 32 rows per tile, two per SM, so
+  // that eight warps instead of four feed the SM's tensor pipes and each CTA stages half the operand
+  if constexpr (!SPLIT && LN == 0 && KSLICE == 512 && KSPLIT == 8 && NW == 4 && WT != B200DEC_W_BF16) {
+    static const bool deal_rows = getenv("B200DEC_NO_ROW_DEAL") == nullptr;
+    if (deal_rows && a.rows > 32 && a.rows <= 64 && !a.head) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s);
+  }
   if (a.rows <= 64) {
     if constexpr (LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024)
       return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>(a, pdl, s);

@@ -281,22 +281,25 @@ def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
         np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=5e-3, rtol=2e-3 if ok == nv.OUT_F16 else 1e-4)
 
 
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_INT8", "W_INT8_24"])
 @pytest.mark.parametrize("n,k", [(1024, 1024), (1024, 4096), (3072, 1024)])
-@pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])
-def test_linear_umma_plain_and_stream_update(nv, pk, n, k, rows):
-    """The tcgen05 projection without a LayerNorm (the o, cross-o and fc2 shapes: K split 4 or 8 ways, K = 4096 in
-    passes of 64 rows): a plain fp32 store, then the residual update that also leaves the next LayerNorm's fp16
-    operand and partial sums."""
+@pytest.mark.parametrize("rows", [1, 13, 33, 50, 64, 100, 128])
+def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
+    """A projection without a LayerNorm (the o, cross-o and fc2 shapes) on the tcgen05 kernel (K split 4 or 8 ways,
+    K = 4096 in passes of 64 rows) and on the mma.sync kernel (fc2 at 33-64 rows: the rows dealt over two CTAs per
+    tile): a plain fp32 store, then the residual update that also leaves the next LayerNorm's fp16 operand and
+    partial sums."""
     rng = np.random.default_rng(n + k + rows)
     lib = nv.lib()
+    kind = getattr(nv, kind)
     a = (rng.standard_normal((rows, k)) * 0.5).astype(np.float16)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     b = (rng.standard_normal(n) * 0.1).astype(np.float32)
-    pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA)
+    pc = pk.pack_linear(cuda(w), cuda(b), kind)
     cs = pc.struct()
     a_d = cuda(a)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    prod = a.astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy().astype(np.float64).T + b
+    prod = a.astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8_24 if kind == nv.W_INT8_24 else nv.W_INT8).cpu().numpy().astype(np.float64).T + b
     out = torch.zeros(rows, n, device="cuda")
     link = nv.LnLink(None, None, None, None, 0, 0, nv.ptr(status))
     nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(a_d), nv.A_F16, None, k, rows, nv.ptr(out), nv.OUT_F32, n,
@@ -310,7 +313,7 @@ def test_linear_umma_plain_and_stream_update(nv, pk, n, k, rows):
     gam = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
     g_d = cuda(gam)
     slots = lib.b200dec_linear_stat_slots(C.byref(cs))
-    assert slots == (n // 128) * pc.ksplit
+    assert kind != nv.W_INT8_UMMA or slots == (n // 128) * pc.ksplit
     for _ in range(2):
         x = cuda(x0.copy())
         x16 = torch.zeros(rows, n, dtype=torch.float16, device="cuda")

@@ -140,6 +140,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
     p.out = reinterpret_cast<char*>(p.out) + (size_t)row0 * p.ldo * (p.out_kind == B200DEC_OUT_F16 ? 2 : 4);
     if (p.out16) p.out16 += (size_t)row0 * p.ldo;
     if (p.stats_out) p.stats_out += (size_t)row0 * (gridDim.y * KSPLIT) * 2;
+    if (p.stats_in) p.stats_in += (size_t)row0 * p.stats_slots * 2;
     p.rows = p.rows - row0 < 32 ? p.rows - row0 : 32;
   }
   using T = WTraits<WT>;
@@ -563,11 +564,16 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT>
 int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
   if (a.rows <= 16) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s);
-  // fc2 (K = 4096 in slices of 512, 64 channels per CTA): 33-64 rows as two CTAs of 32 rows per tile, two per SM, so
-  // that eight warps instead of four feed the SM's tensor pipes and each CTA stages half the operand
-  if constexpr (!SPLIT && LN == 0 && KSLICE == 512 && KSPLIT == 8 && NW == 4 && WT != B200DEC_W_BF16) {
-    static const bool deal_rows = getenv("B200DEC_NO_ROW_DEAL") == nullptr;
-    if (deal_rows && a.rows > 32 && a.rows <= 64 && !a.head) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s);
+  // The 64-channel tiles with K split eight ways (fc2; o, cross-o; cross-q): 33-64 rows as two CTAs of 32 rows per
+  // tile, two per SM, so that eight warps instead of four feed the SM's tensor pipes, each CTA stages half the operand
+  // and two latency chains overlap (measured: p50 step 0.504 -> 0.479 ms at 64 rows). B200DEC_ROW_DEAL masks the three
+  // groups (1 | 2 | 4) for A/B runs.
+  if constexpr (!SPLIT && (LN == 0 || LN == 2) && (KSLICE == 512 || KSLICE == 128) && KSPLIT == 8 && NW == 4 &&
+                WT != B200DEC_W_BF16) {
+    static const int deal_rows = getenv("B200DEC_ROW_DEAL") ? atoi(getenv("B200DEC_ROW_DEAL")) : 7;
+    const int bit = KSLICE == 512 ? 1 : LN == 0 ? 2 : 4;
+    if ((deal_rows & bit) && a.rows > 32 && a.rows <= 64 && !a.head)
+      return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s);
   }
   if (a.rows <= 64) {
     if constexpr (LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024)

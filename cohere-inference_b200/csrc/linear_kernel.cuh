@@ -134,14 +134,14 @@ struct LinSmem {
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) {
   LinArgs p = p_in;
-  if constexpr (MB == 32) {  // the rows are dealt over blockIdx.z, 32 each (plain fp16 operand only)
-    const int row0 = blockIdx.z * 32;
+  if (gridDim.z > 1) {  // the rows are dealt over blockIdx.z, MB each (fp16 operands only)
+    const int row0 = blockIdx.z * MB;
     p.a = reinterpret_cast<const char*>(p.a) + (size_t)row0 * p.lda * 2;
     p.out = reinterpret_cast<char*>(p.out) + (size_t)row0 * p.ldo * (p.out_kind == B200DEC_OUT_F16 ? 2 : 4);
     if (p.out16) p.out16 += (size_t)row0 * p.ldo;
     if (p.stats_out) p.stats_out += (size_t)row0 * (gridDim.y * KSPLIT) * 2;
     if (p.stats_in) p.stats_in += (size_t)row0 * p.stats_slots * 2;
-    p.rows = p.rows - row0 < 32 ? p.rows - row0 : 32;
+    p.rows = p.rows - row0 < MB ? p.rows - row0 : MB;
   }
   using T = WTraits<WT>;
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
@@ -542,14 +542,14 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
 }
 
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
-int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
+int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream, bool deal = false) {
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   static_assert(S::TOTAL <= 227 * 1024, "tile does not fit in shared memory");
   auto kern = linear_kernel<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   // idempotent; set on every call so that it holds on every device of the process
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear: smem attribute: %s", cudaGetErrorString(e));
-  const dim3 grid(KSPLIT, a.N / (NW * 16), MB == 32 ? (a.rows + 31) / 32 : 1);
+  const dim3 grid(KSPLIT, a.N / (NW * 16), deal ? (a.rows + MB - 1) / MB : 1);  // deal: MB rows per CTA
 #ifdef B200DEC_TIMELINE
   LinArgs b = a;
   b.stamps = timeline_next(grid.x * grid.y, (LN ? 2000000 : 1000000) + a.N / 16 * 1000 + KSLICE * KSPLIT / 16);
@@ -564,16 +564,25 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream) {
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT>
 int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
   if (a.rows <= 16) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s);
-  // The 64-channel tiles with K split eight ways (fc2; o, cross-o; cross-q): 33-64 rows as two CTAs of 32 rows per
-  // tile, two per SM, so that eight warps instead of four feed the SM's tensor pipes, each CTA stages half the operand
-  // and two latency chains overlap (measured: p50 step 0.504 -> 0.479 ms at 64 rows). B200DEC_ROW_DEAL masks the three
-  // groups (1 | 2 | 4) for A/B runs.
-  if constexpr (!SPLIT && (LN == 0 || LN == 2) && (KSLICE == 512 || KSLICE == 128) && KSPLIT == 8 && NW == 4 &&
-                WT != B200DEC_W_BF16) {
-    static const int deal_rows = getenv("B200DEC_ROW_DEAL") ? atoi(getenv("B200DEC_ROW_DEAL")) : 7;
-    const int bit = KSLICE == 512 ? 1 : LN == 0 ? 2 : 4;
-    if ((deal_rows & bit) && a.rows > 32 && a.rows <= 64 && !a.head)
-      return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s);
+  // The 64-channel tiles with K split eight ways (fc2; o, cross-o; cross-q): above 32 rows the rows are dealt over
+  // several CTAs per tile that share an SM (grid.z), so that eight or more warps instead of four feed the SM's tensor
+  // pipes, each CTA stages a fraction of the operand and several latency chains overlap. Measured at 64 rows: p50 step
+  // 0.504 -> 0.467 ms. fc2 (K slices of 512, 140 registers): two CTAs of 32 rows; the K = 1024 ones (slices of 128, 94
+  // registers): four CTAs of 16 rows, above 64 rows four of 32. B200DEC_ROW_DEAL masks the groups for A/B runs
+  // (1 fc2, 2 o / cross-o, 4 cross-q, 16 the 16-row form, 32 above 64 rows; 8 the 8-warp LayerNorm readers, off).
+  if constexpr (!SPLIT && (LN == 0 || LN == 2) && WT != B200DEC_W_BF16 &&
+                (((KSLICE == 512 || KSLICE == 128) && KSPLIT == 8 && NW == 4) ||
+                 (KSLICE == 256 && KSPLIT == 4 && NW == 8 && LN == 2))) {
+    static const int deal_rows = getenv("B200DEC_ROW_DEAL") ? atoi(getenv("B200DEC_ROW_DEAL")) : 1 + 2 + 4 + 16 + 32;
+    const int bit = NW == 8 ? 8 : KSLICE == 512 ? 1 : LN == 0 ? 2 : 4;
+    if ((deal_rows & bit) && !a.head) {
+      if (a.rows > 32 && a.rows <= 64) {
+        if (KSLICE == 128 && (deal_rows & 16)) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s, true);
+        return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s, true);
+      }
+      if (a.rows > 64 && KSLICE == 128 && (deal_rows & 32))
+        return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s, true);
+    }
   }
   if (a.rows <= 64) {
     if constexpr (LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 64>::TOTAL <= 227 * 1024)

@@ -155,7 +155,9 @@ def make_config1() -> None:
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    ref = sys.argv[1]
     make_packers(ref)
     make_decoder_small()
     make_config1()

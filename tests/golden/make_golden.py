@@ -1,7 +1,7 @@
 """Generates the golden vectors in this directory. Run once in the build container, where the reference checkout and
 transformers are present; the tests only read the .npz files.
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 packers.npz   outputs of the reference's own pure-torch packers (kernels/stream_decoder.py prepare_w8,
               kernels/fast_encoder.py quantize_rows maths, kernels/sparse.py prune_24_magnitude / compress_24) on seeded

@@ -12,7 +12,11 @@ are timed after W warm-up passes.
              fill_cross (cross-K/V prefill), admit, 457 replays, finished rows read back to the host.
   roofline   the dominant kernel (attention over the bf16 KV cache): algorithmic KV bytes per launch / its launch
              duration measured here with CUDA events, against the measured HBM copy bandwidth; `step` gives the same
-             for the whole decoding step (weights + KV bytes / replay time).
+             for the whole decoding step (weights + KV bytes / replay time) and `classes` splits the step's time into
+             attention, layer projections and the rest (whole passes that launch only those kernels).
+  stream     BASELINE configs 4 and 5 as extra keys: the seeded request stream through 128 slots per GPU with the 2:4
+             feed-forward weights, admitted and evicted between graph replays (config 5: 8000 requests dealt
+             round-robin over the ranks).
   cpu_baseline / --impl reference   the reference's CPU arithmetic (transformers fp32 decoder, else the numpy port) on
              the host cores, on a bounded sample of the same workload.
 With --gpus N (launched by torchrun, one rank per GPU) every rank decodes its own batch: replicas, no collective on
@@ -38,6 +42,7 @@ sys.path.insert(0, ROOT)
 
 BATCH, PROMPT, NEW, FRAMES = 64, 10, 448, (50, 375)
 FALLBACK_HBM_GBS = 6650.0
+KV_PREFETCH_MB = 0
 
 
 def measured_peak() -> tuple[float, str]:
@@ -116,7 +121,8 @@ def run_ours(args) -> None:
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
-                        head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8, proj_umma=False if args.no_proj_umma else (args.proj_umma or True))
+                        head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8,
+                        proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch)
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -145,13 +151,18 @@ def run_ours(args) -> None:
         e.record(dec.stream)
         return s, e
 
+    prefill_pairs = []
+
     def e2e_pass():
         """Host buffers in, host tokens out, everything on the decoder stream."""
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f = torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(dec.stream):
             s.record(dec.stream)
             mem = memory_host.to(dev, non_blocking=True)
             dec.fill_cross(mem, lens, slots)
+            f.record(dec.stream)
+        prefill_pairs.append((s, f))
         token_loop(False)
         with torch.cuda.stream(dec.stream):
             out_host.copy_(dec.out[:BATCH], non_blocking=True)
@@ -173,8 +184,8 @@ def run_ours(args) -> None:
         dp.barrier(dev)
         torch.cuda.synchronize()
     dec.check_status()
-    ms = sum(s.elapsed_time(e) for s, e in pairs)
-    ms = dp.max_over_ranks(ms, dev)
+    my_ms = sum(s.elapsed_time(e) for s, e in pairs)  # this rank's own device time
+    ms = dp.max_over_ranks(my_ms, dev)
     tokens = BATCH * NEW * args.steps
     value = world * tokens / (ms / 1e3)
     # drop the gaps between passes (admit + set_active): keep intervals that end at a step event of the same pass
@@ -182,6 +193,23 @@ def run_ours(args) -> None:
     step_ms = [a.elapsed_time(b) for i, (a, b) in enumerate(zip(step_events[:-1], step_events[1:]))
                if (i + 1) % per_pass != 0]
     p50 = statistics.median(step_ms)
+
+    # ---- the step's time by class of kernel: whole passes that launch only the embedding / vocabulary projection /
+    # pick (1), those plus the layer projections (1 | 2), those plus the attention kernels (1 | 4). The pick runs in
+    # all three, so positions advance as in a real pass and every launch moves the bytes it moves there (the values
+    # are meaningless). One pass each after one warm-up pass.
+    class_ms = {}
+    if not args.no_classes:
+        for mask in (1, 3, 5):
+            dec.capture_classes(mask)
+            resident_pass()
+            dec.stream.synchronize()
+            s, e = resident_pass()
+            dec.stream.synchronize()
+            class_ms[mask] = s.elapsed_time(e)
+        dec.capture_classes(0)
+        resident_pass()  # a whole pass again: caches and slot state as after the timed passes
+        dec.stream.synchronize()
 
     # ---- algorithmic bytes of the passes (exact positions and lengths) and the step's roofline
     total_bytes = sum(dec.step_bytes([min(t, steps_per_pass)] * BATCH, lens) for t in range(steps_per_pass))
@@ -243,10 +271,22 @@ def run_ours(args) -> None:
     dp.barrier(dev)
     e2e_ms = dp.max_over_ranks(sum(s.elapsed_time(e) for s, e in pairs), dev)
     e2e_value = world * tokens / (e2e_ms / 1e3)
+    prefill_ms = sum(s.elapsed_time(f) for s, f in prefill_pairs[-args.steps:]) / args.steps
     assert (out_host[:, PROMPT:PROMPT + NEW] != dec.pad).any()
 
     all_stats = dp.gather_stats(dict(steps=steps_per_pass * args.steps, new_tokens=tokens, bytes=total_bytes * args.steps,
-                                     gpu_us=int(ms * 1e3)), dev)
+                                     gpu_us=int(my_ms * 1e3), p50_step_ns=int(p50 * 1e6)), dev)
+    chains_per_step, launches_per_step = len(dec.row_ranges(BATCH)), dec.launches(BATCH)
+    weight_bytes, head_bytes = dec.weight_bytes, dec.head.stream_bytes()
+    # ---- BASELINE configs 4 / 5: the request stream (extra keys of the line)
+    stream = {}
+    if not args.no_stream:
+        del dec
+        torch.cuda.empty_cache()
+        if world == 1:
+            stream["config4"] = stream_workload(args, dev, rank, local, world, 2000)
+        stream["config5"] = stream_workload(args, dev, rank, local, world, args.stream_requests)
+        dec = None
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import cpu_baseline
@@ -254,15 +294,38 @@ def run_ours(args) -> None:
         cpu = {"value": round(r["tokens_per_s"], 1), "unit": "tokens/s", "cores": r["cores"], "kind": r["kind"],
                "sample": r["sample"], "ms_per_step": round(r["ms_per_step"], 2)}
     if rank == 0:
+        classes = None
+        if class_ms:
+            # bytes of a pass by class: the attention kernels' keys, values and appends; the layer projections' weights;
+            # the vocabulary projection's weights and the embedding rows
+            head_b = head_bytes + BATCH * 2 * 1024 * 2
+            proj_b = weight_bytes - head_bytes
+            kv_b = total_bytes / steps_per_pass - proj_b - head_b
+            t1, t12, t14 = class_ms[1], class_ms[3], class_ms[5]
+
+            def entry(b_step, ms_pass):
+                us = ms_pass * 1e3 / steps_per_pass
+                return {"bytes_per_step": int(b_step), "us_per_step": round(us, 1),
+                        "frac": round(b_step / (us / 1e6) / 1e9 / peak, 4) if us > 0 else None}
+            classes = {"attention": entry(kv_b, t14 - t1), "projections": entry(proj_b, t12 - t1),
+                       "embed_head_pick": entry(head_b, t1),
+                       "sum_us": round((t14 + t12 - t1) * 1e3 / steps_per_pass, 1),
+                       "how": "whole passes (457 replays, real positions) that launch only the class's kernels beside "
+                              "the embedding / vocabulary projection / pick; time of a class = its pass minus the pass "
+                              "of those three alone; bytes and fraction of the measured HBM peak per step"}
         line = {
-            "metric": "decoded tokens/s at batch 64, weight-only int8" + (", int8 KV caches" if args.kv_int8 else ""), "value": round(value, 1), "unit": "tokens/s",
+            "metric": "decoded tokens/s at batch 64, weight-only int8" + (", int8 KV caches" if args.kv_int8 else ""),
+            "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights x fp16, fp32 accumulate",
-            "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 weights x fp16, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "BASELINE config 3: 8 layers x 1024, 16 heads x 64, GELU, vocab 16384; batch 64 per GPU, "
                                    "encoder lengths U[50,375], 10-token prompts + 448 new tokens, one CUDA graph per "
                                    "decoding step; a bench step = one pass = 457 replays",
-                       "batch_per_gpu": BATCH, "new_tokens": NEW, "kv_cache": "int8 + fp32 scale per head vector" if args.kv_int8 else "bf16", "parallelism": f"dp{world} replicas", "chains_per_step": len(dec.row_ranges(BATCH)),
+                       "batch_per_gpu": BATCH, "new_tokens": NEW,
+                       "kv_cache": "int8 + fp32 scale per head vector" if args.kv_int8 else "bf16",
+                       "parallelism": f"dp{world} replicas", "chains_per_step": chains_per_step,
+                       "kv_prefetch_mb": args.kv_prefetch,
                        "l2": "inputs larger than L2: each replay streams ~0.2-1.9 GB of KV cache and weights",
                        "weights": "seed-0 random init N(0, 0.02)"},
             "p50_step_ms": round(p50, 4),
@@ -271,21 +334,27 @@ def run_ours(args) -> None:
             "row_steps_per_s": round(world * BATCH * steps_per_pass * args.steps / (ms / 1e3), 1),
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(memory_host.numel() * 4),
                     "d2h_bytes_per_step": int(out_host.numel() * 8 + steps_per_pass * (BATCH + 1)),
-                    "ms_per_step": round(e2e_ms / args.steps, 3)},
-            "gpu_launches": dec.launches_per_step * len(dec.row_ranges(BATCH)) * steps_per_pass * args.steps,
+                    "ms_per_step": round(e2e_ms / args.steps, 3),
+                    # host -> device copy of the encoder memory + fill_cross (cross-K/V prefill), this rank
+                    "prefill_ms": round(prefill_ms, 3)},
+            "gpu_launches": launches_per_step * steps_per_pass * args.steps,
             "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention_pair") + " kernel <64, cross> (64 rows x 16 heads), replayed from a CUDA graph",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
-                         # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the ncu capture summarised in
-                         # profiles/attention_kernel_config3.md (55.73 MB + 0.20 MB for 55.44 MB of K/V), scaled by bytes
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one such launch from an ncu capture of a
+                         # smaller case (27.7 MB of keys and values), scaled by bytes: a stored figure, not measured by
+                         # this run (no number taken under a profiler is a bench value, and ncu is not run from here)
                          "traffic": None if args.kv_int8 else int(kv_bytes * ATTN_TRAFFIC_PER_BYTE),
-                         "traffic_source": "ncu, profiles/attention_kernel_config3.md",
+                         "traffic_source": "stored: ncu capture of this kernel, scaled by bytes; not re-measured by this run",
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
-                                  "frac_of_8TBs": round(step_gbs / 8000, 4)}},
+                                  "frac_of_8TBs": round(step_gbs / 8000, 4)},
+                         "classes": classes},
+            "stream": stream or None,
             "cpu_baseline": cpu,
             "clocks": clocks.summary(),
             "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in all_stats],
+            "per_rank_p50_step_ms": [round(s["p50_step_ns"] / 1e6, 4) for s in all_stats],
             "wall_s": round(t_wall, 3),
         }
         emit(json.dumps(line), flush=True)
@@ -306,7 +375,7 @@ def run_profile(args) -> None:
     B = args.profile_slots
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=B, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         buckets=(B,), int8=True, eos=-1, graphs=False, ffn_sparse=args.sparse, chains=args.chains,
-                        attn_ring=args.attn_ring)
+                        attn_ring=args.attn_ring, kv_prefetch_mb=args.kv_prefetch)
     rng = np.random.default_rng(1000)
     lens = rng.integers(FRAMES[0], FRAMES[1] + 1, B).tolist()
     prompts = [torch.from_numpy(rng.integers(0, 16384, PROMPT).astype(np.int64)) for _ in range(B)]
@@ -333,28 +402,22 @@ def run_profile(args) -> None:
                       "weight_bytes": dec.weight_bytes, "launches_per_step": dec.launches_per_step}))
 
 
-def run_stream(args) -> None:
-    """BASELINE configs 4 / 5 (not the headline line): continuous batching, 128 slots per GPU, 2:4 int8 feed-forward
-    weights, a seeded Poisson stream of `--requests` requests dealt round-robin over the ranks, admitted and evicted
-    between graph replays by DecodeScheduler. Prints one JSON line: delivered new tokens / device time of the whole
-    run (max over ranks), occupancy, and the run's algorithmic bytes against the measured HBM peak."""
+def stream_workload(args, dev, rank: int, local: int, world: int, n_requests: int) -> dict | None:
+    """BASELINE configs 4 / 5: continuous batching, 128 slots per GPU, 2:4 int8 feed-forward weights, a seeded Poisson
+    stream of n_requests requests dealt round-robin over the ranks, admitted and evicted between graph replays by
+    DecodeScheduler. Device time of the whole run (max over ranks), delivered new tokens, occupancy (whole run, and
+    over the steady part between ramp-up and drain), and the run's algorithmic bytes against the measured HBM peak.
+    Every rank calls this; rank 0 gets the summary."""
     from cohere_inference_b200 import DecodeScheduler, StreamDecoder, synthetic_model, synthetic_requests
     from cohere_inference_b200 import dataparallel as dp
-    rank, local, world = dp.init()
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
+    from cohere_inference_b200.synth import request_memory
     SLOTS = 128
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=SLOTS, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         int8=True, ffn_sparse=True, eos=-1, pdl=args.pdl, attn_ring=args.attn_ring,
-                        head_umma=not args.no_head_umma)
-    mine = dp.partition(synthetic_requests(args.requests, seed=0, slots=SLOTS * world), rank, world)
-
-    def memory_of(req):
-        g = torch.Generator(device=dev).manual_seed(req.mem_seed)
-        return torch.randn(req.frames, 1024, device=dev, generator=g)
-
-    sched = DecodeScheduler(dec, memory_of, account_bytes=True)
-    clocks = ClockSampler(local).__enter__()
+                        head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched)
+    mine = dp.partition(synthetic_requests(n_requests, seed=0, slots=SLOTS * world, fill=args.fill), rank, world)
+    # encoder memory of each request in pinned host memory (the scheduler copies it to the device at admission)
+    sched = DecodeScheduler(dec, lambda r: torch.from_numpy(request_memory(r)).pin_memory(), account_bytes=True)
     dp.barrier(dev)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -365,33 +428,56 @@ def run_stream(args) -> None:
     torch.cuda.synchronize()
     dp.barrier(dev)
     wall = time.perf_counter() - t0
-    clocks.__exit__()
     dec.check_status()
     st = sched.stats
     ms = dp.max_over_ranks(e0.elapsed_time(e1), dev)
+    times = sched.step_time_summary()
     stats = dp.gather_stats(dict(steps=st.steps, row_steps=st.row_steps, padded_row_steps=st.padded_row_steps,
                                  slot_steps=st.slot_steps, admitted=st.admitted, evicted=st.evicted,
                                  new_tokens=st.new_tokens, delivered_tokens=st.delivered_tokens, bytes=st.bytes,
-                                 gpu_us=int(e0.elapsed_time(e1) * 1e3)), dev)
+                                 gpu_us=int(e0.elapsed_time(e1) * 1e3), steady_row_steps=st.steady_row_steps,
+                                 steady_slot_steps=st.steady_slot_steps,
+                                 p50_step_ns=int(times.get("p50_ms", 0) * 1e6)), dev)
     assert all(o is not None for o in out) and st.evicted == len(mine)
-    if rank == 0:
-        peak, peak_kind = measured_peak()
-        tokens = sum(s["new_tokens"] for s in stats)
-        gbs = sum(s["bytes"] for s in stats) / world / (ms / 1e3) / 1e9
-        emit(json.dumps({
-            "metric": "decoded tokens/s, continuous batching, 128 slots per GPU, 2:4 int8 feed-forward", "impl": "ours",
-            "value": round(tokens / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "higher_is_better": True,
-            "scaling": "strong", "data": "synthetic",
-            "config": {"workload": f"BASELINE config {'4' if world == 1 else '5'}: {args.requests} requests, encoder "
-                                   "lengths U[50,375], targets U[16,448], Poisson arrivals for ~95 % full slots, "
-                                   "admission and eviction between graph replays", "slots_per_gpu": SLOTS},
+    del sched, dec
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    tokens = sum(s["new_tokens"] for s in stats)
+    gbs = sum(s["bytes"] for s in stats) / world / (ms / 1e3) / 1e9
+    return {"workload": f"{n_requests} requests (encoder lengths U[50,375], targets U[16,448], Poisson arrivals at "
+                        f"{args.fill:.2f} x the service rate) dealt round-robin over {world} GPU(s), 128 slots each, 2:4 "
+                        "int8 feed-forward weights; host memory -> prefill -> decode -> tokens on the host",
+            "tokens_per_s": round(tokens / (ms / 1e3), 1), "n_gpus": world,
+            "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in stats],
             "steps": [s["steps"] for s in stats], "ms_per_step": round(ms / max(s["steps"] for s in stats), 4),
+            "p50_step_ms": [round(s["p50_step_ns"] / 1e6, 4) for s in stats],
             "occupancy": round(sum(s["row_steps"] for s in stats) / max(1, sum(s["slot_steps"] for s in stats)), 4),
+            "occupancy_steady": round(sum(s["steady_row_steps"] for s in stats) /
+                                      max(1, sum(s["steady_slot_steps"] for s in stats)), 4),
             "padding": round(sum(s["padded_row_steps"] for s in stats) / max(1, sum(s["row_steps"] for s in stats)), 4),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peak, "unit": "GB/s",
-                         "frac": round(gbs / peak, 4), "peak_source": peak_kind, "what": "whole run, per GPU"},
-            "per_rank_tokens_per_s": [round(s["new_tokens"] / (s["gpu_us"] / 1e6), 1) for s in stats],
-            "clocks": clocks.summary(), "wall_s": round(wall, 2)}), flush=True)
+                         "frac": round(gbs / peak, 4), "peak_source": peak_kind,
+                         "what": "whole run incl. host scheduling, per GPU"},
+            "wall_s": round(wall, 2)}
+
+
+def run_stream(args) -> None:
+    """`--workload stream`: only the request stream (configs 4 / 5), one JSON line."""
+    from cohere_inference_b200 import dataparallel as dp
+    rank, local, world = dp.init()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    with ClockSampler(local) as clocks:
+        r = stream_workload(args, dev, rank, local, world, args.requests)
+    if rank == 0:
+        emit(json.dumps({"metric": "decoded tokens/s, continuous batching, 128 slots per GPU, 2:4 int8 feed-forward",
+                         "impl": "ours", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                         "higher_is_better": True, "scaling": "strong", "data": "synthetic",
+                         "config": {"workload": f"BASELINE config {'4' if world == 1 else '5'}: " + r["workload"]},
+                         **{k: v for k, v in r.items() if k not in ("workload", "tokens_per_s", "n_gpus")},
+                         "clocks": clocks.summary()}), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
 
@@ -455,6 +541,15 @@ def main() -> None:
     ap.add_argument("--workload", default="batch64", choices=["batch64", "stream"],
                     help="batch64: BASELINE config 3 (the headline line); stream: configs 4 / 5, continuous batching")
     ap.add_argument("--requests", type=int, default=2000, help="stream workload: requests in the whole stream")
+    ap.add_argument("--stream-requests", type=int, default=8000, help="requests of the config-5 stream run by the default "
+                    "invocation (dealt round-robin over the ranks)")
+    ap.add_argument("--fill", type=float, default=1.05, help="stream workloads: arrival rate as a multiple of the rate "
+                    "at which 128 slots per GPU serve requests")
+    ap.add_argument("--no-stream", action="store_true", help="skip the stream workloads of the default invocation")
+    ap.add_argument("--no-classes", action="store_true", help="skip the per-class passes")
+    ap.add_argument("--kv-prefetch", type=int, default=KV_PREFETCH_MB, help="MB of an attention launch's keys and values "
+                    "that the projections before it start towards L2 (0: off)")
+    ap.add_argument("--device-sched", action="store_true", help="stream workloads: the active list lives on the device")
     args = ap.parse_args()
     # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 themselves (NCCL's
     # version banner, for one) are pointed at stderr, the result goes to a copy of the original descriptor

@@ -43,20 +43,8 @@ struct AttnArgs {
   int* status;
   int ldq, H, cap, slots, out_kind, rows, splits;
   float scale_log2;  // head_dim^-0.5 * log2(e)
-#ifdef B200DEC_STAMPS
-  long long* stamps;  // per CTA 12 timer values (latency studies only)
-#endif
 };
 
-#ifdef B200DEC_STAMPS
-#define ATTN_STAMP(i)                                                                                               \
-  do {                                                                                                              \
-    if (p.stamps && threadIdx.x == 0)                                                                               \
-      p.stamps[((blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 12 + (i)] = stamp_clock();         \
-  } while (0)
-#else
-#define ATTN_STAMP(i)
-#endif
 
 // One CTA's pass over keys [start, end) of (slot s, head h) for the query of row r, plus (with_new) the row's new key:
 // on return threads tid < D hold the pass's running maximum M, sum L and un-normalised output O for dim tid.
@@ -133,7 +121,6 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
       if (j0 + u * NG < end) attend(kk[u], vv[u], j + u * NG < end);  // warp-uniform condition
     }
   }
-  ATTN_STAMP(3);
   // merge the groups
   __syncthreads();  // the arrays may still be read by a previous pass
   if (gl == 0) s_m[grp] = m, s_l[grp] = l;
@@ -265,7 +252,6 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
       }
     }
   }
-  ATTN_STAMP(3);
   __syncthreads();  // the arrays may still be read by a previous pass
   if (gl == 0) s_m[grp] = m, s_l[grp] = l;
 #pragma unroll
@@ -324,12 +310,10 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p
 
   const int h = blockIdx.x, r = blockIdx.y, sp = blockIdx.z, nsp = p.splits;
   const int tid = threadIdx.x;
-  ATTN_STAMP(0);
   pdl_wait();
 
   int s, n;
   row_state<SELF>(p, r, tid == 0, s, n);
-  ATTN_STAMP(2);
   const int chunk = (n + nsp - 1) / nsp, start = sp * chunk, end = min(n, start + chunk);
   float M, L, O;
   attend_pass<D, SELF, Q8>(p, r, s, h, n, start, end, sp == 0, s_m, s_l, s_acc, M, L, O);
@@ -339,7 +323,6 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p
   pdl_trigger();
   if (nsp == 1) {
     if (tid < D) store_out<D>(p, r, h, O / L);
-    ATTN_STAMP(7);
     return;
   }
   // split: partial to the workspace, the last CTA of this (row, head) merges
@@ -388,10 +371,10 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
   __shared__ int t_slot[TABLE ? 1 : PAIR_MAX_ROWS], t_n[TABLE ? 1 : PAIR_MAX_ROWS];
   __shared__ int s_pair[2];
 
+  cluster_arrive_entry();  // the peer may be written to only once it has started: see cluster_wait_entry() below
   cg::cluster_group cluster = cg::this_cluster();
   const int role = blockIdx.x, h = blockIdx.y, i = blockIdx.z, rows = p.rows;
   const int tid = threadIdx.x;
-  ATTN_STAMP(0);
   int r_long, r_short, s_long, s_short, n_long, n_short;
   if constexpr (TABLE) {
     // the step's schedule (built beside the embedding, at least two kernels ago: readable before the wait): two
@@ -419,7 +402,6 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
     r_long = s_pair[0], r_short = s_pair[1];
     s_long = t_slot[r_long], s_short = t_slot[r_short], n_long = t_n[r_long], n_short = t_n[r_short];
   }
-  ATTN_STAMP(2);
   const bool solo = r_long == r_short;  // the middle row of an odd count
   // keys [cut, n_long) of the long row go to CTA 1 (a multiple of 16 keeps both CTAs' loads aligned to whole groups)
   int cut = n_long;
@@ -431,7 +413,8 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
     attend_pass<D, SELF, Q8>(p, r_long, s_long, h, n_long, 0, cut, true, s_m, s_l, s_acc, M, L, O);
     pdl_trigger();  // late: see attention_kernel
     if (helped) {
-      cluster.sync();  // the peer's partial has landed
+      cluster_wait_entry();  // completes the phase opened at entry (a thread may not arrive twice in a row)
+      cluster.sync();        // the peer's partial has landed
       if (tid < D) {
         const float pm = s_peer[D], pl = s_peer[D + 1], po = s_peer[tid];
         const float mm = fmaxf(M, pm), w0 = ex2(M - mm), w1 = ex2(pm - mm);
@@ -447,13 +430,13 @@ __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnA
     if (helped) {
       attend_pass<D, SELF, Q8>(p, r_long, s_long, h, n_long, cut, n_long, false, s_m, s_l, s_acc, M, L, O);
       pdl_trigger();
+      cluster_wait_entry();  // CTA 0 has started (it arrived at its entry, long ago by now)
       float* peer = cluster.map_shared_rank(s_peer, 0);
       if (tid < D) peer[tid] = O;
       if (tid == 0) peer[D] = M, peer[D + 1] = L;
       cluster.sync();
     }
   }
-  ATTN_STAMP(7);
 }
 
 int pick_splits(int rows, int heads, int cap) {
@@ -513,9 +496,6 @@ int run_attention(const char* what, int self, const int32_t* active, const float
   // a large batch: rows paired long with short, two CTAs per pair and head
   const bool pair = sched || (p.splits == 1 && rows * heads >= 512 && rows <= PAIR_MAX_ROWS);
   const dim3 grid = pair ? dim3(2, heads, (rows + 1) / 2) : dim3(heads, rows, p.splits);
-#ifdef B200DEC_TIMELINE
-  p.stamps = timeline_next(grid.x * grid.y * grid.z, self ? 3000000 : 4000000);
-#endif
   const cudaStream_t st = (cudaStream_t)stream;
   const cudaError_t e = ks ? launch_attention<true>(pair, sched != nullptr, head_dim, self, grid, st, pdl, p)
                            : launch_attention<false>(pair, sched != nullptr, head_dim, self, grid, st, pdl, p);

@@ -88,14 +88,6 @@ DEVI void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
 }
 DEVI void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NCW * 32) : "memory"); }
 
-#ifdef B200DEC_STAMPS
-__device__ long long* g_attn_stamps;  // per CTA: total, consumer wait, producer wait, chunks (latency studies only)
-#define ATTN_T0(v) const long long v = clock64()
-#define ATTN_ACC(acc, v) acc += clock64() - v
-#else
-#define ATTN_T0(v)
-#define ATTN_ACC(acc, v)
-#endif
 
 DEVI float ex2(float x) {
   float y;
@@ -185,8 +177,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
     if (lane != 0) return;
     uint32_t it = 0;
     bool ok = true;
-    long long t_pwait = 0;
-    (void)t_pwait;
     for (int pass = 0; pass < passes && ok; ++pass) {
       const int u = unit_of_pass(pass, total);
       Unit w;
@@ -194,9 +184,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
       const size_t base = ((size_t)w.s * p.H + w.h) * p.cap * D;
       for (int c = 0; c < w.nchunks; ++c, ++it) {
         const int st = it % NSTAGE, j = w.k0 + c * CK;
-        ATTN_T0(tp);
         ok = mbar_wait(&empty[st], ((it / NSTAGE) & 1) ^ 1);
-        ATTN_ACC(t_pwait, tp);
         if (!ok) break;
         const uint32_t bytes = (uint32_t)max(0, min(CK, w.k1 - j)) * KEY_BYTES;
         const bool kv_new = SELF && w.sp == 0;
@@ -216,9 +204,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
         }
       }
     }
-#ifdef B200DEC_STAMPS
-    if (g_attn_stamps) g_attn_stamps[blockIdx.x * 4 + 2] = t_pwait;
-#endif
     if (!ok) {
       atomicOr(p.status, B200DEC_ST_TIMEOUT);
       // the copies already issued must land before this CTA's shared memory is given away
@@ -235,9 +220,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
   const int kg = lane / LPK, ql = lane % LPK;  // key within the warp's group, lane within the key
   const int pa = ROT ? ((ql + 4 * (kg & 1)) & 7) : ql, pb = ROT ? (pa ^ 4) : (ql + LPK);  // this lane's two pieces
   uint32_t it = 0;
-  long long t_cwait = 0;
-  (void)t_cwait;
-  ATTN_T0(t_begin);
   bool dead = false;  // set when a bounded wait ran out: the warp then only keeps the consumers' barrier pattern
   for (int pass = 0; pass < passes; ++pass) {
     const int u = unit_of_pass(pass, total);
@@ -298,9 +280,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
     for (int c = 0; c < w.nchunks; ++c, ++it) {
       if (dead) continue;  // a wait ran out earlier: keep the barrier pattern, skip the work
       const int st = it % NSTAGE, j = w.k0 + c * CK;
-      ATTN_T0(tc);
       const bool got = mbar_wait(&full[st], (it / NSTAGE) & 1);
-      ATTN_ACC(t_cwait, tc);
       if (!got) {
         dead = true;
         atomicOr(p.status, B200DEC_ST_TIMEOUT);
@@ -427,13 +407,6 @@ __global__ void __launch_bounds__(NTHREADS, 2) attention_kernel(const AttnArgs p
     }
     consumer_sync();  // w_m / w_l / w_acc / s_last are free for the next unit
   }
-#ifdef B200DEC_STAMPS
-  if (g_attn_stamps && tid == 0) {
-    g_attn_stamps[blockIdx.x * 4 + 0] = clock64() - t_begin;
-    g_attn_stamps[blockIdx.x * 4 + 1] = t_cwait;
-    g_attn_stamps[blockIdx.x * 4 + 3] = it;
-  }
-#endif
 }
 
 }  // namespace
@@ -452,10 +425,7 @@ int b200dec_attention_ring(int self, const int32_t* active, const float* q, int 
   B200_REQUIRE(out_kind == B200DEC_OUT_F16 || out_kind == B200DEC_OUT_F32, "attention_ring: out_kind");
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  // tuning knobs (environment, read once): ring stages per CTA and CTAs per SM
-  static const int env_stages = [] { const char* v = getenv("B200DEC_ATTN_STAGES"); return v ? atoi(v) : 0; }();
-  static const int env_ctas = [] { const char* v = getenv("B200DEC_ATTN_CTAS"); return v ? atoi(v) : 0; }();
-  const int per_sm = env_ctas >= 1 && env_ctas <= 4 ? env_ctas : 2;
+  constexpr int per_sm = 2;  // CTAs per SM, four ring stages each (the measured optimum of 1-4 CTAs x 2-8 stages)
   // Units are whole (row, head) caches when there are enough of them to fill every CTA; a small batch splits each
   // cache into spans (multiples of a chunk) whose partials the last span to finish merges.
   const int ck = CHUNK_BYTES / (head_dim * 2), items = rows * heads;
@@ -472,7 +442,7 @@ int b200dec_attention_ring(int self, const int32_t* active, const float* q, int 
   p.ldq = ldq, p.H = heads, p.cap = cap, p.slots = slots, p.out_kind = out_kind, p.rows = rows, p.nspan = nspan;
   p.span = span;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.nstage = env_stages >= 2 && env_stages <= MAX_STAGE ? env_stages : 4;
+  p.nstage = 4;
   const size_t smem = (size_t)p.nstage * (2 * CHUNK_BYTES + (self ? 3 : 1) * head_dim * 4);
   const long long units = (long long)rows * heads * nspan;
   const dim3 grid((unsigned)(units < (long long)per_sm * sms ? units : (long long)per_sm * sms));

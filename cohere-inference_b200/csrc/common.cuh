@@ -60,22 +60,13 @@ inline cudaError_t launch_kernel(Kern kern, dim3 grid, dim3 block, size_t smem, 
   return cudaLaunchKernelEx(&cfg, kern, args);
 }
 
-// ---- timeline study builds (-DB200DEC_TIMELINE): every launch gets the next slice of a device buffer, 12 slots per
-// CTA, and its CTAs store the global nanosecond timer there at their phase boundaries -------------------------------
-#ifdef B200DEC_TIMELINE
-#define B200DEC_STAMPS 1
-namespace b200dec_detail {
-long long* timeline_next(int ctas, int kind);  // host side, rowops.cu; nullptr when no buffer is set
-}
-using b200dec_detail::timeline_next;
-DEVI long long stamp_clock() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#else
-DEVI long long stamp_clock() { return clock64(); }
-#endif
+// ---- thread-block clusters -----------------------------------------------------------------------------------------
+// A CTA may touch the shared memory of another CTA of its cluster only once that CTA has started. Every clustered
+// kernel therefore arrives at the cluster barrier as its first instruction and completes that phase (the wait) just
+// before its first remote store; in between lie the weight prefetch and the wait for the previous kernel, so the
+// pair costs nothing on the critical path. Each thread that arrives must wait before it arrives again (cluster.sync()).
+DEVI void cluster_arrive_entry() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+DEVI void cluster_wait_entry() { asm volatile("barrier.cluster.wait;" ::: "memory"); }
 
 // ---- loads --------------------------------------------------------------------------------------------------------
 // Read-once streams (weights, KV cache): no L1 allocation.
@@ -104,6 +95,36 @@ DEVI void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
 DEVI void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// ---- prefetch of an attention launch's keys and values into L2 -----------------------------------------------------
+// The step alternates between projections (bound by latency, HBM nearly idle) and attention (bound by HBM). A
+// projection that runs between two attention launches can therefore start the next launch's cache stream early: one
+// thread per CTA asks the bulk-copy engine to bring runs of keys and values into L2 and goes on; nothing waits for
+// them. The rows come from the step's row schedule (b200dec_row_schedule), whose fourth word is the number of keys
+// of the row to prefetch (the launch's total is capped by the plan's budget so that it stays inside L2).
+struct KvPrefetch {
+  const int4* sched;  // (rows, 4) {row, slot, length, keys to prefetch}; null: nothing to do
+  const char* k;      // caches (slots + 1, H, cap, vec_bytes)
+  const char* v;
+  int rows, heads, cap, vec_bytes;
+};
+DEVI void prefetch_l2(const void* p, uint32_t bytes) {  // bytes: a multiple of 16, p 16-byte aligned
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// Called by one thread of every CTA of a grid of `nctas` CTAs (this one's index `cta`): runs of up to 16 KB.
+DEVI void kv_prefetch_issue(const KvPrefetch& f, int cta, int nctas) {
+  const int ops = f.rows * f.heads * 2;
+  for (int o = cta; o < ops; o += nctas) {
+    const int i = o / (2 * f.heads), rem = o % (2 * f.heads), h = rem >> 1;
+    const int4 e = __ldcg(f.sched + i);
+    const int keys = e.w < f.cap ? e.w : f.cap;
+    if (keys <= 0 || e.y < 0) continue;
+    const char* src = ((rem & 1) ? f.v : f.k) + ((size_t)e.y * f.heads + h) * f.cap * f.vec_bytes;
+    const long long bytes = (long long)keys * f.vec_bytes;
+    for (long long off = 0; off < bytes; off += 16384)
+      prefetch_l2(src + off, (uint32_t)(bytes - off < 16384 ? bytes - off : 16384));
+  }
+}
 
 // ---- conversions --------------------------------------------------------------------------------------------------
 DEVI float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }

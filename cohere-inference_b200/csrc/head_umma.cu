@@ -56,20 +56,10 @@ struct HeadArgs {
   int* status;
   float ln_eps;
   int lda, rows, N;
-#ifdef B200DEC_STAMPS
-  long long* stamps;  // per CTA 12 timer values (latency studies only)
-#endif
+  uint32_t wait_limit;  // polls before a wait gives up
+  int withhold;         // tests only: the producer stops after three blocks, so the waits behind it run out
 };
 
-#ifdef B200DEC_STAMPS
-#define HEAD_STAMP(i)                                                                   \
-  do {                                                                                  \
-    if (p.stamps && (threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == ((i) == 6 ? NWORK : 0)) \
-      p.stamps[blockIdx.x * 12 + (i)] = stamp_clock();                                  \
-  } while (0)
-#else
-#define HEAD_STAMP(i)
-#endif
 
 DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 DEVI void mbar_init(uint64_t* bar, int count) {
@@ -81,9 +71,9 @@ DEVI void mbar_arrive(uint64_t* bar) {
 DEVI void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-DEVI bool mbar_wait(uint64_t* bar, uint32_t parity) {  // bounded; false when the limit ran out
+DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {  // bounded; false when the limit ran out
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
@@ -157,7 +147,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;  // channels [128 tile, +128)
-  HEAD_STAMP(0);
   const uint8_t* wsrc = p.w + (size_t)tile * NKB * RAW_BYTES;
 
   if (tid == 0) {
@@ -181,28 +170,35 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_d = tmem_base;
-  HEAD_STAMP(1);
 
   if (warp == NWORK + 1) {
     // ---- producer: the tile's sixteen weight blocks through the raw ring (independent of the previous kernel) -------
     if (lane == 0) {
       bool ok = true;
+      int issued = 0;
       for (int kb = 0; kb < NKB && ok; ++kb) {
+        if (p.withhold && kb == 3) break;  // tests only: nothing sets the barriers of block 3
         const int st = kb % RAW_STAGES;
-        ok = mbar_wait(&raw_empty[st], ((kb / RAW_STAGES) & 1) ^ 1);
+        ok = mbar_wait(&raw_empty[st], ((kb / RAW_STAGES) & 1) ^ 1, p.wait_limit);
         if (!ok) break;
         mbar_expect_tx(&raw_full[st], RAW_BYTES);
         bulk_load(raws + st * RAW_BYTES, wsrc + (size_t)kb * RAW_BYTES, RAW_BYTES, &raw_full[st]);
+        issued = kb + 1;
       }
-      if (!ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+      if (!ok) {
+        atomicOr(p.status, B200DEC_ST_TIMEOUT);
+        // the copies already issued must land before this CTA's shared memory is given away (bounded)
+        for (int kb = issued > RAW_STAGES ? issued - RAW_STAGES : 0; kb < issued; ++kb)
+          mbar_wait(&raw_full[kb % RAW_STAGES], (kb / RAW_STAGES) & 1, p.wait_limit);
+      }
     }
   } else if (warp == NWORK) {
     // ---- MMA issue: one lane, four instructions per block, the block's A tile released by the commit ---------------
     if (lane == 0) {
-      bool ok = mbar_wait(&x_full, 0);
+      bool ok = mbar_wait(&x_full, 0, p.wait_limit);
       for (int kb = 0; kb < NKB && ok; ++kb) {
         const int st = kb % A_STAGES;
-        ok = mbar_wait(&a_full[st], (kb / A_STAGES) & 1);
+        ok = mbar_wait(&a_full[st], (kb / A_STAGES) & 1, p.wait_limit);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a0 = smem_u32(as + st * A_BYTES), b0 = smem_u32(xs + kb * XB_BYTES);
@@ -213,13 +209,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
       }
       if (!ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
       umma_commit(&d_full);  // arrives when everything issued so far has completed (also after a time-out)
-      HEAD_STAMP(6);
     }
   } else {
     // ---- workers: normalise the rows into the B tiles, then widen weight blocks, then the epilogue ------------------
     pdl_wait();
     pdl_trigger();
-    HEAD_STAMP(2);
     if (p.xg) {
       // The operand exists already (row * gamma as fp16): 16-byte asynchronous copies straight into the swizzled
       // tiles, and the rows' statistics from the partial sums (four threads per row, fixed order).
@@ -295,7 +289,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
     fence_async_shared();  // the MMA reads these tiles through the async proxy
     __syncwarp();
     if (lane == 0) mbar_arrive(&x_full);
-    HEAD_STAMP(3);
 
     bool ok = true;
     const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile (= its tensor-memory lane)
@@ -303,7 +296,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
     for (int kb = 0; kb < NKB; ++kb) {
       if (!ok) break;
       const int rs = kb % RAW_STAGES, st = kb % A_STAGES;
-      ok = mbar_wait(&raw_full[rs], (kb / RAW_STAGES) & 1);
+      ok = mbar_wait(&raw_full[rs], (kb / RAW_STAGES) & 1, p.wait_limit);
       if (!ok) break;
       uint4 r[2];
 #pragma unroll
@@ -311,7 +304,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
         r[j] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + (2 * hf + j) * 2048 + ch * 16);
       __syncwarp();
       if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the block's bytes are in registers
-      ok = mbar_wait(&a_empty[st], ((kb / A_STAGES) & 1) ^ 1);
+      ok = mbar_wait(&a_empty[st], ((kb / A_STAGES) & 1) ^ 1, p.wait_limit);
       if (!ok) break;
       unsigned char* row = as + st * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
 #pragma unroll
@@ -327,12 +320,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
       if (lane == 0) mbar_arrive(&a_full[st]);
     }
     if (!ok && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
-    HEAD_STAMP(4);
 
     // ---- epilogue ---------------------------------------------------------------------------------------------------
-    const bool got = mbar_wait(&d_full, 0);
+    const bool got = mbar_wait(&d_full, 0, p.wait_limit);
     if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
-    HEAD_STAMP(5);
     tc_fence_after();
     float* outs = reinterpret_cast<float*>(as);  // (64 rows, OUT_LD): the rings are idle once d_full has fired
     {
@@ -391,7 +382,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
       }
     }
   }
-  HEAD_STAMP(7);
   // ---- release the tensor memory: after every warp is done with it ----------------------------------------------------
   tc_fence_before();
   __syncthreads();
@@ -420,7 +410,7 @@ namespace b200dec_detail {
 // (x null; w->ln_g / ln_bias fold the LayerNorm into the epilogue).
 int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, const float* stats, int stats_slots,
                    const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx, float* logits,
-                   int32_t* status, int pdl, void* stream) {
+                   int32_t* status, int pdl, void* stream, int wait_limit, int withhold) {
   B200_REQUIRE(w && w->w && w->scale && (x || xg) && ln && ln->w && ln->b && part_max && part_idx && status,
                "head_umma: null pointer");
   B200_REQUIRE(!xg || (stats && stats_slots >= 1 && w->ln_g && w->ln_bias && ((uintptr_t)xg & 15) == 0 && lda % 8 == 0),
@@ -444,9 +434,7 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, cons
     a.part_max = part_max + (size_t)r0 * np, a.part_idx = part_idx + (size_t)r0 * np;
     a.logits = logits ? logits + (size_t)r0 * w->n : nullptr;
     a.status = status, a.lda = lda, a.rows = rows - r0 < UN ? rows - r0 : UN, a.N = w->n;
-#ifdef B200DEC_TIMELINE
-    a.stamps = timeline_next(np, 5000000);
-#endif
+    a.wait_limit = wait_limit > 0 ? (uint32_t)wait_limit : WAIT_LIMIT, a.withhold = withhold;
     e = launch_kernel(head_umma_kernel, dim3(np), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream, 0, pdl, a);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma launch: %s", cudaGetErrorString(e));
   }
@@ -467,7 +455,7 @@ int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* str
 
 int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,
                       float* part_max, int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream) {
-  return head_umma_impl(w, x, nullptr, nullptr, 0, ln, lda, rows, part_max, part_idx, logits, status, pdl, stream);
+  return head_umma_impl(w, x, nullptr, nullptr, 0, ln, lda, rows, part_max, part_idx, logits, status, pdl, stream, 0, 0);
 }
 
 int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const float* stats, int stats_slots,
@@ -475,7 +463,7 @@ int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const floa
                              float* logits, int32_t* status, int pdl, void* stream) {
   B200_REQUIRE(xg, "head_umma_linked: null operand");
   return head_umma_impl(w, nullptr, xg, stats, stats_slots, ln, lda, rows, part_max, part_idx, logits, status, pdl,
-                        stream);
+                        stream, 0, 0);
 }
 
 }  // extern "C"

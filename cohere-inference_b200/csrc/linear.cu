@@ -32,8 +32,6 @@
 // In step s of a block a lane holds 4 consecutive k of its two channels: (k, k+1) is fragment slot (2t, 2t+1) and
 // (k+2, k+3) slot (2t+8, 2t+9); the activation fragment of the same lane takes the same 4 k, so the permutation of K
 // inside a 16-step never has to be undone.
-#include <cstdlib>
-
 #include "linear_kernel.cuh"
 
 using namespace b200dec_detail;
@@ -102,7 +100,7 @@ namespace {
 
 int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
                int out_kind, int ldo, int act, float* pmax, int* pidx, float* logits, int head, int pdl, void* stream,
-               const b200dec_ln_link* link = nullptr) {
+               const b200dec_ln_link* link = nullptr, const KvPrefetch* pf = nullptr) {
   B200_REQUIRE(w && w->w && a, "linear: null pointer");
   B200_REQUIRE(rows >= 1 && rows <= 128, "linear: rows %d outside 1..128", rows);
   if (w->kind == B200DEC_W_INT8_UMMA) {  // the tcgen05 kernel of linear_umma.cu
@@ -140,10 +138,10 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   } else {
     B200_REQUIRE(pmax && pidx, "head: null partials");
   }
-  static const bool split_wide = getenv("B200DEC_FC2_ONE_PASS") == nullptr;
-  // K = 4096 at more than 64 rows: its 128-row tile takes a whole SM's shared memory, and clusters of eight such CTAs
-  // could not all be placed at once (some started 9 us late); two passes of 64 rows are faster
-  const bool two_pass_wide = split_wide && rows > 64 && w->k == 4096;
+  // K = 4096 at more than 64 rows with fp32 or bf16 operands: the 128-row tile takes a whole SM's shared memory, and
+  // clusters of eight such CTAs could not all be placed at once (some started 9 us late); two passes of 64 rows are
+  // faster. fp16 rows on int8 / 2:4 weights are dealt over four CTAs of 32 rows per tile instead (one pass).
+  const bool two_pass_wide = rows > 64 && w->k == 4096 && (split || lnorm != 0 || w->kind == B200DEC_W_BF16);
   if (rows > 64 && (two_pass_wide || !fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, rows)) &&
       fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, 64)) {
     // this operand does not fit shared memory for 128 rows at this K slice: two passes of up to 64 rows (the weights
@@ -151,7 +149,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
     const size_t asz = (split || lnorm == 1) ? 4 : 2, osz = out_kind == B200DEC_OUT_F16 ? 2 : 4;
     const int np = head ? (w->n / (16 * w->warps)) * w->ksplit : 0;
     const int rc = run_linear(w, a, a_kind, ln, lda, 64, out, out_kind, ldo, act, pmax, pidx, logits, head, pdl, stream,
-                              link);
+                              link, pf);
     if (rc) return rc;
     b200dec_ln_link up = lk;  // the second pass: the same link 64 rows further
     if (up.out16) up.out16 = (char*)up.out16 + (size_t)64 * ldo * 2;
@@ -169,6 +167,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   p.stats_in = lk.stats_in, p.stats_slots = lk.stats_slots;
   if (lnorm) p.ln_w = ln->w, p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
   p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.out_kind = out_kind, p.act = act, p.head = head;
+  if (pf) p.pf = *pf;
   cudaStream_t s = (cudaStream_t)stream;
   switch (w->kind) {
     case B200DEC_W_INT8: return launch_int8(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);
@@ -181,10 +180,20 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
 }  // namespace
 
 namespace b200dec_detail {
+// launches one call of linear_impl makes (1, or 2 when the rows go in two passes)
+int linear_passes(const b200dec_weight* w, int a_kind, bool ln, int rows) {
+  if (w->kind == B200DEC_W_INT8_UMMA) return (w->k == 4 * D_MODEL && rows > 64) ? 2 : 1;
+  const bool split = a_kind == B200DEC_A_F32_SPLIT;
+  const int lnorm = !ln ? 0 : a_kind == B200DEC_A_F16_ROWS16 ? 2 : 1;
+  const bool two_pass_wide = rows > 64 && w->k == 4096 && (split || lnorm != 0 || w->kind == B200DEC_W_BF16);
+  return (rows > 64 && (two_pass_wide || !fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, rows)) &&
+          fits_any(w->kind, split, lnorm, w->warps, w->k, w->ksplit, 64)) ? 2 : 1;
+}
 int linear_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, void* out,
-                int out_kind, int ldo, int act, int pdl, void* stream, const b200dec_ln_link* link) {
+                int out_kind, int ldo, int act, int pdl, void* stream, const b200dec_ln_link* link,
+                const KvPrefetch* pf) {
   return run_linear(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, nullptr, nullptr, nullptr, 0, pdl, stream,
-                    link);
+                    link, pf);
 }
 int head_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows, float* pmax,
               int* pidx, float* logits, int pdl, void* stream) {
@@ -197,13 +206,13 @@ extern "C" {
 
 int b200dec_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                    void* out, int out_kind, int ldo, int act, int pdl, void* stream) {
-  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, nullptr);
+  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, nullptr, nullptr);
 }
 
 int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                           void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,
                           void* stream) {
-  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, link);
+  return linear_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, pdl, stream, link, nullptr);
 }
 
 int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,

@@ -34,19 +34,8 @@ struct LinArgs {
   float* logits;
   float ln_eps;
   int lda, ldo, rows, N, out_kind, act, head;
-#ifdef B200DEC_STAMPS
-  long long* stamps;  // per CTA 12 clock64() values at the phase boundaries (latency studies only)
-#endif
+  KvPrefetch pf;  // keys and values of the next attention launch to start on their way into L2 (sched null: none)
 };
-
-#ifdef B200DEC_STAMPS
-#define B200_STAMP(i)                                                                                        \
-  do {                                                                                                       \
-    if (p.stamps && threadIdx.x == 0) p.stamps[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (i)] = stamp_clock(); \
-  } while (0)
-#else
-#define B200_STAMP(i)
-#endif
 
 template <int WT>
 struct WTraits;
@@ -133,6 +122,7 @@ struct LinSmem {
 // channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) {
+  cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   LinArgs p = p_in;
   if (gridDim.z > 1) {  // the rows are dealt over blockIdx.z, MB each (fp16 operands only)
     const int row0 = blockIdx.z * MB;
@@ -164,8 +154,6 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
   const int nt16 = blockIdx.y * NW + warp;  // this warp's 16 channels
   const int k0 = rank * KSLICE;
-
-  B200_STAMP(0);
   // ---- prologue: the warp's whole weight slice into registers (independent of the previous kernel) -------------
   uint4 wr[NBLK][2];
   uint32_t mr[WT == B200DEC_W_INT8_24 ? NBLK : 1][2];
@@ -199,9 +187,10 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
       }
     }
   }
-  B200_STAMP(1);
   pdl_wait();
-  B200_STAMP(2);
+  if (p.pf.sched && tid == 0)
+    kv_prefetch_issue(p.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                      gridDim.x * gridDim.y * gridDim.z);
 
   // ---- stage the activations of this K slice ---------------------------------------------------------------------
   const int ntiles = (p.rows + 7) >> 3, rows8 = ntiles * 8;
@@ -230,6 +219,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
         for (int i = 0; i < 4; ++i)
           v[j][i] = (r < p.rows && lane + 32 * i < p.stats_slots) ? __ldcg(part + lane + 32 * i) : make_float2(0.f, 0.f);
       }
+      cluster_wait_entry();
 #pragma unroll
       for (int j = 0; j < RPW; ++j) {
         const int r = rank + KSPLIT * (warp + NW * j);
@@ -271,12 +261,10 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
 #pragma unroll
       for (int j = 0; j < J; ++j) gam[j] = __ldg(reinterpret_cast<const float4*>(p.ln_w + k0 + (j * 8 + l8) * 4));
     }
-    B200_STAMP(8);
     if constexpr (S::RAW_STAGE) {
       cp_async_wait_all();
       __syncthreads();
     }
-    B200_STAMP(9);
     float s1[RPG], s2[RPG];
 #pragma unroll
     for (int it = 0; it < RPG; ++it) {  // no early exit: the iterations are independent and interleave
@@ -313,6 +301,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
           s1[it] += __shfl_xor_sync(0xffffffffu, s1[it], o);
           s2[it] += __shfl_xor_sync(0xffffffffu, s2[it], o);
         }
+      cluster_wait_entry();
 #pragma unroll
       for (int it = 0; it < RPG; ++it) {
         const int r = (tid >> 3) + it * (NT / 8);
@@ -321,7 +310,6 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
     }
   }
   __syncthreads();
-  B200_STAMP(3);
   pdl_trigger();  // the next kernel may start its weight prefetch while this one multiplies
 
   // ---- multiply: consecutive MMAs go to different accumulators (up to 8 row tiles in flight) ----------------------
@@ -398,11 +386,11 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
       }
     }
   }
-  B200_STAMP(4);
 
   // ---- partial tile -> the CTAs that own its channels (distributed shared memory), one cluster barrier ------------
   // Straight from the accumulators: a warp's store instruction covers 8 consecutive channels (32 bytes) of 4 rows,
   // all owned by one CTA of the cluster.
+  if constexpr (LN == 0) cluster_wait_entry();  // with a LayerNorm the statistics were the first remote stores
   {
     const int ch0 = warp * 16 + g, ch1 = ch0 + 8;
     float* dst0 = cluster.map_shared_rank(recv, ch0 / CPR) + rank * MB * CPR + ch0 % CPR;
@@ -438,9 +426,7 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
       lb_pre = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
     }
   }
-  B200_STAMP(5);
   cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this
-  B200_STAMP(6);
 
   const int padded = (items + 31) & ~31;
   for (int it = tid; it < padded; it += NT) {
@@ -538,7 +524,6 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
       }
     }
   }
-  B200_STAMP(7);
 }
 
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
@@ -550,13 +535,7 @@ int launch_one(const LinArgs& a, bool pdl, cudaStream_t stream, bool deal = fals
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear: smem attribute: %s", cudaGetErrorString(e));
   const dim3 grid(KSPLIT, a.N / (NW * 16), deal ? (a.rows + MB - 1) / MB : 1);  // deal: MB rows per CTA
-#ifdef B200DEC_TIMELINE
-  LinArgs b = a;
-  b.stamps = timeline_next(grid.x * grid.y, (LN ? 2000000 : 1000000) + a.N / 16 * 1000 + KSLICE * KSPLIT / 16);
-  e = launch_kernel(kern, grid, dim3(NW * 32), S::TOTAL, stream, KSPLIT, pdl, b);
-#else
   e = launch_kernel(kern, grid, dim3(NW * 32), S::TOTAL, stream, KSPLIT, pdl, a);
-#endif
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear launch: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -568,20 +547,18 @@ int launch_mb(const LinArgs& a, bool pdl, cudaStream_t s) {
   // several CTAs per tile that share an SM (grid.z), so that eight or more warps instead of four feed the SM's tensor
   // pipes, each CTA stages a fraction of the operand and several latency chains overlap. Measured at 64 rows: p50 step
   // 0.504 -> 0.467 ms. fc2 (K slices of 512, 140 registers): two CTAs of 32 rows; the K = 1024 ones (slices of 128, 94
-  // registers): four CTAs of 16 rows, above 64 rows four of 32. B200DEC_ROW_DEAL masks the groups for A/B runs
-  // (1 fc2, 2 o / cross-o, 4 cross-q, 16 the 16-row form, 32 above 64 rows; 8 the 8-warp LayerNorm readers, off).
-  if constexpr (!SPLIT && (LN == 0 || LN == 2) && WT != B200DEC_W_BF16 &&
-                (((KSLICE == 512 || KSLICE == 128) && KSPLIT == 8 && NW == 4) ||
-                 (KSLICE == 256 && KSPLIT == 4 && NW == 8 && LN == 2))) {
-    static const int deal_rows = getenv("B200DEC_ROW_DEAL") ? atoi(getenv("B200DEC_ROW_DEAL")) : 1 + 2 + 4 + 16 + 32;
-    const int bit = NW == 8 ? 8 : KSLICE == 512 ? 1 : LN == 0 ? 2 : 4;
-    if ((deal_rows & bit) && !a.head) {
+  // registers): four CTAs of 16 rows, above 64 rows four of 32. (The 8-warp LayerNorm readers measured no gain from
+  // dealing and keep one CTA per tile.)
+  if constexpr (!SPLIT && (LN == 0 || LN == 2) && WT != B200DEC_W_BF16 && (KSLICE == 512 || KSLICE == 128) &&
+                KSPLIT == 8 && NW == 4) {
+    if (!a.head) {
       if (a.rows > 32 && a.rows <= 64) {
-        if (KSLICE == 128 && (deal_rows & 16)) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s, true);
+        if (KSLICE == 128) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 16>(a, pdl, s, true);
         return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s, true);
       }
-      if (a.rows > 64 && KSLICE == 128 && (deal_rows & 32))
-        return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s, true);
+      // above 64 rows: four CTAs of 32 rows per tile, also for fc2 (the weights come from HBM once; a 128-row tile
+      // of K slices of 512 would fill an SM's shared memory, and two passes of 64 rows would read the weights twice)
+      if (a.rows > 64) return launch_one<WT, SPLIT, LN, NW, KSLICE, KSPLIT, 32>(a, pdl, s, true);
     }
   }
   if (a.rows <= 64) {

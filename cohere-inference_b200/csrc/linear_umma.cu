@@ -48,6 +48,8 @@ struct UArgs {
   int* status;
   float ln_eps;
   int lda, ldo, rows, N, K, out_kind, act, stats_slots;
+  uint32_t wait_limit;  // polls before the wait for the MMAs gives up
+  int withhold;         // tests only: the commit is left out, so that wait runs out
 };
 
 // MB: row capacity (MMA N); KSPLIT: CTAs per cluster; NKB: 64-k blocks per CTA
@@ -64,9 +66,9 @@ DEVI uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_share
 DEVI void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 DEVI void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 DEVI void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-DEVI bool mbar_wait(uint64_t* bar, uint32_t parity) {  // bounded; false when the limit ran out
+DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {  // bounded; false when the limit ran out
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
@@ -146,6 +148,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   __shared__ __align__(8) uint64_t d_full;
   __shared__ uint32_t tmem_base;
 
+  cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = blockIdx.x, tile = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -192,6 +195,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
       for (int i = 0; i < 4; ++i)
         v[j][i] = (r < p.rows && lane + 32 * i < p.stats_slots) ? __ldcg(part + lane + 32 * i) : make_float2(0.f, 0.f);
     }
+    cluster_wait_entry();
 #pragma unroll
     for (int j = 0; j < RPW; ++j) {
       const int r = rank + KSPLIT * (warp + 8 * j);
@@ -229,13 +233,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
 #pragma unroll
       for (int k = 0; k < KB / 16; ++k) umma_f16<MB>(tmem_d, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), (b | k) != 0);
     }
-    umma_commit(&d_full);
+    if (!p.withhold) umma_commit(&d_full);
   }
-  const bool got = mbar_wait(&d_full, 0);
+  const bool got = mbar_wait(&d_full, 0, p.wait_limit);
   if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
   tc_fence_after();
 
   // ---- partial tile -> the CTAs that own its channels (CPR consecutive channels each) ---------------------------------
+  if constexpr (!LN) cluster_wait_entry();  // with a LayerNorm the statistics were the first remote stores
   {
     float* dst = cluster.map_shared_rank(recv, ch / CPR) + (size_t)rank * MB * CPR + ch % CPR;
 #pragma unroll
@@ -387,6 +392,7 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
     }
     p.lda = lda, p.ldo = ldo, p.rows = rows - r0 < pass ? rows - r0 : pass, p.N = w->n, p.K = w->k;
     p.out_kind = out_kind, p.act = act;
+    p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, ln != nullptr, pdl, s);

@@ -25,31 +25,8 @@ int check_launch(const char* what) {
   return 0;
 }
 
-#ifdef B200DEC_TIMELINE
-static long long* g_tl_base = nullptr;
-static long long g_tl_cap = 0, g_tl_used = 0;
-static int g_tl_n = 0, g_tl_kind[4096], g_tl_ctas[4096];
-static long long g_tl_off[4096];
-long long* timeline_next(int ctas, int kind) {
-  if (!g_tl_base || g_tl_n >= 4096 || g_tl_used + (long long)ctas * 12 > g_tl_cap) return nullptr;
-  long long* at = g_tl_base + g_tl_used;
-  g_tl_kind[g_tl_n] = kind, g_tl_ctas[g_tl_n] = ctas, g_tl_off[g_tl_n] = g_tl_used, ++g_tl_n;
-  g_tl_used += (long long)ctas * 12;
-  return at;
-}
-#endif
 }  // namespace b200dec_detail
 
-#ifdef B200DEC_TIMELINE
-extern "C" void b200dec_timeline_set(long long* base, long long capacity) {
-  g_tl_base = base, g_tl_cap = capacity, g_tl_used = 0, g_tl_n = 0;
-}
-extern "C" int b200dec_timeline_get(int* kinds, int* ctas, long long* offsets, int max) {
-  const int n = g_tl_n < max ? g_tl_n : max;
-  for (int i = 0; i < n; ++i) kinds[i] = g_tl_kind[i], ctas[i] = g_tl_ctas[i], offsets[i] = g_tl_off[i];
-  return n;
-}
-#endif
 
 namespace {
 
@@ -105,10 +82,14 @@ struct SchedArgs {
   int* sched_cross;
   int* status;
   int slots, seq, frames, rows;
+  int prefetch_keys;     // most keys (over all rows of a table) marked for prefetch into L2; 0: none
 };
 
 DEVI void rank_rows(const SchedArgs& p, const int* len, bool self, int* out, int* t_s, int* t_n) {
   const int cap = self ? p.seq : p.frames;
+  __shared__ int s_total;
+  if (threadIdx.x == 0) s_total = 0;
+  __syncthreads();
   for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
     int s = p.active[r];
     if (s < 0 || s > p.slots) {
@@ -121,13 +102,19 @@ DEVI void rank_rows(const SchedArgs& p, const int* len, bool self, int* out, int
       n = self ? max(0, min(n, cap - 1)) : max(1, min(n, cap));
     }
     t_s[r] = s, t_n[r] = n;
+    atomicAdd(&s_total, n);
   }
   __syncthreads();
+  const int total = s_total;
   for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
     const int n = t_n[r];
     int rank = 0;
     for (int j = 0; j < p.rows; ++j) rank += (t_n[j] > n) || (t_n[j] == n && j < r);  // ties by row
-    *reinterpret_cast<int4*>(out + 4 * rank) = make_int4(r, t_s[r], n, 0);
+    // the row's share of the prefetch budget: all its keys when the launch fits, else in proportion (whole 1 KB runs)
+    int pf = 0;
+    if (p.prefetch_keys > 0)
+      pf = total <= p.prefetch_keys ? n : (int)((long long)n * p.prefetch_keys / total) & ~7;
+    *reinterpret_cast<int4*>(out + 4 * rank) = make_int4(r, t_s[r], n, pf);
   }
   __syncthreads();
 }
@@ -456,14 +443,15 @@ int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos,
                   const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1, float* x,
                   void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream, const int32_t* cross_len,
                   int seq, int frames, int32_t* sched_self, int32_t* sched_cross, void* x16, const float* next_gamma,
-                  float* stats) {
+                  float* stats, int prefetch_keys) {
   B200_REQUIRE(active && tok && pos && embed && pos_table && x && status && ln0.w && ln0.b && (!hn || (ln1.w && ln1.b)),
                "embed_ln: null pointer");
   B200_REQUIRE(rows >= 1, "embed_ln: rows %d", rows);
   B200_REQUIRE(!x16 || (next_gamma && stats), "embed_ln: the fp16 operand needs the next gamma and a place for the sums");
   const bool sched = (sched_self || sched_cross) && rows <= SCHED_MAX_ROWS;
   B200_REQUIRE(!sched || !sched_cross || cross_len, "embed_ln: a cross schedule needs the frame counts");
-  EmbedArgs p{SchedArgs{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, sched ? rows : 0},
+  EmbedArgs p{SchedArgs{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, sched ? rows : 0,
+                        prefetch_keys},
               active, tok, pos, (const __nv_bfloat16*)embed, (const __nv_bfloat16*)pos_table, ln0, ln1, x, x16, next_gamma,
               stats, hn, status, vocab, max_pos, slots, hn_kind, rows};
   const cudaError_t e = launch_kernel(embed_ln_kernel, dim3((rows + 3) / 4 + (sched ? 1 : 0)), dim3(128), 0,
@@ -506,7 +494,7 @@ int b200dec_embed_ln(const int32_t* active, const int64_t* tok, const int32_t* p
                      const void* pos_table, int vocab, int max_pos, int slots, b200dec_norm ln0, b200dec_norm ln1,
                      float* x, void* hn, int hn_kind, int rows, int32_t* status, int pdl, void* stream) {
   return embed_ln_impl(active, tok, pos, embed, pos_table, vocab, max_pos, slots, ln0, ln1, x, hn, hn_kind, rows, status,
-                       pdl, stream, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr);
+                       pdl, stream, nullptr, 0, 0, nullptr, nullptr, nullptr, nullptr, nullptr, 0);
 }
 
 int b200dec_ln_rows16(const float* x, const float* gamma, int rows, void* out16, float* stats, void* stream) {
@@ -517,12 +505,13 @@ int b200dec_ln_rows16(const float* x, const float* gamma, int rows, void* out16,
 }
 
 int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_t* cross_len, int slots, int seq,
-                         int frames, int rows, int32_t* sched_self, int32_t* sched_cross, int32_t* status,
-                         void* stream) {
+                         int frames, int rows, int prefetch_keys, int32_t* sched_self, int32_t* sched_cross,
+                         int32_t* status, void* stream) {
   B200_REQUIRE(active && status && (sched_self || sched_cross), "row_schedule: null pointer");
   B200_REQUIRE((!sched_self || pos) && (!sched_cross || cross_len), "row_schedule: a table without its lengths");
   B200_REQUIRE(rows >= 1 && rows <= SCHED_MAX_ROWS, "row_schedule: rows %d (1..%d)", rows, SCHED_MAX_ROWS);
-  SchedArgs p{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, rows};
+  B200_REQUIRE(prefetch_keys >= 0, "row_schedule: prefetch_keys %d", prefetch_keys);
+  SchedArgs p{active, pos, cross_len, sched_self, sched_cross, status, slots, seq, frames, rows, prefetch_keys};
   const cudaError_t e = launch_kernel(row_schedule_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 0, 0, p);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "row_schedule launch: %s", cudaGetErrorString(e));
   return 0;

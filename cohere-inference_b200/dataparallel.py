@@ -14,7 +14,8 @@ import torch
 import torch.distributed as dist
 
 STAT_FIELDS = ("steps", "row_steps", "padded_row_steps", "slot_steps", "admitted", "evicted", "new_tokens",
-               "delivered_tokens", "bytes", "h2d_bytes", "d2h_bytes", "elapsed_us", "gpu_us")
+               "delivered_tokens", "bytes", "h2d_bytes", "d2h_bytes", "elapsed_us", "gpu_us", "steady_row_steps",
+               "steady_slot_steps", "p50_step_ns")
 
 
 def env_world() -> tuple[int, int, int]:
@@ -49,7 +50,7 @@ def partition(requests: list, rank: int, world: int) -> list:
 
 
 def gather_stats(stats: dict, device: torch.device | str = "cpu") -> list[dict]:
-    """Every rank's stats (STAT_FIELDS, missing = 0) on every rank; one all_gather of 13 int64."""
+    """Every rank's stats (STAT_FIELDS, missing = 0) on every rank; one all_gather of 16 int64."""
     vec = torch.tensor([int(stats.get(k, 0)) for k in STAT_FIELDS], dtype=torch.int64, device=device)
     if dist.is_initialized() and dist.get_world_size() > 1:
         out = [torch.zeros_like(vec) for _ in range(dist.get_world_size())]

@@ -33,8 +33,8 @@ class Norm(C.Structure):
 
 
 class LnLink(C.Structure):
-    _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32), ("_pad", i32),
-                ("status", vp)]
+    _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32),
+                ("wait_limit", i32), ("status", vp), ("withhold", i32), ("_pad", i32)]
 
 
 class Layer(C.Structure):
@@ -48,6 +48,7 @@ class Plan(C.Structure):
                 ("slots", i32), ("seq", i32), ("frames", i32), ("vocab", i32),
                 ("max_prompt", i32), ("out_cols", i32), ("pad", i32), ("eos", i32),
                 ("a_kind", i32), ("max_pos", i32), ("head_a_kind", i32), ("pdl", i32), ("attn_ring", i32), ("kv_int8", i32),
+                ("kv_prefetch_mb", i32), ("wait_limit", i32), ("withhold", i32), ("classes", i32),
                 ("embed", vp), ("pos_table", vp), ("emb_ln", Norm), ("final_ln", Norm), ("layer", C.POINTER(Layer)),
                 ("head", Weight),
                 ("active", vp), ("tok", vp), ("pos", vp), ("plen", vp), ("limit", vp), ("cross_len", vp),
@@ -61,6 +62,7 @@ class Plan(C.Structure):
 PROTOTYPES = {
     "b200dec_last_error": (C.c_char_p, []),
     "b200dec_version": (C.c_int, []),
+    "b200dec_sizeof": (C.c_int, [C.c_int]),
     "b200dec_quantize_rows": (C.c_int, [vp, C.c_int, C.c_int, vp, vp, vp]),
     "b200dec_prepare_w8": (C.c_int, [vp, C.c_int, C.c_int, vp, vp, vp]),
     "b200dec_prune24": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
@@ -98,7 +100,7 @@ PROTOTYPES = {
                                               C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_scatter_kv_q8": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                         vp]),
-    "b200dec_row_schedule": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]),
+    "b200dec_row_schedule": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]),
     "b200dec_attention_paired": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, f32, vp,
                                            C.c_int, C.c_int, C.c_int, vp]),
     "b200dec_attention_ring": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
@@ -106,6 +108,9 @@ PROTOTYPES = {
     "b200dec_attention_static": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                            f32, vp, C.c_int, C.c_int, vp, C.c_int, vp]),
     "b200dec_scatter_kv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+    "b200dec_admit": (C.c_int, [C.POINTER(Plan), vp, C.c_int, vp, C.c_int, vp]),
+    "b200dec_admit_record_ints": (C.c_int, [C.c_int]),
+    "b200dec_compact_active": (C.c_int, [C.POINTER(Plan), C.c_int, vp, C.c_int, vp]),
     "b200dec_step": (C.c_int, [C.POINTER(Plan), C.c_int, vp]),
     "b200dec_step_rows": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_int, vp]),
     "b200dec_step_launches": (C.c_int, [C.POINTER(Plan), C.c_int]),
@@ -129,6 +134,10 @@ def lib() -> C.CDLL:
         for name, (res, args) in PROTOTYPES.items():
             fn = getattr(handle, name)
             fn.restype, fn.argtypes = res, args
+        for which, struct in enumerate((Weight, Norm, Layer, Plan, LnLink)):  # this binding against the built library
+            if handle.b200dec_sizeof(which) != C.sizeof(struct):
+                raise NativeError(f"{struct.__name__}: {C.sizeof(struct)} bytes here, {handle.b200dec_sizeof(which)} "
+                                  f"in {LIB_PATH}: rebuild the library (build.py --force)")
         _lib = handle
     return _lib
 

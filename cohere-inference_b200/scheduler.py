@@ -13,6 +13,10 @@ over any object with the StreamDecoder API:
     free the slot only when that copy has completed (pipeline.py:223-239);
   * the delivered tokens are out[:plen + (first eos + 1 | min(len, max_new))] (pipeline.py:241-247).
 
+With a decoder whose active list lives on the device (`decoder.device_sched`: `admit` appends the new slots, every
+step drops the rows that ended) the host never sends a row list: it only picks the bucket that holds its own count of
+slots not yet evicted, which is never less than the device's live count.
+
 Requests arrive in virtual time measured in decoding steps (`request.arrival`), so a seeded stream gives the same
 schedule on every run; when nothing is live the clock jumps to the next arrival. The encoder of the reference is out
 of scope here: `memory_of(request)` supplies the encoder output (frames, enc_dim) of a request, on the host or the
@@ -34,6 +38,8 @@ class SchedulerStats:
     row_steps: int = 0          # live rows summed over steps (includes prompt-feeding steps and LAG re-runs)
     padded_row_steps: int = 0   # bucket sizes summed over steps
     slot_steps: int = 0         # slots * steps, the denominator of occupancy
+    steady_row_steps: int = 0   # the same two over the steady part of the stream: from the first step with 90 % of the
+    steady_slot_steps: int = 0  # slots live until the last request has been admitted (no ramp-up, no drain)
     admitted: int = 0
     evicted: int = 0
     new_tokens: int = 0         # generated (non-prompt) tokens delivered
@@ -48,6 +54,10 @@ class SchedulerStats:
     def occupancy(self) -> float:
         return self.row_steps / self.slot_steps if self.slot_steps else 0.0
 
+    @property
+    def steady_occupancy(self) -> float:
+        return self.steady_row_steps / self.steady_slot_steps if self.steady_slot_steps else 0.0
+
 
 class DecodeScheduler:
     LAG = 1
@@ -61,6 +71,9 @@ class DecodeScheduler:
         self.account_bytes = account_bytes
         self.trace = trace
         self.stats = SchedulerStats()
+        self.device_sched = bool(getattr(decoder, "device_sched", False))
+        self.step_ms: deque = deque(maxlen=4096)  # device time between the ends of consecutive steps, newest last
+        self._prev_ev = None
         cols = decoder.out.shape[1]
         if self.cuda:
             self.out_host = torch.zeros(decoder.slots + 1, cols, dtype=torch.long).pin_memory()
@@ -73,9 +86,18 @@ class DecodeScheduler:
     def _event(self):
         if not self.cuda:
             return None
-        ev = torch.cuda.Event()
+        ev = torch.cuda.Event(enable_timing=True)
         ev.record(self.dec.stream)
         return ev
+
+    def step_time_summary(self) -> dict:
+        """p50 / p90 / p99 / max of the recorded step times in ms (the reference keeps per-stage times in
+        Pipeline.stats, kernels/pipeline.py:82-83, 172-178)."""
+        if not self.step_ms:
+            return {}
+        v = np.sort(np.asarray(self.step_ms))
+        pick = lambda q: float(v[min(len(v) - 1, int(q * len(v)))])  # noqa: E731
+        return {"steps": len(v), "p50_ms": pick(0.5), "p90_ms": pick(0.9), "p99_ms": pick(0.99), "max_ms": float(v[-1])}
 
     def _flags(self) -> np.ndarray:
         f = self.dec.flags
@@ -131,7 +153,7 @@ class DecodeScheduler:
         steps: deque = deque()
         copies: deque = deque()
         pos_of: dict[int, int] = {}  # host mirror of each live slot's position, for byte accounting
-        step_no, clock, bucket, changed = 0, 0.0, 1, False
+        step_no, clock, bucket, changed, ramped = 0, 0.0, 1, False, False
         while waiting or active or copies or steps:
             # -- admit what has arrived and fits
             new_slots, new_idx, frames = [], [], 0
@@ -158,7 +180,7 @@ class DecodeScheduler:
             # -- one step over the live slots
             if active:
                 if changed:
-                    bucket = dec.set_active(active)
+                    bucket = dec.bucket(len(active)) if self.device_sched else dec.set_active(active)
                     changed = False
                 if self.account_bytes:
                     st.bytes += dec.step_bytes([pos_of[s] for s in active],
@@ -174,6 +196,10 @@ class DecodeScheduler:
                 st.row_steps += len(active)
                 st.padded_row_steps += bucket
                 st.slot_steps += dec.slots
+                ramped = ramped or len(active) >= 0.9 * dec.slots
+                if ramped and waiting:
+                    st.steady_row_steps += len(active)
+                    st.steady_slot_steps += dec.slots
                 st.bucket_steps[bucket] = st.bucket_steps.get(bucket, 0) + 1
                 step_no += 1
                 clock = max(clock, float(step_no))
@@ -185,6 +211,9 @@ class DecodeScheduler:
                 k, ev = steps.popleft()
                 if ev is not None:
                     ev.synchronize()
+                    if self._prev_ev is not None and self._prev_ev[0] == k - 1:
+                        self.step_ms.append(self._prev_ev[1].elapsed_time(ev))
+                    self._prev_ev = (k, ev)
                 flags = self._flags()
                 ended = [s for s in active if flags[s] and admitted_at[s] <= k]
                 if ended:
@@ -192,10 +221,12 @@ class DecodeScheduler:
                     active = [s for s in active if s not in gone]
                     changed = True
                     if self.cuda:
+                        torch.cuda.nvtx.range_push("b200dec.evict")
                         with torch.cuda.stream(dec.stream):
                             for s in ended:
                                 self._copy_out(s)
                             cev = self._event()
+                        torch.cuda.nvtx.range_pop()
                     else:
                         for s in ended:
                             self._copy_out(s)

@@ -8,16 +8,16 @@ is one CUDA-graph launch per bucket of row counts; the prompt is fed by the step
 end flags are copied to pinned host memory by the graph.
 
 What differs underneath: every kernel is hand-written CUDA for sm_100a behind a C-ABI (include/b200dec.h), there is no
-Triton and no cuBLAS on the step; `int8=True` quantises every projection (also o, cross q, cross o and the cross K/V
-projections), `ffn_sparse=True` additionally stores fc1/fc2 2:4; the residual stream is fp32; heads x head_dim may be
+Triton and no cuBLAS on the step; `int8=True` quantises every projection of the step (also o, cross q and cross o; the
+prefill's projections keep bf16 weights), `ffn_sparse=True` additionally stores fc1/fc2 2:4; the residual stream is fp32; heads x head_dim may be
 8 x 128 or 16 x 64 and the feed-forward activation ReLU or GELU (read from model.config).
 """
 
 from __future__ import annotations
 
 import ctypes as C
-import os
 
+import numpy as np
 import torch
 
 from . import native as nv
@@ -99,7 +99,8 @@ class StreamDecoder:
                  max_audio_s: float = 36.0, buckets=None, int8: bool = False, *, ffn_sparse: bool = False,
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
-                 head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True):
+                 head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True,
+                 kv_prefetch_mb: int = 0, device_sched: bool = False):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -110,7 +111,11 @@ class StreamDecoder:
         (False: launch the kernels directly, for debugging). chains: a step's rows are split into up to this many
         independent kernel chains that run concurrently (parallel branches of the graph), so that one chain's
         attention overlaps the others' projections; results do not depend on it. attn_ring: use the persistent
-        bulk-copy attention kernel (csrc/attention_ring.cu) instead of the one-CTA-per-(row, head) kernel."""
+        bulk-copy attention kernel (csrc/attention_ring.cu) instead of the one-CTA-per-(row, head) kernel.
+        kv_prefetch_mb: the projections between two attention launches start up to this many MB of the next launch's
+        keys and values on their way into L2 (0: off). device_sched: the active list lives on the device: `admit`
+        appends to it, every step drops the rows that ended and leaves the live count in `live` (pinned), so a
+        scheduler never calls set_active after an eviction."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
         dec, cfg = model.model.decoder, model.config
@@ -127,6 +132,8 @@ class StreamDecoder:
         self.scale = self.d ** -0.5
         self.int8, self.ffn_sparse, self.pdl, self.use_graphs = int8, ffn_sparse, pdl, graphs
         self.attn_ring = bool(attn_ring)
+        self.kv_prefetch_mb, self.device_sched = int(kv_prefetch_mb), bool(device_sched)
+        assert not (self.device_sched and chains > 1), "the device-side active list goes with a single chain"
         self.act = ACTS[cfg.hidden_act]
         kind = nv.W_INT8 if int8 else nv.W_BF16
         ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
@@ -149,11 +156,12 @@ class StreamDecoder:
             head_kind = nv.W_INT8_UMMA if (head_umma and int8 and self.vocab % 128 == 0) else kind
             self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
                                     a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
-            # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection, kept as the
-            # fp32 values the quantised (or bf16) weights stand for
-            self.proj = _PrefillLinear(dequantized(dec.proj.weight, kind), f(dec.proj.bias))
+            # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection; these run
+            # once per request, not in the step, and keep bf16 weights in every mode, as the reference does
+            # (kernels/stream_decoder.py:91-94, 232)
+            self.proj = _PrefillLinear(dequantized(dec.proj.weight, nv.W_BF16), f(dec.proj.bias))
             self.cross = _PrefillLinear(
-                torch.cat([dequantized(w, kind) for layer in dec.layers
+                torch.cat([dequantized(w, nv.W_BF16) for layer in dec.layers
                            for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)]),
                 torch.cat([f(b) for layer in dec.layers
                            for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)]))
@@ -168,28 +176,32 @@ class StreamDecoder:
             # mode (stream_decoder.py:102-115); otherwise bf16
             self.kv_int8 = bool(kv_int8)
             assert not (self.kv_int8 and attn_ring), "the ring attention kernel reads bf16 caches only"
-            bf = dict(device=dev, dtype=torch.int8 if self.kv_int8 else torch.bfloat16)
-            self.self_k = torch.zeros(L, S + 1, self.h, self.seq, self.d, **bf)
-            self.self_v = torch.zeros_like(self.self_k)
-            self.cross_k = torch.zeros(L, S + 1, self.h, self.frames, self.d, **bf)
-            self.cross_v = torch.zeros_like(self.cross_k)
-            self.self_ks = self.self_vs = self.cross_ks = self.cross_vs = None
-            if self.kv_int8:
-                self.self_ks = torch.ones(L, S + 1, self.h, self.seq, device=dev)
-                self.self_vs = torch.ones_like(self.self_ks)
-                self.cross_ks = torch.ones(L, S + 1, self.h, self.frames, device=dev)
-                self.cross_vs = torch.ones_like(self.cross_ks)
+            # KV caches: (layer, slot incl. the dummy, head, position, dim); int8 caches carry one fp32 scale per vector
+            kv_dtype = torch.int8 if self.kv_int8 else torch.bfloat16
+            for name, cap in (("self", self.seq), ("cross", self.frames)):
+                for part in "kv":
+                    setattr(self, f"{name}_{part}", torch.zeros(L, S + 1, self.h, cap, self.d, device=dev, dtype=kv_dtype))
+                    setattr(self, f"{name}_{part}s",
+                            torch.ones(L, S + 1, self.h, cap, device=dev) if self.kv_int8 else None)
+            # slot state, one entry per slot and one for the dummy; names, types and initial values are those of the
+            # reference's StreamDecoder (kernels/stream_decoder.py:116-131), which is what its callers read
             i32 = dict(device=dev, dtype=torch.int32)
-            self.cross_len = torch.ones(S + 1, **i32)
-            self.tok = torch.full((S + 1,), self.pad, device=dev, dtype=torch.long)
-            self.pos = torch.zeros(S + 1, **i32)
-            self.plen = torch.ones(S + 1, **i32)
-            self.limit = torch.zeros(S + 1, **i32)
-            self.finished = torch.ones(S + 1, device=dev, dtype=torch.uint8)
-            self.forced = torch.full((S + 1, max_prompt), self.pad, device=dev, dtype=torch.long)
-            self.out = torch.full((S + 1, self.seq + 1), self.pad, device=dev, dtype=torch.long)
+            state = dict(cross_len=(torch.int32, (), 1), tok=(torch.long, (), self.pad), pos=(torch.int32, (), 0),
+                         plen=(torch.int32, (), 1), limit=(torch.int32, (), 0), finished=(torch.uint8, (), 1),
+                         forced=(torch.long, (max_prompt,), self.pad), out=(torch.long, (self.seq + 1,), self.pad))
+            for name, (dtype, tail, value) in state.items():
+                setattr(self, name, torch.full((S + 1, *tail), value, device=dev, dtype=dtype))
             self.active = torch.full((bm,), S, **i32)
             self.status = torch.zeros(1, **i32)
+            self.n_active = torch.zeros(1, **i32)  # device_sched: live rows at the front of `active`
+            self.live = torch.zeros(1, dtype=torch.int32).pin_memory()  # its copy after the newest finished step
+            # host -> device staging: packed admission records / row lists through a ring of pinned buffers
+            self._rec_ints = nv.lib().b200dec_admit_record_ints(max_prompt)
+            self._admit_cap = max(bm, 16)
+            self.admit_buf = torch.zeros(self._admit_cap * self._rec_ints, **i32)
+            self._ring = [(torch.zeros(self._admit_cap * self._rec_ints, dtype=torch.int32).pin_memory(),
+                           torch.cuda.Event()) for _ in range(8)]
+            self._ring_at = 0
             adt = torch.float16 if self.a_kind == nv.A_F16 else torch.float32
             f32 = dict(device=dev, dtype=torch.float32)
             self.x = torch.zeros(bm, self.width, **f32)
@@ -220,7 +232,7 @@ class StreamDecoder:
             self.chains = max(1, int(chains))
             self.side_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(self.chains - 1)]
             self._build_plan()
-            self.launches_per_step = lib.b200dec_step_launches(C.byref(self.plan), 1)
+            self.launches_per_step = lib.b200dec_step_launches(C.byref(self.plan), min(self.buckets))
             self.weight_bytes = sum(p.stream_bytes() for ly in self.layers for p in ly.projections()) + \
                 self.head.stream_bytes()
             if graphs:
@@ -258,10 +270,7 @@ class StreamDecoder:
                      "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
                      "xh", "ln_stats", "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
-        if os.environ.get("B200DEC_NO_XH"):  # tuning runs: the projections convert the fp32 rows themselves
-            p.xh = None
-        if os.environ.get("B200DEC_NO_SCHED"):  # tuning runs: rank the rows inside every attention launch instead
-            p.sched_self = p.sched_cross = None
+        p.kv_prefetch_mb = int(self.kv_prefetch_mb)
         self.plan = p
 
     def _step(self, b: int) -> None:
@@ -284,7 +293,16 @@ class StreamDecoder:
                     done = torch.cuda.Event()
                     done.record(side)
                     main.wait_event(done)
+        if self.device_sched:  # rows that ended leave the device's active list; the host learns the live count
+            nv.check(nv.lib().b200dec_compact_active(C.byref(self.plan), b, nv.ptr(self.n_active), int(self.pdl) & 1,
+                                                     nv.stream_ptr()))
+            self.live.copy_(self.n_active, non_blocking=True)
         self.flags.copy_(self.finished, non_blocking=True)
+
+    def launches(self, rows: int) -> int:
+        """Kernels one step of `rows` rows launches (summed over its chains)."""
+        count = nv.lib().b200dec_step_launches
+        return sum(count(C.byref(self.plan), n) for _, n in self.row_ranges(rows)) + (1 if self.device_sched else 0)
 
     def row_ranges(self, b: int) -> list[tuple[int, int]]:
         """The (first row, rows) of the concurrent chains a step of b rows is split into: at most `chains` ranges of
@@ -299,28 +317,39 @@ class StreamDecoder:
 
     @torch.no_grad()
     def _capture(self) -> None:
+        """One CUDA graph per bucket, largest first so that the graphs share one memory pool sized by the largest.
+        Each bucket runs once directly before its capture: that sets the kernels' attributes and surfaces launch
+        errors where they can be reported."""
         pool = torch.cuda.graph_pool_handle()
         with torch.cuda.device(self.device), torch.cuda.stream(self.stream):
-            for b in reversed(self.buckets):
-                self._step(b)  # sets the kernels' shared-memory attributes and surfaces launch errors before capture
-                torch.cuda.current_stream().synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool=pool, stream=self.stream):
-                    self._step(b)
-                self.graphs[b] = g
-            self.reset()
+            for rows in sorted(self.buckets, reverse=True):
+                self._step(rows)
+                self.stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=pool, stream=self.stream):
+                    self._step(rows)
+                self.graphs[rows] = graph
+        self.reset()
         self.stream.synchronize()
         self.check_status()
 
+    def capture_classes(self, mask: int) -> None:
+        """A timing aid: from now on a step launches only the kernels of `mask` (b200dec_plan.classes: 1 embedding,
+        vocabulary projection and pick, 2 layer projections, 4 attention; 0 = the whole step again). The graphs are
+        captured anew and every slot is reset; results of partial steps are meaningless."""
+        self.plan.classes = int(mask)
+        if self.use_graphs:
+            self._capture()
+        else:
+            self.reset()
+
     def reset(self) -> None:
-        """All slots free (on the decoder stream)."""
+        """Every slot free and every row on the dummy slot (on the decoder stream). The dummy keeps position 0 and
+        one frame, so the rows that pad a bucket always have a key to attend."""
         with torch.cuda.stream(self.stream):
-            self.finished.fill_(1)
-            self.pos.zero_()
-            self.cross_len.fill_(1)
-            self.active.fill_(self.dummy)
-            self.status.zero_()
-            self.attn_count.zero_()
+            for t, v in ((self.finished, 1), (self.pos, 0), (self.cross_len, 1), (self.active, self.dummy),
+                         (self.status, 0), (self.attn_count, 0), (self.n_active, 0)):
+                t.fill_(v)
 
     def check_status(self) -> None:
         """Synchronises the decoder stream and raises if a kernel met an index outside its tables (the kernels clamp
@@ -336,75 +365,73 @@ class StreamDecoder:
             raise nv.NativeError("decoder kernels reported: " + ", ".join(names))
 
     # ---- host side -----------------------------------------------------------------------------------------------
+    # Everything the host sends per call is packed into one pinned staging buffer and crosses in one asynchronous
+    # copy; the slot fields are then written by one kernel (csrc/slots.cu). Same effects as the reference's methods
+    # (kernels/stream_decoder.py:226-276).
 
     def bucket(self, rows: int) -> int:
-        return next(b for b in self.buckets if b >= rows)
+        """The smallest captured row count that holds `rows` rows."""
+        for b in self.buckets:
+            if b >= rows:
+                return b
+        raise ValueError(f"{rows} rows exceed the largest bucket {self.buckets[-1]}")
 
-    @torch.no_grad()
-    def fill_cross(self, hidden: torch.Tensor, lengths: list[int], slots: list[int]) -> None:
-        """Cross-attention keys and values of packed encoder frames (sum(lengths), enc_dim) into the given slots, on
-        the current stream (the caller orders the decoder stream after it)."""
-        assert hidden.shape[0] == sum(lengths) and len(lengths) == len(slots)
-        assert all(1 <= n <= self.frames for n in lengths), "frames per piece outside 1..%d" % self.frames
-        assert all(0 <= s < self.slots for s in slots)
-        kv = self.cross(self.proj(hidden.float()))
-        slot_of = torch.repeat_interleave(torch.tensor(slots, dtype=torch.int32), torch.tensor(lengths))
-        frame_of = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths])
-        slot_of, frame_of = slot_of.to(self.device, non_blocking=True), frame_of.to(self.device, non_blocking=True)
-        if self.kv_int8:
-            nv.check(nv.lib().b200dec_scatter_kv_q8(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
-                                                    nv.ptr(self.cross_v), nv.ptr(self.cross_ks), nv.ptr(self.cross_vs),
-                                                    kv.shape[0], len(self.layers), self.slots + 1, self.h, self.d,
-                                                    self.frames, nv.stream_ptr()))
-        else:
-            nv.check(nv.lib().b200dec_scatter_kv(nv.ptr(kv), nv.ptr(slot_of), nv.ptr(frame_of), nv.ptr(self.cross_k),
-                                                 nv.ptr(self.cross_v), kv.shape[0], len(self.layers), self.slots + 1,
-                                                 self.h, self.d, self.frames, nv.stream_ptr()))
-        kv.record_stream(torch.cuda.current_stream())
-
-    def admit(self, slots: list[int], prompts: list[torch.Tensor], frames: list[int],
-              max_new: list[int] | None = None) -> None:
-        """Start decoding in the given slots (on the decoder stream): the prompt forced, cross_len frames of audio."""
-        n = len(slots)
-        assert all(0 <= s < self.slots for s in slots) and all(1 <= len(p) <= self.max_prompt for p in prompts)
-        assert all(1 <= f <= self.frames for f in frames)
-        new = max_new or [self.max_new_tokens] * n
-        assert all(1 <= m <= self.max_new_tokens for m in new)
-        idx = torch.tensor(slots, dtype=torch.long)
-        forced = torch.full((n, self.max_prompt), self.pad, dtype=torch.long)
-        plen = torch.tensor([len(p) for p in prompts], dtype=torch.int32)
-        for i, p in enumerate(prompts):
-            forced[i, :len(p)] = torch.as_tensor(p, dtype=torch.long)
-        limit = plen - 1 + torch.tensor(new, dtype=torch.int32)
+    def _stage(self, values: np.ndarray, dst: torch.Tensor) -> None:
+        """int32 values -> dst (device int32, at least as long) through the pinned ring, on the decoder stream."""
+        n = int(values.size)
+        buf, ev = self._ring[self._ring_at]
+        self._ring_at = (self._ring_at + 1) % len(self._ring)
+        ev.synchronize()  # the copy that last used this buffer (several calls ago) has long finished
+        buf.numpy()[:n] = values.reshape(-1)
         with torch.cuda.stream(self.stream):
-            d = lambda t: t.to(self.device, non_blocking=True)  # noqa: E731
-            di = d(idx)
-            self.forced[di] = d(forced)
-            self.out[di] = self.pad
-            self.out[di, :self.max_prompt] = d(forced)
-            self.tok[di] = d(forced[:, 0].contiguous())
-            self.pos[di] = 0
-            self.plen[di] = d(plen)
-            self.limit[di] = d(limit)
-            self.cross_len[di] = d(torch.tensor(frames, dtype=torch.int32))
-            self.finished[di] = 0
-        self.flags[idx] = 0
+            dst[:n].copy_(buf[:n], non_blocking=True)
+            ev.record(self.stream)
+
+    def admit(self, slots: list[int], prompts: list, frames: list[int], max_new: list[int] | None = None) -> None:
+        """Start decoding in `slots`: each gets its prompt (fed token by token as forced choices), its number of
+        encoder frames and its new-token budget (max_new_tokens when not given). On the decoder stream."""
+        n = len(slots)
+        budgets = list(max_new) if max_new else [self.max_new_tokens] * n
+        if not (len(prompts) == len(frames) == len(budgets) == n):
+            raise ValueError("admit: one prompt, frame count and budget per slot")
+        rec = np.full((n, self._rec_ints), self.pad, np.int32)
+        for i, (s, p, f, m) in enumerate(zip(slots, prompts, frames, budgets)):
+            p = np.asarray(p, dtype=np.int64).reshape(-1)
+            if not (0 <= s < self.slots and 1 <= p.size <= self.max_prompt and 1 <= f <= self.frames
+                    and 1 <= m <= self.max_new_tokens):
+                raise ValueError(f"admit: slot {s}, prompt of {p.size}, {f} frames, {m} new tokens out of range")
+            rec[i, :4] = (s, p.size, m, f)
+            rec[i, 4:4 + p.size] = p
+        torch.cuda.nvtx.range_push("b200dec.admit")
+        for i0 in range(0, n, self._admit_cap):  # more requests than the staging buffer holds: several launches
+            part = rec[i0:i0 + self._admit_cap]
+            self._stage(part, self.admit_buf)
+            nv.check(nv.lib().b200dec_admit(C.byref(self.plan), nv.ptr(self.admit_buf), len(part),
+                                            nv.ptr(self.n_active) if self.device_sched else None, max(self.buckets),
+                                            self.stream.cuda_stream))
+        self.flags.numpy()[list(slots)] = 0
+        torch.cuda.nvtx.range_pop()
 
     def set_active(self, slots: list[int]) -> int:
-        """The active list for the next steps (on the decoder stream); returns the bucket."""
+        """The rows of the next steps = these slots, padded with the dummy slot to a bucket; returns the bucket."""
         b = self.bucket(max(1, len(slots)))
-        host = torch.full((b,), self.dummy, dtype=torch.int32)
-        host[:len(slots)] = torch.tensor(slots, dtype=torch.int32)
-        with torch.cuda.stream(self.stream):
-            self.active[:b].copy_(host.pin_memory(), non_blocking=True)
+        rows = np.full(b + 1, self.dummy, np.int32)
+        rows[:len(slots)] = slots
+        rows[b] = len(slots)
+        self._stage(rows[:b], self.active)
+        if self.device_sched:
+            self._stage(rows[b:], self.n_active)
         return b
 
     def step(self, bucket: int) -> None:
+        """One decoding step of `bucket` rows on the decoder stream (a graph replay)."""
+        torch.cuda.nvtx.range_push("b200dec.step")
         with torch.cuda.stream(self.stream):
             if self.use_graphs:
                 self.graphs[bucket].replay()
             else:
                 self._step(bucket)
+        torch.cuda.nvtx.range_pop()
 
     # ---- accounting ------------------------------------------------------------------------------------------------
 

@@ -164,3 +164,32 @@ def config1_inputs(seed: int = 0, batch: int = 1, frames: int = 125, prompt_len:
     memory = rng.standard_normal((batch, frames, hidden), dtype=np.float32)
     prompt = rng.integers(0, vocab, (batch, prompt_len)).astype(np.int64)
     return memory, prompt
+
+
+# The benchmark configurations as parity workloads: the golden generator (tests/golden/make_golden.py, transformers on
+# the CPU) and the GPU tests build their inputs from here, so both sides see the same numbers.
+PARITY_WORKLOADS = {
+    # name: (rows, frames (lo, hi), prompt tokens, new tokens, weight mode, int8 KV caches, input seed)
+    "config2": (8, (375, 375), 10, 448, "bf16", False, 1002),
+    "config3": (64, (50, 375), 10, 448, "int8", False, 1000),
+    "config3_kv8": (64, (50, 375), 10, 448, "int8", True, 1000),
+    "sparse128": (128, (50, 375), 10, 64, "int8_24", False, 1004),
+}
+
+
+def parity_workload(name: str, hidden: int = 1024, vocab: int = 16384) -> SimpleNamespace:
+    """Inputs of one benchmark configuration at full size: .rows, .frames (list), .memory (list of (frames, hidden)
+    fp32 arrays ~ N(0, 1)), .prompts (rows, plen) int64, .new, .mode (weight storage: bf16 / int8 / int8_24),
+    .kv_int8; all from numpy's PCG64 stream of the workload's seed."""
+    rows, (lo, hi), plen, new, mode, kv8, seed = PARITY_WORKLOADS[name]
+    rng = np.random.default_rng(seed)
+    frames = rng.integers(lo, hi + 1, rows).tolist()
+    memory = [rng.standard_normal((t, hidden), dtype=np.float32) for t in frames]
+    prompts = rng.integers(0, vocab, (rows, plen)).astype(np.int64)
+    return SimpleNamespace(name=name, rows=rows, frames=frames, memory=memory, prompts=prompts, new=new, mode=mode,
+                           kv_int8=kv8)
+
+
+def request_memory(req, hidden: int = 1024) -> np.ndarray:
+    """Encoder memory (frames, hidden) ~ N(0, 1) fp32 of a synthetic request, from its own seed."""
+    return np.random.default_rng(req.mem_seed).standard_normal((req.frames, hidden), dtype=np.float32)

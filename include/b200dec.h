@@ -83,6 +83,16 @@ typedef struct b200dec_plan {
   int32_t attn_ring, kv_int8;                /* attn_ring != 0: the attention kernels are b200dec_attention_ring;
                                                 kv_int8 != 0: int8 caches with per-vector scales (the layers'
                                                 self_ks .. cross_vs), attention by the *_q8 entry points */
+  int32_t kv_prefetch_mb;                    /* > 0 (and a step of rows * heads >= 512 with both schedules): the output
+                                                projection after self-attention starts the layer's cross keys and
+                                                values on their way into L2, the one after cross-attention the next
+                                                layer's self keys and values, up to this many MB per attention launch
+                                                (the projections leave HBM idle; L2 holds 126 MB); 0: off */
+  int32_t wait_limit, withhold;              /* as in b200dec_ln_link, for the step's tcgen05 kernels; withhold bit 0
+                                                the vocabulary projection, bit 1 the layer projections (tests only) */
+  int32_t classes;                           /* 0: the whole step. Else only these kernels are launched (a timing aid:
+                                                the results are then meaningless): 1 embedding + vocabulary projection
+                                                + pick, 2 the layer projections, 4 the attention kernels */
   const void* embed;  /* bf16 (vocab, 1024) */
   const void* pos_table; /* bf16 (max_pos, 1024) */
   b200dec_norm emb_ln, final_ln;
@@ -121,6 +131,9 @@ typedef struct b200dec_plan {
 
 const char* b200dec_last_error(void);
 int b200dec_version(void);
+/* sizeof the structures above as this library was compiled (which: 0 b200dec_weight, 1 b200dec_norm, 2 b200dec_layer,
+ * 3 b200dec_plan, 4 b200dec_ln_link), so that a binding in another language can check its own layout. */
+int b200dec_sizeof(int which);
 
 /* ---- packing (init time) ------------------------------------------------------------------------------------ */
 
@@ -177,9 +190,12 @@ typedef struct b200dec_ln_link {
   float* stats_out;
   const float* stats_in;
   int32_t stats_slots;
-  int32_t _pad;
+  int32_t wait_limit; /* B200DEC_W_INT8_UMMA: polls before the wait for the MMAs gives up; 0 = the default (2^22) */
   int32_t* status;  /* required with a B200DEC_W_INT8_UMMA weight (reader, producer or neither): the status word
                        that receives B200DEC_ST_TIMEOUT if the bounded wait for the MMAs ran out */
+  int32_t withhold; /* tests only, B200DEC_W_INT8_UMMA: nonzero leaves out the MMAs' completion signal, so the wait
+                       runs out, the status word gets B200DEC_ST_TIMEOUT and the kernel returns; 0 in production */
+  int32_t _pad;
 } b200dec_ln_link;
 int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                           void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,
@@ -234,13 +250,16 @@ int b200dec_attention_q8(int self, const int32_t* active, const float* q, int ld
                          int pdl, void* stream);
 /* The step's rows ranked by decreasing length, for b200dec_attention_paired: sched_self from pos[slot] (keys in the
  * self cache), sched_cross from cross_len[slot] (encoder frames); either table may be NULL. Entry i of a table is
- * int32 {row, slot, length, 0} of the row of rank i (ties by row), lengths clamped into 0..seq-1 / 1..frames and slots
- * into 0..slots with the status bits of b200dec_attention. rows <= 256. b200dec_step builds both tables with an extra
- * CTA of its embedding kernel; this entry point is for hosts that launch the kernels themselves. No counterpart in the
- * reference (its attention takes rows in batch order, kernels/csrc/dec_attn.cuh:84-188). */
+ * int32 {row, slot, length, prefetch} of the row of rank i (ties by row), lengths clamped into 0..seq-1 / 1..frames and
+ * slots into 0..slots with the status bits of b200dec_attention. prefetch = how many of the row's keys the projections
+ * before the attention launch bring into L2 ahead of it (see b200dec_plan.kv_prefetch_mb): all of them when the
+ * table's lengths add up to at most prefetch_keys, else in proportion; 0 with prefetch_keys = 0. rows <= 256.
+ * b200dec_step builds both tables with an extra CTA of its embedding kernel; this entry point is for hosts that launch
+ * the kernels themselves. No counterpart in the reference (its attention takes rows in batch order,
+ * kernels/csrc/dec_attn.cuh:84-188). */
 int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_t* cross_len, int slots, int seq,
-                         int frames, int rows, int32_t* sched_self, int32_t* sched_cross, int32_t* status,
-                         void* stream);
+                         int frames, int rows, int prefetch_keys, int32_t* sched_self, int32_t* sched_cross,
+                         int32_t* status, void* stream);
 /* b200dec_attention for a large batch (rows * heads >= 512 is where it pays), reading the rows from a schedule: the
  * i-th longest row and the i-th shortest share a cluster of two CTAs that read the same number of keys; the partial
  * of the long row's tail crosses distributed shared memory. Same results as b200dec_attention up to the order of the
@@ -278,6 +297,22 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
 int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
                           float* ck_scale, float* cv_scale, int nrows, int layers, int slots_plus_1, int heads,
                           int head_dim, int frames, void* stream);
+/* Admission of n requests in one launch. records: n packed records of b200dec_admit_record_ints(max_prompt) int32 in
+ * device memory (the host stages them in pinned memory and copies them over in one piece): {slot, prompt length,
+ * new-token budget, encoder frames, max_prompt token ids}. Per record: forced = the prompt padded with `pad`, out =
+ * the prompt then `pad`, tok = prompt[0], pos = 0, plen, limit = plen - 1 + budget, cross_len = frames, finished = 0.
+ * A slot outside 0..slots-1 is skipped, a prompt length or frame count out of range is clamped, both with a status bit.
+ * n_active != NULL: the slots are also appended, in record order, to plan->active at position *n_active (a device
+ * word, advanced by the kernel; max_rows = the list's capacity). Replaces StreamDecoder.admit
+ * (kernels/stream_decoder.py:241-263): one copy and one kernel instead of nine indexed writes and seven copies. */
+int b200dec_admit(const b200dec_plan* plan, const int32_t* records, int n, int32_t* n_active, int max_rows,
+                  void* stream);
+int b200dec_admit_record_ints(int max_prompt);
+/* Tail of a step when the active list lives on the device: the rows of plan->active[0 .. rows) whose slot has not
+ * ended move to the front in their order, the rest point at the dummy slot, *n_active = the live count. rows <= 128.
+ * With it a host never rebuilds the list on eviction (it reads the end flags and the count the step leaves in pinned
+ * memory); the flag scan and compaction of the reference's decoder thread (kernels/pipeline.py:217-231) on the GPU. */
+int b200dec_compact_active(const b200dec_plan* plan, int rows, int32_t* n_active, int pdl, void* stream);
 /* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
  * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
 int b200dec_step(const b200dec_plan* plan, int rows, void* stream);

@@ -70,18 +70,21 @@ LINEARS = ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_att
 def effective_weights(state: dict, layers: int, mode: str = "fp32", tables: str = "fp32") -> dict:
     """fp32 weights the GPU path is defined to compute with, from a transformers-style state dict of fp32 arrays.
 
-    mode: "fp32" as is; "bf16" every Linear weight rounded to bf16; "int8" every Linear weight (not the embeddings)
-    replaced by q * s of quantize_rows (dec_w8.cu:4-5: "exactly those of the dequantized weights"); "int8_24" the
-    same with mlp.fc1 / mlp.fc2 magnitude-pruned 2:4 first. The three projections of self-attention are quantised as
-    one fused (3d, d) matrix the way the reference fuses them (stream_decoder.py:56-57, 87-90): rows are independent,
-    so that equals quantising each alone. tables: "bf16" rounds the token and position tables to bf16 (how the GPU
-    stores them); Linear biases and LayerNorm parameters stay fp32."""
+    mode: "fp32" as is; "bf16" every Linear weight rounded to bf16; "int8" every Linear weight of the decoding step
+    (not the embeddings) replaced by q * s of quantize_rows (dec_w8.cu:4-5: "exactly those of the dequantized
+    weights"); "int8_24" the same with mlp.fc1 / mlp.fc2 magnitude-pruned 2:4 first. The weights of the prefill
+    (decoder.proj and the cross-attention k_proj / v_proj, which run once per request and not in the step) stay bf16
+    in the int8 modes, as the reference keeps them (stream_decoder.py:91-94, 232). The three projections of
+    self-attention are quantised as one fused (3d, d) matrix the way the reference fuses them (stream_decoder.py:56-57,
+    87-90): rows are independent, so that equals quantising each alone. tables: "bf16" rounds the token and position
+    tables to bf16 (how the GPU stores them); Linear biases and LayerNorm parameters stay fp32."""
     out = {k: np.asarray(v, dtype=F32) for k, v in state.items() if not k.startswith("model.encoder")}
     lin = [f"model.decoder.layers.{i}.{n}.weight" for i in range(layers) for n in LINEARS]
     lin += ["proj_out.weight", "model.decoder.proj.weight"]
     for k in lin:
         w = out[k]
-        if mode == "bf16":
+        prefill = k == "model.decoder.proj.weight" or ".encoder_attn.k_proj." in k or ".encoder_attn.v_proj." in k
+        if mode == "bf16" or (prefill and mode in ("int8", "int8_24")):
             out[k] = bf16_round(w)
         elif mode in ("int8", "int8_24"):
             if mode == "int8_24" and (".mlp.fc1." in k or ".mlp.fc2." in k):

@@ -12,6 +12,15 @@ decoder_small.npz  transformers' CohereAsrDecoder + proj_out (the reference's FA
 decoder_config1.npz  the same model class at the benchmark architecture (8 layers, 1024 wide, 16 heads x 64, GELU, vocab
               16384), batch 1, memory [1, 125, 1024], 10-token prompt + 64 forced new tokens, seed 0, fp32: greedy
               argmax of all 73 steps and the logits at every 64th vocabulary entry.
+decoder_config2.npz, decoder_config3.npz, decoder_config3_kv8.npz, decoder_sparse128.npz
+              the benchmark configurations at full size (cohere_inference_b200.synth.PARITY_WORKLOADS): the same
+              transformers model loaded with the weights the mode stores (bf16-rounded / int8-dequantised / 2:4-pruned
+              and dequantised, oracle.decoder.effective_weights), a padded batch with an encoder attention mask, greedy
+              with the prompt forced. Per row and step: the token fed, the un-forced argmax, the top logit, the gap to
+              the runner-up, and (every 4th step) the logits at every 256th vocabulary entry. The kv8 file keeps keys
+              and values the way an int8 cache does (a Cache subclass rounds them on entry, see RoundingCache).
+stream300.npz the first 300 requests of synthetic_requests(seed 0), each decoded greedily on its own (as one padded
+              batch) with the 2:4 model: the token sequence every request must deliver through the scheduler.
 """
 
 from __future__ import annotations
@@ -154,11 +163,143 @@ def make_config1() -> None:
                         top2_gap=np.sort(logits, -1)[:, -1] - np.sort(logits, -1)[:, -2])
 
 
+def effective_model(mode: str):
+    """transformers' model loaded with the fp32 values the GPU mode multiplies by."""
+    from oracle.decoder import effective_weights, state_to_numpy
+    synth = synthetic_model(0)
+    w = effective_weights(state_to_numpy(synth), synth.config.num_hidden_layers, mode, tables="bf16")
+    synth.load_state_dict({k: torch.from_numpy(v) for k, v in w.items()}, strict=False)
+    return hf_model(synth)
+
+
+def _bf16(t: torch.Tensor) -> torch.Tensor:
+    return t.to(torch.bfloat16).float()
+
+
+def _q8(t: torch.Tensor) -> torch.Tensor:
+    """What an int8 cache returns for vectors t (..., D): bf16-round, scale = absmax / 127 (1 for a zero vector),
+    q = rint(clamp(x * (1 / scale))), x ~ q * scale; all fp32 (kernels/csrc/dec_attn.cuh:46-63 of the reference)."""
+    t = _bf16(t)
+    mx = t.abs().amax(-1, keepdim=True)
+    sc = torch.where(mx > 0, mx / 127.0, torch.ones_like(mx))
+    q = torch.round(torch.clamp(t * (1.0 / sc), -127.0, 127.0))
+    return q * sc
+
+
+def rounding_caches():
+    """An EncoderDecoderCache whose keys and values are stored as an int8 cache would hold them. The step that appends
+    a self-attention pair attends it as the bf16 values (the reference's dec_attention_q8 does, dec_attn.cuh:100-106);
+    cross keys and values are read back quantised from their first use on."""
+    from transformers.cache_utils import DynamicCache, EncoderDecoderCache
+
+    class SelfQ8(DynamicCache):
+        def update(self, key_states, value_states, layer_idx, *a, **kw):
+            k, v = super().update(_q8(key_states), _q8(value_states), layer_idx, *a, **kw)
+            k, v = k.clone(), v.clone()
+            n = key_states.shape[2]
+            k[:, :, -n:], v[:, :, -n:] = _bf16(key_states), _bf16(value_states)
+            return k, v
+
+    class CrossQ8(DynamicCache):
+        def update(self, key_states, value_states, layer_idx, *a, **kw):
+            return super().update(_q8(key_states), _q8(value_states), layer_idx, *a, **kw)
+
+    return EncoderDecoderCache(SelfQ8(), CrossQ8())
+
+
+@torch.no_grad()
+def hf_batch_greedy(model, memory: list, prompts: np.ndarray, new, kv_int8: bool = False, sub_steps: int = 4,
+                    sub_vocab: int = 256, log=None) -> dict:
+    """Greedy decoding of a ragged batch on the CPU: memory[r] (T_r, d) zero-padded to the longest with an encoder
+    attention mask, the prompt forced, `new` tokens per row (an int, or one per row: rows past their end keep
+    stepping and are ignored). Returns per row and step the token fed, the un-forced argmax, the top logit and its
+    gap to the runner-up, every sub_steps-th step's logits at every sub_vocab-th entry, and the sequences."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    B, plen = prompts.shape
+    new = np.full(B, new) if np.isscalar(new) else np.asarray(new)
+    T, d = max(len(m) for m in memory), memory[0].shape[1]
+    mem, mask = torch.zeros(B, T, d), torch.zeros(B, T, dtype=torch.long)
+    for r, m in enumerate(memory):
+        mem[r, :len(m)] = torch.from_numpy(m)
+        mask[r, :len(m)] = 1
+    steps = plen - 1 + int(new.max())
+    dec, past = model.model.decoder, (rounding_caches() if kv_int8 else None)
+    tok = torch.from_numpy(prompts[:, :1].copy())
+    fed, am, top1, gap, sub = [], [], [], [], []
+    seq = np.zeros((B, plen + int(new.max())), np.int64)
+    seq[:, :plen] = prompts
+    for t in range(steps):
+        o = dec(input_ids=tok, encoder_hidden_states=mem, encoder_attention_mask=mask, past_key_values=past,
+                use_cache=True)
+        past = o.past_key_values
+        logits = model.proj_out(o.last_hidden_state[:, -1]).float()
+        v, i = logits.topk(2, -1)
+        a = logits.argmax(-1)
+        fed.append(tok[:, 0].numpy().copy()), am.append(a.numpy()), top1.append(v[:, 0].numpy())
+        gap.append((v[:, 0] - v[:, 1]).numpy())
+        if t % sub_steps == 0:
+            sub.append(logits[:, ::sub_vocab].numpy().copy())
+        nxt = torch.from_numpy(prompts[:, t + 1].copy()) if t + 1 < plen else a
+        seq[:, t + 1] = nxt.numpy()
+        tok = nxt[:, None]
+        if log and t % 50 == 0:
+            log(f"  step {t}/{steps}")
+    return dict(fed=np.stack(fed, 1).astype(np.int16), argmax=np.stack(am, 1).astype(np.int16),
+                top1=np.stack(top1, 1).astype(np.float32), gap=np.stack(gap, 1).astype(np.float32),
+                logits_sub=np.stack(sub, 1).astype(np.float32), seq=seq.astype(np.int16), new=new.astype(np.int32))
+
+
+def check_batched_equals_rows() -> None:
+    """The padded, masked batch gives each row what it gets alone (small model)."""
+    synth = synthetic_model(1, heads=4, head_dim=16, act="gelu", layers=2, hidden=64, ffn=128, vocab=96, max_pos=32,
+                            bias_std=0.05)
+    model = hf_model(synth)
+    rng = np.random.default_rng(3)
+    memory = [rng.standard_normal((t, 64), dtype=np.float32) for t in (7, 3, 5)]
+    prompts = rng.integers(0, 96, (3, 4)).astype(np.int64)
+    both = hf_batch_greedy(model, memory, prompts, 6, sub_steps=1, sub_vocab=1)
+    for r in range(3):
+        alone = hf_batch_greedy(model, memory[r:r + 1], prompts[r:r + 1], 6, sub_steps=1, sub_vocab=1)
+        assert np.array_equal(alone["seq"][0], both["seq"][r])
+        assert np.abs(alone["logits_sub"][0] - both["logits_sub"][r]).max() < 1e-5
+
+
+def make_workloads(names) -> None:
+    from cohere_inference_b200.synth import parity_workload
+    for name in names:
+        wl = parity_workload(name)
+        print(name, "rows", wl.rows, "mode", wl.mode, flush=True)
+        out = hf_batch_greedy(effective_model(wl.mode), wl.memory, wl.prompts, wl.new, kv_int8=wl.kv_int8,
+                              log=lambda m: print(m, flush=True))
+        np.savez_compressed(os.path.join(HERE, f"decoder_{name}.npz"), frames=np.array(wl.frames, np.int32),
+                            memory_checksum=np.float64(sum(float(m.astype(np.float64).sum()) for m in wl.memory)),
+                            **out)
+
+
+def make_stream(n: int = 300) -> None:
+    from cohere_inference_b200.synth import request_memory, synthetic_requests
+    reqs = synthetic_requests(2000, seed=0, slots=128)[:n]
+    out = hf_batch_greedy(effective_model("int8_24"), [request_memory(r) for r in reqs],
+                          np.stack([r.prompt for r in reqs]), [r.target for r in reqs], sub_steps=10 ** 6,
+                          log=lambda m: print(m, flush=True))
+    np.savez_compressed(os.path.join(HERE, "stream300.npz"), seq=out["seq"], new=out["new"], gap=out["gap"],
+                        frames=np.array([r.frames for r in reqs], np.int32))
+
+
 if __name__ == "__main__":
     if len(sys.argv) < 2:
-        sys.exit("usage: make_golden.py <path of the reference checkout>")
+        sys.exit("usage: make_golden.py <path of the reference checkout> [part ...]")
     ref = sys.argv[1]
-    make_packers(ref)
-    make_decoder_small()
-    make_config1()
+    only = sys.argv[2:]  # optional: the parts to (re)make
+    if not only or "packers" in only:
+        make_packers(ref)
+    if not only or "small" in only:
+        make_decoder_small()
+    if not only or "config1" in only:
+        make_config1()
+    check_batched_equals_rows()
+    from cohere_inference_b200.synth import PARITY_WORKLOADS
+    make_workloads([n for n in PARITY_WORKLOADS if not only or n in only])
+    if not only or "stream300" in only:
+        make_stream()
     print("ok", cib.__name__)

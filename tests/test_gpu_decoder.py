@@ -281,3 +281,86 @@ def test_full_size_run_properties(model16, name, rows, kw):
     print(f"{name}: alone vs in the batch, greedy agreement {min(agree):.4f} over {new} steps")
     # int8 caches: a last-bit difference in a key can move its quantised value by a whole step, so near-ties flip more
     assert min(agree) >= (0.99 if kw.get("kv_int8") else 0.995)
+
+
+@pytest.mark.parametrize("mode,kw,min_agree,max_err", [("int8", dict(int8=True), 0.85, 0.15),
+                                                        ("int8_24", dict(int8=True, ffn_sparse=True), 0.0, 10.0)])
+def test_config1_quantised_against_fp32_golden(model16, golden_dir, mode, kw, min_agree, max_err):
+    """What the quantisation itself costs: BASELINE config 1 with int8 (and 2:4) weights against the transformers run
+    on the ORIGINAL fp32 weights. The 2e-2 / 99.5 % bars of the other tests are against the weights a mode stores
+    (the reference's own definition, dec_w8.cu:4-5); this one is reported, with a loose gate for dense int8 and none
+    for 2:4 (magnitude pruning of random-init weights removes half of every feed-forward product)."""
+    g = np.load(os.path.join(golden_dir, "decoder_config1.npz"))
+    memory, prompt = config1_inputs(0)
+    seq = np.concatenate([prompt[0], g["argmax"][9:]]).astype(np.int64)  # 10 + 64 golden tokens
+    dec = _decoder(model16, slots=2, max_new_tokens=1, max_prompt=len(seq), max_audio_s=10.0, eos=-1, record=True, **kw)
+    lg, am = _run_teacher_forced(dec, [memory[0]], [seq], 73, [1])
+    err = np.abs(lg[:, 0, ::64] - g["logits_sub"]).max()
+    agree = (am[:, 0] == g["argmax"]).mean()
+    flips = g["top2_gap"][am[:, 0] != g["argmax"]]
+    print(f"config1 {mode} vs fp32 weights: max-abs logit error {err:.2e}, greedy agreement {agree:.4f}; golden top-2 "
+          f"gap: median {np.median(g['top2_gap']):.3f}, at the flipped steps {np.sort(flips)[:5]}")
+    assert err <= max_err and agree >= min_agree
+
+
+def test_admit_and_device_active_list_match_the_oracle(model16):
+    """b200dec_admit through the public method (one packed copy, one kernel) leaves the slot state the reference's
+    admit defines, and with device_sched the device's own active list follows admissions and ends."""
+    from oracle.decoder import StreamOracle, OracleConfig
+    dec = _decoder(model16, slots=6, max_new_tokens=8, max_prompt=5, max_audio_s=10.0, eos=-1, int8=True,
+                   device_sched=True)
+    so = StreamOracle({}, OracleConfig.of(model16.config), slots=6, max_new_tokens=8, max_prompt=5, frames=dec.frames,
+                      eos=-1)
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, 16384, n).astype(np.int64) for n in (5, 1, 3)]
+    slots, frames, new = [4, 0, 3], [50, 77, 126], [2, 8, 5]
+    with torch.cuda.stream(dec.stream):
+        dec.fill_cross(torch.randn(sum(frames), 1024, device="cuda"), frames, slots)
+    dec.admit(slots, prompts, frames, new)
+    so.admit(slots, prompts, frames, new)
+    dec.stream.synchronize()
+    for name in ("tok", "pos", "plen", "limit", "cross_len", "finished", "forced", "out"):
+        got, want = getattr(dec, name).cpu().numpy(), getattr(so, name)
+        keep = slots if name in ("tok", "plen", "limit", "forced", "out") else slice(None)
+        assert np.array_equal(got[keep], want[keep]), name
+    assert dec.flags.numpy()[slots].tolist() == [0, 0, 0]
+    assert int(dec.n_active.item()) == 3 and dec.active.cpu().tolist()[:3] == slots
+    # slot 4 ends after plen - 1 + 2 = 6 steps; the step that ends it also drops it from the device's list
+    b = dec.bucket(3)
+    for t in range(6):
+        dec.step(b)
+    dec.stream.synchronize()
+    assert dec.flags.numpy()[4] == 1 and int(dec.live.item()) == 2
+    assert dec.active.cpu().tolist()[:b] == [0, 3] + [dec.dummy] * (b - 2)
+    dec.admit([5], [prompts[1]], [60], [3])  # appended behind the live rows
+    dec.stream.synchronize()
+    assert dec.active.cpu().tolist()[:3] == [0, 3, 5] and int(dec.n_active.item()) == 3
+    dec.check_status()
+    with pytest.raises(ValueError):
+        dec.admit([9], [prompts[0]], [60])  # no such slot
+
+
+@pytest.mark.parametrize("bit,what", [(1, "vocabulary projection"), (2, "layer projections")])
+def test_bounded_wait_runs_out_and_the_context_survives(bit, what):
+    """The tcgen05 kernels bound every wait. With a short limit and the test-only `withhold` switch (the producer of
+    a barrier is left out, nothing faults and nothing is in flight), the wait runs out: the kernel returns, the status
+    word carries the time-out, check_status raises, and the next ordinary steps on the same context give the same
+    bits as before."""
+    from cohere_inference_b200 import native as nv
+    model = synthetic_model(0, layers=2)
+    rng = np.random.default_rng(5)
+    memory = [rng.standard_normal((60, 1024)).astype(np.float32) for _ in range(3)]
+    prompts = [rng.integers(0, 16384, 6).astype(np.int64) for _ in range(3)]
+    dec = _decoder(model, slots=4, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, record=True, int8=True,
+                   graphs=False)
+    want, _ = _run_teacher_forced(dec, memory, prompts, 4)
+    dec.admit([0, 1, 2], [torch.from_numpy(p) for p in prompts], [60] * 3)
+    dec.plan.wait_limit, dec.plan.withhold = 2048, bit
+    dec.step(dec.set_active([0, 1, 2]))
+    with pytest.raises(nv.NativeError, match="bounded wait"):
+        dec.check_status()
+    dec.plan.wait_limit, dec.plan.withhold = 0, 0
+    with torch.cuda.stream(dec.stream):
+        dec.status.zero_()
+    got, _ = _run_teacher_forced(dec, memory, prompts, 4)
+    assert np.array_equal(got, want), what

@@ -596,7 +596,7 @@ def test_row_schedule_and_paired_attention(nv, H, D, rows, self_):
     scale = D ** -0.5
     for _ in range(2):
         nv.check(lib.b200dec_row_schedule(nv.ptr(a_d), nv.ptr(n_d) if self_ else None, None if self_ else nv.ptr(n_d), S,
-                                          cap, cap, rows, nv.ptr(sched) if self_ else None,
+                                          cap, cap, rows, 0, nv.ptr(sched) if self_ else None,
                                           None if self_ else nv.ptr(sched), nv.ptr(status), nv.stream_ptr()))
         nv.check(lib.b200dec_attention_paired(self_, nv.ptr(sched), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), H, D, cap,
                                               scale, nv.ptr(out), nv.OUT_F32, rows, 0, nv.stream_ptr()))
@@ -628,7 +628,7 @@ def test_row_schedule_reports_bad_state(nv):
     lens = cuda(np.array([5, 400, 7, 1], np.int32))        # 400 frames > the capacity of 100
     sched = torch.zeros(3, 4, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    nv.check(lib.b200dec_row_schedule(nv.ptr(active), None, nv.ptr(lens), 3, 100, 100, 3, None, nv.ptr(sched),
+    nv.check(lib.b200dec_row_schedule(nv.ptr(active), None, nv.ptr(lens), 3, 100, 100, 3, 0, None, nv.ptr(sched),
                                       nv.ptr(status), nv.stream_ptr()))
     torch.cuda.synchronize()
     assert int(status.item()) == nv.ST_SLOT_RANGE | nv.ST_FRAMES_RANGE
@@ -705,7 +705,7 @@ def test_attention_q8(nv, H, D, rows, self_, paired):
     a_d, q_d, n_d = cuda(active), cuda(q), cuda(n)
     if paired:
         nv.check(lib.b200dec_row_schedule(nv.ptr(a_d), nv.ptr(n_d) if self_ else None, None if self_ else nv.ptr(n_d), S,
-                                          cap, cap, rows, nv.ptr(sched) if self_ else None,
+                                          cap, cap, rows, 0, nv.ptr(sched) if self_ else None,
                                           None if self_ else nv.ptr(sched), nv.ptr(status), nv.stream_ptr()))
         nv.check(lib.b200dec_attention_paired_q8(self_, nv.ptr(sched), nv.ptr(q_d), ld, nv.ptr(kd), nv.ptr(vd), nv.ptr(ksd),
                                                  nv.ptr(vsd), H, D, cap, scale, nv.ptr(out), nv.OUT_F32, rows, 0,

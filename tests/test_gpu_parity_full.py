@@ -1,0 +1,112 @@
+"""Parity at full size on a B200: the benchmark configurations (BASELINE configs 2, 3, 3 with int8 caches, and a
+128-row bucket of the 2:4 model) teacher-forced along the token sequences that transformers' fp32 decoder produced on
+the CPU for the weights each mode stores (tests/golden/decoder_<name>.npz, made by tests/golden/make_golden.py).
+Every row-step is compared: the un-forced argmax, the logit at the golden argmax, and at every 4th step the logits at
+every 256th vocabulary entry. Bars as the benchmark definition states them: max-abs logit error <= 2e-2, greedy
+agreement >= 99.5 %."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from cohere_inference_b200.synth import parity_workload, request_memory, synthetic_model, synthetic_requests
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2
+MODES = {"bf16": {}, "int8": dict(int8=True), "int8_24": dict(int8=True, ffn_sparse=True)}
+
+
+@pytest.fixture(scope="module")
+def model16():
+    return synthetic_model(0).cuda()
+
+
+@pytest.mark.parametrize("name", ["config2", "config3", "config3_kv8", "sparse128"])
+def test_teacher_forced_against_transformers_golden(model16, golden_dir, name):
+    from cohere_inference_b200 import StreamDecoder
+    wl = parity_workload(name)
+    g = np.load(os.path.join(golden_dir, f"decoder_{name}.npz"))
+    B, plen = wl.prompts.shape
+    total = plen + wl.new
+    steps = total - 1
+    seq = g["seq"].astype(np.int64)
+    assert seq.shape == (B, total) and g["argmax"].shape == (B, steps)
+    # the whole golden sequence goes in as a forced prompt, so every step feeds the golden token; the decoder records
+    # its own un-forced choice and the step's logits
+    dec = StreamDecoder(model16, slots=B, max_new_tokens=1, max_prompt=total, max_audio_s=30.0, buckets=(B,), eos=-1,
+                        record=True, kv_int8=wl.kv_int8, **MODES[wl.mode])
+    slots = list(range(B))
+    with torch.cuda.stream(dec.stream):
+        dec.fill_cross(torch.from_numpy(np.concatenate(wl.memory)).cuda(), wl.frames, slots)
+    dec.admit(slots, list(seq), wl.frames, [1] * B)
+    b = dec.set_active(slots)
+    assert b == B
+    gold_arg = torch.from_numpy(g["argmax"].astype(np.int64)).cuda()
+    gold_top = torch.from_numpy(g["top1"]).cuda()
+    gold_sub = torch.from_numpy(g["logits_sub"]).cuda()
+    rows = torch.arange(B, device="cuda")
+    agree = torch.zeros(B, steps, dtype=torch.bool, device="cuda")
+    err_top = torch.zeros(B, steps, device="cuda")
+    err_sub = torch.zeros(B, gold_sub.shape[1], device="cuda")
+    with torch.cuda.stream(dec.stream):
+        for t in range(steps):
+            dec.step(b)
+            agree[:, t] = dec.argmax[:B] == gold_arg[:, t]
+            err_top[:, t] = (dec.logits[rows, gold_arg[:, t]] - gold_top[:, t]).abs()
+            if t % 4 == 0:
+                err_sub[:, t // 4] = (dec.logits[:B, ::256] - gold_sub[:, t // 4]).abs().amax(1)
+    dec.stream.synchronize()
+    dec.check_status()
+    assert dec.pos.cpu().tolist()[:B] == [steps] * B
+    agree, err_top, err_sub = agree.cpu().numpy(), err_top.cpu().numpy(), err_sub.cpu().numpy()
+    gap = g["gap"]
+    rate = agree.mean()
+    # a disagreement where the golden's top two logits are further apart than twice the tolerance would be an error of
+    # its own; the others are near-ties that either side may resolve differently
+    wide = (~agree) & (gap > 2 * LOGIT_TOL)
+    worst = np.unravel_index(np.argmax(err_top), err_top.shape)
+    print(f"{name}: {B * steps} row-steps, greedy agreement {rate:.5f} ({(~agree).sum()} differ, largest golden gap "
+          f"among them {gap[~agree].max() if (~agree).any() else 0:.2e}), max-abs logit error {max(err_top.max(), err_sub.max()):.2e} "
+          f"(top logit: row {worst[0]} step {worst[1]}; sampled entries {err_sub.max():.2e})")
+    assert err_top.max() <= LOGIT_TOL and err_sub.max() <= LOGIT_TOL
+    assert rate >= 0.995
+    assert not wide.any()
+
+
+@pytest.mark.parametrize("device_sched", [False, True])
+def test_scheduler_stream_2to4_model_against_golden(model16, golden_dir, device_sched):
+    """BASELINE config 4 in small: 300 requests of the seeded stream through 128 slots with the 2:4 feed-forward
+    weights, admitted and evicted between graph replays; every delivered sequence against the golden one of the
+    request decoded alone (tests/golden/stream300.npz), up to the first divergence (a flipped near-tie changes what
+    follows)."""
+    from cohere_inference_b200 import DecodeScheduler, StreamDecoder
+    g = np.load(os.path.join(golden_dir, "stream300.npz"))
+    n = g["seq"].shape[0]
+    reqs = synthetic_requests(2000, seed=0, slots=128)[:n]
+    assert [r.frames for r in reqs] == g["frames"].tolist() and [r.target for r in reqs] == g["new"].tolist()
+    dec = StreamDecoder(model16, slots=128, max_new_tokens=448, max_prompt=16, max_audio_s=30.0, eos=-1, int8=True,
+                        ffn_sparse=True, device_sched=device_sched)
+    sched = DecodeScheduler(dec, lambda r: torch.from_numpy(request_memory(r)))
+    got = sched.run(reqs)
+    dec.check_status()
+    st = sched.stats
+    assert st.admitted == st.evicted == n and sorted(sched.free) == list(range(128))
+    assert st.new_tokens == int(g["new"].sum())
+    same = total = whole = 0
+    for i, r in enumerate(reqs):
+        want = g["seq"][i, :10 + r.target].astype(np.int64)
+        assert len(got[i]) == len(want) and np.array_equal(got[i][:10], r.prompt)
+        diff = np.nonzero(got[i] != want)[0]
+        k = diff[0] if len(diff) else len(want)
+        same += k - 10
+        total += (k - 10) + (1 if len(diff) else 0)
+        whole += not len(diff)
+        if len(diff):  # the first divergence must be a near-tie of the golden run
+            assert g["gap"][i, diff[0] - 1] <= 2 * LOGIT_TOL, (i, diff[0], g["gap"][i, diff[0] - 1])
+    print(f"stream (device_sched={device_sched}): {same}/{total} tokens equal to the golden before the first divergence, "
+          f"{whole}/{n} sequences equal throughout, occupancy {st.occupancy:.3f}, {st.steps} steps; "
+          f"step times {sched.step_time_summary()}")
+    assert same / total >= 0.995

@@ -37,6 +37,9 @@ def test_structs_match_header_sizes():
     from cohere_inference_b200 import native
     assert ctypes.sizeof(native.Weight) == 72 and ctypes.sizeof(native.Norm) == 24  # 6 pointers + 5 ints, padded
     assert ctypes.sizeof(native.Layer) == 3 * 24 + 6 * 72 + 8 * 8
+    lib = native.lib()  # and every structure against the library as compiled
+    for which, struct in enumerate((native.Weight, native.Norm, native.Layer, native.Plan, native.LnLink)):
+        assert lib.b200dec_sizeof(which) == ctypes.sizeof(struct), struct.__name__
 
 
 def test_missing_library_fails_loudly(monkeypatch):

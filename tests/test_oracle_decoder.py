@@ -47,3 +47,28 @@ def test_config1_greedy_matches_transformers(golden_dir):
     np.testing.assert_allclose(logits[:, ::64], g["logits_sub"], atol=1e-4, rtol=0)
     assert np.array_equal(argmax_first(logits), g["argmax"])
     assert np.array_equal(so.out[0, :10], prompt[0]) and np.array_equal(so.out[0, 10:74], g["argmax"][9:])
+
+
+@pytest.mark.parametrize("name,rows", [("config2", (0,)), ("config3", (0, 63)), ("config3_kv8", (5,)), ("sparse128", (127,))])
+def test_full_size_goldens_pin_the_oracle(golden_dir, name, rows):
+    """The full-size goldens (transformers on the weights each mode stores) against the numpy oracle on a few rows:
+    teacher-forced along the golden's own tokens, the first 13 steps, logits at every 256th entry and the top logit."""
+    from cohere_inference_b200.synth import parity_workload
+    g = np.load(os.path.join(golden_dir, f"decoder_{name}.npz"))
+    wl = parity_workload(name)
+    assert np.array_equal(g["frames"], wl.frames)
+    assert abs(sum(float(m.astype(np.float64).sum()) for m in wl.memory) - float(g["memory_checksum"])) < 1e-6
+    assert np.array_equal(g["seq"][:, :wl.prompts.shape[1]], wl.prompts)
+    model = synthetic_model(0)
+    w = effective_weights(state_to_numpy(model), 8, wl.mode, tables="bf16")
+    dec = OracleDecoder(w, OracleConfig.of(model.config), kv_round="int8" if wl.kv_int8 else None)
+    for r in rows:
+        cross, cache = [dec.cross_kv(wl.memory[r])], [dec.new_self_cache()]
+        for t in range(13):
+            assert g["fed"][r, t] == g["seq"][r, t]
+            logits = dec.step(g["fed"][r, t:t + 1].astype(np.int64), np.array([t]), cache, cross)[0]
+            assert abs(float(logits[g["argmax"][r, t]]) - float(g["top1"][r, t])) <= 1e-4
+            if g["gap"][r, t] > 1e-3:
+                assert int(argmax_first(logits)) == int(g["argmax"][r, t])
+            if t % 4 == 0:
+                np.testing.assert_allclose(logits[::256], g["logits_sub"][r, t // 4], atol=1e-4, rtol=0)

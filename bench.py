@@ -410,14 +410,17 @@ def stream_workload(args, dev, rank: int, local: int, world: int, n_requests: in
     Every rank calls this; rank 0 gets the summary."""
     from cohere_inference_b200 import DecodeScheduler, StreamDecoder, synthetic_model, synthetic_requests
     from cohere_inference_b200 import dataparallel as dp
-    from cohere_inference_b200.synth import request_memory
     SLOTS = 128
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=SLOTS, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         int8=True, ffn_sparse=True, eos=-1, pdl=args.pdl, attn_ring=args.attn_ring,
                         head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched)
     mine = dp.partition(synthetic_requests(n_requests, seed=0, slots=SLOTS * world, fill=args.fill), rank, world)
-    # encoder memory of each request in pinned host memory (the scheduler copies it to the device at admission)
-    sched = DecodeScheduler(dec, lambda r: torch.from_numpy(request_memory(r)).pin_memory(), account_bytes=True)
+    # encoder memory in pinned host memory: 16 seeded N(0, 1) blocks of the longest length, a request takes the first
+    # `frames` rows of one of them (the scheduler copies them to the device at admission); drawing every request's own
+    # block would make the host the bottleneck of the run without changing a byte the GPU moves
+    g = torch.Generator().manual_seed(1234 + rank)
+    pool = torch.randn(16, FRAMES[1], 1024, generator=g).pin_memory()
+    sched = DecodeScheduler(dec, lambda r: pool[r.mem_seed % 16, :r.frames], account_bytes=True)
     dp.barrier(dev)
     torch.cuda.synchronize()
     t0 = time.perf_counter()

@@ -108,6 +108,11 @@ PROTOTYPES = {
     "b200dec_attention_static": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int,
                                            f32, vp, C.c_int, C.c_int, vp, C.c_int, vp]),
     "b200dec_scatter_kv": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+    "b200dec_prefill_rows_bytes": (i64, [C.c_int, C.c_int]),
+    "b200dec_prefill_pack_rows": (C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp]),
+    "b200dec_prefill_tile_weight": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
+    "b200dec_prefill_gemm": (C.c_int, [vp, C.c_int, C.c_int, vp, vp, C.c_int, C.c_int, vp, vp, C.c_int, vp, vp, vp, vp,
+                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     "b200dec_admit": (C.c_int, [C.POINTER(Plan), vp, C.c_int, vp, C.c_int, vp]),
     "b200dec_admit_record_ints": (C.c_int, [C.c_int]),
     "b200dec_compact_active": (C.c_int, [C.POINTER(Plan), C.c_int, vp, C.c_int, vp]),

@@ -55,41 +55,22 @@ class _Layer:
         return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
 
 
-class _PrefillLinear:
-    """y = x W^T + b for the cross-K/V prefill (fill_cross; reference: the two F.linear of stream_decoder.py:232), as
-    ONE bf16 tensor-core GEMM (library GEMM, fp32 accumulate and output) that keeps fp32-level accuracy: with
-    x = xh + xl and W = Wh + Wl (bf16 pairs), x W^T = xh Wh^T + xl Wh^T + xh Wl^T up to 2^-17 relative, written as a
-    single product of [xh | xl | xh | 1 1 0..] with [Wh | Wh | Wl | bh bl 0..] (the bias rides in two extra columns)."""
+class _PrefillWeight:
+    """One projection of the cross-attention prefill (fill_cross; the reference's two F.linear, kernels/
+    stream_decoder.py:232) for csrc/prefill_gemm.cu: the weight rounded to bf16 in the kernel's tile image, the bias
+    fp32. Output channels are padded with zero rows to a multiple of 256."""
 
     def __init__(self, w: torch.Tensor, b: torch.Tensor):
         n, k = w.shape
-        self.n, self.k, self.ka = n, k, 3 * k + 8
-        bf = torch.bfloat16
-        wh = w.to(bf)
-        wa = torch.zeros(n, self.ka, dtype=bf, device=w.device)
-        wa[:, :k] = wh
-        wa[:, k:2 * k] = wh
-        wa[:, 2 * k:3 * k] = (w - wh.float()).to(bf)
-        bh = b.to(bf)
-        wa[:, 3 * k] = bh
-        wa[:, 3 * k + 1] = (b - bh.float()).to(bf)
-        self.wa = wa
-        self.tail = torch.zeros(self.ROWS, 8, dtype=bf, device=w.device)  # the columns that pick up the bias
-        self.tail[:, :2] = 1
-
-    ROWS = 256  # the row count is padded to a multiple: a handful of GEMM shapes, each planned by the library once
-
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
-        m, k = x.shape
-        mp = -(-m // self.ROWS) * self.ROWS
-        if mp != m:
-            x = torch.nn.functional.pad(x, (0, 0, 0, mp - m))
-        xh = x.to(torch.bfloat16)
-        xl = (x - xh.float()).to(torch.bfloat16)
-        if self.tail.shape[0] < mp:
-            self.tail = self.tail[:1].expand(mp, 8).contiguous()
-        xa = torch.cat([xh, xl, xh, self.tail[:mp]], 1)
-        return torch.mm(xa, self.wa.t(), out_dtype=torch.float32)[:m]
+        assert k % 64 == 0, "prefill: the input width must be a multiple of 64"
+        self.n, self.k = -(-n // 256) * 256, k
+        wb = torch.zeros(self.n, k, dtype=torch.bfloat16, device=w.device)
+        wb[:n] = w.detach().to(torch.bfloat16)
+        self.image = torch.empty(self.n * k * 2, dtype=torch.uint8, device=w.device)
+        nv.check(nv.lib().b200dec_prefill_tile_weight(nv.ptr(wb), self.n, k, nv.ptr(self.image), nv.stream_ptr()))
+        torch.cuda.current_stream().synchronize()
+        self.bias = torch.zeros(self.n, device=w.device)
+        self.bias[:n] = b.detach().float()
 
 
 class StreamDecoder:
@@ -159,12 +140,13 @@ class StreamDecoder:
             # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection; these run
             # once per request, not in the step, and keep bf16 weights in every mode, as the reference does
             # (kernels/stream_decoder.py:91-94, 232)
-            self.proj = _PrefillLinear(dequantized(dec.proj.weight, nv.W_BF16), f(dec.proj.bias))
-            self.cross = _PrefillLinear(
-                torch.cat([dequantized(w, nv.W_BF16) for layer in dec.layers
+            self.proj = _PrefillWeight(f(dec.proj.weight), f(dec.proj.bias))
+            self.cross = _PrefillWeight(
+                torch.cat([f(w) for layer in dec.layers
                            for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)]),
                 torch.cat([f(b) for layer in dec.layers
                            for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)]))
+            assert self.proj.n == self.width and self.cross.n == len(dec.layers) * 2 * self.width
             L, S = len(self.layers), slots
             self.slots, self.dummy = S, S
             self.max_prompt = max_prompt
@@ -376,16 +358,56 @@ class StreamDecoder:
                 return b
         raise ValueError(f"{rows} rows exceed the largest bucket {self.buckets[-1]}")
 
-    def _stage(self, values: np.ndarray, dst: torch.Tensor) -> None:
-        """int32 values -> dst (device int32, at least as long) through the pinned ring, on the decoder stream."""
+    def _stage(self, values: np.ndarray, dst: torch.Tensor, stream: torch.cuda.Stream | None = None) -> None:
+        """int32 values -> dst (device int32, at least as long) through the pinned ring, on `stream` (default: the
+        decoder stream)."""
+        stream = stream or self.stream
         n = int(values.size)
         buf, ev = self._ring[self._ring_at]
         self._ring_at = (self._ring_at + 1) % len(self._ring)
         ev.synchronize()  # the copy that last used this buffer (several calls ago) has long finished
         buf.numpy()[:n] = values.reshape(-1)
-        with torch.cuda.stream(self.stream):
+        with torch.cuda.stream(stream):
             dst[:n].copy_(buf[:n], non_blocking=True)
-            ev.record(self.stream)
+            ev.record(stream)
+
+    @torch.no_grad()
+    def fill_cross(self, hidden: torch.Tensor, lengths: list[int], slots: list[int]) -> None:
+        """Cross-attention keys and values of packed encoder frames (sum(lengths), enc_dim), piece i = lengths[i]
+        frames for slots[i], into the slot caches; on the current stream (the caller orders the decoder stream after
+        it, as with the reference's method). Two tcgen05 products, the second writing the caches itself."""
+        m = int(hidden.shape[0])
+        if not (len(lengths) == len(slots) and m == sum(lengths) and hidden.shape[1] == self.proj.k):
+            raise ValueError("fill_cross: hidden must hold sum(lengths) rows of the encoder width, one length per slot")
+        if not all(1 <= n <= self.frames for n in lengths) or not all(0 <= s < self.slots for s in slots):
+            raise ValueError(f"fill_cross: 1..{self.frames} frames per piece, slots 0..{self.slots - 1}")
+        if m == 0:
+            return
+        lib, cur = nv.lib(), torch.cuda.current_stream()
+        x = hidden.float().contiguous()
+        pieces = np.zeros((len(slots), 4), np.int32)
+        pieces[:, 0] = np.concatenate([[0], np.cumsum(lengths[:-1])])
+        pieces[:, 1], pieces[:, 2] = lengths, slots
+        table = torch.empty(pieces.size, dtype=torch.int32, device=self.device)
+        if pieces.size <= self._ring[0][0].numel():
+            self._stage(pieces, table, cur)
+        else:
+            table.copy_(torch.from_numpy(pieces.reshape(-1)))
+        img = lambda k: torch.empty(lib.b200dec_prefill_rows_bytes(m, k) + 1024, dtype=torch.uint8, device=self.device)  # noqa: E731
+        aligned = lambda t: t.data_ptr() + (-t.data_ptr()) % 1024  # noqa: E731
+        a0, a1 = img(self.proj.k), img(self.proj.n)
+        s = cur.cuda_stream
+        nv.check(lib.b200dec_prefill_pack_rows(nv.ptr(x), m, self.proj.k, x.shape[1], aligned(a0), s))
+        nv.check(lib.b200dec_prefill_gemm(aligned(a0), m, self.proj.k, nv.ptr(self.proj.image), nv.ptr(self.proj.bias),
+                                          self.proj.n, 0, aligned(a1), None, 0, None, None, None, None, 0, 0, 0, 0, 0,
+                                          nv.ptr(self.status), s))
+        nv.check(lib.b200dec_prefill_gemm(aligned(a1), m, self.cross.k, nv.ptr(self.cross.image), nv.ptr(self.cross.bias),
+                                          self.cross.n, 2 if self.kv_int8 else 1, None, nv.ptr(table), len(slots),
+                                          nv.ptr(self.cross_k), nv.ptr(self.cross_v), nv.ptr(self.cross_ks),
+                                          nv.ptr(self.cross_vs), len(self.layers), self.slots + 1, self.h, self.d,
+                                          self.frames, nv.ptr(self.status), s))
+        for t in (x, table, a0, a1):
+            t.record_stream(cur)
 
     def admit(self, slots: list[int], prompts: list, frames: list[int], max_new: list[int] | None = None) -> None:
         """Start decoding in `slots`: each gets its prompt (fed token by token as forced choices), its number of

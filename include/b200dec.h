@@ -297,6 +297,30 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
 int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
                           float* ck_scale, float* cv_scale, int nrows, int layers, int slots_plus_1, int heads,
                           int head_dim, int frames, void* stream);
+/* ---- cross-attention prefill (fill_cross) on the tcgen05 tensor cores ----------------------------------------------
+ * C(m, n) = A(m, k) W(n, k)^T + bias with fp32 rows A (used as two bf16 halves, about 16 bits of mantissa), bf16
+ * weights and fp32 accumulation; the result goes (mode 0) into the operand image of the next product, or (modes 1, 2)
+ * straight into the slot caches. Together these replace the two chained F.linear of StreamDecoder.fill_cross
+ * (kernels/stream_decoder.py:229-239) and dec_scatter_kv / dec_scatter_kv_q8 (kernels/csrc/decoder_ops.cu:163-204,
+ * 292-327): no (frames x layers * 2 * d) intermediate exists and the host builds no per-frame index vectors.
+ * Operands live in global memory as images of their shared-memory tiles: */
+int64_t b200dec_prefill_rows_bytes(int m, int k); /* bytes of the image of m fp32 rows of k values (k % 64 == 0) */
+/* x (m, ldx) fp32 -> its image (1 KB aligned, b200dec_prefill_rows_bytes(m, k) bytes). */
+int b200dec_prefill_pack_rows(const float* x, int m, int k, int ldx, void* image, void* stream);
+/* w (n, k) bf16 row-major (n % 256 == 0, k % 64 == 0) -> its image (1 KB aligned, n * k * 2 bytes); init time. */
+int b200dec_prefill_tile_weight(const void* w_bf16, int n, int k, void* image, void* stream);
+/* mode 0: next_image = the image of the m result rows (n values each) for the next product.
+ * mode 1: n = layers * 2 * heads * head_dim; row r of the product is frame (r - first) of the slot of the piece that
+ *   holds it, pieces (n_pieces, 4) int32 {first row, frames, slot, 0} in device memory, first rows ascending from 0;
+ *   channel ((layer * 2 + kv) * heads + head) * head_dim + d goes to the bf16 cache (layers, slots_plus_1, heads,
+ *   frames, head_dim) of keys (kv = 0) or values. Rows outside every piece or past the cache are dropped.
+ * mode 2: the same into int8 caches with one fp32 scale per head vector (layers, slots_plus_1, heads, frames),
+ *   quantised as b200dec_scatter_kv_q8 does.
+ * status receives B200DEC_ST_TIMEOUT if a bounded wait inside the kernel ran out. */
+int b200dec_prefill_gemm(const void* rows_image, int m, int k, const void* weight_image, const float* bias, int n,
+                         int mode, void* next_image, const int32_t* pieces, int n_pieces, void* ck, void* cv,
+                         float* ck_scale, float* cv_scale, int layers, int slots_plus_1, int heads, int head_dim,
+                         int frames, int32_t* status, void* stream);
 /* Admission of n requests in one launch. records: n packed records of b200dec_admit_record_ints(max_prompt) int32 in
  * device memory (the host stages them in pinned memory and copies them over in one piece): {slot, prompt length,
  * new-token budget, encoder frames, max_prompt token ids}. Per record: forced = the prompt padded with `pad`, out =

@@ -219,20 +219,6 @@ def test_scheduler_stream_matches_oracle(model16, state16):
     assert same / total >= 0.98
 
 
-def test_prefill_linear_split_operand():
-    """The cross-K/V prefill GEMM (bf16 tensor cores on hi + lo operand pairs, bias in extra columns) against fp64:
-    fp32-level accuracy, far inside the bf16 rounding of the cache it feeds."""
-    from cohere_inference_b200.stream_decoder import _PrefillLinear
-    rng = np.random.default_rng(3)
-    x = rng.standard_normal((301, 1024)).astype(np.float32)
-    w = (rng.standard_normal((2048, 1024)) * 0.03).astype(np.float32)
-    b = rng.standard_normal(2048).astype(np.float32)
-    got = _PrefillLinear(torch.from_numpy(w).cuda(), torch.from_numpy(b).cuda())(torch.from_numpy(x).cuda())
-    assert got.dtype == torch.float32 and got.is_contiguous()
-    want = x.astype(np.float64) @ w.astype(np.float64).T + b
-    np.testing.assert_allclose(got.cpu().numpy(), want, atol=1e-4, rtol=3e-5)  # 2^-17 of |b| <= 4, plus the sum's
-
-
 @pytest.mark.parametrize("name,rows,kw", [("config3", 64, dict(int8=True)), ("config2", 8, dict()),
                                           ("config3_kv8", 64, dict(int8=True, kv_int8=True))])
 def test_full_size_run_properties(model16, name, rows, kw):

@@ -791,3 +791,93 @@ def test_scatter_kv(nv):
         want_k[:, slot_of[i], :, frame_of[i]] = r[i, :, 0]
         want_v[:, slot_of[i], :, frame_of[i]] = r[i, :, 1]
     assert np.array_equal(ck.float().cpu().numpy(), want_k) and np.array_equal(cv.float().cpu().numpy(), want_v)
+
+
+# ---- cross-attention prefill: the tcgen05 GEMM with the cache scatter as its epilogue ---------------------------------
+
+def _image_rows(img, m, k):
+    """Decode an operand image (csrc/prefill_gemm.cu) back to (m, k) fp32 = high + low bf16 halves."""
+    raw = img.view(torch.int16).cpu().numpy().view(np.uint16)
+    r, c = np.meshgrid(np.arange(m), np.arange(k), indexing="ij")
+    nkb = k // 64
+
+    def at(block):  # uint16 index of element (r, c) in the given k-block of its row tile
+        rr, chunk = r % 128, (c % 64) // 8
+        off = (rr >> 3) * 1024 + (rr & 7) * 128 + ((chunk ^ (rr & 7)) << 4) + (c % 8) * 2
+        return (((r // 128) * (2 * nkb) + block) * 16384 + off) // 2
+    hi = raw[at(c // 64)].astype(np.uint32) << 16
+    lo = raw[at(nkb + c // 64)].astype(np.uint32) << 16
+    return hi.view(np.float32).astype(np.float64) + lo.view(np.float32).astype(np.float64)
+
+
+def _prefill_setup(nv, m, k, n, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = bf16_round((rng.standard_normal((n, k)) * 0.03).astype(np.float32))
+    b = rng.standard_normal(n).astype(np.float32)
+    lib = nv.lib()
+    wimg = torch.empty(n * k * 2, dtype=torch.uint8, device="cuda")
+    nv.check(lib.b200dec_prefill_tile_weight(nv.ptr(cuda(w).to(torch.bfloat16)), n, k, nv.ptr(wimg), nv.stream_ptr()))
+    ximg = torch.zeros(lib.b200dec_prefill_rows_bytes(m, k), dtype=torch.uint8, device="cuda")
+    assert ximg.data_ptr() % 1024 == 0 and wimg.data_ptr() % 1024 == 0
+    nv.check(lib.b200dec_prefill_pack_rows(nv.ptr(cuda(x)), m, k, k, nv.ptr(ximg), nv.stream_ptr()))
+    want = x.astype(np.float64) @ w.astype(np.float64).T + b
+    return x, w, b, ximg, wimg, want
+
+
+@pytest.mark.parametrize("m,k,n", [(301, 1024, 512), (128, 1280, 256), (1000, 64, 1024)])
+def test_prefill_gemm_operand_image(nv, m, k, n):
+    """mode 0: rows x weights^T + bias, handed on as the next product's operand (two bf16 halves): fp32-level accuracy."""
+    x, w, b, ximg, wimg, want = _prefill_setup(nv, m, k, n, 3)
+    np.testing.assert_allclose(_image_rows(ximg, m, k), x, atol=0, rtol=2.0 ** -16)  # the split keeps ~16 bits
+    lib = nv.lib()
+    out = torch.zeros(lib.b200dec_prefill_rows_bytes(m, n), dtype=torch.uint8, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(cuda(b)), n, 0, nv.ptr(out), None, 0,
+                                          None, None, None, None, 0, 0, 0, 0, 0, nv.ptr(status), nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    got = _image_rows(out, m, n)
+    np.testing.assert_allclose(got, want, atol=2e-4 * np.sqrt(k / 1024), rtol=3e-5)
+
+
+@pytest.mark.parametrize("H,D,q8", [(4, 64, False), (2, 128, False), (4, 64, True), (2, 128, True)])
+def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
+    """modes 1 / 2: the product written straight into the slot caches by (piece -> slot, frame); untouched cache cells
+    keep their contents; int8 caches hold what the reference's quantiser makes of the bf16-rounded values."""
+    L, S1, T, k = 2, 5, 160, 1024
+    n = L * 2 * H * D
+    pieces = np.array([[0, 100, 3, 0], [100, 160, 0, 0], [260, 41, 4, 0]], np.int32)
+    m = 301
+    x, w, b, ximg, wimg, want = _prefill_setup(nv, m, k, n, 11)
+    lib = nv.lib()
+    dt = torch.int8 if q8 else torch.bfloat16
+    ck = torch.full((L, S1, H, T, D), 7, dtype=dt, device="cuda")
+    cv = torch.full((L, S1, H, T, D), 7, dtype=dt, device="cuda")
+    cks = torch.full((L, S1, H, T), -1.0, device="cuda") if q8 else None
+    cvs = torch.full((L, S1, H, T), -1.0, device="cuda") if q8 else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(cuda(b)), n, 2 if q8 else 1, None,
+                                      nv.ptr(cuda(pieces)), len(pieces), nv.ptr(ck), nv.ptr(cv), nv.ptr(cks), nv.ptr(cvs),
+                                      L, S1, H, D, T, nv.ptr(status), nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    kv = want.reshape(m, L, 2, H, D)
+    touched = np.zeros((S1, T), bool)
+    for first, frames, slot, _ in pieces:
+        touched[slot, :frames] = True
+        for which, cache, scales in ((0, ck, cks), (1, cv, cvs)):
+            ref = kv[first:first + frames, :, which].transpose(1, 2, 0, 3)  # (L, H, frames, D)
+            got = cache[:, slot, :, :frames].float().cpu().numpy()
+            if not q8:
+                np.testing.assert_allclose(got, ref, atol=1e-6, rtol=2.0 ** -8)  # one bf16 rounding
+            else:
+                sc = scales[:, slot, :, :frames].cpu().numpy()
+                rb = bf16_round(ref.astype(np.float32))
+                np.testing.assert_allclose(sc, np.abs(rb).max(-1) / 127, rtol=2.0 ** -7)
+                assert np.abs(got * sc[..., None] - rb).max() <= 0.51 * sc.max() + 2.0 ** -7 * np.abs(rb).max()
+    for cache in (ck, cv):  # cells of no piece are untouched
+        assert (cache.float().cpu().numpy().transpose(0, 2, 1, 3, 4)[:, :, ~touched] == 7).all()
+    if q8:
+        assert (cks.cpu().numpy().transpose(0, 2, 1, 3)[:, :, ~touched] == -1).all()

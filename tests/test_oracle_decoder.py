@@ -62,13 +62,16 @@ def test_full_size_goldens_pin_the_oracle(golden_dir, name, rows):
     model = synthetic_model(0)
     w = effective_weights(state_to_numpy(model), 8, wl.mode, tables="bf16")
     dec = OracleDecoder(w, OracleConfig.of(model.config), kv_round="int8" if wl.kv_int8 else None)
+    # int8 caches: a last-bit difference between the two fp32 computations can move a cached value by one quantisation
+    # step (scale = absmax / 127), which shows in the logits at the 1e-4 level
+    tol = 1e-3 if wl.kv_int8 else 1e-4
     for r in rows:
         cross, cache = [dec.cross_kv(wl.memory[r])], [dec.new_self_cache()]
         for t in range(13):
             assert g["fed"][r, t] == g["seq"][r, t]
             logits = dec.step(g["fed"][r, t:t + 1].astype(np.int64), np.array([t]), cache, cross)[0]
-            assert abs(float(logits[g["argmax"][r, t]]) - float(g["top1"][r, t])) <= 1e-4
-            if g["gap"][r, t] > 1e-3:
+            assert abs(float(logits[g["argmax"][r, t]]) - float(g["top1"][r, t])) <= tol
+            if g["gap"][r, t] > 10 * tol:
                 assert int(argmax_first(logits)) == int(g["argmax"][r, t])
             if t % 4 == 0:
-                np.testing.assert_allclose(logits[::256], g["logits_sub"][r, t // 4], atol=1e-4, rtol=0)
+                np.testing.assert_allclose(logits[::256], g["logits_sub"][r, t // 4], atol=tol, rtol=0)

@@ -123,6 +123,8 @@ def run_ours(args) -> None:
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
                         head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8,
                         proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch)
+    digest = dec.weights_digest()
+    dp.check_identical(digest, dev)  # replicas: the same packed bits on every GPU, before anything is timed
     lens, memory_host, prompts = make_inputs(1000 + rank)
     memory_host = memory_host.pin_memory()
     memory_dev = memory_host.to(dev)
@@ -327,7 +329,7 @@ def run_ours(args) -> None:
                        "parallelism": f"dp{world} replicas", "chains_per_step": chains_per_step,
                        "kv_prefetch_mb": args.kv_prefetch,
                        "l2": "inputs larger than L2: each replay streams ~0.2-1.9 GB of KV cache and weights",
-                       "weights": "seed-0 random init N(0, 0.02)"},
+                       "weights": "seed-0 random init N(0, 0.02)", "packed_weights_sha256": digest[:16]},
             "p50_step_ms": round(p50, 4),
             "tokens_per_s_per_gpu": round(value / world, 1),
             # every row advances one position per replay, the 9 prompt-feeding steps of a sequence included

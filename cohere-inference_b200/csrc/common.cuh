@@ -98,31 +98,29 @@ DEVI void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory");
 
 // ---- prefetch of an attention launch's keys and values into L2 -----------------------------------------------------
 // The step alternates between projections (bound by latency, HBM nearly idle) and attention (bound by HBM). A
-// projection that runs between two attention launches can therefore start the next launch's cache stream early: one
-// thread per CTA asks the bulk-copy engine to bring runs of keys and values into L2 and goes on; nothing waits for
-// them. The rows come from the step's row schedule (b200dec_row_schedule), whose fourth word is the number of keys
-// of the row to prefetch (the launch's total is capped by the plan's budget so that it stays inside L2).
+// projection that runs between two attention launches can therefore start the next launch's cache stream early: its
+// threads issue L2 prefetches over runs of keys and values and go on; nothing waits for them. The rows come from the
+// step's row schedule (b200dec_row_schedule), whose fourth word is the number of keys of the row to prefetch (the launch's total is capped by the plan's budget so that it stays inside L2).
 struct KvPrefetch {
   const int4* sched;  // (rows, 4) {row, slot, length, keys to prefetch}; null: nothing to do
   const char* k;      // caches (slots + 1, H, cap, vec_bytes)
   const char* v;
-  int rows, heads, cap, vec_bytes;
+  int rows, heads, cap, vec_bytes, slots;  // slots: the last valid slot index (the dummy)
 };
-DEVI void prefetch_l2(const void* p, uint32_t bytes) {  // bytes: a multiple of 16, p 16-byte aligned
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-// Called by one thread of every CTA of a grid of `nctas` CTAs (this one's index `cta`): runs of up to 16 KB.
-DEVI void kv_prefetch_issue(const KvPrefetch& f, int cta, int nctas) {
+DEVI void prefetch_l2_line(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// Called by every thread of every CTA of a grid of `nctas` CTAs (this one's index `cta`, `nthreads` threads each): the
+// grid's CTAs share out the (row, head, key | value) runs, a CTA's threads the 128-byte lines of a run (slots and key
+// counts are clamped into the caches first).
+DEVI void kv_prefetch_issue(const KvPrefetch& f, int cta, int nctas, int tid, int nthreads) {
   const int ops = f.rows * f.heads * 2;
   for (int o = cta; o < ops; o += nctas) {
     const int i = o / (2 * f.heads), rem = o % (2 * f.heads), h = rem >> 1;
     const int4 e = __ldcg(f.sched + i);
     const int keys = e.w < f.cap ? e.w : f.cap;
-    if (keys <= 0 || e.y < 0) continue;
+    if (keys <= 0 || e.y < 0 || e.y > f.slots) continue;
     const char* src = ((rem & 1) ? f.v : f.k) + ((size_t)e.y * f.heads + h) * f.cap * f.vec_bytes;
-    const long long bytes = (long long)keys * f.vec_bytes;
-    for (long long off = 0; off < bytes; off += 16384)
-      prefetch_l2(src + off, (uint32_t)(bytes - off < 16384 ? bytes - off : 16384));
+    const int bytes = keys * f.vec_bytes;
+    for (int off = tid * 128; off < bytes; off += nthreads * 128) prefetch_l2_line(src + off);
   }
 }
 

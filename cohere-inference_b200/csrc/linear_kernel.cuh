@@ -188,9 +188,9 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
     }
   }
   pdl_wait();
-  if (p.pf.sched && tid == 0)
+  if (p.pf.sched)
     kv_prefetch_issue(p.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
-                      gridDim.x * gridDim.y * gridDim.z);
+                      gridDim.x * gridDim.y * gridDim.z, tid, NT);
 
   // ---- stage the activations of this K slice ---------------------------------------------------------------------
   const int ntiles = (p.rows + 7) >> 3, rows8 = ntiles * 8;

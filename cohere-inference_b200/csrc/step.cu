@@ -152,7 +152,8 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   auto prefetch = [&](const int32_t* sched, const void* k, const void* v, int cap) {
     KvPrefetch f{};
     if (prefetch_keys > 0 && k && v)
-      f = KvPrefetch{reinterpret_cast<const int4*>(sched), (const char*)k, (const char*)v, rows, pl->heads, cap, vec_bytes};
+      f = KvPrefetch{reinterpret_cast<const int4*>(sched), (const char*)k, (const char*)v, rows, pl->heads, cap, vec_bytes,
+                     pl->slots};
     return f;
   };
 

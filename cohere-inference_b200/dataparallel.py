@@ -73,3 +73,15 @@ def max_over_ranks(value: float, device: torch.device | str = "cpu") -> float:
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def check_identical(digest: str, device: torch.device | str = "cpu") -> None:
+    """Every rank holds the same packed weights: one all_gather of the 32-byte SHA-256 digest
+    (StreamDecoder.weights_digest); raises on the ranks that differ from rank 0."""
+    mine = torch.tensor(list(bytes.fromhex(digest)), dtype=torch.uint8, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        out = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+        dist.all_gather(out, mine)
+        if not torch.equal(out[0], mine):
+            raise RuntimeError(f"rank {dist.get_rank()}: packed weights differ from rank 0's "
+                               f"({digest[:16]}... vs {bytes(out[0].cpu().tolist()).hex()[:16]}...)")

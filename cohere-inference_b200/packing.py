@@ -8,8 +8,6 @@ reference-format tensors were made from, so tests can check both.
 
 from __future__ import annotations
 
-import os
-
 from dataclasses import dataclass
 
 import torch
@@ -79,11 +77,7 @@ def tile_config(n: int, k: int, kind: int, a_kind: int = nv.A_F16, ln: bool = Fa
     """The first preferred (warps, ksplit) of the shape whose shared-memory footprint fits `max_rows` rows in one
     pass; if none does, the first valid one (the library then makes two passes of 64 rows)."""
     fits = nv.lib().b200dec_linear_fits
-    override = {}
-    for item in filter(None, os.environ.get("B200DEC_TILES", "").split(";")):  # "3072x1024:8,4;..." (tuning runs)
-        shape, ws = item.split(":")
-        override[tuple(int(v) for v in shape.split("x"))] = [tuple(int(v) for v in ws.split(","))]
-    prefs = override.get((n, k), []) + TILE_CONFIG.get((n, k), []) + [(w, s) for s in (8, 4, 2, 1) for w in (4, 8)]
+    prefs = TILE_CONFIG.get((n, k), []) + [(w, s) for s in (8, 4, 2, 1) for w in (4, 8)]
     valid = [(w, s) for w, s in prefs if n % (16 * w) == 0 and (k, s) in ((1024, 8), (1024, 4), (1024, 2), (4096, 8))
              and (16 * w) % (8 * s) == 0 and (k // s) % {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_INT8_24: 128}[kind] == 0
              and (not ln or k == 1024)]

@@ -418,6 +418,8 @@ class StreamDecoder:
             raise ValueError("admit: one prompt, frame count and budget per slot")
         rec = np.full((n, self._rec_ints), self.pad, np.int32)
         for i, (s, p, f, m) in enumerate(zip(slots, prompts, frames, budgets)):
+            if isinstance(p, torch.Tensor):
+                p = p.detach().cpu().numpy()
             p = np.asarray(p, dtype=np.int64).reshape(-1)
             if not (0 <= s < self.slots and 1 <= p.size <= self.max_prompt and 1 <= f <= self.frames
                     and 1 <= m <= self.max_new_tokens):
@@ -454,6 +456,38 @@ class StreamDecoder:
             else:
                 self._step(bucket)
         torch.cuda.nvtx.range_pop()
+
+    # ---- identity of the packed weights -----------------------------------------------------------------------------
+
+    def packed_tensors(self) -> dict[str, torch.Tensor]:
+        """Every tensor the kernels read as a weight (tiled projections, scales, biases, folded LayerNorm vectors,
+        tables, norms, prefill images), by name, in a fixed order."""
+        out: dict[str, torch.Tensor] = {"embed": self.embed, "pos_table": self.pos_table}
+        for name, (w, b, _) in (("emb_ln", self.emb_ln), ("final_ln", self.final_ln)):
+            out[name + ".w"], out[name + ".b"] = w, b
+        packs = [(f"layer{i}.{n}", getattr(ly, n)) for i, ly in enumerate(self.layers)
+                 for n in ("qkv", "o", "cq", "co", "fc1", "fc2")] + [("head", self.head)]
+        for name, p in packs:
+            for field in ("tiled", "meta", "scale", "bias", "ln_g", "ln_bias"):
+                t = getattr(p, field)
+                if t is not None:
+                    out[f"{name}.{field}"] = t
+        for i, ly in enumerate(self.layers):
+            for j, (w, b, _) in enumerate(ly.norms):
+                out[f"layer{i}.ln{j + 1}.w"], out[f"layer{i}.ln{j + 1}.b"] = w, b
+        for name, p in (("prefill.proj", self.proj), ("prefill.cross", self.cross)):
+            out[name + ".image"], out[name + ".bias"] = p.image, p.bias
+        return out
+
+    def weights_digest(self) -> str:
+        """SHA-256 over the packed weights (names, shapes, dtypes and bytes as the kernels read them). Replicas of a
+        data-parallel job compare it before they start (dataparallel.check_identical): the same bits on every GPU."""
+        import hashlib
+        h = hashlib.sha256()
+        for name, t in self.packed_tensors().items():
+            h.update(f"{name}|{tuple(t.shape)}|{t.dtype}|".encode())
+            h.update(t.detach().contiguous().view(torch.uint8).cpu().numpy().tobytes())
+        return h.hexdigest()
 
     # ---- accounting ------------------------------------------------------------------------------------------------
 

@@ -282,8 +282,9 @@ int b200dec_attention_ring(int self, const int32_t* active, const float* q, int 
  * would not see the allocation). No counterpart in the reference. The workspace is an array inside the library
  * instead (4.3 MB per GPU, held until the process exits), good for rows * heads <= 512; larger calls are refused
  * with an error. The first call on each device looks the array's address up and should come before any stream
- * capture. All calls on a device share the array: two calls whose kernels overlap on the GPU (different streams)
- * race on it. Allocates nothing, frees nothing. */
+ * capture. The device that is current at the call must be the device of `stream`: the array's address is looked up
+ * for the current device. All calls on a device share the array: two calls whose kernels overlap on the GPU
+ * (different streams) race on it. Allocates nothing, frees nothing. */
 int b200dec_attention_static(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
                              const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                              int out_kind, int rows, int32_t* status, int pdl, void* stream);

@@ -817,24 +817,27 @@ def _prefill_setup(nv, m, k, n, seed):
     b = rng.standard_normal(n).astype(np.float32)
     lib = nv.lib()
     wimg = torch.empty(n * k * 2, dtype=torch.uint8, device="cuda")
-    nv.check(lib.b200dec_prefill_tile_weight(nv.ptr(cuda(w).to(torch.bfloat16)), n, k, nv.ptr(wimg), nv.stream_ptr()))
+    w_d = cuda(w).to(torch.bfloat16)
+    nv.check(lib.b200dec_prefill_tile_weight(nv.ptr(w_d), n, k, nv.ptr(wimg), nv.stream_ptr()))
     ximg = torch.zeros(lib.b200dec_prefill_rows_bytes(m, k), dtype=torch.uint8, device="cuda")
     assert ximg.data_ptr() % 1024 == 0 and wimg.data_ptr() % 1024 == 0
-    nv.check(lib.b200dec_prefill_pack_rows(nv.ptr(cuda(x)), m, k, k, nv.ptr(ximg), nv.stream_ptr()))
+    x_d = cuda(x)  # device copies are kept in variables: a temporary would be freed (and its memory reused) at once
+    nv.check(lib.b200dec_prefill_pack_rows(nv.ptr(x_d), m, k, k, nv.ptr(ximg), nv.stream_ptr()))
+    torch.cuda.synchronize()
     want = x.astype(np.float64) @ w.astype(np.float64).T + b
-    return x, w, b, ximg, wimg, want
+    return x, w, cuda(b), ximg, wimg, want
 
 
 @pytest.mark.parametrize("m,k,n", [(301, 1024, 512), (128, 1280, 256), (1000, 64, 1024)])
 def test_prefill_gemm_operand_image(nv, m, k, n):
     """mode 0: rows x weights^T + bias, handed on as the next product's operand (two bf16 halves): fp32-level accuracy."""
-    x, w, b, ximg, wimg, want = _prefill_setup(nv, m, k, n, 3)
+    x, w, b_d, ximg, wimg, want = _prefill_setup(nv, m, k, n, 3)
     np.testing.assert_allclose(_image_rows(ximg, m, k), x, atol=0, rtol=2.0 ** -16)  # the split keeps ~16 bits
     lib = nv.lib()
     out = torch.zeros(lib.b200dec_prefill_rows_bytes(m, n), dtype=torch.uint8, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     for _ in range(2):
-        nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(cuda(b)), n, 0, nv.ptr(out), None, 0,
+        nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(b_d), n, 0, nv.ptr(out), None, 0,
                                           None, None, None, None, 0, 0, 0, 0, 0, nv.ptr(status), nv.stream_ptr()))
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -850,7 +853,8 @@ def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
     n = L * 2 * H * D
     pieces = np.array([[0, 100, 3, 0], [100, 160, 0, 0], [260, 41, 4, 0]], np.int32)
     m = 301
-    x, w, b, ximg, wimg, want = _prefill_setup(nv, m, k, n, 11)
+    x, w, b_d, ximg, wimg, want = _prefill_setup(nv, m, k, n, 11)
+    pieces_d = cuda(pieces)
     lib = nv.lib()
     dt = torch.int8 if q8 else torch.bfloat16
     ck = torch.full((L, S1, H, T, D), 7, dtype=dt, device="cuda")
@@ -858,8 +862,8 @@ def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
     cks = torch.full((L, S1, H, T), -1.0, device="cuda") if q8 else None
     cvs = torch.full((L, S1, H, T), -1.0, device="cuda") if q8 else None
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(cuda(b)), n, 2 if q8 else 1, None,
-                                      nv.ptr(cuda(pieces)), len(pieces), nv.ptr(ck), nv.ptr(cv), nv.ptr(cks), nv.ptr(cvs),
+    nv.check(lib.b200dec_prefill_gemm(nv.ptr(ximg), m, k, nv.ptr(wimg), nv.ptr(b_d), n, 2 if q8 else 1, None,
+                                      nv.ptr(pieces_d), len(pieces), nv.ptr(ck), nv.ptr(cv), nv.ptr(cks), nv.ptr(cvs),
                                       L, S1, H, D, T, nv.ptr(status), nv.stream_ptr()))
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -875,7 +879,7 @@ def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
             else:
                 sc = scales[:, slot, :, :frames].cpu().numpy()
                 rb = bf16_round(ref.astype(np.float32))
-                np.testing.assert_allclose(sc, np.abs(rb).max(-1) / 127, rtol=2.0 ** -7)
+                np.testing.assert_allclose(sc, np.abs(rb).max(-1) / 127, rtol=2.0 ** -6)  # one bf16 step of the largest
                 assert np.abs(got * sc[..., None] - rb).max() <= 0.51 * sc.max() + 2.0 ** -7 * np.abs(rb).max()
     for cache in (ck, cv):  # cells of no piece are untouched
         assert (cache.float().cpu().numpy().transpose(0, 2, 1, 3, 4)[:, :, ~touched] == 7).all()

@@ -404,6 +404,44 @@ def run_profile(args) -> None:
                       "weight_bytes": dec.weight_bytes, "launches_per_step": dec.launches_per_step}))
 
 
+def run_profile_prefill(args) -> None:
+    """A short run for a profiler: fill_cross (the two tcgen05 products of the cross-K/V prefill) on `--profile-frames`
+    encoder frames in pieces of up to 375, 2 warm-up calls, then `--profile-prefill N` calls between
+    cudaProfilerStart/Stop; prints the frames, the FLOPs of one call and its CUDA-event time without a profiler."""
+    from cohere_inference_b200 import StreamDecoder, synthetic_model
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dec = StreamDecoder(synthetic_model(0).to(dev), slots=64, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
+                        buckets=(1,), int8=True, eos=-1, kv_int8=args.kv_int8)
+    lens, left = [], args.profile_frames
+    while left > 0:
+        lens.append(min(left, FRAMES[1]))
+        left -= lens[-1]
+    assert len(lens) <= 64
+    hidden = torch.randn(sum(lens), 1024, device=dev)
+    slots = list(range(len(lens)))
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(dec.stream):
+        for _ in range(2):
+            dec.fill_cross(hidden, lens, slots)
+        s.record(dec.stream)
+        dec.fill_cross(hidden, lens, slots)
+        e.record(dec.stream)
+    dec.stream.synchronize()
+    torch.cuda.profiler.start()
+    with torch.cuda.stream(dec.stream):
+        for _ in range(args.profile_prefill):
+            dec.fill_cross(hidden, lens, slots)
+    dec.stream.synchronize()
+    torch.cuda.profiler.stop()
+    dec.check_status()
+    m = sum(lens)
+    flops = 2 * 2 * m * 1024 * (1024 + 16384)  # both bf16 halves of the rows against both weight matrices
+    emit(json.dumps({"profile_prefill_calls": args.profile_prefill, "frames": m, "pieces": len(lens), "flops_per_call": flops,
+                     "ms_per_call": round(s.elapsed_time(e), 4),
+                     "tflops": round(flops / (s.elapsed_time(e) / 1e3) / 1e12, 1)}))
+
+
 def stream_workload(args, dev, rank: int, local: int, world: int, n_requests: int) -> dict | None:
     """BASELINE configs 4 / 5: continuous batching, 128 slots per GPU, 2:4 int8 feed-forward weights, a seeded Poisson
     stream of n_requests requests dealt round-robin over the ranks, admitted and evicted between graph replays by
@@ -540,6 +578,8 @@ def main() -> None:
     ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")
     ap.add_argument("--chains", type=int, default=1, help="concurrent kernel chains a step's rows are split into")
     ap.add_argument("--profile", type=int, default=0, help="profiler mode: this many directly launched steps")
+    ap.add_argument("--profile-prefill", type=int, default=0, help="profiler mode: this many fill_cross calls")
+    ap.add_argument("--profile-frames", type=int, default=2048, help="encoder frames of a profiled fill_cross call")
     ap.add_argument("--profile-slots", type=int, default=BATCH)
     ap.add_argument("--profile-pos", type=int, default=225)
     ap.add_argument("--sparse", action="store_true", help="profiler mode: 2:4 feed-forward weights")
@@ -563,7 +603,9 @@ def main() -> None:
     sys.stdout.flush()
     os.dup2(2, 1)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.profile:
+    if args.profile_prefill:
+        run_profile_prefill(args)
+    elif args.profile:
         run_profile(args)
     elif args.impl == "reference":
         run_reference(args)

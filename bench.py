@@ -377,7 +377,7 @@ def run_profile(args) -> None:
     B = args.profile_slots
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=B, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         buckets=(B,), int8=True, eos=-1, graphs=False, ffn_sparse=args.sparse, chains=args.chains,
-                        attn_ring=args.attn_ring, kv_prefetch_mb=args.kv_prefetch)
+                        attn_ring=args.attn_ring, kv_prefetch_mb=args.kv_prefetch, kv_int8=args.kv_int8)
     rng = np.random.default_rng(1000)
     lens = rng.integers(FRAMES[0], FRAMES[1] + 1, B).tolist()
     prompts = [torch.from_numpy(rng.integers(0, 16384, PROMPT).astype(np.int64)) for _ in range(B)]

@@ -142,126 +142,178 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
 
 // ---- int8 caches: one fp32 scale per head vector (the format of the reference's int8 mode) ---------------------------
 // vector -> scale = absmax / 127 (1 when the vector is zero), q = rint(clamp(x * (1 / scale), +-127)); x ~ q * scale.
-// int8 byte j of a word as an exact float: the byte (biased by 128) becomes the low mantissa bits of 1.5 * 2^23.
-DEVI float q8_float(uint32_t biased_word, int j) {
-  return __uint_as_float(__byte_perm(biased_word, 0x4B400000u, 0x7650 | j)) - 12583040.f;
+//
+// Half the bytes per key only pay if the instructions per byte do not double, so this pass does its arithmetic on
+// pairs: a key (or value) of D int8 is read by D / 16 lanes with one 16-byte load each; four bytes become two half2
+// with two byte permutes and two subtractions (the byte, biased by 128, is the low mantissa of the half 1024 + u;
+// exact); the dot product runs as half2 multiply-adds, eight products per accumulator lane, then fp32 (query
+// pre-scaled and rounded to fp16); the weighted values accumulate in half2 as well (a lane group sees only
+// n / 32 keys, about ten, so the sums stay short) and are merged across groups in fp32. A warp takes 4 x (32 / lanes
+// per key) consecutive keys per iteration and fetches their scales with one coalesced load, handed round by shuffles.
+// Against the fp64 result on the dequantised caches this costs about 1e-3 relative (fp16 products), below what the
+// int8 rounding of the caches itself does; whole-step parity is tested with int8 caches on the golden sequences.
+constexpr int Q8_LANE_DIMS = 16;
+
+// 4 two's-complement bytes -> half2(q0, q1), half2(q2, q3), exact
+DEVI void widen_s8x4(uint32_t w, __half2& lo, __half2& hi) {
+  const uint32_t x = w ^ 0x80808080u;
+  const uint32_t a = __byte_perm(x, 0x64646464u, 0x4140), b = __byte_perm(x, 0x64646464u, 0x4342);
+  const __half2 off = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));  // 1024 + 128
+  lo = __hsub2(*reinterpret_cast<const __half2*>(&a), off);
+  hi = __hsub2(*reinterpret_cast<const __half2*>(&b), off);
 }
 
-// The same pass as attend_range over int8 caches, with the same lane layout: a key (or value) of D int8 is read by
-// D / 8 lanes with one 8-byte load each, its scale by every lane of the group. The row's new key and value are rounded
-// to bf16, quantised into the cache, and attended in that step as the bf16 values (the quantised copy serves the later
-// steps), as the reference does.
+// The same pass as attend_range over int8 caches. The row's new key and value are rounded to bf16, quantised into the
+// cache, and attended in that step as the bf16 values (the quantised copy serves the later steps), as the reference
+// does.
 template <int D, bool SELF>
 DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int start, int end, bool with_new,
                           float* s_m, float* s_l, float (*s_acc)[D + 4], float& M, float& L, float& O) {
-  constexpr int LPK = D / 8;           // lanes per key
-  constexpr int NG = NTHREADS / LPK;   // key groups per CTA
-  constexpr int U = 4;                 // keys in flight per group
-  const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
+  constexpr int LPK = D / Q8_LANE_DIMS;  // lanes per key
+  constexpr int GPW = 32 / LPK;          // keys per warp-wide load = lane groups per warp
+  constexpr int U = 4;                   // keys in flight per group
+  constexpr int KPW = U * GPW;           // keys per warp and iteration
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane / LPK, gl = lane % LPK, grp = warp * GPW + g;
   const int8_t* k8 = reinterpret_cast<const int8_t*>(p.k);
   const int8_t* v8 = reinterpret_cast<const int8_t*>(p.v);
-
-  float q[8];
-  {
-    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * 8;
-    const float4 a = ld_cg_f4(qp), b = ld_cg_f4(qp + 4);
-    q[0] = a.x * p.scale_log2, q[1] = a.y * p.scale_log2, q[2] = a.z * p.scale_log2, q[3] = a.w * p.scale_log2;
-    q[4] = b.x * p.scale_log2, q[5] = b.y * p.scale_log2, q[6] = b.z * p.scale_log2, q[7] = b.w * p.scale_log2;
-  }
   const size_t vec0 = ((size_t)s * p.H + h) * p.cap;  // index of key 0: scales, and * D the vectors
-  float m = -1e30f, l = 0.f, acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
-  // kf, vf: the lane's 8 dims of a key and a value as floats still to be multiplied by ksc, vsc
-  auto attend = [&](const float (&kf)[8], float ksc, const float (&vf)[8], float vsc, bool valid) {
-    float d = (q[0] * kf[0] + q[1] * kf[1]) + (q[2] * kf[2] + q[3] * kf[3]) + (q[4] * kf[4] + q[5] * kf[5]) +
-              (q[6] * kf[6] + q[7] * kf[7]);
+  // the lane's 16 dims of the query, pre-scaled into log2 units, as fp16 pairs
+  __half2 qh[8];
+  {
+    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * Q8_LANE_DIMS;
 #pragma unroll
-    for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    const float sc = valid ? d * ksc : -INFINITY;
-    const float mn = fmaxf(m, sc), a = ex2(m - mn), e0 = ex2(sc - mn), e = e0 * vsc;
-    l = l * a + e0;
+    for (int i = 0; i < 4; ++i) {
+      const float4 a = ld_cg_f4(qp + 4 * i);
+      qh[2 * i] = __floats2half2_rn(a.x * p.scale_log2, a.y * p.scale_log2);
+      qh[2 * i + 1] = __floats2half2_rn(a.z * p.scale_log2, a.w * p.scale_log2);
+    }
+  }
+  float m = -1e30f, l = 0.f;
+  __half2 acc[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = acc[i] * a + e * vf[i];
-    m = mn;
-  };
-  auto widen = [&](const uint2& w, float (&f)[8]) {
-    const uint32_t b0 = w.x ^ 0x80808080u, b1 = w.y ^ 0x80808080u;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) f[i] = q8_float(b0, i), f[4 + i] = q8_float(b1, i);
-  };
+  for (int i = 0; i < 8; ++i) acc[i] = __float2half2_rn(0.f);
 
   if (SELF && with_new && tid < 32) {
-    // warp 0: group 0 (lanes 0 .. LPK-1) holds the new key and value; all lanes go through the shuffles
-    const float* kp = p.q + (size_t)r * p.ldq + (p.H + h) * D + gl * 8;
+    // warp 0: group 0 (lanes 0 .. LPK-1) holds the new key and value in fp32; all lanes go through the shuffles
+    const float* qp = p.q + (size_t)r * p.ldq + h * D + gl * Q8_LANE_DIMS;
+    const float* kp = qp + p.H * D;
     const float* vp = kp + p.H * D;
-    float kn[8], vn[8];
+    float kn[16], vn[16], d = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float4 a = ld_cg_f4(kp + 4 * i), b = ld_cg_f4(vp + 4 * i);
+    for (int i = 0; i < 4; ++i) {
+      const float4 qa = ld_cg_f4(qp + 4 * i), a = ld_cg_f4(kp + 4 * i), b = ld_cg_f4(vp + 4 * i);
       const uint32_t k01 = pack_bf16(a.x, a.y), k23 = pack_bf16(a.z, a.w), v01 = pack_bf16(b.x, b.y), v23 = pack_bf16(b.z, b.w);
       kn[4 * i] = bf16_lo(k01), kn[4 * i + 1] = bf16_hi(k01), kn[4 * i + 2] = bf16_lo(k23), kn[4 * i + 3] = bf16_hi(k23);
       vn[4 * i] = bf16_lo(v01), vn[4 * i + 1] = bf16_hi(v01), vn[4 * i + 2] = bf16_lo(v23), vn[4 * i + 3] = bf16_hi(v23);
+      d += (qa.x * kn[4 * i] + qa.y * kn[4 * i + 1]) + (qa.z * kn[4 * i + 2] + qa.w * kn[4 * i + 3]);
     }
-    auto quantise = [&](const float (&f)[8], int8_t* dst, float* scale) {
+    auto quantise = [&](const float (&f)[16], int8_t* dst, float* scale) {
       float mx = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));
+      for (int i = 0; i < 16; ++i) mx = fmaxf(mx, fabsf(f[i]));
 #pragma unroll
       for (int o = 1; o < LPK; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float sc = mx > 0.f ? __fdiv_rn(mx, 127.f) : 1.f, inv = __fdiv_rn(1.f, sc);
-      uint32_t w[2] = {0, 0};
+      uint32_t w[4] = {0, 0, 0, 0};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 16; ++i) {
         const int qi = __float2int_rn(fminf(fmaxf(__fmul_rn(f[i], inv), -127.f), 127.f));
         w[i >> 2] |= (uint32_t)(qi & 0xff) << ((i & 3) * 8);
       }
-      if (grp == 0) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+      if (g == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
         if (gl == 0) *scale = sc;
       }
     };
-    quantise(kn, const_cast<int8_t*>(k8) + (vec0 + n) * D + gl * 8, p.ks + vec0 + n);
-    quantise(vn, const_cast<int8_t*>(v8) + (vec0 + n) * D + gl * 8, p.vs + vec0 + n);
-    attend(kn, 1.f, vn, 1.f, grp == 0);
+    quantise(kn, const_cast<int8_t*>(k8) + (vec0 + n) * D + gl * Q8_LANE_DIMS, p.ks + vec0 + n);
+    quantise(vn, const_cast<int8_t*>(v8) + (vec0 + n) * D + gl * Q8_LANE_DIMS, p.vs + vec0 + n);
+    d *= p.scale_log2;
+#pragma unroll
+    for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (g == 0) {  // the first key this group sees: weight 1
+      m = d, l = 1.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = __floats2half2_rn(vn[2 * i], vn[2 * i + 1]);
+    }
   }
 
-  const int8_t* kb = k8 + vec0 * D + gl * 8;
-  const int8_t* vb = v8 + vec0 * D + gl * 8;
-  const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
-  for (int j0 = first; j0 < end; j0 += NG * U) {
-    const int j = j0 + (grp % (32 / LPK));
-    uint2 kk[U], vv[U];
-    float ksc[U], vsc[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int jj = j + u * NG;
-      const bool ok = jj < end;
-      kk[u] = ok ? ld_stream8(kb + (size_t)jj * D) : make_uint2(0, 0);
-      vv[u] = ok ? ld_stream8(vb + (size_t)jj * D) : make_uint2(0, 0);
-      ksc[u] = ok ? __uint_as_float(ld_stream4(p.ks + vec0 + jj)) : 1.f;
-      vsc[u] = ok ? __uint_as_float(ld_stream4(p.vs + vec0 + jj)) : 1.f;
+  const int8_t* kb = k8 + vec0 * D + gl * Q8_LANE_DIMS;
+  const int8_t* vb = v8 + vec0 * D + gl * Q8_LANE_DIMS;
+  // whole-warp trip count: every lane runs the same number of iterations (shuffles), invalid keys are masked
+  for (int k0 = start + warp * KPW; k0 < end; k0 += (NTHREADS / 32) * KPW) {
+    // the scales of the warp's KPW keys: lane i fetches those of key k0 + i
+    float ks_l = 1.f, vs_l = 1.f;
+    if (lane < KPW && k0 + lane < end) {
+      ks_l = __uint_as_float(ld_stream4(p.ks + vec0 + k0 + lane));
+      vs_l = __uint_as_float(ld_stream4(p.vs + vec0 + k0 + lane));
     }
+    uint4 kw[U], vw[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (j0 + u * NG < end) {  // warp-uniform condition
-        float kf[8], vf[8];
-        widen(kk[u], kf), widen(vv[u], vf);
-        attend(kf, ksc[u], vf, vsc[u], j + u * NG < end);
+      const int j = k0 + u * GPW + g;
+      const bool ok = j < end;
+      kw[u] = ok ? ld_stream16(kb + (size_t)j * D) : make_uint4(0, 0, 0, 0);
+      vw[u] = ok ? ld_stream16(vb + (size_t)j * D) : make_uint4(0, 0, 0, 0);
+    }
+    float sc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t w[4] = {kw[u].x, kw[u].y, kw[u].z, kw[u].w};
+      __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __half2 lo, hi;
+        widen_s8x4(w[i], lo, hi);
+        a0 = __hfma2(qh[2 * i], lo, a0);
+        a1 = __hfma2(qh[2 * i + 1], hi, a1);
+      }
+      const float2 f = __half22float2(__hadd2(a0, a1));
+      float d = f.x + f.y;
+#pragma unroll
+      for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const float ksc = __shfl_sync(0xffffffffu, ks_l, u * GPW + g);
+      sc[u] = (k0 + u * GPW + g < end) ? d * ksc : -INFINITY;
+    }
+    const float mn = fmaxf(fmaxf(m, fmaxf(sc[0], sc[1])), fmaxf(sc[2], sc[3]));
+    const float a = ex2(m - mn);
+    const __half2 ah = __float2half2_rn(a);
+    l *= a;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = __hmul2(acc[i], ah);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const float e = ex2(sc[u] - mn);
+      const float vsc = __shfl_sync(0xffffffffu, vs_l, u * GPW + g);
+      l += e;
+      const __half2 eh = __float2half2_rn(e * vsc);
+      const uint32_t w[4] = {vw[u].x, vw[u].y, vw[u].z, vw[u].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __half2 lo, hi;
+        widen_s8x4(w[i], lo, hi);
+        acc[2 * i] = __hfma2(eh, lo, acc[2 * i]);
+        acc[2 * i + 1] = __hfma2(eh, hi, acc[2 * i + 1]);
       }
     }
+    m = mn;
   }
+  // merge the groups
   __syncthreads();  // the arrays may still be read by a previous pass
   if (gl == 0) s_m[grp] = m, s_l[grp] = l;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) s_acc[grp][gl * 8 + i] = acc[i];
+  for (int i = 0; i < 8; ++i) {
+    const float2 f = __half22float2(acc[i]);
+    s_acc[grp][gl * Q8_LANE_DIMS + 2 * i] = f.x, s_acc[grp][gl * Q8_LANE_DIMS + 2 * i + 1] = f.y;
+  }
   __syncthreads();
+  constexpr int NG = NTHREADS / LPK;
   M = -1e30f, L = 0.f, O = 0.f;
   if (tid < D) {
-#pragma unroll
+#pragma unroll 8
     for (int gi = 0; gi < NG; ++gi) M = fmaxf(M, s_m[gi]);
-#pragma unroll
+#pragma unroll 8
     for (int gi = 0; gi < NG; ++gi) {
       const float w = ex2(s_m[gi] - M);
       L += w * s_l[gi];
@@ -303,7 +355,7 @@ DEVI void row_state(const AttnArgs& p, int r, bool report, int& s, int& n) {
 
 template <int D, bool SELF, bool Q8>
 __global__ void __launch_bounds__(NTHREADS, 7) attention_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (D / 8);
+  constexpr int NG = NTHREADS / (Q8 ? D / Q8_LANE_DIMS : D / 8);  // lane groups = partial (max, sum, output) sets
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ int s_last;
@@ -364,7 +416,7 @@ constexpr int PAIR_MAX_ROWS = 256;
 
 template <int D, bool SELF, bool TABLE, bool Q8>
 __global__ void __launch_bounds__(NTHREADS, 7) attention_pair_kernel(const AttnArgs p) {
-  constexpr int NG = NTHREADS / (D / 8);
+  constexpr int NG = NTHREADS / (Q8 ? D / Q8_LANE_DIMS : D / 8);
   __shared__ float s_m[NG], s_l[NG];
   __shared__ float s_acc[NG][D + 4];
   __shared__ float s_peer[D + 2];  // CTA 0: the partial its peer computed for the long row

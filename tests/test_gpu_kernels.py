@@ -735,7 +735,9 @@ def test_attention_q8(nv, H, D, rows, self_, paired):
                 V = np.concatenate([vf[s, h, :n[s]], vn[None]])
             else:
                 K, V = kf[s, h, :n[s]], vf[s, h, :n[s]]
-            np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=3e-5, rtol=1e-4)
+            # the int8 pass multiplies in fp16 pairs (exact int8 -> fp16, query and softmax weights rounded to fp16):
+            # about 1e-3 relative, well below the int8 rounding of real caches
+            np.testing.assert_allclose(got[r, h * D:(h + 1) * D], _attention_ref(qq, K, V, scale), atol=4e-3, rtol=2e-3)
 
 
 def test_pick_semantics(nv):

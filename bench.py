@@ -343,10 +343,10 @@ def run_ours(args) -> None:
             "roofline": {"bound": "hbm", "kernel": ("attention_ring" if args.attn_ring else "attention_pair") + " kernel <64, cross> (64 rows x 16 heads), replayed from a CUDA graph",
                          "achieved": round(attn_gbs, 1), "peak": peak, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                          "peak_source": peak_kind, "bytes_per_launch": kv_bytes, "us_per_launch": round(attn_us, 2),
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one such launch from an ncu capture of a
-                         # smaller case (27.7 MB of keys and values), scaled by bytes: a stored figure, not measured by
-                         # this run (no number taken under a profiler is a bench value, and ncu is not run from here)
-                         "traffic": None if args.kv_int8 else int(kv_bytes * ATTN_TRAFFIC_PER_BYTE),
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one such launch from an ncu capture of the
+                         # same kernel on the same 64 rows: a stored figure, scaled by bytes, not measured by this run
+                         # (no number taken under a profiler is a bench value, and ncu is not run from here)
+                         "traffic": int(kv_bytes * (ATTN_TRAFFIC_PER_BYTE_Q8 if args.kv_int8 else ATTN_TRAFFIC_PER_BYTE)),
                          "traffic_source": "stored: ncu capture of this kernel, scaled by bytes; not re-measured by this run",
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
@@ -364,7 +364,10 @@ def run_ours(args) -> None:
         torch.distributed.destroy_process_group()
 
 
-ATTN_TRAFFIC_PER_BYTE = (55.73 + 0.20) / 55.44   # measured DRAM traffic / algorithmic K/V bytes, cross-attention launch
+# measured DRAM traffic (ncu dram__bytes_read.sum + dram__bytes_write.sum of one cross-attention launch over the
+# benchmark's 64 rows) / algorithmic key and value bytes of that launch: bf16 caches, int8 caches with their scales
+ATTN_TRAFFIC_PER_BYTE = (55.73 + 0.28) / 55.44
+ATTN_TRAFFIC_PER_BYTE_Q8 = 30.04 / 29.45
 
 
 def run_profile(args) -> None:

@@ -877,7 +877,7 @@ def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
             ref = kv[first:first + frames, :, which].transpose(1, 2, 0, 3)  # (L, H, frames, D)
             got = cache[:, slot, :, :frames].float().cpu().numpy()
             if not q8:
-                np.testing.assert_allclose(got, ref, atol=1e-6, rtol=2.0 ** -8)  # one bf16 rounding
+                np.testing.assert_allclose(got, ref, atol=1e-4, rtol=2.0 ** -8)  # one bf16 rounding of a ~fp32 sum
             else:
                 sc = scales[:, slot, :, :frames].cpu().numpy()
                 rb = bf16_round(ref.astype(np.float32))

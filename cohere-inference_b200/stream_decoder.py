@@ -26,33 +26,39 @@ from .packing import PackedLinear, dequantized, pack_linear
 ACTS = {"relu": nv.ACT_RELU, "gelu": nv.ACT_GELU}
 
 
+def _fp32(t: torch.Tensor) -> torch.Tensor:
+    return t.detach().float().contiguous()
+
+
 class _Layer:
-    """Packed projections and fp32 norms of one decoder layer (reference: _Layer, stream_decoder.py:51-62)."""
+    """One decoder layer as the step's kernels read it: six packed projections (q, k and v fused into one, as the
+    reference fuses them, kernels/stream_decoder.py:56-57) and the three LayerNorms in fp32. The projections that
+    follow a LayerNorm (qkv, cross-q, fc1) are packed together with that norm's folded vectors."""
+
+    # name -> (modules whose weights are stacked, index of the LayerNorm folded into it or None, feed-forward?)
+    SPEC = {"qkv": (("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"), 0, False),
+            "o": (("self_attn.o_proj",), None, False),
+            "cq": (("encoder_attn.q_proj",), 1, False),
+            "co": (("encoder_attn.o_proj",), None, False),
+            "fc1": (("mlp.fc1",), 2, True),
+            "fc2": (("mlp.fc2",), None, True)}
 
     def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool,
                  umma: frozenset = frozenset()):
-        sa, ca = layer.self_attn, layer.encoder_attn
-        f = lambda t: t.detach().float().contiguous()  # noqa: E731
-        self.norms = [(f(m.weight), f(m.bias), float(m.eps)) for m in
+        self.norms = [(_fp32(m.weight), _fp32(m.bias), float(m.eps)) for m in
                       (layer.input_layernorm, layer.post_attention_layernorm, layer.final_layernorm)]
-        cat = lambda *p: torch.cat([f(x) for x in p]).contiguous()  # noqa: E731
-
-        def pk(w, b, k, ln=None):  # ln: the norm this projection folds in (it reads the fp32 residual stream)
-            return pack_linear(w, b, k, keep_reference, a_kind=a_kind, ln=ln and ln[:2], max_rows=max_rows)
-
-        # umma: the projections that run on the tcgen05 kernel (dense int8 only)
-        uk = lambda name, k: nv.W_INT8_UMMA if (name in umma and k == nv.W_INT8) else k  # noqa: E731
-
-        self.qkv = pk(cat(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight),
-                      cat(sa.q_proj.bias, sa.k_proj.bias, sa.v_proj.bias), uk("qkv", kind), self.norms[0])
-        self.o = pk(sa.o_proj.weight, sa.o_proj.bias, uk("o", kind))
-        self.cq = pk(ca.q_proj.weight, ca.q_proj.bias, uk("cq", kind), self.norms[1])
-        self.co = pk(ca.o_proj.weight, ca.o_proj.bias, uk("co", kind))
-        self.fc1 = pk(layer.mlp.fc1.weight, layer.mlp.fc1.bias, uk("fc1", ffn_kind), self.norms[2])
-        self.fc2 = pk(layer.mlp.fc2.weight, layer.mlp.fc2.bias, uk("fc2", ffn_kind))
+        for name, (paths, norm, ffn) in self.SPEC.items():
+            mods = [layer.get_submodule(p) for p in paths]
+            k = ffn_kind if ffn else kind
+            if name in umma and k == nv.W_INT8:  # dense int8 on the tcgen05 kernel
+                k = nv.W_INT8_UMMA
+            packed = pack_linear(torch.cat([_fp32(m.weight) for m in mods]), torch.cat([_fp32(m.bias) for m in mods]),
+                                 k, keep_reference, a_kind=a_kind, max_rows=max_rows,
+                                 ln=None if norm is None else self.norms[norm][:2])
+            setattr(self, name, packed)
 
     def projections(self) -> list[PackedLinear]:
-        return [self.qkv, self.o, self.cq, self.co, self.fc1, self.fc2]
+        return [getattr(self, name) for name in self.SPEC]
 
 
 class _PrefillWeight:

@@ -53,8 +53,7 @@ int b200dec_sizeof(int which) {
 }
 
 // Kernels one b200dec_step of `rows` rows launches: embedding, per layer six projections (a projection whose tile does
-// not hold the rows goes in two passes) and two attention kernels, the vocabulary projection (64 rows per pass on the
-// tcgen05 kernel), the pick.
+// not hold the rows goes in two passes) and two attention kernels, the vocabulary projection, the pick.
 int b200dec_step_launches(const b200dec_plan* pl, int rows) {
   if (!pl || !pl->layer || rows < 1) return 0;
   const bool linked = pl->xh && pl->ln_stats && pl->a_kind == B200DEC_A_F16 && pl->layer[0].qkv.kind != B200DEC_W_BF16;
@@ -66,7 +65,7 @@ int b200dec_step_launches(const b200dec_plan* pl, int rows) {
          linear_passes(&ly.cq, ln_kind, true, rows) + linear_passes(&ly.co, pl->a_kind, false, rows) +
          linear_passes(&ly.fc1, ln_kind, true, rows) + linear_passes(&ly.fc2, pl->a_kind, false, rows);
   }
-  n += pl->head.kind == B200DEC_W_INT8_UMMA ? (rows + 63) / 64 : linear_passes(&pl->head, pl->head_a_kind, true, rows);
+  n += pl->head.kind == B200DEC_W_INT8_UMMA ? 1 : linear_passes(&pl->head, pl->head_a_kind, true, rows);
   return n;
 }
 

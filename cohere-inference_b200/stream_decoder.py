@@ -87,7 +87,7 @@ class StreamDecoder:
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
                  head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True,
-                 kv_prefetch_mb: int = 0, device_sched: bool = False):
+                 kv_prefetch_mb: int = 0, device_sched: bool = False, _packed: tuple | None = None):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
         accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
@@ -105,13 +105,12 @@ class StreamDecoder:
         scheduler never calls set_active after an eviction."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
-        dec, cfg = model.model.decoder, model.config
-        self.embed_src = dec.embed_tokens.weight
-        dev = self.embed_src.device
+        cfg = model.config
+        dev = model.device if _packed else model.model.decoder.embed_tokens.weight.device
         assert dev.type == "cuda", "StreamDecoder needs the model on a CUDA device: there is no CPU path"
         self.device = dev
         self.buckets = tuple(b for b in (buckets or self.BUCKETS) if b <= slots)
-        self.model, self.max_new_tokens = model, max_new_tokens
+        self.model, self.max_new_tokens = (None if _packed else model), max_new_tokens
         self.h, self.d, self.width = cfg.num_attention_heads, cfg.head_dim, cfg.hidden_size
         assert self.width == 1024 and (self.h, self.d) in ((8, 128), (16, 64)), "1024 wide, 8 x 128 or 16 x 64 heads"
         self.eos = cfg.eos_token_id if eos is None else eos
@@ -121,38 +120,26 @@ class StreamDecoder:
         self.attn_ring = bool(attn_ring)
         self.kv_prefetch_mb, self.device_sched = int(kv_prefetch_mb), bool(device_sched)
         assert not (self.device_sched and chains > 1), "the device-side active list goes with a single chain"
-        self.act = ACTS[cfg.hidden_act]
+        self.act, self._act_name, self._cfg_eos = ACTS[cfg.hidden_act], cfg.hidden_act, cfg.eos_token_id
         kind = nv.W_INT8 if int8 else nv.W_BF16
         ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
         self.a_kind = nv.A_F16 if int8 else nv.A_F32_SPLIT
         self.head_a_kind = nv.A_F32_SPLIT if (head_split or not int8) else nv.A_F16
         bm = max(self.buckets)
         with torch.cuda.device(dev):
-            f = lambda t: t.detach().float().contiguous()  # noqa: E731
-            self.embed = dec.embed_tokens.weight.detach().to(torch.bfloat16).contiguous()
-            self.pos_table = dec.pos_emb.weight.detach().to(torch.bfloat16).contiguous()
-            self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
-            ln = lambda m: (f(m.weight), f(m.bias), float(m.eps))  # noqa: E731
-            self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
             # proj_umma: the dense int8 projections that run on the tcgen05 kernel of csrc/linear_umma.cu: True = qkv and
             # fc1 (the two with enough multiply per CTA to gain; the narrow ones and fc2 measured 1-2 % slower there
             # than on mma.sync), "all", or a comma-separated subset of qkv,o,cq,co,fc1,fc2
             names = "qkv,fc1" if proj_umma is True else "qkv,o,cq,co,fc1,fc2" if proj_umma == "all" else (proj_umma or "")
             umma = frozenset(n for n in names.split(",") if n) if int8 else frozenset()
-            self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma) for layer in dec.layers]
-            head_kind = nv.W_INT8_UMMA if (head_umma and int8 and self.vocab % 128 == 0) else kind
-            self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
-                                    a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
-            # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection; these run
-            # once per request, not in the step, and keep bf16 weights in every mode, as the reference does
-            # (kernels/stream_decoder.py:91-94, 232)
-            self.proj = _PrefillWeight(f(dec.proj.weight), f(dec.proj.bias))
-            self.cross = _PrefillWeight(
-                torch.cat([f(w) for layer in dec.layers
-                           for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)]),
-                torch.cat([f(b) for layer in dec.layers
-                           for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)]))
-            assert self.proj.n == self.width and self.cross.n == len(dec.layers) * 2 * self.width
+            self._pack_options = dict(int8=bool(int8), ffn_sparse=bool(ffn_sparse), head_split=bool(head_split),
+                                      head_umma=bool(head_umma), proj_umma=",".join(sorted(umma)), max_rows=bm)
+            if _packed:
+                self._load_packed(*_packed)
+            else:
+                self._pack_from_model(model, kind, ffn_kind, bm, keep_reference, umma, head_umma)
+            self.vocab, self.max_pos = self.embed.shape[0], self.pos_table.shape[0]
+            assert self.proj.n == self.width and self.cross.n == len(self.layers) * 2 * self.width
             L, S = len(self.layers), slots
             self.slots, self.dummy = S, S
             self.max_prompt = max_prompt
@@ -228,6 +215,98 @@ class StreamDecoder:
             else:
                 self.reset()
                 self.stream.synchronize()
+
+    # ---- weights: packed from a model, or loaded as packed ---------------------------------------------------------
+
+    def _pack_from_model(self, model, kind, ffn_kind, bm, keep_reference, umma, head_umma) -> None:
+        dec = model.model.decoder
+        self.embed = dec.embed_tokens.weight.detach().to(torch.bfloat16).contiguous()
+        self.pos_table = dec.pos_emb.weight.detach().to(torch.bfloat16).contiguous()
+        ln = lambda m: (_fp32(m.weight), _fp32(m.bias), float(m.eps))  # noqa: E731
+        self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
+        self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma) for layer in dec.layers]
+        head_kind = nv.W_INT8_UMMA if (head_umma and self.int8 and self.embed.shape[0] % 128 == 0) else kind
+        self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
+                                a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
+        # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection; these run once
+        # per request, not in the step, and keep bf16 weights in every mode, as the reference does
+        # (kernels/stream_decoder.py:91-94, 232)
+        self.proj = _PrefillWeight(_fp32(dec.proj.weight), _fp32(dec.proj.bias))
+        self.cross = _PrefillWeight(
+            torch.cat([_fp32(w) for layer in dec.layers
+                       for w in (layer.encoder_attn.k_proj.weight, layer.encoder_attn.v_proj.weight)]),
+            torch.cat([_fp32(b) for layer in dec.layers
+                       for b in (layer.encoder_attn.k_proj.bias, layer.encoder_attn.v_proj.bias)]))
+
+    def _load_packed(self, manifest: dict, tensors: dict) -> None:
+        """The weights exactly as save_packed wrote them (same tiling, same bits): nothing is re-quantised."""
+        if manifest["pack_options"] != self._pack_options:
+            raise ValueError(f"packed with {manifest['pack_options']}, asked for {self._pack_options}")
+        t = {k: v.to(self.device) for k, v in tensors.items()}
+        self.embed, self.pos_table = t["embed"], t["pos_table"]
+        eps = manifest["eps"]
+        self.emb_ln, self.final_ln = ((t[n + ".w"], t[n + ".b"], eps[n]) for n in ("emb_ln", "final_ln"))
+
+        def packed(name: str) -> PackedLinear:
+            m = manifest["projections"][name]
+            return PackedLinear(m["kind"], m["n"], m["k"], t[name + ".tiled"], t.get(name + ".meta"), t.get(name + ".scale"),
+                                t.get(name + ".bias"), m["warps"], m["ksplit"], ln_g=t.get(name + ".ln_g"),
+                                ln_bias=t.get(name + ".ln_bias"))
+        self.layers = []
+        for i in range(manifest["layers"]):
+            ly = object.__new__(_Layer)
+            ly.norms = [(t[f"layer{i}.ln{j}.w"], t[f"layer{i}.ln{j}.b"], eps[f"layer{i}.ln{j}"]) for j in (1, 2, 3)]
+            for name in _Layer.SPEC:
+                setattr(ly, name, packed(f"layer{i}.{name}"))
+            self.layers.append(ly)
+        self.head = packed("head")
+        for name in ("proj", "cross"):
+            w = object.__new__(_PrefillWeight)
+            w.image, w.bias = t[f"prefill.{name}.image"], t[f"prefill.{name}.bias"]
+            w.n, w.k = manifest["prefill"][name]
+            setattr(self, name, w)
+
+    def save_packed(self, path: str) -> str:
+        """Writes the packed weights (every tensor of packed_tensors(), as the kernels read them) with a manifest: the
+        model's configuration, the packing options, every projection's kind and tile, and the SHA-256 of the lot.
+        StreamDecoder.from_packed(path) gives a decoder with the same bits without the original model. Returns the
+        digest."""
+        digest = self.weights_digest()
+        proj = {f"layer{i}.{n}": getattr(ly, n) for i, ly in enumerate(self.layers) for n in _Layer.SPEC}
+        proj["head"] = self.head
+        eps = {"emb_ln": self.emb_ln[2], "final_ln": self.final_ln[2]}
+        eps.update({f"layer{i}.ln{j + 1}": ly.norms[j][2] for i, ly in enumerate(self.layers) for j in range(3)})
+        manifest = dict(
+            format=1, sha256=digest, layers=len(self.layers), eps=eps, pack_options=self._pack_options,
+            config=dict(num_attention_heads=self.h, head_dim=self.d, hidden_size=self.width, hidden_act=self._act_name,
+                        eos_token_id=self._cfg_eos, pad_token_id=self.pad),
+            projections={k: dict(kind=p.kind, n=p.n, k=p.k, warps=p.warps, ksplit=p.ksplit) for k, p in proj.items()},
+            prefill=dict(proj=(self.proj.n, self.proj.k), cross=(self.cross.n, self.cross.k)))
+        torch.save(dict(manifest=manifest, tensors={k: v.detach().cpu() for k, v in self.packed_tensors().items()}), path)
+        return digest
+
+    @classmethod
+    def from_packed(cls, path: str, device: torch.device | str = "cuda", **kw) -> "StreamDecoder":
+        """A decoder from a file written by save_packed: the manifest's digest is checked against the loaded bytes
+        before anything else. kw: the run-time arguments of the constructor (slots, max_new_tokens, max_prompt,
+        max_audio_s, buckets, eos, record, pdl, kv_int8, device_sched, ...); the packing options come from the file
+        (the largest bucket must be the one the weights were tiled for)."""
+        from types import SimpleNamespace
+        from .synth import _EncoderStub
+        blob = torch.load(path, map_location="cpu", weights_only=True)
+        man = blob["manifest"]
+        if man.get("format") != 1:
+            raise ValueError(f"{path}: unknown packed-weight format {man.get('format')}")
+        shim = SimpleNamespace(config=SimpleNamespace(**man["config"]), device=torch.device(device),
+                               model=SimpleNamespace(encoder=_EncoderStub()))
+        if shim.device.index is None:
+            shim.device = torch.device("cuda", torch.cuda.current_device())
+        po = man["pack_options"]
+        self = cls(shim, int8=po["int8"], ffn_sparse=po["ffn_sparse"], head_split=po["head_split"],
+                   head_umma=po["head_umma"], proj_umma=po["proj_umma"] or False, _packed=(man, blob["tensors"]), **kw)
+        if self.weights_digest() != man["sha256"]:
+            raise ValueError(f"{path}: the packed weights do not match the manifest's SHA-256")
+        return self
 
     # ---- the step ------------------------------------------------------------------------------------------------
 

@@ -214,7 +214,8 @@ int b200dec_head_partials(const b200dec_weight* w);
 /* The same vocabulary projection on the fifth-generation tensor cores (tcgen05.mma, accumulator in tensor memory):
  * x (rows, lda) fp32 is normalised by ln inside the kernel (ln is required), w->kind must be B200DEC_W_INT8_UMMA
  * (w->w from b200dec_tile_int8_umma, K = 1024, N a multiple of 128; w->warps, ksplit, ln_g, ln_bias unused) and the
- * partials are one per 128 channels (b200dec_head_partials() = N / 128). rows <= 128, 64 per pass. Replaces the same
+ * partials are one per 128 channels (b200dec_head_partials() = N / 128). rows <= 128 (above 64 rows a second set of
+ * CTAs of the same launch takes rows 64..; the weights come from HBM once). Replaces the same
  * reference code as b200dec_head_argmax. status receives B200DEC_ST_TIMEOUT if a bounded wait ran out. */
 int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,
                       float* part_max, int32_t* part_idx, float* logits, int32_t* status, int pdl, void* stream);

@@ -350,3 +350,31 @@ def test_bounded_wait_runs_out_and_the_context_survives(bit, what):
         dec.status.zero_()
     got, _ = _run_teacher_forced(dec, memory, prompts, 4)
     assert np.array_equal(got, want), what
+
+
+def test_packed_weights_round_trip(tmp_path):
+    """save_packed -> from_packed: the same digest, the same bits out of the step, without the original model; a
+    changed byte is caught by the manifest's SHA-256."""
+    from cohere_inference_b200 import StreamDecoder
+    model = synthetic_model(0, layers=2)
+    rng = np.random.default_rng(6)
+    memory = [rng.standard_normal((70, 1024)).astype(np.float32) for _ in range(3)]
+    prompts = [rng.integers(0, 16384, 4).astype(np.int64) for _ in range(3)]
+    run = dict(slots=4, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, record=True)
+    dec = _decoder(model, int8=True, ffn_sparse=True, **run)
+    want, _ = _run_teacher_forced(dec, memory, prompts, 5)
+    path = str(tmp_path / "decoder.b200dec")
+    digest = dec.save_packed(path)
+    assert digest == dec.weights_digest() and len(digest) == 64
+    del dec
+    again = StreamDecoder.from_packed(path, **run)
+    assert again.weights_digest() == digest and again.model is None
+    got, _ = _run_teacher_forced(again, memory, prompts, 5)
+    assert np.array_equal(got, want)
+    blob = torch.load(path, weights_only=True)
+    blob["tensors"]["layer1.fc2.tiled"][123] ^= 1
+    torch.save(blob, path)
+    with pytest.raises(ValueError, match="SHA-256"):
+        StreamDecoder.from_packed(path, **run)
+    with pytest.raises(ValueError, match="packed with"):  # tiled for buckets up to 4 rows, asked for up to 2
+        StreamDecoder.from_packed(path, **dict(run, slots=2))

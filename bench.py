@@ -122,7 +122,8 @@ def run_ours(args) -> None:
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
                         head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8,
-                        proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch)
+                        proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch,
+                        exchange=args.exchange)
     digest = dec.weights_digest()
     dp.check_identical(digest, dev)  # replicas: the same packed bits on every GPU, before anything is timed
     lens, memory_host, prompts = make_inputs(1000 + rank)
@@ -597,6 +598,8 @@ def main() -> None:
     ap.add_argument("--no-classes", action="store_true", help="skip the per-class passes")
     ap.add_argument("--kv-prefetch", type=int, default=KV_PREFETCH_MB, help="MB of an attention launch's keys and values "
                     "that the projections before it start towards L2 (0: off)")
+    ap.add_argument("--exchange", type=int, default=1, help="how a cluster's CTAs hand over partial results: 0 stores + "
+                    "cluster barrier, 1 st.async onto per-CTA mbarriers")
     ap.add_argument("--device-sched", action="store_true", help="stream workloads: the active list lives on the device")
     args = ap.parse_args()
     # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 themselves (NCCL's

@@ -65,8 +65,51 @@ inline cudaError_t launch_kernel(Kern kern, dim3 grid, dim3 block, size_t smem, 
 // kernel therefore arrives at the cluster barrier as its first instruction and completes that phase (the wait) just
 // before its first remote store; in between lie the weight prefetch and the wait for the previous kernel, so the
 // pair costs nothing on the critical path. Each thread that arrives must wait before it arrives again (cluster.sync()).
-DEVI void cluster_arrive_entry() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
-DEVI void cluster_wait_entry() { asm volatile("barrier.cluster.wait;" ::: "memory"); }
+DEVI void cluster_arrive_entry() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+DEVI void cluster_wait_entry() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
+// ---- exchange of partial results inside a cluster without a barrier -------------------------------------------------
+// Every store into a peer's shared memory (st.async) also counts its bytes on an mbarrier of that peer; a CTA that
+// knows how many bytes it is owed waits on its own mbarrier only (bounded), instead of a barrier across the cluster that
+// first has to see every CTA's stores acknowledged. A CTA leaves once it holds everything it is owed, so nobody writes
+// into a CTA that has gone. The mbarrier is initialised before the entry arrive (release) above, and peers complete
+// that phase (acquire) before their first store, so it is never touched uninitialised.
+DEVI uint32_t smem_addr_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+DEVI uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {  // the same shared-memory offset in CTA `rank`
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+DEVI void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(remote_addr),
+               "r"(__float_as_uint(v)), "r"(remote_bar)
+               : "memory");
+}
+DEVI void st_async_f32x2(uint32_t remote_addr, float2 v, uint32_t remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.b32 [%0], {%1, %2}, [%3];" ::"r"(remote_addr),
+               "r"(__float_as_uint(v.x)), "r"(__float_as_uint(v.y)), "r"(remote_bar)
+               : "memory");
+}
+DEVI void xbar_init(uint64_t* bar) {  // one arrival: the owner's expect_tx
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr_u32(bar)));
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+DEVI void xbar_expect(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr_u32(bar)), "r"(bytes) : "memory");
+}
+DEVI bool xbar_wait(uint64_t* bar, uint32_t limit) {  // phase 0; false when the limit ran out
+  const uint32_t addr = smem_addr_u32(bar);
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(addr), "r"(0)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
 
 // ---- loads --------------------------------------------------------------------------------------------------------
 // Read-once streams (weights, KV cache): no L1 allocation.

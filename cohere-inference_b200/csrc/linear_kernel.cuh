@@ -35,6 +35,8 @@ struct LinArgs {
   float ln_eps;
   int lda, ldo, rows, N, out_kind, act, head;
   KvPrefetch pf;  // keys and values of the next attention launch to start on their way into L2 (sched null: none)
+  int async_x;    // the cluster's partial results travel by st.async onto per-CTA mbarriers (else stores + barrier)
+  int* status;    // async_x: receives B200DEC_ST_TIMEOUT if the bounded wait for the partials runs out
 };
 
 template <int WT>
@@ -122,6 +124,8 @@ struct LinSmem {
 // channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) {
+  __shared__ __align__(8) uint64_t xbar;  // counts the bytes this CTA is owed by its cluster (async_x)
+  if (p_in.async_x && threadIdx.x == 0) xbar_init(&xbar);
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   LinArgs p = p_in;
   if (gridDim.z > 1) {  // the rows are dealt over blockIdx.z, MB each (fp16 operands only)
@@ -188,6 +192,8 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
     }
   }
   pdl_wait();
+  if (p.async_x && tid == 0)  // partial tiles from every CTA of the cluster (this one included) and the rows' sums
+    xbar_expect(&xbar, (uint32_t)(KSPLIT * p.rows * CPR * 4 + (LN == 2 ? p.rows * 8 : LN == 1 ? KSPLIT * p.rows * 8 : 0)));
   if (p.pf.sched)
     kv_prefetch_issue(p.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                       gridDim.x * gridDim.y * gridDim.z, tid, NT);
@@ -225,7 +231,13 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
         const int r = rank + KSPLIT * (warp + NW * j);
         float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
         s1 = warp_sum(s1), s2 = warp_sum(s2);
-        if (r < p.rows && lane < KSPLIT) cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
+        if (r < p.rows && lane < KSPLIT) {
+          if (p.async_x)
+            st_async_f32x2(map_to_rank(smem_addr_u32(stats + r), lane), make_float2(s1, s2),
+                           map_to_rank(smem_addr_u32(&xbar), lane));
+          else
+            cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
+        }
       }
     }
     cp_async_wait_all();
@@ -305,7 +317,13 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
 #pragma unroll
       for (int it = 0; it < RPG; ++it) {
         const int r = (tid >> 3) + it * (NT / 8);
-        if (r < p.rows && l8 < KSPLIT) cluster.map_shared_rank(stats, l8)[rank * MB + r] = make_float2(s1[it], s2[it]);
+        if (r < p.rows && l8 < KSPLIT) {
+          if (p.async_x)
+            st_async_f32x2(map_to_rank(smem_addr_u32(stats + rank * MB + r), l8), make_float2(s1[it], s2[it]),
+                           map_to_rank(smem_addr_u32(&xbar), l8));
+          else
+            cluster.map_shared_rank(stats, l8)[rank * MB + r] = make_float2(s1[it], s2[it]);
+        }
       }
     }
   }
@@ -393,14 +411,29 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
   if constexpr (LN == 0) cluster_wait_entry();  // with a LayerNorm the statistics were the first remote stores
   {
     const int ch0 = warp * 16 + g, ch1 = ch0 + 8;
-    float* dst0 = cluster.map_shared_rank(recv, ch0 / CPR) + rank * MB * CPR + ch0 % CPR;
-    float* dst1 = cluster.map_shared_rank(recv, ch1 / CPR) + rank * MB * CPR + ch1 % CPR;
+    if (p.async_x) {
+      const uint32_t d0 = map_to_rank(smem_addr_u32(recv + rank * MB * CPR + ch0 % CPR), ch0 / CPR);
+      const uint32_t d1 = map_to_rank(smem_addr_u32(recv + rank * MB * CPR + ch1 % CPR), ch1 / CPR);
+      const uint32_t b0 = map_to_rank(smem_addr_u32(&xbar), ch0 / CPR), b1 = map_to_rank(smem_addr_u32(&xbar), ch1 / CPR);
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-      if (nb < ntiles) {
-        const int r = nb * 8 + 2 * t;
-        if (r < p.rows) dst0[r * CPR] = acc[nb][0], dst1[r * CPR] = acc[nb][2];
-        if (r + 1 < p.rows) dst0[(r + 1) * CPR] = acc[nb][1], dst1[(r + 1) * CPR] = acc[nb][3];
+      for (int nb = 0; nb < NB; ++nb) {
+        if (nb < ntiles) {
+          const int r = nb * 8 + 2 * t;
+          if (r < p.rows) st_async_f32(d0 + r * CPR * 4, acc[nb][0], b0), st_async_f32(d1 + r * CPR * 4, acc[nb][2], b1);
+          if (r + 1 < p.rows)
+            st_async_f32(d0 + (r + 1) * CPR * 4, acc[nb][1], b0), st_async_f32(d1 + (r + 1) * CPR * 4, acc[nb][3], b1);
+        }
+      }
+    } else {
+      float* dst0 = cluster.map_shared_rank(recv, ch0 / CPR) + rank * MB * CPR + ch0 % CPR;
+      float* dst1 = cluster.map_shared_rank(recv, ch1 / CPR) + rank * MB * CPR + ch1 % CPR;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        if (nb < ntiles) {
+          const int r = nb * 8 + 2 * t;
+          if (r < p.rows) dst0[r * CPR] = acc[nb][0], dst1[r * CPR] = acc[nb][2];
+          if (r + 1 < p.rows) dst0[(r + 1) * CPR] = acc[nb][1], dst1[(r + 1) * CPR] = acc[nb][3];
+        }
       }
     }
   }
@@ -426,7 +459,11 @@ __global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) 
       lb_pre = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
     }
   }
-  cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this
+  if (p.async_x) {  // everything this CTA is owed has landed (nobody writes to it afterwards: it may leave)
+    if (!xbar_wait(&xbar, 1u << 22) && lane == 0 && p.status) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+  } else {
+    cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this
+  }
 
   const int padded = (items + 31) & ~31;
   for (int it = tid; it < padded; it += NT) {

@@ -50,7 +50,6 @@ struct UArgs {
   int lda, ldo, rows, N, K, out_kind, act, stats_slots;
   uint32_t wait_limit;  // polls before the wait for the MMAs gives up
   int withhold;         // tests only: the commit is left out, so that wait runs out
-  int async_x;          // the cluster's partial results travel by st.async onto per-CTA mbarriers (else stores + barrier)
 };
 
 // MB: row capacity (MMA N); KSPLIT: CTAs per cluster; NKB: 64-k blocks per CTA
@@ -146,10 +145,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   unsigned char* xs = smem + S::OFF_X;
   float* recv = reinterpret_cast<float*>(smem + S::OFF_RECV);  // [KSPLIT][MB][CPR]
   float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
-  __shared__ __align__(8) uint64_t d_full, xbar;  // xbar: counts the bytes this CTA is owed by its cluster (async_x)
+  __shared__ __align__(8) uint64_t d_full;
   __shared__ uint32_t tmem_base;
 
-  if (p.async_x && threadIdx.x == 0) xbar_init(&xbar);
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = blockIdx.x, tile = blockIdx.y;
@@ -176,8 +174,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   pdl_wait();
-  if (p.async_x && tid == 0)  // partial tiles from every CTA of the cluster (this one included) and the rows' sums
-    xbar_expect(&xbar, (uint32_t)(KSPLIT * p.rows * CPR * 4 + (LN ? p.rows * 8 : 0)));
 
   // ---- stage this K slice of the operand into swizzled tiles; the cluster adds up the rows' statistics -------------
   const int k0 = rank * KSLICE;
@@ -205,13 +201,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
       const int r = rank + KSPLIT * (warp + 8 * j);
       float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
       s1 = warp_sum(s1), s2 = warp_sum(s2);
-      if (r < p.rows && lane < KSPLIT) {
-        if (p.async_x)
-          st_async_f32x2(map_to_rank(smem_addr_u32(stats + r), lane), make_float2(s1, s2),
-                         map_to_rank(smem_addr_u32(&xbar), lane));
-        else
-          cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
-      }
+      if (r < p.rows && lane < KSPLIT) cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
     }
   }
   // ---- widen the weights into the A tiles ---------------------------------------------------------------------------
@@ -253,8 +243,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   if constexpr (!LN) cluster_wait_entry();  // with a LayerNorm the statistics were the first remote stores
   {
     float* dst = cluster.map_shared_rank(recv, ch / CPR) + (size_t)rank * MB * CPR + ch % CPR;
-    const uint32_t adst = map_to_rank(smem_addr_u32(recv + (size_t)rank * MB * CPR + ch % CPR), ch / CPR);
-    const uint32_t abar = map_to_rank(smem_addr_u32(&xbar), ch / CPR);
 #pragma unroll
     for (int c0 = 0; c0 < MB / 2; c0 += 32) {
       uint32_t d[32];
@@ -262,10 +250,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const int r = hf * (MB / 2) + c0 + i;
-        if (r < p.rows) {
-          if (p.async_x) st_async_f32(adst + r * CPR * 4, __uint_as_float(d[i]), abar);
-          else dst[r * CPR] = __uint_as_float(d[i]);
-        }
+        if (r < p.rows) dst[r * CPR] = __uint_as_float(d[i]);
       }
     }
   }
@@ -283,11 +268,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   if (add && tid < items)
     resid = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + (size_t)(tid / GPR) * p.ldo + n_mine));
   tc_fence_before();
-  if (p.async_x) {  // everything this CTA is owed has landed (nobody writes to it afterwards: it may leave)
-    if (!xbar_wait(&xbar, p.wait_limit) && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
-  } else {
-    cluster.sync();  // all partials and statistics have landed; nobody touches remote shared memory after this
-  }
+  cluster.sync();  // all partials and statistics have landed; nobody touches remote shared memory after this
 
   const int padded = (items + 31) & ~31;
   for (int it = tid; it < padded; it += NTHREADS) {  // NTHREADS % GPR == 0: a thread keeps its four channels
@@ -412,7 +393,6 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
     p.lda = lda, p.ldo = ldo, p.rows = rows - r0 < pass ? rows - r0 : pass, p.N = w->n, p.K = w->k;
     p.out_kind = out_kind, p.act = act;
     p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
-    p.async_x = lk.exchange == 1;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
     if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, ln != nullptr, pdl, s);

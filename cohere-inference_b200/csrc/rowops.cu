@@ -254,6 +254,8 @@ struct PickArgs {
   const int* limit;
   int64_t* out;
   int64_t* argmax;
+  uint8_t* flags_host;  // pinned host memory mapped into the device's address space, or null: the end flags, written
+                        // through (posted writes over the bus: the step waits for no copy)
   int partials, rows, dummy, max_prompt, out_cols, eos;
 };
 
@@ -281,14 +283,19 @@ __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   if (lane != 0) return;
   if (arg == 0x7fffffff) arg = 0;  // a row of NaN
   if (p.argmax) p.argmax[s] = arg;
-  if (p.finished[s]) return;  // ended at an earlier step: nothing moves until the host retires the slot
+  if (p.finished[s]) {  // ended at an earlier step: nothing moves until the host retires the slot
+    if (p.flags_host) p.flags_host[s] = 1;
+    return;
+  }
   const int at = p.pos[s] + 1;
   const bool in_prompt = at < p.plen[s];
   const int64_t nt = in_prompt ? p.forced[(size_t)s * p.max_prompt + min(at, p.max_prompt - 1)] : (int64_t)arg;
   if (at < p.out_cols) p.out[(size_t)s * p.out_cols + at] = nt;
   p.tok[s] = nt;
   p.pos[s] = at;
-  p.finished[s] = (!in_prompt && (nt == p.eos || at >= p.limit[s])) ? 1 : 0;
+  const uint8_t done = (!in_prompt && (nt == p.eos || at >= p.limit[s])) ? 1 : 0;
+  p.finished[s] = done;
+  if (p.flags_host) p.flags_host[s] = done;
 }
 
 // kv (nrows, L * 2 * H * D) fp32 -> bf16 caches (L, S1, H, T, D); one thread per 8 values
@@ -471,12 +478,12 @@ int layer_norm_impl(const float* x, b200dec_norm ln, void* hn, int hn_kind, int 
 
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
-              const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax, int pdl,
-              void* stream) {
+              const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
+              uint8_t* flags_host, int pdl, void* stream) {
   B200_REQUIRE(part_max && part_idx && active && tok && pos && finished && forced && plen && limit && out,
                "pick: null pointer");
   B200_REQUIRE(rows >= 1 && partials >= 1 && max_prompt >= 1, "pick: sizes");
-  PickArgs p{part_max, part_idx, active, tok, pos, finished, forced, plen, limit, out, argmax,
+  PickArgs p{part_max, part_idx, active, tok, pos, finished, forced, plen, limit, out, argmax, flags_host,
              partials, rows, dummy, max_prompt, out_cols, eos};
   const cudaError_t e = launch_kernel(pick_kernel, dim3((rows + 3) / 4), dim3(128), 0, (cudaStream_t)stream, 0, pdl, p);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "pick launch: %s", cudaGetErrorString(e));
@@ -524,9 +531,9 @@ int b200dec_layer_norm(const float* x, b200dec_norm ln, void* hn, int hn_kind, i
 int b200dec_pick(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows,
                  int dummy, int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
                  const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
-                 int pdl, void* stream) {
+                 uint8_t* flags_host, int pdl, void* stream) {
   return pick_impl(part_max, part_idx, partials, active, rows, dummy, tok, pos, finished, forced, max_prompt, plen,
-                   limit, out, out_cols, eos, argmax, pdl, stream);
+                   limit, out, out_cols, eos, argmax, flags_host, pdl, stream);
 }
 
 int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(128) admit_kernel(const AdmitArgs p) {
 struct CompactArgs {
   int32_t* active;
   int32_t* n_active;
+  int32_t* live_host;  // pinned host memory mapped into the device's address space, or null: the live count
   const uint8_t* finished;
   int rows, dummy;
 };
@@ -105,7 +106,10 @@ __global__ void __launch_bounds__(128) compact_kernel(const CompactArgs p) {
   __syncthreads();  // every row has been read
   if (live) p.active[before] = s;
   if (r >= total && r < p.rows) p.active[r] = p.dummy;
-  if (r == 0) *p.n_active = total;
+  if (r == 0) {
+    *p.n_active = total;
+    if (p.live_host) *p.live_host = total;
+  }
 }
 
 }  // namespace
@@ -129,10 +133,11 @@ int b200dec_admit(const b200dec_plan* pl, const int32_t* records, int n, int32_t
   return check_launch("admit");
 }
 
-int b200dec_compact_active(const b200dec_plan* pl, int rows, int32_t* n_active, int pdl, void* stream) {
+int b200dec_compact_active(const b200dec_plan* pl, int rows, int32_t* n_active, int32_t* live_host, int pdl,
+                           void* stream) {
   B200_REQUIRE(pl && pl->active && pl->finished && n_active, "compact_active: null pointer");
   B200_REQUIRE(rows >= 1 && rows <= 128, "compact_active: rows %d (1..128)", rows);
-  CompactArgs a{const_cast<int32_t*>(pl->active), n_active, pl->finished, rows, pl->slots};
+  CompactArgs a{const_cast<int32_t*>(pl->active), n_active, live_host, pl->finished, rows, pl->slots};
   const cudaError_t e = launch_kernel(compact_kernel, dim3(1), dim3(128), 0, (cudaStream_t)stream, 0, pdl != 0, a);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "compact_active launch: %s", cudaGetErrorString(e));
   return 0;

@@ -22,8 +22,8 @@ int embed_ln_impl(const int32_t* active, const int64_t* tok, const int32_t* pos,
 int linear_passes(const b200dec_weight* w, int a_kind, bool ln, int rows);
 int pick_impl(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows, int dummy,
               int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
-              const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax, int pdl,
-              void* stream);
+              const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
+              uint8_t* flags_host, int pdl, void* stream);
 }  // namespace b200dec_detail
 
 using namespace b200dec_detail;
@@ -223,7 +223,8 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     B200_TRY_IN(1, head_impl(&pl->head, x, pl->head_a_kind, &pl->final_ln, D_MODEL, rows, head_max, head_idx, logits, pdl,
                        stream));
   B200_TRY_IN(1, pick_impl(head_max, head_idx, partials, active, rows, pl->slots, pl->tok, pl->pos, pl->finished, pl->forced,
-                     pl->max_prompt, pl->plen, pl->limit, pl->out, pl->out_cols, pl->eos, pl->argmax, pdl, stream));
+                     pl->max_prompt, pl->plen, pl->limit, pl->out, pl->out_cols, pl->eos, pl->argmax, pl->flags_host, pdl,
+                           stream));
   return 0;
 }
 

@@ -52,7 +52,7 @@ class Plan(C.Structure):
                 ("embed", vp), ("pos_table", vp), ("emb_ln", Norm), ("final_ln", Norm), ("layer", C.POINTER(Layer)),
                 ("head", Weight),
                 ("active", vp), ("tok", vp), ("pos", vp), ("plen", vp), ("limit", vp), ("cross_len", vp),
-                ("finished", vp), ("forced", vp), ("out", vp), ("status", vp),
+                ("finished", vp), ("forced", vp), ("out", vp), ("flags_host", vp), ("status", vp),
                 ("x", vp), ("qkv", vp), ("cq", vp), ("att", vp), ("mid", vp),
                 ("attn_part", vp), ("attn_count", vp), ("head_max", vp), ("head_idx", vp),
                 ("xh", vp), ("ln_stats", vp), ("sched_self", vp), ("sched_cross", vp), ("logits", vp), ("argmax", vp)]
@@ -90,7 +90,7 @@ PROTOTYPES = {
                                            vp, vp, C.c_int, vp]),
     "b200dec_tile_int8_umma": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_pick": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, vp, vp, vp, C.c_int,
-                               C.c_int, vp, C.c_int, vp]),
+                               C.c_int, vp, vp, C.c_int, vp]),
     "b200dec_attention": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, f32,
                                     vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
     "b200dec_attention_scratch_floats": (i64, [C.c_int, C.c_int, C.c_int]),
@@ -115,7 +115,7 @@ PROTOTYPES = {
                                        C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp]),
     "b200dec_admit": (C.c_int, [C.POINTER(Plan), vp, C.c_int, vp, C.c_int, vp]),
     "b200dec_admit_record_ints": (C.c_int, [C.c_int]),
-    "b200dec_compact_active": (C.c_int, [C.POINTER(Plan), C.c_int, vp, C.c_int, vp]),
+    "b200dec_compact_active": (C.c_int, [C.POINTER(Plan), C.c_int, vp, vp, C.c_int, vp]),
     "b200dec_step": (C.c_int, [C.POINTER(Plan), C.c_int, vp]),
     "b200dec_step_rows": (C.c_int, [C.POINTER(Plan), C.c_int, C.c_int, vp]),
     "b200dec_step_launches": (C.c_int, [C.POINTER(Plan), C.c_int]),

@@ -341,6 +341,8 @@ class StreamDecoder:
                      "xh", "ln_stats", "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
         p.kv_prefetch_mb, p.exchange = int(self.kv_prefetch_mb), self.exchange
+        # pinned host memory is addressable from the device: the pick writes the end flags straight into `flags`
+        p.flags_host = self.flags.data_ptr()
         self.plan = p
 
     def _step(self, b: int) -> None:
@@ -364,10 +366,8 @@ class StreamDecoder:
                     done.record(side)
                     main.wait_event(done)
         if self.device_sched:  # rows that ended leave the device's active list; the host learns the live count
-            nv.check(nv.lib().b200dec_compact_active(C.byref(self.plan), b, nv.ptr(self.n_active), int(self.pdl) & 1,
-                                                     nv.stream_ptr()))
-            self.live.copy_(self.n_active, non_blocking=True)
-        self.flags.copy_(self.finished, non_blocking=True)
+            nv.check(nv.lib().b200dec_compact_active(C.byref(self.plan), b, nv.ptr(self.n_active), self.live.data_ptr(),
+                                                     int(self.pdl) & 1, nv.stream_ptr()))
 
     def launches(self, rows: int) -> int:
         """Kernels one step of `rows` rows launches (summed over its chains)."""
@@ -420,6 +420,7 @@ class StreamDecoder:
             for t, v in ((self.finished, 1), (self.pos, 0), (self.cross_len, 1), (self.active, self.dummy),
                          (self.status, 0), (self.attn_count, 0), (self.n_active, 0)):
                 t.fill_(v)
+        self.flags.fill_(1)  # the host's copy (the steps write it through; nothing is in flight at a reset)
 
     def check_status(self) -> None:
         """Synchronises the decoder stream and raises if a kernel met an index outside its tables (the kernels clamp

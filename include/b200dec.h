@@ -109,6 +109,10 @@ typedef struct b200dec_plan {
   uint8_t* finished;
   const int64_t* forced;
   int64_t* out;
+  uint8_t* flags_host;    /* NULL, or (slots + 1) bytes of pinned host memory as the device addresses it: the pick
+                             writes every row's end flag there as well, so the host reads the flags after the step's
+                             event without a device-to-host copy in the step (the reference's step ends with that copy,
+                             kernels/stream_decoder.py:199) */
   int32_t* status;        /* one word, B200DEC_ST_* bits */
   /* scratch owned by the caller */
   float* x;       /* (max rows, 1024) residual stream */
@@ -231,11 +235,12 @@ int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const floa
 /* q (n, k) int8 row-major (b200dec_quantize_rows) -> the 8 KB block layout of b200dec_head_umma, n*k bytes. */
 int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* stream);
 /* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and
- * finished slots change nothing. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
+ * finished slots change nothing. flags_host: NULL, or pinned host memory (device-addressable) that receives each
+ * row's end flag too. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
 int b200dec_pick(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows,
                  int dummy, int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
                  const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
-                 int pdl, void* stream);
+                 uint8_t* flags_host, int pdl, void* stream);
 /* One new token per row against its slot's cache. self != 0: q | k | v in qkv (rows, 3 * H * D) fp32, the new key and
  * value are written at n[s] and attended, keys 0..n[s]; else q (rows, H * D) over n[s] frames. Caches bf16
  * (slots + 1, H, cap, D). Replaces dec_attention (kernels/csrc/decoder_ops.cu:85-104, 235-261; dec_attn.cuh:84-188). */
@@ -338,10 +343,12 @@ int b200dec_admit(const b200dec_plan* plan, const int32_t* records, int n, int32
                   void* stream);
 int b200dec_admit_record_ints(int max_prompt);
 /* Tail of a step when the active list lives on the device: the rows of plan->active[0 .. rows) whose slot has not
- * ended move to the front in their order, the rest point at the dummy slot, *n_active = the live count. rows <= 128.
+ * ended move to the front in their order, the rest point at the dummy slot, *n_active = the live count (also written to
+ * live_host, pinned host memory as the device addresses it, when not NULL). rows <= 128.
  * With it a host never rebuilds the list on eviction (it reads the end flags and the count the step leaves in pinned
  * memory); the flag scan and compaction of the reference's decoder thread (kernels/pipeline.py:217-231) on the GPU. */
-int b200dec_compact_active(const b200dec_plan* plan, int rows, int32_t* n_active, int pdl, void* stream);
+int b200dec_compact_active(const b200dec_plan* plan, int rows, int32_t* n_active, int32_t* live_host, int pdl,
+                           void* stream);
 /* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
  * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
 int b200dec_step(const b200dec_plan* plan, int rows, void* stream);

@@ -761,10 +761,14 @@ def test_pick_semantics(nv):
     tok = torch.zeros(S + 1, dtype=torch.long, device="cuda")
     out = torch.full((S + 1, cols), -1, dtype=torch.long, device="cuda")
     arg = torch.full((S + 1,), -1, dtype=torch.long, device="cuda")
+    host_flags = torch.full((S + 1,), 9, dtype=torch.uint8).pin_memory()
     nv.check(nv.lib().b200dec_pick(nv.ptr(d["pm"]), nv.ptr(d["pi"]), np_, nv.ptr(d["active"]), 5, S, nv.ptr(tok),
                                    nv.ptr(d["pos"]), nv.ptr(d["fin"]), nv.ptr(d["forced"]), P, nv.ptr(d["plen"]),
-                                   nv.ptr(d["limit"]), nv.ptr(out), cols, 70, nv.ptr(arg), 0, nv.stream_ptr()))
+                                   nv.ptr(d["limit"]), nv.ptr(out), cols, 70, nv.ptr(arg), host_flags.data_ptr(), 0,
+                                   nv.stream_ptr()))
     torch.cuda.synchronize()
+    # the end flags also land in pinned host memory, written by the kernel itself (rows on real slots only)
+    assert host_flags.numpy().tolist() == [0, 1, 1, 1, 9, 9]
     tok, out, arg = tok.cpu().numpy(), out.cpu().numpy(), arg.cpu().numpy()
     pos2, fin2 = d["pos"].cpu().numpy(), d["fin"].cpu().numpy()
     assert (tok[0], pos2[0], fin2[0], out[0, 1], arg[0]) == (101, 1, 0, 101, 30)

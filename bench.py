@@ -457,7 +457,8 @@ def stream_workload(args, dev, rank: int, local: int, world: int, n_requests: in
     SLOTS = 128
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=SLOTS, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         int8=True, ffn_sparse=True, eos=-1, pdl=args.pdl, attn_ring=args.attn_ring,
-                        head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched)
+                        head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched,
+                        exchange=args.exchange)
     mine = dp.partition(synthetic_requests(n_requests, seed=0, slots=SLOTS * world, fill=args.fill), rank, world)
     # encoder memory in pinned host memory: 16 seeded N(0, 1) blocks of the longest length, a request takes the first
     # `frames` rows of one of them (the scheduler copies them to the device at admission); drawing every request's own

@@ -254,8 +254,9 @@ struct PickArgs {
   const int* limit;
   int64_t* out;
   int64_t* argmax;
-  uint8_t* flags_host;  // pinned host memory mapped into the device's address space, or null: the end flags, written
-                        // through (posted writes over the bus: the step waits for no copy)
+  uint8_t* flags_host;  // pinned host memory mapped into the device's address space, or null: a row that ends sets
+                        // its slot's byte there (one posted write over the bus per ending row: the step waits for
+                        // no copy); the host clears the byte when it admits into the slot
   int partials, rows, dummy, max_prompt, out_cols, eos;
 };
 
@@ -283,10 +284,7 @@ __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   if (lane != 0) return;
   if (arg == 0x7fffffff) arg = 0;  // a row of NaN
   if (p.argmax) p.argmax[s] = arg;
-  if (p.finished[s]) {  // ended at an earlier step: nothing moves until the host retires the slot
-    if (p.flags_host) p.flags_host[s] = 1;
-    return;
-  }
+  if (p.finished[s]) return;  // ended at an earlier step: nothing moves until the host retires the slot
   const int at = p.pos[s] + 1;
   const bool in_prompt = at < p.plen[s];
   const int64_t nt = in_prompt ? p.forced[(size_t)s * p.max_prompt + min(at, p.max_prompt - 1)] : (int64_t)arg;
@@ -295,7 +293,7 @@ __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   p.pos[s] = at;
   const uint8_t done = (!in_prompt && (nt == p.eos || at >= p.limit[s])) ? 1 : 0;
   p.finished[s] = done;
-  if (p.flags_host) p.flags_host[s] = done;
+  if (done && p.flags_host) p.flags_host[s] = 1;
 }
 
 // kv (nrows, L * 2 * H * D) fp32 -> bf16 caches (L, S1, H, T, D); one thread per 8 values

@@ -5,7 +5,7 @@ Drop-in for kernels/stream_decoder.py:65-276 of the reference: the same construc
 `set_active`, `step`, `reset`, `bucket`) with the same meaning, so the reference's Pipeline (kernels/pipeline.py) can
 drive it unchanged. Row r of a step works on slot active[r]; rows past the live ones point at the dummy slot; a step
 is one CUDA-graph launch per bucket of row counts; the prompt is fed by the steps themselves as forced tokens; the
-end flags are copied to pinned host memory by the graph.
+end flags land in pinned host memory, written through by the step's last kernel (no copy node in the graph).
 
 What differs underneath: every kernel is hand-written CUDA for sm_100a behind a C-ABI (include/b200dec.h), there is no
 Triton and no cuBLAS on the step; `int8=True` quantises every projection of the step (also o, cross q and cross o; the
@@ -203,7 +203,7 @@ class StreamDecoder:
             self.sched_cross = torch.zeros(bm, 4, **i32)
             self.logits = torch.zeros(bm, self.vocab, **f32) if record else None
             self.argmax = torch.zeros(S + 1, device=dev, dtype=torch.long) if record else None
-            # host side: the end flags after each step (pinned, copied by the step itself)
+            # host side: the end flags after each step (pinned, written by the step itself)
             self.flags = torch.ones(S + 1, dtype=torch.uint8).pin_memory()
             self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
             self.stream = torch.cuda.Stream(device=dev, priority=-1)
@@ -311,6 +311,19 @@ class StreamDecoder:
             raise ValueError(f"{path}: the packed weights do not match the manifest's SHA-256")
         return self
 
+    @classmethod
+    def from_checkpoint(cls, path: str, device: torch.device | str = "cuda", dtype: torch.dtype | None = None,
+                        **kw) -> "StreamDecoder":
+        """A decoder from a Cohere Transcribe checkpoint directory (config.json + *.safetensors, single or sharded):
+        only the decoder's tensors are read, the encoder is never built (checkpoint.load_decoder). The reference gets
+        the same weights by loading the whole model through transformers (server.py:264-267). dtype: convert the
+        stored floating-point tensors first (None: as stored). kw: the constructor's arguments."""
+        from .checkpoint import load_decoder
+        dev = torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        return cls(load_decoder(path, dtype).to(dev), **kw)
+
     # ---- the step ------------------------------------------------------------------------------------------------
 
     def _build_plan(self) -> None:
@@ -341,7 +354,8 @@ class StreamDecoder:
                      "xh", "ln_stats", "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
         p.kv_prefetch_mb, p.exchange = int(self.kv_prefetch_mb), self.exchange
-        # pinned host memory is addressable from the device: the pick writes the end flags straight into `flags`
+        # pinned host memory is addressable from the device: a row that ends sets its byte of `flags` from the pick
+        # kernel (admit() clears it on the host, as the reference does)
         p.flags_host = self.flags.data_ptr()
         self.plan = p
 

@@ -109,10 +109,11 @@ typedef struct b200dec_plan {
   uint8_t* finished;
   const int64_t* forced;
   int64_t* out;
-  uint8_t* flags_host;    /* NULL, or (slots + 1) bytes of pinned host memory as the device addresses it: the pick
-                             writes every row's end flag there as well, so the host reads the flags after the step's
-                             event without a device-to-host copy in the step (the reference's step ends with that copy,
-                             kernels/stream_decoder.py:199) */
+  uint8_t* flags_host;    /* NULL, or (slots + 1) bytes of pinned host memory as the device addresses it: a row that
+                             ends at a step sets its slot's byte there (the pick kernel, one posted write), so the host
+                             reads the flags after the step's event without a device-to-host copy in the step (the
+                             reference's step ends with that copy, kernels/stream_decoder.py:199); the host clears a
+                             slot's byte when it admits into it (kernels/stream_decoder.py:263) */
   int32_t* status;        /* one word, B200DEC_ST_* bits */
   /* scratch owned by the caller */
   float* x;       /* (max rows, 1024) residual stream */
@@ -235,8 +236,8 @@ int b200dec_head_umma_linked(const b200dec_weight* w, const void* xg, const floa
 /* q (n, k) int8 row-major (b200dec_quantize_rows) -> the 8 KB block layout of b200dec_head_umma, n*k bytes. */
 int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* stream);
 /* Greedy choice from the partials, prompt forcing, output row, position advance, end flag; rows on the dummy slot and
- * finished slots change nothing. flags_host: NULL, or pinned host memory (device-addressable) that receives each
- * row's end flag too. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
+ * finished slots change nothing. flags_host: NULL, or pinned host memory (device-addressable) in which a row that ends
+ * at this step sets its slot's byte. Replaces the bookkeeping of dec_pick (kernels/csrc/decoder_ops.cu:148-159, 304-314). */
 int b200dec_pick(const float* part_max, const int32_t* part_idx, int partials, const int32_t* active, int rows,
                  int dummy, int64_t* tok, int32_t* pos, uint8_t* finished, const int64_t* forced, int max_prompt,
                  const int32_t* plen, const int32_t* limit, int64_t* out, int out_cols, int eos, int64_t* argmax,
@@ -350,7 +351,7 @@ int b200dec_admit_record_ints(int max_prompt);
 int b200dec_compact_active(const b200dec_plan* plan, int rows, int32_t* n_active, int32_t* live_host, int pdl,
                            void* stream);
 /* The whole step for `rows` rows: embed, `layers` layers, head, pick. Replaces StreamDecoder._step
- * (kernels/stream_decoder.py:176-199) minus the D2H copy of the flags, which stays with the caller. */
+ * (kernels/stream_decoder.py:176-199); its D2H copy of the flags becomes plan->flags_host, or stays with the caller. */
 int b200dec_step(const b200dec_plan* plan, int rows, void* stream);
 /* The same for rows [row0, row0 + rows) of the step's batch only. Disjoint row ranges share no scratch, so a caller
  * may run several ranges concurrently on forked streams to overlap one range's attention (bound by HBM) with another's

@@ -380,3 +380,31 @@ def test_packed_weights_round_trip(tmp_path):
         StreamDecoder.from_packed(path, **run)
     with pytest.raises(ValueError, match="packed with"):  # tiled for buckets up to 4 rows, asked for up to 2
         StreamDecoder.from_packed(path, **dict(run, slots=2))
+
+
+@pytest.mark.parametrize("style,shards", [("original", 3), ("module", 1)])
+def test_decoder_from_a_checkpoint_directory(tmp_path, style, shards):
+    """StreamDecoder.from_checkpoint reads config.json + *.safetensors (the names a published checkpoint carries, or
+    the module names; one file or shards) and builds the same decoder as the module does: same digest of the packed
+    weights, same bits out of the step. The real model's shape: 8 heads of 128, ReLU, 1280-wide encoder frames."""
+    from cohere_inference_b200 import StreamDecoder
+    from test_checkpoint import original_names, write_checkpoint
+    model = synthetic_model(4, heads=8, head_dim=128, act="relu", layers=2, bias_std=0.05, dtype=torch.bfloat16)
+    torch.manual_seed(1)
+    model.model.decoder.proj = torch.nn.Linear(1280, 1024).to(torch.bfloat16).requires_grad_(False)
+    model.config.encoder_hidden_size = 1280
+    write_checkpoint(str(tmp_path), model, names=original_names() if style == "original" else None, shards=shards,
+                     encoder_hidden=1280)
+    rng = np.random.default_rng(8)
+    memory = [rng.standard_normal((n, 1280)).astype(np.float32) for n in (70, 33, 101)]
+    prompts = [rng.integers(0, 16384, 4).astype(np.int64) for _ in range(3)]
+    run = dict(slots=4, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, record=True, int8=True)
+    dec = _decoder(model, **run)
+    want, _ = _run_teacher_forced(dec, memory, prompts, 5)
+    digest = dec.weights_digest()
+    del dec
+    again = StreamDecoder.from_checkpoint(str(tmp_path), **run)
+    assert again.weights_digest() == digest
+    assert (again.h, again.d, again.proj.k) == (8, 128, 1280)
+    got, _ = _run_teacher_forced(again, memory, prompts, 5)
+    assert np.array_equal(got, want)

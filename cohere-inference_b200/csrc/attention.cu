@@ -641,6 +641,9 @@ extern "C" int b200dec_attention_static(int self, const int32_t* active, const f
   // the caller's stream first. A memset is not an allocation.
   e = cudaMemsetAsync(count, 0, (size_t)rows * heads * sizeof(int32_t), (cudaStream_t)stream);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "attention_static: clearing the counters: %s", cudaGetErrorString(e));
+  // The kernel's predecessor on the stream is the memset above, not a kernel: there is nothing to launch it
+  // programmatically after, so `pdl` is accepted for symmetry with b200dec_attention and not used.
+  (void)pdl;
   return b200dec_attention(self, active, q, ldq, kcache, vcache, n, slots, heads, head_dim, cap, scale, out, out_kind,
-                           rows, scratch, count, status, pdl, stream);
+                           rows, scratch, count, status, 0, stream);
 }

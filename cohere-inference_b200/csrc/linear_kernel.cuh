@@ -122,8 +122,18 @@ struct LinSmem {
 // slice's (a - c) and (a - c)^2, and the finishing CTA applies  y = rstd * (acc * scale - (mean - c) * g) + bias',
 // which equals LayerNorm(a) W^T + bias exactly (g and bias' are precomputed per output channel). NW warps = 16 NW
 // channels per CTA; KSLICE k-values per CTA, KSPLIT CTAs per cluster (K = KSLICE * KSPLIT); MB: row capacity.
+// CTAs per SM the register allocation must leave room for. The 2:4 fc2 at 65-128 rows is dealt as 8 x 16 x 4 = 512
+// CTAs of 32 rows: they only run as one wave with four per SM, i.e. at no more than 128 registers (the compiler sits at
+// 128-129 for that tile; the one register more cost a second wave, +3 us per launch, 5 % of a 128-row step). The dense
+// int8 tile of the same shape also serves fc2 at 33-64 rows (two CTAs of 32 rows per tile, one wave either way), where
+// holding it to 128 registers instead of its 140 measured 1.3 us slower per launch: it keeps its registers.
+template <int WT, int NW, int KSLICE, int MB>
+constexpr int linear_min_ctas() {
+  return (WT == B200DEC_W_INT8_24 && NW == 4 && KSLICE == 512 && MB == 32) ? 4 : 1;
+}
+
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
-__global__ void __launch_bounds__(NW * 32, 1) linear_kernel(const LinArgs p_in) {
+__global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()) linear_kernel(const LinArgs p_in) {
   __shared__ __align__(8) uint64_t xbar;  // counts the bytes this CTA is owed by its cluster (async_x)
   if (p_in.async_x && threadIdx.x == 0) xbar_init(&xbar);
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store

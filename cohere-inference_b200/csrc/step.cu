@@ -174,20 +174,25 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
                                                  : KvPrefetch{};
     B200_TRY_IN(2, linear_impl(&ly.qkv, ln_src, ln_kind, &ly.ln1, D_MODEL, rows, qkv, B200DEC_OUT_F32, 3 * hd,
                          B200DEC_ACT_NONE, pdl, stream, &r1, nullptr));
+    // The paired attention kernels read their two schedule entries before they wait for their predecessor, which is
+    // sound while a kernel sits between the one that builds the schedule (the embedding) and them. With the
+    // projections left out (classes) the first self-attention would follow the embedding directly and the two CTAs of
+    // a pair could see different versions of an entry and disagree on their hand-off: it is then launched plainly.
+    const int pdl_self = (i == 0 && !(want & 2)) ? 0 : pdl_attn;
     if (pl->kv_int8 && paired)
       B200_TRY_IN(4, b200dec_attention_paired_q8(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, ly.self_ks, ly.self_vs,
-                                           pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
+                                           pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, pdl_self, stream));
     else if (pl->kv_int8)
       B200_TRY_IN(4, b200dec_attention_q8(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, ly.self_ks, ly.self_vs, pl->pos,
                                     pl->slots, pl->heads, pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part,
-                                    attn_count, pl->status, pdl_attn, stream));
+                                    attn_count, pl->status, pdl_self, stream));
     else if (paired)
       B200_TRY_IN(4, b200dec_attention_paired(1, sched_self, qkv, 3 * hd, ly.self_k, ly.self_v, pl->heads, pl->head_dim,
-                                        pl->seq, scale, att, ok_a, rows, pdl_attn, stream));
+                                        pl->seq, scale, att, ok_a, rows, pdl_self, stream));
     else
       B200_TRY_IN(4, attention(1, active, qkv, 3 * hd, ly.self_k, ly.self_v, pl->pos, pl->slots, pl->heads,
                                  pl->head_dim, pl->seq, scale, att, ok_a, rows, attn_part, attn_count, pl->status,
-                                 pdl_attn, stream));
+                                 pdl_self, stream));
     B200_TRY_IN(2, linear_impl(&ly.o, att, pl->a_kind, nullptr, hd, rows, x, B200DEC_OUT_F32_ADD, D_MODEL, B200DEC_ACT_NONE,
                          pdl_after, stream, &p2, &f_cross));
     B200_TRY_IN(2, linear_impl(&ly.cq, ln_src, ln_kind, &ly.ln2, D_MODEL, rows, cq, B200DEC_OUT_F32, hd, B200DEC_ACT_NONE, pdl,

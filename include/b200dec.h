@@ -273,7 +273,10 @@ int b200dec_row_schedule(const int32_t* active, const int32_t* pos, const int32_
 /* b200dec_attention for a large batch (rows * heads >= 512 is where it pays), reading the rows from a schedule: the
  * i-th longest row and the i-th shortest share a cluster of two CTAs that read the same number of keys; the partial
  * of the long row's tail crosses distributed shared memory. Same results as b200dec_attention up to the order of the
- * softmax merge. sched: (rows, 4) int32 from b200dec_row_schedule, 16-byte aligned. */
+ * softmax merge. sched: (rows, 4) int32 from b200dec_row_schedule, 16-byte aligned. With pdl != 0 the kernel reads its
+ * schedule entries before it waits for its predecessor on the stream: the schedule must then be complete before that
+ * predecessor starts, i.e. at least one kernel must lie between the one that writes the schedule and this launch
+ * (the two CTAs of a pair must see the same entries); launch with pdl = 0 directly behind the schedule's writer. */
 int b200dec_attention_paired(int self, const int32_t* sched, const float* q, int ldq, void* kcache, void* vcache,
                              int heads, int head_dim, int cap, float scale, void* out, int out_kind, int rows,
                              int pdl, void* stream);
@@ -294,7 +297,9 @@ int b200dec_attention_ring(int self, const int32_t* active, const float* q, int 
  * with an error. The first call on each device looks the array's address up and should come before any stream
  * capture. The device that is current at the call must be the device of `stream`: the array's address is looked up
  * for the current device. All calls on a device share the array: two calls whose kernels overlap on the GPU
- * (different streams) race on it. Allocates nothing, frees nothing. */
+ * (different streams) race on it. `pdl` is accepted and not used: the call first clears its arrival counters with a
+ * memset on `stream`, so the kernel's predecessor is never a kernel. After the first call it may be captured into a
+ * CUDA graph (memset node + kernel node) and replayed. Allocates nothing, frees nothing. */
 int b200dec_attention_static(int self, const int32_t* active, const float* q, int ldq, void* kcache, void* vcache,
                              const int32_t* n, int slots, int heads, int head_dim, int cap, float scale, void* out,
                              int out_kind, int rows, int32_t* status, int pdl, void* stream);

@@ -244,6 +244,46 @@ def test_linear_linked_layernorm(nv, pk, kind, n, rows):
         np.testing.assert_allclose(out.cpu().numpy(), want.astype(np.float32), atol=4e-3, rtol=1e-4)
 
 
+@pytest.mark.parametrize("offset,atol", [(0.0, 4e-3), (8.0, 8e-3), (32.0, 3e-2)])
+@pytest.mark.parametrize("kind", ["W_INT8", "W_INT8_UMMA"])
+def test_linked_layernorm_error_grows_with_the_row_offset(nv, pk, offset, atol, kind):
+    """The int8 modes stage a row as fp16(row * gamma), unshifted, with plain fp32 sums for the statistics: a row
+    whose mean is `offset` standard deviations away from zero loses log2(offset) bits of its deviations to the fp16
+    rounding (and the variance E[x^2] - mean^2 loses 2 * log2(offset) of its 24). The bound that is documented, against
+    LayerNorm in float64: exact-mode error at offset 0, twice that at 8, under 3e-2 at 32 (outputs are O(1))."""
+    rng = np.random.default_rng(int(offset) + 5)
+    rows, k, n = 64, 1024, 3072
+    lib = nv.lib()
+    gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
+    g_d, b_d = cuda(gam), cuda(bet)
+    sign = np.where(rng.random((rows, 1)) < 0.5, -1.0, 1.0)
+    x = (rng.standard_normal((rows, k)) + offset * sign).astype(np.float32)
+    x_d = cuda(x)
+    x16 = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
+    sums = torch.zeros(rows, 2, device="cuda")
+    nv.check(lib.b200dec_ln_rows16(nv.ptr(x_d), nv.ptr(g_d), rows, nv.ptr(x16), nv.ptr(sums), nv.stream_ptr()))
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    b = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    if kind == "W_INT8_UMMA":
+        pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA, ln=(g_d, b_d))
+    else:
+        pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8, a_kind=nv.A_F16, ln=(g_d, b_d), max_rows=rows)
+    norm, cs = nv.norm(g_d, b_d, 1e-5), pc.struct()
+    out = torch.zeros(rows, n, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rlink = nv.LnLink(None, None, None, nv.ptr(sums), 1, 0, nv.ptr(status))
+    nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(x16), nv.A_F16_ROWS16, C.byref(norm), k, rows, nv.ptr(out),
+                                       nv.OUT_F32, n, nv.ACT_NONE, C.byref(rlink), 0, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    wd = pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy().astype(np.float64)
+    x64 = x.astype(np.float64)
+    ln = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * gam + bet
+    want = ln @ wd.T + b
+    err = np.abs(out.cpu().numpy() - want).max()
+    assert int(status.item()) == 0 and err <= atol, err
+
+
 @pytest.mark.parametrize("n,act,out_kind", [(3072, "ACT_NONE", "OUT_F32"), (4096, "ACT_GELU", "OUT_F16"),
                                             (1024, "ACT_RELU", "OUT_F32")])
 @pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])

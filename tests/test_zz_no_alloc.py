@@ -68,3 +68,47 @@ def test_static_workspace_refuses_sizes_beyond_its_capacity():
                                       0.125, nv.ptr(out), nv.OUT_F32, 64, nv.ptr(status), 0, nv.stream_ptr())
     assert rc == 1 and b"exceeds the built-in workspace" in lib.b200dec_last_error()
     torch.cuda.synchronize()
+
+
+def test_static_call_captured_into_a_graph_and_replayed():
+    """After its first (set-up) call the entry point is two stream operations, a memset of the arrival counters and the
+    kernel: captured into a CUDA graph with the programmatic-launch flag set (which the entry point ignores, its
+    kernel follows a memset) and replayed twice on changed inputs, it gives the regular entry point's bits each time."""
+    from cohere_inference_b200 import native as nv
+    lib = nv.lib()
+    H, D, self_, rows, S, cap = 16, 64, 1, 5, 8, 300
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc, vc, active, n, q = _inputs(200, rows, H, D, S, cap, self_)
+    ld = q.shape[1]
+    out = torch.zeros(rows, H * D, device="cuda")
+    k2, v2 = kc.clone(), vc.clone()
+
+    def static_call():
+        nv.check(lib.b200dec_attention_static(self_, nv.ptr(active), nv.ptr(q), ld, nv.ptr(k2), nv.ptr(v2), nv.ptr(n), S, H,
+                                              D, cap, D ** -0.5, nv.ptr(out), nv.OUT_F32, rows, nv.ptr(status), 1,
+                                              nv.stream_ptr()))
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        static_call()  # the set-up call: looks the array's address up, outside any capture
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        static_call()
+    for replay in range(2):
+        kc_r, vc_r, active_r, n_r, q_r = _inputs(300 + replay, rows, H, D, S, cap, self_)
+        for dst, src in ((k2, kc_r), (v2, vc_r), (active, active_r), (n, n_r), (q, q_r)):
+            dst.copy_(src)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        k3, v3 = kc_r.clone(), vc_r.clone()
+        want = torch.zeros(rows, H * D, device="cuda")
+        part = torch.zeros(lib.b200dec_attention_scratch_floats(rows, H, D), device="cuda")
+        count = torch.zeros(rows * H, dtype=torch.int32, device="cuda")
+        nv.check(lib.b200dec_attention(self_, nv.ptr(active_r), nv.ptr(q_r), ld, nv.ptr(k3), nv.ptr(v3), nv.ptr(n_r), S, H,
+                                       D, cap, D ** -0.5, nv.ptr(want), nv.OUT_F32, rows, nv.ptr(part), nv.ptr(count),
+                                       nv.ptr(status), 0, nv.stream_ptr()))
+        torch.cuda.synchronize()
+        assert torch.equal(out, want) and torch.equal(k2, k3) and torch.equal(v2, v3)
+        assert float(out.abs().max()) > 0
+    assert int(status.item()) == 0

@@ -5,7 +5,7 @@ Drop-in for kernels/stream_decoder.py:65-276 of the reference: the same construc
 `set_active`, `step`, `reset`, `bucket`) with the same meaning, so the reference's Pipeline (kernels/pipeline.py) can
 drive it unchanged. Row r of a step works on slot active[r]; rows past the live ones point at the dummy slot; a step
 is one CUDA-graph launch per bucket of row counts; the prompt is fed by the steps themselves as forced tokens; the
-end flags land in pinned host memory, written through by the step's last kernel (no copy node in the graph).
+a row that ends sets its flag in pinned host memory from the step's last kernel (no copy node in the graph).
 
 What differs underneath: every kernel is hand-written CUDA for sm_100a behind a C-ABI (include/b200dec.h), there is no
 Triton and no cuBLAS on the step; `int8=True` quantises every projection of the step (also o, cross q and cross o; the
@@ -360,7 +360,8 @@ class StreamDecoder:
         self.plan = p
 
     def _step(self, b: int) -> None:
-        """Bucket b's kernels and the flags' copy on the current stream (reference: _step, stream_decoder.py:176-199)."""
+        """Bucket b's kernels on the current stream (reference: _step, stream_decoder.py:176-199; the end flags reach
+        `flags` from the pick kernel)."""
         ranges = self.row_ranges(b)
         if len(ranges) == 1:
             nv.check(nv.lib().b200dec_step(C.byref(self.plan), b, nv.stream_ptr()))

@@ -134,8 +134,13 @@ constexpr int linear_min_ctas() {
 
 template <int WT, bool SPLIT, int LN, int NW, int KSLICE, int KSPLIT, int MB>
 __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()) linear_kernel(const LinArgs p_in) {
-  __shared__ __align__(8) uint64_t xbar;  // counts the bytes this CTA is owed by its cluster (async_x)
-  if (p_in.async_x && threadIdx.x == 0) xbar_init(&xbar);
+  // How the cluster's partial results travel. st.async onto an mbarrier of the owning CTA pays while a CTA is owed few
+  // values (each one also updates that mbarrier): measured at rows x 16 NW = 2048 values per CTA -0.2 to -0.4 us per
+  // launch against stores + a cluster barrier, at 16384 (the 2:4 fc1 at 128 rows) +1.2 us. The choice is a property
+  // of the tile, so only one of the two paths is compiled into a kernel.
+  constexpr bool ASYNC_X = MB * NW <= 256;
+  __shared__ __align__(8) uint64_t xbar;  // counts the bytes this CTA is owed by its cluster (ASYNC_X)
+  if (ASYNC_X && threadIdx.x == 0) xbar_init(&xbar);
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   LinArgs p = p_in;
   if (gridDim.z > 1) {  // the rows are dealt over blockIdx.z, MB each (fp16 operands only)
@@ -147,10 +152,6 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
     if (p.stats_in) p.stats_in += (size_t)row0 * p.stats_slots * 2;
     p.rows = p.rows - row0 < MB ? p.rows - row0 : MB;
   }
-  // st.async pays while a CTA is owed few values (each one also updates the owner's mbarrier): measured at
-  // rows x 16 NW = 2048 values per CTA -0.2 to -0.4 us per launch against stores + barrier, at 16384 (the 2:4 fc1 at
-  // 128 rows) +1.2 us. Every CTA of a cluster has the same rows, so they agree.
-  p.async_x = p.async_x && p.rows * NW <= 256;
   using T = WTraits<WT>;
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
@@ -206,7 +207,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
     }
   }
   pdl_wait();
-  if (p.async_x && tid == 0)  // partial tiles from every CTA of the cluster (this one included) and the rows' sums
+  if (ASYNC_X && tid == 0)  // partial tiles from every CTA of the cluster (this one included) and the rows' sums
     xbar_expect(&xbar, (uint32_t)(KSPLIT * p.rows * CPR * 4 + (LN == 2 ? p.rows * 8 : LN == 1 ? KSPLIT * p.rows * 8 : 0)));
   if (p.pf.sched)
     kv_prefetch_issue(p.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
@@ -246,7 +247,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
         float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
         s1 = warp_sum(s1), s2 = warp_sum(s2);
         if (r < p.rows && lane < KSPLIT) {
-          if (p.async_x)
+          if constexpr (ASYNC_X)
             st_async_f32x2(map_to_rank(smem_addr_u32(stats + r), lane), make_float2(s1, s2),
                            map_to_rank(smem_addr_u32(&xbar), lane));
           else
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
       for (int it = 0; it < RPG; ++it) {
         const int r = (tid >> 3) + it * (NT / 8);
         if (r < p.rows && l8 < KSPLIT) {
-          if (p.async_x)
+          if constexpr (ASYNC_X)
             st_async_f32x2(map_to_rank(smem_addr_u32(stats + rank * MB + r), l8), make_float2(s1[it], s2[it]),
                            map_to_rank(smem_addr_u32(&xbar), l8));
           else
@@ -425,7 +426,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
   if constexpr (LN == 0) cluster_wait_entry();  // with a LayerNorm the statistics were the first remote stores
   {
     const int ch0 = warp * 16 + g, ch1 = ch0 + 8;
-    if (p.async_x) {
+    if constexpr (ASYNC_X) {
       const uint32_t d0 = map_to_rank(smem_addr_u32(recv + rank * MB * CPR + ch0 % CPR), ch0 / CPR);
       const uint32_t d1 = map_to_rank(smem_addr_u32(recv + rank * MB * CPR + ch1 % CPR), ch1 / CPR);
       const uint32_t b0 = map_to_rank(smem_addr_u32(&xbar), ch0 / CPR), b1 = map_to_rank(smem_addr_u32(&xbar), ch1 / CPR);
@@ -473,7 +474,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
       lb_pre = __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine));
     }
   }
-  if (p.async_x) {  // everything this CTA is owed has landed (nobody writes to it afterwards: it may leave)
+  if constexpr (ASYNC_X) {  // everything this CTA is owed has landed (nobody writes to it afterwards: it may leave)
     if (!xbar_wait(&xbar, 1u << 22) && lane == 0 && p.status) atomicOr(p.status, B200DEC_ST_TIMEOUT);
   } else {
     cluster.sync();  // all partials (and slice statistics) have landed; nobody touches remote shared memory after this

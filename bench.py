@@ -139,8 +139,7 @@ def run_ours(args) -> None:
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
                         int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
                         head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8,
-                        proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch,
-                        exchange=args.exchange)
+                        proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch)
     digest = dec.weights_digest()
     dp.check_identical(digest, dev)  # replicas: the same packed bits on every GPU, before anything is timed
     lens, memory_host, prompts = make_inputs(1000 + rank)
@@ -482,8 +481,7 @@ def stream_workload(args, dev, rank: int, local: int, world: int, n_requests: in
     SLOTS = 128
     dec = StreamDecoder(synthetic_model(0).to(dev), slots=SLOTS, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0,
                         int8=True, ffn_sparse=True, eos=-1, pdl=args.pdl, attn_ring=args.attn_ring,
-                        head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched,
-                        exchange=args.exchange)
+                        head_umma=not args.no_head_umma, kv_prefetch_mb=args.kv_prefetch, device_sched=args.device_sched)
     mine = dp.partition(synthetic_requests(n_requests, seed=0, slots=SLOTS * world, fill=args.fill), rank, world)
     # encoder memory in pinned host memory: 16 seeded N(0, 1) blocks of the longest length, a request takes the first
     # `frames` rows of one of them (the scheduler copies them to the device at admission); drawing every request's own
@@ -626,8 +624,6 @@ def main() -> None:
                     "(what the default invocation starts as a child process)")
     ap.add_argument("--kv-prefetch", type=int, default=KV_PREFETCH_MB, help="MB of an attention launch's keys and values "
                     "that the projections before it start towards L2 (0: off)")
-    ap.add_argument("--exchange", type=int, default=1, help="how a cluster's CTAs hand over partial results: 0 stores + "
-                    "cluster barrier, 1 st.async onto per-CTA mbarriers")
     ap.add_argument("--device-sched", action="store_true", help="stream workloads: the active list lives on the device")
     args = ap.parse_args()
     # stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 themselves (NCCL's

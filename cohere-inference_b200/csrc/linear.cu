@@ -168,7 +168,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   if (lnorm) p.ln_w = ln->w, p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
   p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.out_kind = out_kind, p.act = act, p.head = head;
   if (pf) p.pf = *pf;
-  p.async_x = lk.exchange == 1 && lk.status != nullptr, p.status = lk.status;
+  p.status = lk.status;
   cudaStream_t s = (cudaStream_t)stream;
   switch (w->kind) {
     case B200DEC_W_INT8: return launch_int8(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);

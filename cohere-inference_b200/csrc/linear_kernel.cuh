@@ -35,8 +35,7 @@ struct LinArgs {
   float ln_eps;
   int lda, ldo, rows, N, out_kind, act, head;
   KvPrefetch pf;  // keys and values of the next attention launch to start on their way into L2 (sched null: none)
-  int async_x;    // the cluster's partial results travel by st.async onto per-CTA mbarriers (else stores + barrier)
-  int* status;    // async_x: receives B200DEC_ST_TIMEOUT if the bounded wait for the partials runs out
+  int* status;    // or null: receives B200DEC_ST_TIMEOUT if the bounded wait for the cluster's partial results runs out
 };
 
 template <int WT>

@@ -125,13 +125,13 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
   const bool head_linked = xh && pl->head.kind == B200DEC_W_INT8_UMMA && pl->head.ln_g && pl->head.ln_bias;
   auto producer = [&](const float* gamma) {
     b200dec_ln_link l{};
-    l.status = pl->status, l.wait_limit = pl->wait_limit, l.withhold = (pl->withhold >> 1) & 1, l.exchange = pl->exchange;
+    l.status = pl->status, l.wait_limit = pl->wait_limit, l.withhold = (pl->withhold >> 1) & 1;
     if (xh && gamma) l.next_gamma = gamma, l.out16 = xh, l.stats_out = stats;
     return l;
   };
   auto reader = [&](int slots) {
     b200dec_ln_link l{};
-    l.status = pl->status, l.wait_limit = pl->wait_limit, l.withhold = (pl->withhold >> 1) & 1, l.exchange = pl->exchange;
+    l.status = pl->status, l.wait_limit = pl->wait_limit, l.withhold = (pl->withhold >> 1) & 1;
     if (xh) l.stats_in = stats, l.stats_slots = slots;
     return l;
   };

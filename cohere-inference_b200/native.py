@@ -34,7 +34,7 @@ class Norm(C.Structure):
 
 class LnLink(C.Structure):
     _fields_ = [("next_gamma", vp), ("out16", vp), ("stats_out", vp), ("stats_in", vp), ("stats_slots", i32),
-                ("wait_limit", i32), ("status", vp), ("withhold", i32), ("exchange", i32)]
+                ("wait_limit", i32), ("status", vp), ("withhold", i32)]
 
 
 class Layer(C.Structure):
@@ -48,7 +48,7 @@ class Plan(C.Structure):
                 ("slots", i32), ("seq", i32), ("frames", i32), ("vocab", i32),
                 ("max_prompt", i32), ("out_cols", i32), ("pad", i32), ("eos", i32),
                 ("a_kind", i32), ("max_pos", i32), ("head_a_kind", i32), ("pdl", i32), ("attn_ring", i32), ("kv_int8", i32),
-                ("kv_prefetch_mb", i32), ("wait_limit", i32), ("withhold", i32), ("exchange", i32), ("_pad1", i32), ("classes", i32),
+                ("kv_prefetch_mb", i32), ("wait_limit", i32), ("withhold", i32), ("classes", i32),
                 ("embed", vp), ("pos_table", vp), ("emb_ln", Norm), ("final_ln", Norm), ("layer", C.POINTER(Layer)),
                 ("head", Weight),
                 ("active", vp), ("tok", vp), ("pos", vp), ("plen", vp), ("limit", vp), ("cross_len", vp),

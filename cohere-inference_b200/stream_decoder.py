@@ -87,7 +87,7 @@ class StreamDecoder:
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
                  head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True,
-                 kv_prefetch_mb: int = 0, device_sched: bool = False, exchange: int = 1,
+                 kv_prefetch_mb: int = 0, device_sched: bool = False,
                  _packed: tuple | None = None):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
@@ -103,9 +103,7 @@ class StreamDecoder:
         kv_prefetch_mb: the projections between two attention launches start up to this many MB of the next launch's
         keys and values on their way into L2 (0: off). device_sched: the active list lives on the device: `admit`
         appends to it, every step drops the rows that ended and leaves the live count in `live` (pinned), so a
-        scheduler never calls set_active after an eviction. exchange: how the CTAs of a projection's cluster hand
-        over their partial results: 1 (default) st.async onto an mbarrier of the owning CTA, which waits only for what
-        it is owed; 0 plain stores and one barrier over the cluster (4 % slower on the benchmark step)."""
+        scheduler never calls set_active after an eviction."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
         cfg = model.config
@@ -121,7 +119,7 @@ class StreamDecoder:
         self.scale = self.d ** -0.5
         self.int8, self.ffn_sparse, self.pdl, self.use_graphs = int8, ffn_sparse, pdl, graphs
         self.attn_ring = bool(attn_ring)
-        self.kv_prefetch_mb, self.device_sched, self.exchange = int(kv_prefetch_mb), bool(device_sched), int(exchange)
+        self.kv_prefetch_mb, self.device_sched = int(kv_prefetch_mb), bool(device_sched)
         assert not (self.device_sched and chains > 1), "the device-side active list goes with a single chain"
         self.act, self._act_name, self._cfg_eos = ACTS[cfg.hidden_act], cfg.hidden_act, cfg.eos_token_id
         kind = nv.W_INT8 if int8 else nv.W_BF16
@@ -353,7 +351,7 @@ class StreamDecoder:
                      "qkv", "cq", "att", "mid", "attn_part", "attn_count", "head_max", "head_idx",
                      "xh", "ln_stats", "sched_self", "sched_cross", "logits", "argmax"):
             setattr(p, name, nv.ptr(getattr(self, name)))
-        p.kv_prefetch_mb, p.exchange = int(self.kv_prefetch_mb), self.exchange
+        p.kv_prefetch_mb = int(self.kv_prefetch_mb)
         # pinned host memory is addressable from the device: a row that ends sets its byte of `flags` from the pick
         # kernel (admit() clears it on the host, as the reference does)
         p.flags_host = self.flags.data_ptr()

@@ -90,7 +90,6 @@ typedef struct b200dec_plan {
                                                 (the projections leave HBM idle; L2 holds 126 MB); 0: off */
   int32_t wait_limit, withhold;              /* as in b200dec_ln_link, for the step's tcgen05 kernels; withhold bit 0
                                                 the vocabulary projection, bit 1 the layer projections (tests only) */
-  int32_t exchange, _pad1;                   /* as b200dec_ln_link.exchange, for the step's projections */
   int32_t classes;                           /* 0: the whole step. Else only these kernels are launched (a timing aid:
                                                 the results are then meaningless): 1 embedding + vocabulary projection
                                                 + pick, 2 the layer projections, 4 the attention kernels */
@@ -198,12 +197,11 @@ typedef struct b200dec_ln_link {
   int32_t stats_slots;
   int32_t wait_limit; /* B200DEC_W_INT8_UMMA: polls before the wait for the MMAs gives up; 0 = the default (2^22) */
   int32_t* status;  /* required with a B200DEC_W_INT8_UMMA weight (reader, producer or neither): the status word
-                       that receives B200DEC_ST_TIMEOUT if the bounded wait for the MMAs ran out */
+                       that receives B200DEC_ST_TIMEOUT if the bounded wait for the MMAs ran out; the mma.sync kinds
+                       report there if the bounded wait for their cluster's partial results ran out (tiles that
+                       exchange them by st.async) */
   int32_t withhold; /* tests only, B200DEC_W_INT8_UMMA: nonzero leaves out the MMAs' completion signal, so the wait
                        runs out, the status word gets B200DEC_ST_TIMEOUT and the kernel returns; 0 in production */
-  int32_t exchange; /* how the CTAs of a cluster hand over their partial results (mma.sync kinds): 0 = stores into
-                       the owner's shared memory + one cluster barrier; 1 = st.async onto an mbarrier of the owner,
-                       which waits (bounded, status = the time-out word) only for what it is owed */
 } b200dec_ln_link;
 int b200dec_linear_linked(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                           void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int pdl,

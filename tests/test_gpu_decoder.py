@@ -84,8 +84,7 @@ def test_config1_bf16_against_transformers_golden(model16, golden_dir):
                                      ("int8_kv8", dict(int8=True, kv_int8=True)),
                                      ("int8_umma_all", dict(int8=True, proj_umma="all")),
                                      ("int8_no_umma", dict(int8=True, proj_umma=False)),
-                                     ("int8_barrier_exchange", dict(int8=True, exchange=0)),
-                                     ("int8_24_barrier_exchange", dict(int8=True, ffn_sparse=True, exchange=0, proj_umma=False))])
+                                     ("int8_24_no_umma", dict(int8=True, ffn_sparse=True, proj_umma=False))])
 def test_ragged_batch_logits_and_greedy_agreement(model16, state16, mode, kw):
     """Five rows with different prompts, prompt lengths and encoder lengths (50..375), 40 steps, the padding rows of
     bucket 8 on the dummy slot; the oracle runs the weights the mode stores (and, for int8 caches, quantises its keys

@@ -287,6 +287,32 @@ def run_ours(args) -> None:
     attn_us = ks.elapsed_time(ke) * 1e3 / (reps * L)
     attn_gbs = kv_bytes / (attn_us / 1e6) / 1e9
 
+    # ---- the same launch with nothing but its loads (b200dec_read_probe): one CTA per (row, head) as above, each reading
+    # its share of the launch's bytes from the cross caches, six disjoint regions in turn (333 MB > L2), replayed from a
+    # graph with the same launch attribute. What a launch of this size can read at all: ramp-up and tail included.
+    items = BATCH * dec.h
+    per_cta = (kv_bytes // items) // 16 * 16
+    region = -(-items * per_cta // (1 << 20)) + 4 << 20  # bytes between the starts of two regions
+    flat = dec.cross_k.view(torch.uint8).reshape(-1)
+    n_regions = min(6, (flat.numel() - items * per_cta) // region + 1)
+    bare_us = None
+    if n_regions >= 3:
+        def probe_launches():
+            for i in range(reps * L):
+                nv.check(lib.b200dec_read_probe(flat.data_ptr() + (i % n_regions) * region, items, per_cta, None,
+                                                1 if args.pdl & 2 else 0, nv.stream_ptr(dec.stream)))
+        probe_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(dec.stream):
+            probe_launches()
+            with torch.cuda.graph(probe_graph, stream=dec.stream):
+                probe_launches()
+            probe_graph.replay()
+            ks.record(dec.stream)
+            probe_graph.replay()
+            ke.record(dec.stream)
+        dec.stream.synchronize()
+        bare_us = ks.elapsed_time(ke) * 1e3 / (reps * L)
+
     # ---- end to end through the public API, host buffers
     for _ in range(min(args.warmup, 2)):
         e2e_pass()
@@ -376,6 +402,13 @@ def run_ours(args) -> None:
                          "step": {"bytes_per_step_mean": int(total_bytes / steps_per_pass),
                                   "achieved": round(step_gbs, 1), "frac": round(step_gbs / peak, 4),
                                   "frac_of_8TBs": round(step_gbs / 8000, 4)},
+                         # a launch of the same grid that only loads the same number of bytes (b200dec_read_probe):
+                         # the kernel's time against it says how much of the distance to `peak` is the size of the
+                         # launch (ramp-up and tail of 55 MB) rather than the kernel
+                         "bare_read": None if bare_us is None else {
+                             "us_per_launch": round(bare_us, 2), "achieved": round(items * per_cta / (bare_us / 1e6) / 1e9, 1),
+                             "unit": "GB/s", "bytes_per_launch": items * per_cta,
+                             "kernel_time_over_bare_read": round(attn_us / bare_us, 3)},
                          "classes": classes},
             "stream": stream or None,
             "cpu_baseline": cpu,

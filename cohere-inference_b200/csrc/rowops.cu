@@ -296,6 +296,33 @@ __global__ void __launch_bounds__(128) pick_kernel(const PickArgs p) {
   if (done && p.flags_host) p.flags_host[s] = 1;
 }
 
+// A measurement aid, not a step of the decoder: every CTA reads its own contiguous run of `chunk16` 16-byte pieces with
+// the attention kernels' loads (streaming, 8 in flight per thread) and does nothing else. What it reaches is the
+// speed a launch of that grid and that many bytes can read at all, ramp-up and tail included.
+struct ProbeArgs {
+  const uint4* src;
+  size_t chunk16;
+  uint32_t* sink;
+};
+
+__global__ void __launch_bounds__(128) read_probe_kernel(const ProbeArgs a) {
+  constexpr int U = 8;
+  pdl_wait();
+  const uint4* p = a.src + (size_t)blockIdx.x * a.chunk16;
+  const size_t chunk16 = a.chunk16;
+  uint32_t* sink = a.sink;
+  uint32_t acc = 0;
+  for (size_t i = threadIdx.x; i < chunk16; i += 128 * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = i + u * 128 < chunk16 ? ld_stream16(p + i + u * 128) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc += (v[u].x ^ v[u].y) + (v[u].z ^ v[u].w);
+  }
+  pdl_trigger();
+  if (acc == 0x9e3779b9u && sink) *sink = acc;  // keeps the loads alive; practically never taken
+}
+
 // kv (nrows, L * 2 * H * D) fp32 -> bf16 caches (L, S1, H, T, D); one thread per 8 values
 __global__ void scatter_kv_kernel(const float* __restrict__ kv, const int* __restrict__ slot_of,
                                   const int* __restrict__ frame_of, __nv_bfloat16* ck, __nv_bfloat16* cv, int nrows,
@@ -544,6 +571,16 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
       kv, slot_of, frame_of, (__nv_bfloat16*)ck, (__nv_bfloat16*)cv, nrows, layers, slots_plus_1, heads, head_dim,
       frames);
   return check_launch("scatter_kv");
+}
+
+int b200dec_read_probe(const void* src, int ctas, int64_t bytes_per_cta, int32_t* sink, int pdl, void* stream) {
+  B200_REQUIRE(src && ((uintptr_t)src & 15) == 0, "read_probe: src must be 16-byte aligned");
+  B200_REQUIRE(ctas >= 1 && ctas <= 65535 * 16 && bytes_per_cta >= 16 && bytes_per_cta % 16 == 0,
+               "read_probe: ctas %d, bytes_per_cta %lld (a multiple of 16)", ctas, (long long)bytes_per_cta);
+  const ProbeArgs a{reinterpret_cast<const uint4*>(src), (size_t)(bytes_per_cta / 16), reinterpret_cast<uint32_t*>(sink)};
+  const cudaError_t e = launch_kernel(read_probe_kernel, dim3(ctas), dim3(128), 0, (cudaStream_t)stream, 0, pdl != 0, a);
+  if (e != cudaSuccess) return fail(B200DEC_ECUDA, "read_probe launch: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,

@@ -98,6 +98,7 @@ PROTOTYPES = {
                                        f32, vp, C.c_int, C.c_int, vp, vp, vp, C.c_int, vp]),
     "b200dec_attention_paired_q8": (C.c_int, [C.c_int, vp, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, f32, vp,
                                               C.c_int, C.c_int, C.c_int, vp]),
+    "b200dec_read_probe": (C.c_int, [vp, C.c_int, C.c_int64, vp, C.c_int, vp]),
     "b200dec_scatter_kv_q8": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                         vp]),
     "b200dec_row_schedule": (C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]),

@@ -311,6 +311,13 @@ int b200dec_scatter_kv(const float* kv, const int32_t* slot_of, const int32_t* f
 int b200dec_scatter_kv_q8(const float* kv, const int32_t* slot_of, const int32_t* frame_of, void* ck, void* cv,
                           float* ck_scale, float* cv_scale, int nrows, int layers, int slots_plus_1, int heads,
                           int head_dim, int frames, void* stream);
+/* A measurement aid, no counterpart in the reference and not a step of the decoder: `ctas` CTAs of 128 threads each
+ * read `bytes_per_cta` contiguous bytes of src (CTA c from src + c * bytes_per_cta) with the attention kernels' loads
+ * (16 bytes per thread, streaming, 8 in flight) and do nothing else. The time of such a launch is what a kernel of
+ * that grid and that many bytes can read at all, ramp-up and tail included; bench.py reports the attention kernel
+ * against it. src: 16-byte aligned, at least ctas * bytes_per_cta bytes; sink: NULL or one word (never written in
+ * practice). */
+int b200dec_read_probe(const void* src, int ctas, int64_t bytes_per_cta, int32_t* sink, int pdl, void* stream);
 /* ---- cross-attention prefill (fill_cross) on the tcgen05 tensor cores ----------------------------------------------
  * C(m, n) = A(m, k) W(n, k)^T + bias with fp32 rows A (used as two bf16 halves, about 16 bits of mantissa), bf16
  * weights and fp32 accumulation; the result goes (mode 0) into the operand image of the next product, or (modes 1, 2)

@@ -932,3 +932,24 @@ def test_prefill_gemm_cache_epilogue(nv, H, D, q8):
         assert (cache.float().cpu().numpy().transpose(0, 2, 1, 3, 4)[:, :, ~touched] == 7).all()
     if q8:
         assert (cks.cpu().numpy().transpose(0, 2, 1, 3)[:, :, ~touched] == -1).all()
+
+
+def test_read_probe_launches_and_checks_its_arguments(nv):
+    """The measurement aid b200dec_read_probe: a launch that only reads; it must accept a graph capture, leave its sink
+    alone and refuse sizes that are not whole 16-byte pieces."""
+    lib = nv.lib()
+    src = torch.arange(1 << 22, dtype=torch.int32, device="cuda")  # 16 MB
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for pdl in (0, 1):
+        nv.check(lib.b200dec_read_probe(nv.ptr(src), 256, 65536, nv.ptr(sink), pdl, nv.stream_ptr()))
+    torch.cuda.synchronize()
+    assert int(sink.item()) == 0
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        nv.check(lib.b200dec_read_probe(nv.ptr(src), 1024, 16384, None, 0, nv.stream_ptr(side)))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert lib.b200dec_read_probe(nv.ptr(src), 256, 65530, None, 0, nv.stream_ptr()) != 0
+    assert lib.b200dec_read_probe(None, 256, 65536, None, 0, nv.stream_ptr()) != 0
+    assert b"read_probe" in lib.b200dec_last_error()

@@ -55,6 +55,25 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
   constexpr int NG = NTHREADS / LPK;   // key groups per CTA
   constexpr int U = 4;                 // keys in flight per group
   const int tid = threadIdx.x, grp = tid / LPK, gl = tid % LPK;
+  const size_t base = ((size_t)s * p.H + h) * p.cap * D + gl * 8;
+  const __nv_bfloat16* kb = p.k + base;
+  const __nv_bfloat16* vb = p.v + base;
+  // whole-warp trip count: every lane runs the same number of iterations (shuffles), invalid keys are masked
+  const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
+  const int jg = grp % (32 / LPK);
+  uint4 kk[U], vv[U];
+  auto fetch = [&](int j0) {  // this group's U keys and values of the block of NG * U keys at j0
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int jj = j0 + jg + u * NG;
+      const bool ok = jj < end;
+      kk[u] = ok ? ld_stream16(kb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+      vv[u] = ok ? ld_stream16(vb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  // The first block's loads go out before anything waits for the query: they depend on the schedule only, and the
+  // query's round trip to L2 would otherwise stand in front of the first bytes from HBM.
+  if (first < end) fetch(first);
 
   // the query, pre-scaled so that scores are in log2 units
   float q[8];
@@ -64,7 +83,6 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
     q[0] = a.x * p.scale_log2, q[1] = a.y * p.scale_log2, q[2] = a.z * p.scale_log2, q[3] = a.w * p.scale_log2;
     q[4] = b.x * p.scale_log2, q[5] = b.y * p.scale_log2, q[6] = b.z * p.scale_log2, q[7] = b.w * p.scale_log2;
   }
-  const size_t base = ((size_t)s * p.H + h) * p.cap * D + gl * 8;
   float m = -1e30f, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -102,20 +120,9 @@ DEVI void attend_range(const AttnArgs& p, int r, int s, int h, int n, int start,
   }
 
   // cached keys [start, end), group g taking start + g, + NG, ...
-  const __nv_bfloat16* kb = p.k + base;
-  const __nv_bfloat16* vb = p.v + base;
-  // whole-warp trip count: every lane runs the same number of iterations (shuffles), invalid keys are masked
-  const int first = start + (tid >> 5) * (32 / LPK);  // first key of this warp's group 0
   for (int j0 = first; j0 < end; j0 += NG * U) {
-    const int j = j0 + (grp % (32 / LPK));
-    uint4 kk[U], vv[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int jj = j + u * NG;
-      const bool ok = jj < end;
-      kk[u] = ok ? ld_stream16(kb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
-      vv[u] = ok ? ld_stream16(vb + (size_t)jj * D) : make_uint4(0, 0, 0, 0);
-    }
+    if (j0 != first) fetch(j0);
+    const int j = j0 + jg;
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (j0 + u * NG < end) attend(kk[u], vv[u], j + u * NG < end);  // warp-uniform condition

@@ -117,8 +117,12 @@ def classes_in_child() -> tuple[dict, str | None]:
     ({mask: ms per pass}, None) or ({}, why not)."""
     import subprocess
     cmd = [sys.executable, os.path.abspath(__file__), *sys.argv[1:], "--classes-only", "--no-cpu", "--no-stream"]
+    # a plain single process whatever launched this one: none of a distributed launcher's variables go along
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "MASTER_ADDR",
+                        "MASTER_PORT") and not k.startswith("TORCHELASTIC_")}
     try:
-        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600, env=env)
     except subprocess.TimeoutExpired:
         return {}, "the class passes did not end within 600 s"
     lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]

@@ -138,6 +138,11 @@ DEVI void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
 DEVI void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+DEVI void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+DEVI void cp_async_wait_group() {  // until at most N of this thread's committed groups are still in flight
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // ---- prefetch of an attention launch's keys and values into L2 -----------------------------------------------------
 // The step alternates between projections (bound by latency, HBM nearly idle) and attention (bound by HBM). A

@@ -114,6 +114,13 @@ DEVI void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulat
       "l"(da), "l"(db), "r"(UMMA_IDESC), "r"(accumulate)
       : "memory");
 }
+template <uint32_t IDESC>
+DEVI void umma_f16_n(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "n"(IDESC), "r"(accumulate)
+      : "memory");
+}
 DEVI void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -403,6 +410,249 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
   }
 }
 
+// ---- the same projection for the ready fp16 operand, streamed ------------------------------------------------------
+//
+// When the rows arrive as the finished operand (row * gamma in fp16, with their partial sums), nothing has to be
+// normalised, so nothing has to be resident: the operand goes through a ring of k-blocks like the weights do. That
+// frees the 128 KB the resident operand takes, which makes room for 128 rows per CTA (MMA N = 128, 16 KB operand
+// blocks): a 65-128 row batch reads the weights once and runs as one wave of 128 CTAs instead of two sets of them
+// (under the profiler 23.7 us against 29.9; the 128-row step of the request-stream workloads 0.680 ms against 0.697).
+// At up to 64 rows the resident-operand kernel above stays in use: the streamed form measured no faster there (19.8 us
+// against 18.0 cold; its workers also request and await operand blocks), although it keeps the whole weight tile in
+// flight: that kernel is bound by its convert / multiply hand-offs, not by the depth of its weight ring.
+// Operand block kb + LOOK is requested (cp.async, one commit group per block and thread) when block kb's weight tile
+// is handed over; a thread waits for its own pieces of block kb just before that hand-over, so the MMA lane's wait on
+// the tile's barrier covers the operand block as well, and the commit that frees weight stage kb also frees operand
+// stage kb (XS = LOOK + A_STAGES stages: block kb + LOOK reuses the stage of block kb - A_STAGES).
+template <int UNS>
+struct HeadStream {
+  static constexpr int LOOK = 4, XS = LOOK + A_STAGES;
+  static constexpr int XB = UNS * KB * 2;            // one k-block of the operand: 8 or 16 KB
+  static constexpr int RAW = UNS == 64 ? 16 : 11;    // weight blocks in flight: the whole tile, or what fits beside N = 128
+  static constexpr int OFF_X = 0, OFF_A = XS * XB, OFF_RAW = OFF_A + A_STAGES * A_BYTES, USED = OFF_RAW + RAW * RAW_BYTES;
+  static constexpr int BYTES = USED + 1024;
+  static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(UNS >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
+  static_assert(UNS * OUT_LD * 4 <= USED - OFF_A, "epilogue tile fits in the weight rings");
+  static_assert(BYTES + 4096 <= 227 * 1024, "rings + static shared memory fit an SM");
+};
+
+template <int UNS>
+__global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs p) {
+  using C = HeadStream<UNS>;
+  constexpr int RS = C::RAW, LOOK = C::LOOK, XS = C::XS;
+  extern __shared__ unsigned char dyn_smem[];
+  unsigned char* smem = dyn_smem + ((1024 - (smem_u32(dyn_smem) & 1023)) & 1023);  // swizzle atoms are 1 KB aligned
+  unsigned char* xs = smem + C::OFF_X;
+  unsigned char* as = smem + C::OFF_A;
+  unsigned char* raws = smem + C::OFF_RAW;
+  __shared__ __align__(8) uint64_t raw_full[RS], raw_empty[RS], a_full[A_STAGES], a_empty[A_STAGES];
+  __shared__ __align__(8) uint64_t d_full;
+  __shared__ uint32_t tmem_base;
+  __shared__ float s_scale[UM], s_bias[UM], s_g[UM];
+  __shared__ float s_mean[UNS], s_rstd[UNS];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = blockIdx.x;  // channels [128 tile, +128)
+  const uint8_t* wsrc = p.w + (size_t)tile * NKB * RAW_BYTES;
+
+  if (tid == 0) {
+    for (int i = 0; i < RS; ++i) mbar_init(&raw_full[i], 1), mbar_init(&raw_empty[i], NWORK);
+    for (int i = 0; i < A_STAGES; ++i) mbar_init(&a_full[i], NWORK), mbar_init(&a_empty[i], 1);
+    mbar_init(&d_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == NWORK) {  // the MMA warp owns the tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)),
+                 "n"(UNS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (tid < UM) {
+    s_scale[tid] = p.scale[tile * UM + tid];
+    s_bias[tid] = (p.bias ? p.bias[tile * UM + tid] : 0.f) + p.ln_bias[tile * UM + tid];
+    s_g[tid] = p.ln_g[tile * UM + tid];
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_d = tmem_base;
+
+  if (warp == NWORK + 1) {
+    // ---- producer: the tile's sixteen weight blocks through the raw ring (independent of the previous kernel) -------
+    if (lane == 0) {
+      bool ok = true;
+      int issued = 0;
+      for (int kb = 0; kb < NKB && ok; ++kb) {
+        if (p.withhold && kb == 3) break;  // tests only: nothing sets the barriers of block 3
+        const int st = kb % RS;
+        ok = mbar_wait(&raw_empty[st], ((kb / RS) & 1) ^ 1, p.wait_limit);
+        if (!ok) break;
+        mbar_expect_tx(&raw_full[st], RAW_BYTES);
+        bulk_load(raws + st * RAW_BYTES, wsrc + (size_t)kb * RAW_BYTES, RAW_BYTES, &raw_full[st]);
+        issued = kb + 1;
+      }
+      if (!ok) {
+        atomicOr(p.status, B200DEC_ST_TIMEOUT);
+        for (int kb = issued > RS ? issued - RS : 0; kb < issued; ++kb)  // copies in flight land before the CTA leaves
+          mbar_wait(&raw_full[kb % RS], (kb / RS) & 1, p.wait_limit);
+      }
+    }
+  } else if (warp == NWORK) {
+    // ---- MMA issue: one lane; a block's barrier stands for its weight tile and its operand block ------------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < NKB && ok; ++kb) {
+        const int st = kb % A_STAGES;
+        ok = mbar_wait(&a_full[st], (kb / A_STAGES) & 1, p.wait_limit);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(as + st * A_BYTES), b0 = smem_u32(xs + (kb % XS) * C::XB);
+#pragma unroll
+        for (int k = 0; k < KB / 16; ++k)
+          umma_f16_n<C::IDESC>(tmem_d, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), (kb | k) != 0);
+        umma_commit(&a_empty[st]);
+      }
+      if (!ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+      umma_commit(&d_full);  // arrives when everything issued so far has completed (also after a time-out)
+    }
+  } else {
+    // ---- workers: request operand blocks, widen weight blocks, then the epilogue ------------------------------------
+    pdl_wait();
+    pdl_trigger();
+    auto request_x = [&](int kb) {  // this thread's 16-byte pieces of operand block kb; always one commit group
+      if (kb < NKB) {
+        unsigned char* xb = xs + (kb % XS) * C::XB;
+        for (int i = tid; i < UNS * 8; i += NWORK * 32) {
+          const int r = i >> 3, chunk = i & 7;
+          unsigned char* dst = xb + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
+          if (r < p.rows) cp_async16(dst, p.xg + (size_t)r * p.lda + kb * KB + chunk * 8);
+          else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int kb = 0; kb < LOOK; ++kb) request_x(kb);
+    // the rows' statistics from the partial sums: four threads per row, fixed order
+    for (int r0 = 0; r0 < UNS; r0 += NWORK * 8) {
+      const int r = r0 + (tid >> 2), part = tid & 3;
+      float s1 = 0.f, s2 = 0.f;
+      if (r < p.rows) {
+        const float2* ps = reinterpret_cast<const float2*>(p.stats) + (size_t)r * p.stats_slots;
+        for (int i = part; i < p.stats_slots; i += 4) {
+          const float2 v = __ldcg(ps + i);
+          s1 += v.x, s2 += v.y;
+        }
+      }
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 2), s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
+      if (part == 0) {
+        const float mean = s1 * (1.f / D_MODEL);
+        s_mean[r] = mean;
+        s_rstd[r] = rsqrtf(fmaxf(s2 * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the statistics are read by other warps later
+
+    bool ok = true;
+    const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile (= its tensor-memory lane)
+    const int hf = warp >> 2;               // and its half: 16-k pieces 2 hf, 2 hf + 1 of a block, rows hf * UNS / 2 ..
+    for (int kb = 0; kb < NKB; ++kb) {
+      const int rs = kb % RS, st = kb % A_STAGES;
+      ok = mbar_wait(&raw_full[rs], (kb / RS) & 1, p.wait_limit);
+      if (!ok) break;
+      uint4 r[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        r[j] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + (2 * hf + j) * 2048 + ch * 16);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the block's bytes are in registers
+      ok = mbar_wait(&a_empty[st], ((kb / A_STAGES) & 1) ^ 1, p.wait_limit);  // MMA of block kb - A_STAGES is done:
+      if (!ok) break;                                                          // its weight and operand stages are free
+      request_x(kb + LOOK);
+      unsigned char* row = as + st * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
+        const int pj = 2 * hf + j;
+        uint4 lo, hi;
+        widen16(r[j], lo, hi);
+        *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+      }
+      cp_async_wait_group<LOOK>();  // this thread's pieces of operand block kb (and earlier) have landed
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_full[st]);
+    }
+    cp_async_wait_all();  // nothing of this thread's is on its way into the rings any more (also after a time-out)
+    if (!ok && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+
+    // ---- epilogue ---------------------------------------------------------------------------------------------------
+    const bool got = mbar_wait(&d_full, 0, p.wait_limit);
+    if (!got && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+    tc_fence_after();
+    float* outs = reinterpret_cast<float*>(as);  // (UNS rows, OUT_LD): the weight rings are idle once d_full has fired
+    const float sc = s_scale[ch], bi = s_bias[ch], gch = s_g[ch];
+#pragma unroll
+    for (int c0 = 0; c0 < UNS / 2; c0 += 32) {
+      uint32_t d[32];
+      const int row0 = hf * (UNS / 2) + c0;  // accumulator columns = rows
+      const uint32_t taddr = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)row0;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
+            "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]),
+            "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]), "=r"(d[24]),
+            "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int r = 0; r < 32; ++r)
+        outs[(row0 + r) * OUT_LD + ch] = s_rstd[row0 + r] * (__uint_as_float(d[r]) * sc - s_mean[row0 + r] * gch) + bi;
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the workers only
+    // per-row argmax over the tile's channels: four threads per row, 32 channels each, lowest index wins ties
+    for (int r0 = 0; r0 < UNS; r0 += NWORK * 8) {
+      const int r = r0 + (tid >> 2), qt = tid & 3;
+      float best = -INFINITY;
+      int arg = 0x7fffffff;
+      const float* rowp = outs + r * OUT_LD + qt * 32;
+#pragma unroll 8
+      for (int c = 0; c < 32; ++c) {
+        const float v = rowp[c];
+        if (v > best) best = v, arg = tile * UM + qt * 32 + c;
+      }
+#pragma unroll
+      for (int o = 1; o < 4; o <<= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) best = ob, arg = oa;
+      }
+      if (qt == 0 && r < p.rows) {
+        const int np = p.N / UM;
+        p.part_max[(size_t)r * np + tile] = best;
+        p.part_idx[(size_t)r * np + tile] = arg;
+      }
+    }
+    if (p.logits) {
+      for (int rr = warp; rr < p.rows; rr += NWORK)
+        *reinterpret_cast<float4*>(p.logits + (size_t)rr * p.N + tile * UM + lane * 4) =
+            *reinterpret_cast<const float4*>(outs + rr * OUT_LD + lane * 4);
+    }
+  }
+  // ---- release the tensor memory: after every warp is done with it ----------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == NWORK) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(UNS) : "memory");
+  }
+}
+
 // q (n, k) int8 row-major -> blocks [n / 128][k / 64] of 8 KB: [16-k piece j = 0..3][channel t = 0..127][16 bytes],
 // bytes = q + 128
 __global__ void tile_int8_umma_kernel(const int8_t* __restrict__ q, int n, int k, uint8_t* __restrict__ out) {
@@ -445,7 +695,16 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, cons
   a.part_max = part_max, a.part_idx = part_idx, a.logits = logits;
   a.status = status, a.lda = lda, a.rows = rows, a.N = w->n;
   a.wait_limit = wait_limit > 0 ? (uint32_t)wait_limit : WAIT_LIMIT, a.withhold = withhold;
-  // one launch: a set of CTAs per 64 rows (the kernel offsets its rows by blockIdx.y)
+  if (xg && rows > UN) {  // 65-128 rows of the ready operand: streamed, one CTA per tile, the weights read once
+    e = cudaFuncSetAttribute(head_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<128>::BYTES);
+    if (e == cudaSuccess)
+      e = launch_kernel(head_stream_kernel<128>, dim3(np), dim3(NTHREADS), HeadStream<128>::BYTES, (cudaStream_t)stream, 0,
+                        pdl, a);
+    if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma (streamed operand) launch: %s", cudaGetErrorString(e));
+    return 0;
+  }
+  // up to 64 rows, or fp32 rows that the CTA normalises: the operand resident, a set of CTAs per 64 rows (the kernel
+  // offsets its rows by blockIdx.y)
   e = launch_kernel(head_umma_kernel, dim3(np, (rows + UN - 1) / UN), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream, 0,
                     pdl, a);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma launch: %s", cudaGetErrorString(e));

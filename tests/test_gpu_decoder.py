@@ -327,8 +327,11 @@ def test_admit_and_device_active_list_match_the_oracle(model16):
         dec.admit([9], [prompts[0]], [60])  # no such slot
 
 
-@pytest.mark.parametrize("bit,what", [(1, "vocabulary projection"), (2, "layer projections")])
-def test_bounded_wait_runs_out_and_the_context_survives(bit, what):
+@pytest.mark.parametrize("bit,what,slots,buckets", [
+    (1, "vocabulary projection", 4, None),
+    (1, "vocabulary projection, 128-row bucket (the streamed-operand kernel)", 128, (128,)),
+    (2, "layer projections", 4, None)])
+def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, buckets):
     """The tcgen05 kernels bound every wait. With a short limit and the test-only `withhold` switch (the producer of
     a barrier is left out, nothing faults and nothing is in flight), the wait runs out: the kernel returns, the status
     word carries the time-out, check_status raises, and the next ordinary steps on the same context give the same
@@ -338,8 +341,8 @@ def test_bounded_wait_runs_out_and_the_context_survives(bit, what):
     rng = np.random.default_rng(5)
     memory = [rng.standard_normal((60, 1024)).astype(np.float32) for _ in range(3)]
     prompts = [rng.integers(0, 16384, 6).astype(np.int64) for _ in range(3)]
-    dec = _decoder(model, slots=4, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, record=True, int8=True,
-                   graphs=False)
+    dec = _decoder(model, slots=slots, buckets=buckets, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1,
+                   record=True, int8=True, graphs=False)
     want, _ = _run_teacher_forced(dec, memory, prompts, 4)
     dec.admit([0, 1, 2], [torch.from_numpy(p) for p in prompts], [60] * 3)
     dec.plan.wait_limit, dec.plan.withhold = 2048, bit

@@ -413,39 +413,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
 // ---- the same projection for the ready fp16 operand, streamed ------------------------------------------------------
 //
 // When the rows arrive as the finished operand (row * gamma in fp16, with their partial sums), nothing has to be
-// normalised, so nothing has to be resident: the operand goes through a ring of k-blocks like the weights do. That
-// frees the 128 KB the resident operand takes, which makes room for 128 rows per CTA (MMA N = 128, 16 KB operand
-// blocks): a 65-128 row batch reads the weights once and runs as one wave of 128 CTAs instead of two sets of them
-// (under the profiler 23.7 us against 29.9; the 128-row step of the request-stream workloads 0.680 ms against 0.697).
-// At up to 64 rows the resident-operand kernel above stays in use: the streamed form measured no faster there (19.8 us
-// against 18.0 cold; its workers also request and await operand blocks), although it keeps the whole weight tile in
-// flight: that kernel is bound by its convert / multiply hand-offs, not by the depth of its weight ring.
+// normalised, so nothing has to be resident: the operand goes through a ring of k-blocks like the weights do. The
+// 128 KB this frees go into (a) four weight-tile stages instead of two, so the workers hand over two blocks per turn
+// (one proxy fence and one round of barrier traffic per pair; the clock stamps of the resident-operand kernel showed
+// 880 cycles per block in the workers, a serial chain of waits, 100 instructions and a fence, against 130 for the
+// block's four MMAs), and (b) 128 rows per CTA (MMA N = 128, 16 KB operand blocks), so a 65-128 row batch reads the
+// weights once and runs as one wave of 128 CTAs instead of two sets of them.
 // Operand block kb + LOOK is requested (cp.async, one commit group per block and thread) when block kb's weight tile
 // is handed over; a thread waits for its own pieces of block kb just before that hand-over, so the MMA lane's wait on
 // the tile's barrier covers the operand block as well, and the commit that frees weight stage kb also frees operand
-// stage kb (XS = LOOK + A_STAGES stages: block kb + LOOK reuses the stage of block kb - A_STAGES).
+// stage kb (XS = LOOK + AST stages: block kb + LOOK reuses the stage of block kb - AST).
+// The rows' statistics: a warp per row, the row's partial sums read with coalesced loads that are all in flight at
+// once (four threads per row walking 128 slots one after the other took 3.5 us of the resident-operand kernel).
 template <int UNS>
 struct HeadStream {
-  static constexpr int LOOK = 4, XS = LOOK + A_STAGES;
+  static constexpr int AST = 4;                      // weight-tile stages
+  static constexpr int NWK = 16;                     // worker warps: one 16-byte piece of a weight block per thread
+  static constexpr int NT = (NWK + 2) * 32;          // + the MMA warp and the producer warp
+  static constexpr int LOOK = UNS == 64 ? 4 : 2;     // operand blocks requested ahead
+  static constexpr int XS = LOOK + AST;
   static constexpr int XB = UNS * KB * 2;            // one k-block of the operand: 8 or 16 KB
-  static constexpr int RAW = UNS == 64 ? 16 : 11;    // weight blocks in flight: the whole tile, or what fits beside N = 128
-  static constexpr int OFF_X = 0, OFF_A = XS * XB, OFF_RAW = OFF_A + A_STAGES * A_BYTES, USED = OFF_RAW + RAW * RAW_BYTES;
+  static constexpr int RAW = UNS == 64 ? 10 : 7;     // weight blocks in flight: what fits beside the other rings
+  static constexpr int OFF_X = 0, OFF_A = XS * XB, OFF_RAW = OFF_A + AST * A_BYTES, USED = OFF_RAW + RAW * RAW_BYTES;
   static constexpr int BYTES = USED + 1024;
   static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(UNS >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
   static_assert(UNS * OUT_LD * 4 <= USED - OFF_A, "epilogue tile fits in the weight rings");
   static_assert(BYTES + 4096 <= 227 * 1024, "rings + static shared memory fit an SM");
+  static_assert(NKB % 2 == 0 && AST % 2 == 0, "the workers hand over blocks in pairs");
 };
 
 template <int UNS>
-__global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs p) {
+__global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(const HeadArgs p) {
   using C = HeadStream<UNS>;
-  constexpr int RS = C::RAW, LOOK = C::LOOK, XS = C::XS;
+  constexpr int RS = C::RAW, LOOK = C::LOOK, XS = C::XS, AST = C::AST, NWK = C::NWK;
   extern __shared__ unsigned char dyn_smem[];
   unsigned char* smem = dyn_smem + ((1024 - (smem_u32(dyn_smem) & 1023)) & 1023);  // swizzle atoms are 1 KB aligned
   unsigned char* xs = smem + C::OFF_X;
   unsigned char* as = smem + C::OFF_A;
   unsigned char* raws = smem + C::OFF_RAW;
-  __shared__ __align__(8) uint64_t raw_full[RS], raw_empty[RS], a_full[A_STAGES], a_empty[A_STAGES];
+  __shared__ __align__(8) uint64_t raw_full[RS], raw_empty[RS], a_full[AST], a_empty[AST];
   __shared__ __align__(8) uint64_t d_full;
   __shared__ uint32_t tmem_base;
   __shared__ float s_scale[UM], s_bias[UM], s_g[UM];
@@ -456,12 +462,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
   const uint8_t* wsrc = p.w + (size_t)tile * NKB * RAW_BYTES;
 
   if (tid == 0) {
-    for (int i = 0; i < RS; ++i) mbar_init(&raw_full[i], 1), mbar_init(&raw_empty[i], NWORK);
-    for (int i = 0; i < A_STAGES; ++i) mbar_init(&a_full[i], NWORK), mbar_init(&a_empty[i], 1);
+    for (int i = 0; i < RS; ++i) mbar_init(&raw_full[i], 1), mbar_init(&raw_empty[i], NWK);
+    for (int i = 0; i < AST; ++i) mbar_init(&a_full[i], NWK), mbar_init(&a_empty[i], 1);
     mbar_init(&d_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == NWORK) {  // the MMA warp owns the tensor memory
+  if (warp == NWK) {  // the MMA warp owns the tensor memory
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)),
                  "n"(UNS)
                  : "memory");
@@ -477,7 +483,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
   tc_fence_after();
   const uint32_t tmem_d = tmem_base;
 
-  if (warp == NWORK + 1) {
+  if (warp == NWK + 1) {
     // ---- producer: the tile's sixteen weight blocks through the raw ring (independent of the previous kernel) -------
     if (lane == 0) {
       bool ok = true;
@@ -497,13 +503,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
           mbar_wait(&raw_full[kb % RS], (kb / RS) & 1, p.wait_limit);
       }
     }
-  } else if (warp == NWORK) {
+  } else if (warp == NWK) {
     // ---- MMA issue: one lane; a block's barrier stands for its weight tile and its operand block ------------------
     if (lane == 0) {
       bool ok = true;
       for (int kb = 0; kb < NKB && ok; ++kb) {
-        const int st = kb % A_STAGES;
-        ok = mbar_wait(&a_full[st], (kb / A_STAGES) & 1, p.wait_limit);
+        const int st = kb % AST;
+        ok = mbar_wait(&a_full[st], (kb / AST) & 1, p.wait_limit);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a0 = smem_u32(as + st * A_BYTES), b0 = smem_u32(xs + (kb % XS) * C::XB);
@@ -522,7 +528,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
     auto request_x = [&](int kb) {  // this thread's 16-byte pieces of operand block kb; always one commit group
       if (kb < NKB) {
         unsigned char* xb = xs + (kb % XS) * C::XB;
-        for (int i = tid; i < UNS * 8; i += NWORK * 32) {
+        for (int i = tid; i < UNS * 8; i += NWK * 32) {
           const int r = i >> 3, chunk = i & 7;
           unsigned char* dst = xb + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4);
           if (r < p.rows) cp_async16(dst, p.xg + (size_t)r * p.lda + kb * KB + chunk * 8);
@@ -533,56 +539,65 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
     };
 #pragma unroll
     for (int kb = 0; kb < LOOK; ++kb) request_x(kb);
-    // the rows' statistics from the partial sums: four threads per row, fixed order
-    for (int r0 = 0; r0 < UNS; r0 += NWORK * 8) {
-      const int r = r0 + (tid >> 2), part = tid & 3;
-      float s1 = 0.f, s2 = 0.f;
-      if (r < p.rows) {
+    // the rows' statistics from the partial sums (at most 128 per row): a warp per row, all of a warp's loads at once
+    {
+      constexpr int RPW = UNS / NWK;  // 4 or 8 rows per warp
+      float2 v[RPW][4];
+#pragma unroll
+      for (int j = 0; j < RPW; ++j) {
+        const int r = warp + NWK * j;
         const float2* ps = reinterpret_cast<const float2*>(p.stats) + (size_t)r * p.stats_slots;
-        for (int i = part; i < p.stats_slots; i += 4) {
-          const float2 v = __ldcg(ps + i);
-          s1 += v.x, s2 += v.y;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          v[j][i] = (r < p.rows && lane + 32 * i < p.stats_slots) ? __ldcg(ps + lane + 32 * i) : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < RPW; ++j) {
+        const int r = warp + NWK * j;
+        float s1 = (v[j][0].x + v[j][1].x) + (v[j][2].x + v[j][3].x), s2 = (v[j][0].y + v[j][1].y) + (v[j][2].y + v[j][3].y);
+        s1 = warp_sum(s1), s2 = warp_sum(s2);
+        if (lane == 0) {
+          const float mean = s1 * (1.f / D_MODEL);
+          s_mean[r] = mean;
+          s_rstd[r] = rsqrtf(fmaxf(s2 * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
         }
       }
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 1), s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 2), s2 += __shfl_xor_sync(0xffffffffu, s2, 2);
-      if (part == 0) {
-        const float mean = s1 * (1.f / D_MODEL);
-        s_mean[r] = mean;
-        s_rstd[r] = rsqrtf(fmaxf(s2 * (1.f / D_MODEL) - mean * mean, 0.f) + p.ln_eps);
-      }
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the statistics are read by other warps later
+    asm volatile("bar.sync 1, %0;" ::"n"(NWK * 32) : "memory");  // the statistics are read by other warps later
 
     bool ok = true;
     const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile (= its tensor-memory lane)
-    const int hf = warp >> 2;               // and its half: 16-k pieces 2 hf, 2 hf + 1 of a block, rows hf * UNS / 2 ..
-    for (int kb = 0; kb < NKB; ++kb) {
-      const int rs = kb % RS, st = kb % A_STAGES;
-      ok = mbar_wait(&raw_full[rs], (kb / RS) & 1, p.wait_limit);
-      if (!ok) break;
+    const int pj = warp >> 2;               // and its quarter: the 16-k piece pj of a block, rows pj * UNS / 4 .. after
+    for (int kb = 0; kb < NKB && ok; kb += 2) {  // two blocks per turn
       uint4 r[2];
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        r[j] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + (2 * hf + j) * 2048 + ch * 16);
+      for (int b = 0; b < 2; ++b) {
+        const int rs = (kb + b) % RS;
+        ok = ok && mbar_wait(&raw_full[rs], ((kb + b) / RS) & 1, p.wait_limit);
+        if (ok) r[b] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + pj * 2048 + ch * 16);
+      }
+      if (!ok) break;
       __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the block's bytes are in registers
-      ok = mbar_wait(&a_empty[st], ((kb / A_STAGES) & 1) ^ 1, p.wait_limit);  // MMA of block kb - A_STAGES is done:
-      if (!ok) break;                                                          // its weight and operand stages are free
-      request_x(kb + LOOK);
-      unsigned char* row = as + st * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+      if (lane == 0) mbar_arrive(&raw_empty[kb % RS]), mbar_arrive(&raw_empty[(kb + 1) % RS]);  // bytes are in registers
+      // MMAs of blocks kb - AST and kb + 1 - AST are done: their weight and operand stages are free
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
-        const int pj = 2 * hf + j;
-        uint4 lo, hi;
-        widen16(r[j], lo, hi);
+      for (int b = 0; b < 2; ++b)
+        ok = ok && mbar_wait(&a_empty[(kb + b) % AST], (((kb + b) / AST) & 1) ^ 1, p.wait_limit);
+      if (!ok) break;
+      request_x(kb + LOOK);
+      request_x(kb + 1 + LOOK);
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        unsigned char* row = as + ((kb + b) % AST) * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+        uint4 lo, hi;  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
+        widen16(r[b], lo, hi);
         *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
         *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
       }
-      cp_async_wait_group<LOOK>();  // this thread's pieces of operand block kb (and earlier) have landed
+      cp_async_wait_group<LOOK>();  // this thread's pieces of operand blocks kb and kb + 1 (and earlier) have landed
       fence_async_shared();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_full[st]);
+      if (lane == 0) mbar_arrive(&a_full[kb % AST]), mbar_arrive(&a_full[(kb + 1) % AST]);
     }
     cp_async_wait_all();  // nothing of this thread's is on its way into the rings any more (also after a time-out)
     if (!ok && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);
@@ -593,31 +608,41 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
     tc_fence_after();
     float* outs = reinterpret_cast<float*>(as);  // (UNS rows, OUT_LD): the weight rings are idle once d_full has fired
     const float sc = s_scale[ch], bi = s_bias[ch], gch = s_g[ch];
-#pragma unroll
-    for (int c0 = 0; c0 < UNS / 2; c0 += 32) {
-      uint32_t d[32];
-      const int row0 = hf * (UNS / 2) + c0;  // accumulator columns = rows
+    {
+      constexpr int CW = UNS / 4;  // accumulator columns (= rows) per warp: 16 or 32
+      uint32_t d[CW];
+      const int row0 = pj * CW;
       const uint32_t taddr = tmem_d + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)row0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-          : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
-            "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]),
-            "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]), "=r"(d[24]),
-            "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
-          : "r"(taddr)
-          : "memory");
+      if constexpr (CW == 32) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
+              "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]),
+              "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]), "=r"(d[23]), "=r"(d[24]),
+              "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31])
+            : "r"(taddr)
+            : "memory");
+      } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]),
+              "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+            : "r"(taddr)
+            : "memory");
+      }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int r = 0; r < 32; ++r)
+      for (int r = 0; r < CW; ++r)
         outs[(row0 + r) * OUT_LD + ch] = s_rstd[row0 + r] * (__uint_as_float(d[r]) * sc - s_mean[row0 + r] * gch) + bi;
     }
     tc_fence_before();
-    asm volatile("bar.sync 1, %0;" ::"n"(NWORK * 32) : "memory");  // the workers only
+    asm volatile("bar.sync 1, %0;" ::"n"(NWK * 32) : "memory");  // the workers only
     // per-row argmax over the tile's channels: four threads per row, 32 channels each, lowest index wins ties
-    for (int r0 = 0; r0 < UNS; r0 += NWORK * 8) {
-      const int r = r0 + (tid >> 2), qt = tid & 3;
+    if (tid < UNS * 4) {
+      const int r = tid >> 2, qt = tid & 3;  // the shuffles below stay inside a row's four lanes
       float best = -INFINITY;
       int arg = 0x7fffffff;
       const float* rowp = outs + r * OUT_LD + qt * 32;
@@ -639,7 +664,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
       }
     }
     if (p.logits) {
-      for (int rr = warp; rr < p.rows; rr += NWORK)
+      for (int rr = warp; rr < p.rows; rr += NWK)
         *reinterpret_cast<float4*>(p.logits + (size_t)rr * p.N + tile * UM + lane * 4) =
             *reinterpret_cast<const float4*>(outs + rr * OUT_LD + lane * 4);
     }
@@ -647,7 +672,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_stream_kernel(const HeadArgs
   // ---- release the tensor memory: after every warp is done with it ----------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == NWORK) {
+  if (warp == NWK) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(UNS) : "memory");
   }
@@ -695,16 +720,24 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, cons
   a.part_max = part_max, a.part_idx = part_idx, a.logits = logits;
   a.status = status, a.lda = lda, a.rows = rows, a.N = w->n;
   a.wait_limit = wait_limit > 0 ? (uint32_t)wait_limit : WAIT_LIMIT, a.withhold = withhold;
-  if (xg && rows > UN) {  // 65-128 rows of the ready operand: streamed, one CTA per tile, the weights read once
-    e = cudaFuncSetAttribute(head_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<128>::BYTES);
-    if (e == cudaSuccess)
-      e = launch_kernel(head_stream_kernel<128>, dim3(np), dim3(NTHREADS), HeadStream<128>::BYTES, (cudaStream_t)stream, 0,
-                        pdl, a);
+  if (xg) {  // the ready operand: streamed, one CTA per tile whatever the rows (at most 128 partial sums per row)
+    B200_REQUIRE(stats_slots <= 128, "head_umma: %d partial sums per row (at most 128)", stats_slots);
+    if (rows <= UN) {
+      e = cudaFuncSetAttribute(head_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<64>::BYTES);
+      if (e == cudaSuccess)
+        e = launch_kernel(head_stream_kernel<64>, dim3(np), dim3(HeadStream<64>::NT), HeadStream<64>::BYTES, (cudaStream_t)stream, 0,
+                          pdl, a);
+    } else {
+      e = cudaFuncSetAttribute(head_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<128>::BYTES);
+      if (e == cudaSuccess)
+        e = launch_kernel(head_stream_kernel<128>, dim3(np), dim3(HeadStream<128>::NT), HeadStream<128>::BYTES, (cudaStream_t)stream,
+                          0, pdl, a);
+    }
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma (streamed operand) launch: %s", cudaGetErrorString(e));
     return 0;
   }
-  // up to 64 rows, or fp32 rows that the CTA normalises: the operand resident, a set of CTAs per 64 rows (the kernel
-  // offsets its rows by blockIdx.y)
+  // fp32 rows that the CTA normalises: the operand resident, a set of CTAs per 64 rows (the kernel offsets its rows
+  // by blockIdx.y)
   e = launch_kernel(head_umma_kernel, dim3(np, (rows + UN - 1) / UN), dim3(NTHREADS), SMEM_BYTES, (cudaStream_t)stream, 0,
                     pdl, a);
   if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma launch: %s", cudaGetErrorString(e));

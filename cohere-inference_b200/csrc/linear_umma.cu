@@ -173,7 +173,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // ---- widen the weights into the A tiles: they depend on nothing the previous kernel writes, so this happens in
+  // front of the dependency wait, under the previous kernel's tail (the tiles are this CTA's own shared memory)
+#pragma unroll
+  for (int b = 0; b < NKB; ++b) {
+    unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int pj = 2 * hf + j;  // k = 16 pj .. 16 pj + 15 of the block: chunks 2 pj and 2 pj + 1 of the row
+      uint4 lo, hi;
+      widen16(wr[b][j], lo, hi);
+      *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+    }
+  }
   pdl_wait();
+  pdl_trigger();  // at once: the dependent's CTAs need ~2 us to start and fetch their weights, more than is left of this one
 
   // ---- stage this K slice of the operand into swizzled tiles; the cluster adds up the rows' statistics -------------
   const int k0 = rank * KSLICE;
@@ -204,34 +219,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
       if (r < p.rows && lane < KSPLIT) cluster.map_shared_rank(stats, lane)[r] = make_float2(s1, s2);
     }
   }
-  // ---- widen the weights into the A tiles ---------------------------------------------------------------------------
-#pragma unroll
-  for (int b = 0; b < NKB; ++b) {
-    unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int pj = 2 * hf + j;  // k = 16 pj .. 16 pj + 15 of the block: chunks 2 pj and 2 pj + 1 of the row
-      uint4 lo, hi;
-      widen16(wr[b][j], lo, hi);
-      *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
-      *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
-    }
-  }
   cp_async_wait_all();
   fence_async_shared();  // the MMA reads both operands through the async proxy
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  pdl_trigger();
   const uint32_t tmem_d = tmem_base;
 
   // ---- multiply: one lane, 4 instructions per block, completion through an mbarrier ---------------------------------
   if (tid == 0) {
+    // the descriptors of block 0; a k-step of 16 advances a tile's start by 32 bytes = 2 units of its address field, a
+    // block by the tile's size (the tiles are 1 KB aligned and lie below 256 KB: no carry out of the field)
+    const uint64_t da = umma_desc(smem_u32(as)), db = umma_desc(smem_u32(xs));
 #pragma unroll
     for (int b = 0; b < NKB; ++b) {
-      const uint32_t a0 = smem_u32(as + b * A_BYTES), b0 = smem_u32(xs + b * S::XB_BYTES);
 #pragma unroll
-      for (int k = 0; k < KB / 16; ++k) umma_f16<MB>(tmem_d, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), (b | k) != 0);
+      for (int k = 0; k < KB / 16; ++k)
+        umma_f16<MB>(tmem_d, da + (uint64_t)(b * (A_BYTES >> 4) + 2 * k), db + (uint64_t)(b * (S::XB_BYTES >> 4) + 2 * k),
+                     (b | k) != 0);
     }
     if (!p.withhold) umma_commit(&d_full);
   }

@@ -17,7 +17,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libb200dec.so")
-SOURCES = ["linear.cu", "linear_int8.cu", "linear_bf16.cu", "linear_24.cu", "attention.cu", "attention_ring.cu", "head_umma.cu", "linear_umma.cu", "rowops.cu",
+SOURCES = ["linear.cu", "linear_int8.cu", "linear_bf16.cu", "linear_f16.cu", "linear_24.cu", "attention.cu", "attention_ring.cu", "head_umma.cu", "linear_umma.cu", "rowops.cu",
            "slots.cu", "prefill_gemm.cu", "step.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 

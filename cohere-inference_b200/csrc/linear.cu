@@ -83,6 +83,7 @@ bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int ro
     case B200DEC_W_INT8: return fits_int8(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_BF16: return fits_bf16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_24: return fits_24(split, ln, warps, k, ksplit, rows);
+    case B200DEC_W_F16: return fits_f16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_UMMA:  // linear_umma.cu: fp16 rows, plain or as a LayerNorm's ready operand
       return !split && rows <= 128 && ln != 1 &&
              ((k == D_MODEL && (ksplit == 4 || ksplit == 8)) || (k == 4 * D_MODEL && ksplit == 8 && ln == 0));
@@ -114,7 +115,8 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
   B200_REQUIRE((16 * w->warps) % (8 * w->ksplit) == 0, "linear: warps %d too few for ksplit %d", w->warps, w->ksplit);
   B200_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w->w & 15) == 0, "linear: operands must be 16-byte aligned");
   B200_REQUIRE(lda % 8 == 0 && lda >= w->k, "linear: lda %d", lda);
-  B200_REQUIRE((w->kind == B200DEC_W_BF16) == (w->scale == nullptr), "linear: scale present iff int8");
+  B200_REQUIRE((w->kind == B200DEC_W_BF16 || w->kind == B200DEC_W_F16) == (w->scale == nullptr),
+               "linear: scale present iff int8");
   const bool split = a_kind == B200DEC_A_F32_SPLIT;
   B200_REQUIRE(split || a_kind == B200DEC_A_F16 || a_kind == B200DEC_A_F16_ROWS16, "linear: a_kind %d", a_kind);
   // 0: no LayerNorm; 1: folded, the rows are fp32; 2: folded, the rows are fp16 copies of the LayerNorm's input
@@ -174,6 +176,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
     case B200DEC_W_INT8: return launch_int8(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);
     case B200DEC_W_INT8_24: return launch_24(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);
     case B200DEC_W_BF16: return launch_bf16(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);
+    case B200DEC_W_F16: return launch_f16(p, split, lnorm, w->warps, w->k, w->ksplit, pdl, s);
   }
   return fail(B200DEC_EINVAL, "linear: weight kind %d", w->kind);
 }
@@ -239,7 +242,7 @@ int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int
 
 int64_t b200dec_tiled_bytes(int kind, int n, int k) {
   if (kind == B200DEC_W_INT8 || kind == B200DEC_W_INT8_UMMA) return (int64_t)n * k;
-  if (kind == B200DEC_W_BF16) return (int64_t)n * k * 2;
+  if (kind == B200DEC_W_BF16 || kind == B200DEC_W_F16) return (int64_t)n * k * 2;
   if (kind == B200DEC_W_INT8_24) return (int64_t)n * k / 2;
   return -1;
 }

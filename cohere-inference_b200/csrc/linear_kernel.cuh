@@ -49,6 +49,10 @@ struct WTraits<B200DEC_W_BF16> {
   static constexpr int KPB = 32, STEPS = 2, PAD = 64;
 };
 template <>
+struct WTraits<B200DEC_W_F16> {  // the layout of B200DEC_W_BF16, the arithmetic of the int8 kinds
+  static constexpr int KPB = 32, STEPS = 2, PAD = 64;
+};
+template <>
 struct WTraits<B200DEC_W_INT8_24> {
   static constexpr int KPB = 128, STEPS = 8, PAD = 64;
 };
@@ -155,7 +159,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
   using S = LinSmem<WT, SPLIT, LN, NW, KSLICE, KSPLIT, MB>;
   constexpr int KPB = T::KPB, STEPS = T::STEPS, NBLK = KSLICE / KPB, NT = NW * 32, BN = NW * 16, K = KSLICE * KSPLIT;
   constexpr int RS = S::RS, CPR = BN / KSPLIT, GPR = CPR / 4, NB = MB / 8, NBG = NB < 8 ? NB : 8;
-  constexpr bool BF = WT == B200DEC_W_BF16;
+  constexpr bool BF = WT == B200DEC_W_BF16, W16 = BF || WT == B200DEC_W_F16;  // bf16 arithmetic; 16-bit weight layout
   constexpr bool F32SRC = LN == 1 || SPLIT;  // the source rows are fp32
   static_assert(LN != 2 || (!SPLIT && KSLICE <= 256), "fp16 source rows: one fp16 operand, a row's chunks within a warp");
   static_assert(CPR % 8 == 0, "each CTA finishes a multiple of 8 channels");
@@ -362,7 +366,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
         widen_u8(r0[s], af[s][0], af[s][2]);
         widen_u8(r1[s], af[s][1], af[s][3]);
       }
-    } else if constexpr (WT == B200DEC_W_BF16) {
+    } else if constexpr (W16) {
       af[0][0] = wr[b][0].x, af[0][2] = wr[b][0].y, af[1][0] = wr[b][0].z, af[1][2] = wr[b][0].w;
       af[0][1] = wr[b][1].x, af[0][3] = wr[b][1].y, af[1][1] = wr[b][1].z, af[1][3] = wr[b][1].w;
     } else {
@@ -382,7 +386,7 @@ __global__ void __launch_bounds__(NW * 32, linear_min_ctas<WT, NW, KSLICE, MB>()
     for (int c = 0; c < STEPS / 2; ++c) {  // one 16-byte chunk of a row = the lane's k-values of two steps
       int col;                             // first k of the chunk inside the slice
       if constexpr (WT == B200DEC_W_INT8) col = b * 64 + t * 16 + c * 8;
-      else if constexpr (WT == B200DEC_W_BF16) col = b * 32 + t * 8;
+      else if constexpr (W16) col = b * 32 + t * 8;
       else col = b * 128 + (4 * c + t) * 8;
 #pragma unroll
       for (int n0 = 0; n0 < NB; n0 += NBG) {
@@ -670,8 +674,10 @@ bool fits_shape(int warps, int k, int ksplit, int rows) {
 int launch_int8(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
 int launch_bf16(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
 int launch_24(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
+int launch_f16(const LinArgs& a, bool split, int ln, int warps, int k, int ksplit, bool pdl, cudaStream_t s);
 bool fits_int8(bool split, int ln, int warps, int k, int ksplit, int rows);
 bool fits_bf16(bool split, int ln, int warps, int k, int ksplit, int rows);
 bool fits_24(bool split, int ln, int warps, int k, int ksplit, int rows);
+bool fits_f16(bool split, int ln, int warps, int k, int ksplit, int rows);
 
 }  // namespace b200dec_detail

@@ -14,7 +14,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200dec.so")
 
-W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA = 0, 1, 2, 3
+W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA, W_F16 = 0, 1, 2, 3, 4
 A_F16, A_F32_SPLIT, A_F16_ROWS16 = 0, 1, 2
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2

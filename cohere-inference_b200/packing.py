@@ -79,7 +79,7 @@ def tile_config(n: int, k: int, kind: int, a_kind: int = nv.A_F16, ln: bool = Fa
     fits = nv.lib().b200dec_linear_fits
     prefs = TILE_CONFIG.get((n, k), []) + [(w, s) for s in (8, 4, 2, 1) for w in (4, 8)]
     valid = [(w, s) for w, s in prefs if n % (16 * w) == 0 and (k, s) in ((1024, 8), (1024, 4), (1024, 2), (4096, 8))
-             and (16 * w) % (8 * s) == 0 and (k // s) % {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_INT8_24: 128}[kind] == 0
+             and (16 * w) % (8 * s) == 0 and (k // s) % {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_F16: 32, nv.W_INT8_24: 128}[kind] == 0
              and (not ln or k == 1024)]
     assert valid, f"no tile for a ({n}, {k}) projection"
     for w, s in valid:
@@ -129,7 +129,7 @@ class PackedLinear:
 def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep_reference: bool = False, *,
                 a_kind: int | None = None, ln: tuple[torch.Tensor, torch.Tensor] | None = None,
                 max_rows: int = 64) -> PackedLinear:
-    """One (N, K) projection into the streaming layout of the given kind (native.W_BF16 / W_INT8 / W_INT8_24).
+    """One (N, K) projection into the streaming layout of the given kind (native.W_BF16 / W_F16 / W_INT8 / W_INT8_24).
     a_kind and max_rows describe how it will be called (operand precision, most rows): they only choose the CTA
     tile. ln = (gamma, beta) of the LayerNorm this projection folds in: the two per-channel vectors of that fold are
     computed here from the weights the kernel multiplies by."""
@@ -152,8 +152,8 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     dev = w.device
     tiled = torch.empty(lib.b200dec_tiled_bytes(kind, n, k), dtype=torch.uint8, device=dev)
     meta = scale = q = kept = words = None
-    if kind == nv.W_BF16:
-        wb = w.to(torch.bfloat16).contiguous()
+    if kind in (nv.W_BF16, nv.W_F16):  # one tiler for both: it moves 16-bit words
+        wb = (w.to(torch.bfloat16) if kind == nv.W_BF16 else fp16_image(w)).contiguous()
         nv.check(lib.b200dec_tile_bf16(nv.ptr(wb), n, k, nv.ptr(tiled), nv.stream_ptr()))
     elif kind == nv.W_INT8:
         q, scale = quantize_rows(w)
@@ -174,11 +174,23 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     return PackedLinear(kind, n, k, tiled, meta, scale, b, warps, ksplit, q, kept, words, ln_g, ln_bias)
 
 
+def fp16_image(w: torch.Tensor) -> torch.Tensor:
+    """The fp16 weights of a B200DEC_W_F16 projection: the bf16 value the reference multiplies by
+    (server.py:266 loads the model as bf16) rounded to fp16. fp16 has three more mantissa bits than bf16, so every bf16
+    value of magnitude 2^-14 .. 65504 is kept exactly; smaller ones land on the fp16 subnormal grid (absolute error
+    at most 2^-25), larger ones are refused."""
+    wb = w.to(torch.bfloat16).float()
+    assert float(wb.abs().max()) <= 65504.0, "a weight beyond the fp16 range: use the bf16 kind"
+    return wb.to(torch.float16)
+
+
 def dequantized(weight: torch.Tensor, kind: int) -> torch.Tensor:
     """fp32 weights the packed projection multiplies by (what an fp32 comparison should use)."""
     w = _f32(weight)
     if kind == nv.W_BF16:
         return w.to(torch.bfloat16).float()
+    if kind == nv.W_F16:
+        return fp16_image(w).float()
     if kind == nv.W_INT8_24:
         w = prune_24_magnitude(w)
     q, s = quantize_rows(w)

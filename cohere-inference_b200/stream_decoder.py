@@ -87,11 +87,14 @@ class StreamDecoder:
                  eos: int | None = None, record: bool = False, pdl: bool | int = 7, graphs: bool = True,
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
                  head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True,
-                 kv_prefetch_mb: int = 0, device_sched: bool = False,
+                 kv_prefetch_mb: int = 0, device_sched: bool = False, fp16_weights: bool = False,
                  _packed: tuple | None = None):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
-        accumulation); else bf16 weights with the fp32 activations split into two bf16 halves. ffn_sparse: fc1/fc2
+        accumulation); else bf16 weights with the fp32 activations split into two bf16 halves, or with fp16_weights
+        the fp16 image of those bf16 weights (packing.fp16_image) on the int8 mode's pipeline: fp16 activations, the
+        LayerNorms folded through the fp16 copy of the residual stream, twice the weight bytes of int8 and no
+        quantisation error. ffn_sparse: fc1/fc2
         magnitude-pruned 2:4 and stored compressed (needs int8). eos: overrides config.eos_token_id (-1: never end on
         a token). record: keep the last step's logits and every slot's un-forced argmax (teacher forcing, tests).
         pdl: which of the step's kernels launch programmatically after their predecessor (bits: 1 a projection after a
@@ -106,6 +109,7 @@ class StreamDecoder:
         scheduler never calls set_active after an eviction."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
+        assert not (fp16_weights and int8), "fp16_weights is a mode of its own beside int8"
         cfg = model.config
         dev = model.device if _packed else model.model.decoder.embed_tokens.weight.device
         assert dev.type == "cuda", "StreamDecoder needs the model on a CUDA device: there is no CPU path"
@@ -122,10 +126,12 @@ class StreamDecoder:
         self.kv_prefetch_mb, self.device_sched = int(kv_prefetch_mb), bool(device_sched)
         assert not (self.device_sched and chains > 1), "the device-side active list goes with a single chain"
         self.act, self._act_name, self._cfg_eos = ACTS[cfg.hidden_act], cfg.hidden_act, cfg.eos_token_id
-        kind = nv.W_INT8 if int8 else nv.W_BF16
+        self.fp16_weights = bool(fp16_weights)
+        kind = nv.W_INT8 if int8 else nv.W_F16 if fp16_weights else nv.W_BF16
+        half_rows = bool(int8 or fp16_weights)  # activations travel as fp16 rows
         ffn_kind = nv.W_INT8_24 if ffn_sparse else kind
-        self.a_kind = nv.A_F16 if int8 else nv.A_F32_SPLIT
-        self.head_a_kind = nv.A_F32_SPLIT if (head_split or not int8) else nv.A_F16
+        self.a_kind = nv.A_F16 if half_rows else nv.A_F32_SPLIT
+        self.head_a_kind = nv.A_F16 if (fp16_weights or (int8 and not head_split)) else nv.A_F32_SPLIT
         bm = max(self.buckets)
         with torch.cuda.device(dev):
             # proj_umma: the dense int8 projections that run on the tcgen05 kernel of csrc/linear_umma.cu: True = qkv and
@@ -133,7 +139,8 @@ class StreamDecoder:
             # than on mma.sync), "all", or a comma-separated subset of qkv,o,cq,co,fc1,fc2
             names = "qkv,fc1" if proj_umma is True else "qkv,o,cq,co,fc1,fc2" if proj_umma == "all" else (proj_umma or "")
             umma = frozenset(n for n in names.split(",") if n) if int8 else frozenset()
-            self._pack_options = dict(int8=bool(int8), ffn_sparse=bool(ffn_sparse), head_split=bool(head_split),
+            self._pack_options = dict(int8=bool(int8), fp16_weights=bool(fp16_weights), ffn_sparse=bool(ffn_sparse),
+                                      head_split=bool(head_split),
                                       head_umma=bool(head_umma), proj_umma=",".join(sorted(umma)), max_rows=bm)
             if _packed:
                 self._load_packed(*_packed)
@@ -194,9 +201,9 @@ class StreamDecoder:
             self.head_idx = torch.zeros(bm, self.head_partials, **i32)
             # the step's rows ranked by length (self / cross), rebuilt by every step for the paired attention kernel
             # the residual stream times the next LayerNorm's gamma as fp16, and the rows' partial sums (one slot per
-            # finishing CTA of the producer): what the LayerNorm-folding projections stage (int8 / 2:4 weights)
-            self.xh = torch.zeros(bm, self.width, device=dev, dtype=torch.float16) if int8 else None
-            self.ln_stats = torch.zeros(bm, 128, 2, device=dev) if int8 else None
+            # finishing CTA of the producer): what the LayerNorm-folding projections stage (int8, 2:4 and fp16 weights)
+            self.xh = torch.zeros(bm, self.width, device=dev, dtype=torch.float16) if half_rows else None
+            self.ln_stats = torch.zeros(bm, 128, 2, device=dev) if half_rows else None
             self.sched_self = torch.zeros(bm, 4, **i32)
             self.sched_cross = torch.zeros(bm, 4, **i32)
             self.logits = torch.zeros(bm, self.vocab, **f32) if record else None
@@ -303,7 +310,8 @@ class StreamDecoder:
         if shim.device.index is None:
             shim.device = torch.device("cuda", torch.cuda.current_device())
         po = man["pack_options"]
-        self = cls(shim, int8=po["int8"], ffn_sparse=po["ffn_sparse"], head_split=po["head_split"],
+        self = cls(shim, int8=po["int8"], fp16_weights=po.get("fp16_weights", False), ffn_sparse=po["ffn_sparse"],
+                   head_split=po["head_split"],
                    head_umma=po["head_umma"], proj_umma=po["proj_umma"] or False, _packed=(man, blob["tensors"]), **kw)
         if self.weights_digest() != man["sha256"]:
             raise ValueError(f"{path}: the packed weights do not match the manifest's SHA-256")

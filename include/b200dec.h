@@ -20,11 +20,15 @@ extern "C" {
 #endif
 
 enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* weight storage of one projection */
-       B200DEC_W_INT8_UMMA = 3 };  /* int8 in the block layout of the tcgen05 kernels (b200dec_tile_int8_umma): the
+       B200DEC_W_INT8_UMMA = 3,    /* int8 in the block layout of the tcgen05 kernels (b200dec_tile_int8_umma): the
                                       vocabulary projection (b200dec_head_umma) and, through b200dec_linear_linked,
                                       layer projections on fp16 rows (a_kind B200DEC_A_F16, or B200DEC_A_F16_ROWS16
                                       with a LayerNorm): N a multiple of 128, K = 1024 with w->ksplit 4 or 8, or
                                       K = 4096 with w->ksplit 8 and no LayerNorm */
+       B200DEC_W_F16 = 4 };        /* fp16 values in the layout of B200DEC_W_BF16 (b200dec_tile_bf16 moves 16-bit
+                                      words): no scale; multiplied as fp16 x fp16 with fp32 accumulation, so it takes
+                                      every operand kind and tile the int8 weights take (fp16 rows, the linked
+                                      LayerNorm, rows dealt over CTAs) */
 enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1,  /* activation operand of a projection: one fp16, or hi + lo */
        B200DEC_A_F16_ROWS16 = 2 };  /* one fp16, and with a LayerNorm the rows handed in are its ready fp16 operand
                                       (see b200dec_ln_link) */

@@ -81,6 +81,7 @@ def test_config1_bf16_against_transformers_golden(model16, golden_dir):
 
 
 @pytest.mark.parametrize("mode,kw", [("bf16", {}), ("int8", dict(int8=True)), ("int8_24", dict(int8=True, ffn_sparse=True)),
+                                     ("fp16", dict(fp16_weights=True)),
                                      ("int8_kv8", dict(int8=True, kv_int8=True)),
                                      ("int8_umma_all", dict(int8=True, proj_umma="all")),
                                      ("int8_no_umma", dict(int8=True, proj_umma=False)),
@@ -97,7 +98,8 @@ def test_ragged_batch_logits_and_greedy_agreement(model16, state16, mode, kw):
     dec = _decoder(model16, slots=8, max_new_tokens=64, max_prompt=16, max_audio_s=30.0, eos=-1, record=True, **kw)
     slots = [5, 0, 7, 2, 3]
     lg, am = _run_teacher_forced(dec, memory, prompts, steps, slots)
-    w = effective_weights(state16, 8, "int8_24" if "24" in mode else "int8" if mode.startswith("int8") else mode, tables="bf16")
+    # the fp16 mode stores fp16(bf16(w)): the bf16 value itself wherever |w| >= 2^-14, within 2^-25 of it below
+    w = effective_weights(state16, 8, "int8_24" if "24" in mode else "int8" if mode.startswith("int8") else "bf16", tables="bf16")
     so = StreamOracle(w, OracleConfig.of(model16.config), slots=8, max_new_tokens=64, max_prompt=16, frames=dec.frames,
                       kv_round="int8" if mode == "int8_kv8" else None, eos=-1, record=True)
     so.fill_cross(np.concatenate(memory), frames, slots)

@@ -78,6 +78,15 @@ def test_tiled_layouts(nv, pk):
     t = p.tiled.view(torch.bfloat16).float().cpu().numpy().reshape(n // 16, k // 32, 2, 8, 4, 8)
     want = bf16_round(w).reshape(n // 16, 2, 8, k // 32, 4, 8).transpose(0, 3, 1, 2, 4, 5)
     assert np.array_equal(t, want)
+    # fp16: the same layout holding fp16(bf16(w)); with these magnitudes every value is the bf16 one exactly
+    p = pk.pack_linear(cuda(w), None, nv.W_F16)
+    t16 = p.tiled.view(torch.float16).float().cpu().numpy().reshape(n // 16, k // 32, 2, 8, 4, 8)
+    big = np.abs(want) >= 2.0 ** -14
+    assert np.array_equal(t16[big], want[big]) and np.abs(t16 - want).max() <= 2.0 ** -25
+    assert np.array_equal(pk.dequantized(cuda(w), nv.W_F16).cpu().numpy().reshape(n // 16, 2, 8, k // 32, 4, 8)
+                          .transpose(0, 3, 1, 2, 4, 5), t16)
+    with pytest.raises(AssertionError):
+        pk.pack_linear(cuda(w * 1e7), None, nv.W_F16)
     # 2:4: value byte [nt][kb][h][lane][2 s + j] = kept[row][2 G + j], G = 32 kb + 2 (4 (s / 2) + t) + (s & 1);
     # selector nibble s of word [nt][kb][h][lane] = the selector of group G
     p = pk.pack_linear(cuda(w), None, nv.W_INT8_24, keep_reference=True)
@@ -158,7 +167,8 @@ def test_linear_int8(nv, pk, n, k, rows):
     np.testing.assert_allclose(got, want, atol=2e-4, rtol=1e-5)
 
 
-@pytest.mark.parametrize("kind,a_kind", [("W_INT8", "A_F32_SPLIT"), ("W_BF16", "A_F32_SPLIT"), ("W_INT8_24", "A_F16")])
+@pytest.mark.parametrize("kind,a_kind", [("W_INT8", "A_F32_SPLIT"), ("W_BF16", "A_F32_SPLIT"), ("W_INT8_24", "A_F16"),
+                                         ("W_F16", "A_F16"), ("W_F16", "A_F32_SPLIT")])
 @pytest.mark.parametrize("n,k", [(1024, 1024), (4096, 1024), (1024, 4096)])
 @pytest.mark.parametrize("rows", [3, 64, 100])
 def test_linear_kinds(nv, pk, kind, a_kind, n, k, rows):
@@ -169,7 +179,7 @@ def test_linear_kinds(nv, pk, kind, a_kind, n, k, rows):
 
 
 @pytest.mark.parametrize("kind,a_kind", [("W_INT8", "A_F16"), ("W_INT8", "A_F32_SPLIT"), ("W_BF16", "A_F32_SPLIT"),
-                                         ("W_INT8_24", "A_F16")])
+                                         ("W_INT8_24", "A_F16"), ("W_F16", "A_F16")])
 @pytest.mark.parametrize("n", [1024, 3072, 4096])
 @pytest.mark.parametrize("rows", [2, 64, 128])
 def test_linear_layernorm_on_load(nv, pk, kind, a_kind, n, rows):
@@ -187,7 +197,7 @@ def _row_sums(x):
     return np.stack([x.astype(np.float64).sum(1), (x.astype(np.float64) ** 2).sum(1)], 1)
 
 
-@pytest.mark.parametrize("kind", ["W_INT8", "W_INT8_24"])
+@pytest.mark.parametrize("kind", ["W_INT8", "W_INT8_24", "W_F16"])
 @pytest.mark.parametrize("n", [1024, 3072, 4096])
 @pytest.mark.parametrize("rows", [2, 13, 64, 128])
 def test_linear_linked_layernorm(nv, pk, kind, n, rows):

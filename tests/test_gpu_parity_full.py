@@ -17,6 +17,8 @@ pytestmark = pytest.mark.gpu
 
 LOGIT_TOL = 2e-2
 MODES = {"bf16": {}, "int8": dict(int8=True), "int8_24": dict(int8=True, ffn_sparse=True)}
+# the fp16 mode stores fp16(bf16(w)), within 2^-25 of the bf16 weights the config2 golden was made with
+OVERRIDES = {"config2_fp16": ("config2", dict(fp16_weights=True))}
 
 
 @pytest.fixture(scope="module")
@@ -24,9 +26,11 @@ def model16():
     return synthetic_model(0).cuda()
 
 
-@pytest.mark.parametrize("name", ["config2", "config3", "config3_kv8", "sparse128"])
+@pytest.mark.parametrize("name", ["config2", "config2_fp16", "config3", "config3_kv8", "sparse128"])
 def test_teacher_forced_against_transformers_golden(model16, golden_dir, name):
     from cohere_inference_b200 import StreamDecoder
+    label = name
+    name, mode_kw = OVERRIDES.get(name, (name, None))
     wl = parity_workload(name)
     g = np.load(os.path.join(golden_dir, f"decoder_{name}.npz"))
     B, plen = wl.prompts.shape
@@ -37,7 +41,7 @@ def test_teacher_forced_against_transformers_golden(model16, golden_dir, name):
     # the whole golden sequence goes in as a forced prompt, so every step feeds the golden token; the decoder records
     # its own un-forced choice and the step's logits
     dec = StreamDecoder(model16, slots=B, max_new_tokens=1, max_prompt=total, max_audio_s=30.0, buckets=(B,), eos=-1,
-                        record=True, kv_int8=wl.kv_int8, **MODES[wl.mode])
+                        record=True, kv_int8=wl.kv_int8, **(MODES[wl.mode] if mode_kw is None else mode_kw))
     slots = list(range(B))
     with torch.cuda.stream(dec.stream):
         dec.fill_cross(torch.from_numpy(np.concatenate(wl.memory)).cuda(), wl.frames, slots)
@@ -68,7 +72,7 @@ def test_teacher_forced_against_transformers_golden(model16, golden_dir, name):
     # its own; the others are near-ties that either side may resolve differently
     wide = (~agree) & (gap > 2 * LOGIT_TOL)
     worst = np.unravel_index(np.argmax(err_top), err_top.shape)
-    print(f"{name}: {B * steps} row-steps, greedy agreement {rate:.5f} ({(~agree).sum()} differ, largest golden gap "
+    print(f"{label}: {B * steps} row-steps, greedy agreement {rate:.5f} ({(~agree).sum()} differ, largest golden gap "
           f"among them {gap[~agree].max() if (~agree).any() else 0:.2e}), max-abs logit error {max(err_top.max(), err_sub.max()):.2e} "
           f"(top logit: row {worst[0]} step {worst[1]}; sampled entries {err_sub.max():.2e})")
     assert err_top.max() <= LOGIT_TOL and err_sub.max() <= LOGIT_TOL

@@ -141,7 +141,8 @@ def run_ours(args) -> None:
     torch.cuda.set_device(dev)
     model = synthetic_model(0).to(dev)
     dec = StreamDecoder(model, slots=BATCH, max_new_tokens=NEW, max_prompt=16, max_audio_s=30.0, buckets=(BATCH,),
-                        int8=True, eos=-1, pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
+                        int8=not args.fp16_weights, fp16_weights=args.fp16_weights, eos=-1,
+                        pdl=0 if args.no_pdl else args.pdl, chains=args.chains, attn_ring=args.attn_ring,
                         head_split=not args.no_head_split, head_umma=not args.no_head_umma, kv_int8=args.kv_int8,
                         proj_umma=False if args.no_proj_umma else (args.proj_umma or True), kv_prefetch_mb=args.kv_prefetch)
     digest = dec.weights_digest()
@@ -371,11 +372,12 @@ def run_ours(args) -> None:
                               "the embedding / vocabulary projection / pick; time of a class = its pass minus the pass "
                               "of those three alone; bytes and fraction of the measured HBM peak per step"}
         line = {
-            "metric": "decoded tokens/s at batch 64, weight-only int8" + (", int8 KV caches" if args.kv_int8 else ""),
+            "metric": "decoded tokens/s at batch 64, " + ("fp16 weights (not the benchmark's mode)" if args.fp16_weights else
+                                                          "weight-only int8") + (", int8 KV caches" if args.kv_int8 else ""),
             "value": round(value, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 weights x fp16, fp32 accumulate", "data": "synthetic",
+            "dtype": ("fp16 weights" if args.fp16_weights else "int8 weights") + " x fp16, fp32 accumulate", "data": "synthetic",
             "config": {"workload": "BASELINE config 3: 8 layers x 1024, 16 heads x 64, GELU, vocab 16384; batch 64 per GPU, "
                                    "encoder lengths U[50,375], 10-token prompts + 448 new tokens, one CUDA graph per "
                                    "decoding step; a bench step = one pass = 457 replays",
@@ -638,6 +640,8 @@ def main() -> None:
     ap.add_argument("--proj-umma", default="", help="all, or a subset of qkv,o,cq,co,fc1,fc2 on tcgen05 (default: qkv,fc1)")
     ap.add_argument("--no-head-umma", action="store_true", help="vocabulary projection on mma.sync instead of tcgen05")
     ap.add_argument("--no-head-split", action="store_true", help="vocabulary projection on a single fp16 operand")
+    ap.add_argument("--fp16-weights", action="store_true", help="the 16-bit weight mode (fp16 image of the bf16 weights) "
+                    "instead of int8: a separate row, not the benchmark's configuration")
     ap.add_argument("--kv-int8", action="store_true", help="int8 KV caches with per-vector scales (the reference's int8 "
                     "mode); a separate row, the headline keeps bf16 caches")
     ap.add_argument("--attn-ring", action="store_true", help="use the persistent bulk-copy attention kernel")

@@ -425,33 +425,39 @@ __global__ void __launch_bounds__(NTHREADS, 1) head_umma_kernel(const HeadArgs p
 // stage kb (XS = LOOK + AST stages: block kb + LOOK reuses the stage of block kb - AST).
 // The rows' statistics: a warp per row, the row's partial sums read with coalesced loads that are all in flight at
 // once (four threads per row walking 128 slots one after the other took 3.5 us of the resident-operand kernel).
-template <int UNS>
+// fp16 weights (W16, kind B200DEC_W_F16_UMMA) are stored as the images of the swizzled weight tiles: the producer lane
+// copies a block from HBM straight into a weight stage (`cp.async.bulk`, the stage's barrier counts its bytes beside
+// the workers' arrivals for the operand block), there is no raw ring and no widening, the shared memory that ring took
+// holds more weight stages (9 or 7 blocks of 16 KB in flight), and the operand stages are freed by a commit of their
+// own.
+template <int UNS, bool W16>
 struct HeadStream {
-  static constexpr int AST = 4;                      // weight-tile stages
+  static constexpr int AST = W16 ? (UNS == 64 ? 9 : 7) : 4;  // weight-tile stages
   static constexpr int NWK = 16;                     // worker warps: one 16-byte piece of a weight block per thread
   static constexpr int NT = (NWK + 2) * 32;          // + the MMA warp and the producer warp
   static constexpr int LOOK = UNS == 64 ? 4 : 2;     // operand blocks requested ahead
-  static constexpr int XS = LOOK + AST;
+  static constexpr int XS = LOOK + 4;                // int8: block kb + LOOK reuses the stage of block kb - AST
   static constexpr int XB = UNS * KB * 2;            // one k-block of the operand: 8 or 16 KB
-  static constexpr int RAW = UNS == 64 ? 10 : 7;     // weight blocks in flight: what fits beside the other rings
+  static constexpr int RAW = W16 ? 0 : UNS == 64 ? 10 : 7;  // raw weight blocks in flight: what fits beside the other rings
   static constexpr int OFF_X = 0, OFF_A = XS * XB, OFF_RAW = OFF_A + AST * A_BYTES, USED = OFF_RAW + RAW * RAW_BYTES;
   static constexpr int BYTES = USED + 1024;
   static constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(UNS >> 3) << 17) | ((uint32_t)(UM >> 4) << 24);
   static_assert(UNS * OUT_LD * 4 <= USED - OFF_A, "epilogue tile fits in the weight rings");
   static_assert(BYTES + 4096 <= 227 * 1024, "rings + static shared memory fit an SM");
-  static_assert(NKB % 2 == 0 && AST % 2 == 0, "the workers hand over blocks in pairs");
+  static_assert(W16 || (NKB % 2 == 0 && AST % 2 == 0 && XS == LOOK + AST), "the workers hand over blocks in pairs");
+  static_assert(!W16 || AST > XS - LOOK, "a weight stage's previous use is over before the workers arrive for the next");
 };
 
-template <int UNS>
-__global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(const HeadArgs p) {
-  using C = HeadStream<UNS>;
-  constexpr int RS = C::RAW, LOOK = C::LOOK, XS = C::XS, AST = C::AST, NWK = C::NWK;
+template <int UNS, bool W16>
+__global__ void __launch_bounds__(HeadStream<UNS, W16>::NT, 1) head_stream_kernel(const HeadArgs p) {
+  using C = HeadStream<UNS, W16>;
+  constexpr int RS = W16 ? 1 : C::RAW, LOOK = C::LOOK, XS = C::XS, AST = C::AST, NWK = C::NWK;
   extern __shared__ unsigned char dyn_smem[];
   unsigned char* smem = dyn_smem + ((1024 - (smem_u32(dyn_smem) & 1023)) & 1023);  // swizzle atoms are 1 KB aligned
   unsigned char* xs = smem + C::OFF_X;
   unsigned char* as = smem + C::OFF_A;
   unsigned char* raws = smem + C::OFF_RAW;
-  __shared__ __align__(8) uint64_t raw_full[RS], raw_empty[RS], a_full[AST], a_empty[AST];
+  __shared__ __align__(8) uint64_t raw_full[RS], raw_empty[RS], a_full[AST], a_empty[AST], x_empty[XS];
   __shared__ __align__(8) uint64_t d_full;
   __shared__ uint32_t tmem_base;
   __shared__ float s_scale[UM], s_bias[UM], s_g[UM];
@@ -459,11 +465,13 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x;  // channels [128 tile, +128)
-  const uint8_t* wsrc = p.w + (size_t)tile * NKB * RAW_BYTES;
+  const uint8_t* wsrc = p.w + (size_t)tile * NKB * (W16 ? A_BYTES : RAW_BYTES);
 
   if (tid == 0) {
     for (int i = 0; i < RS; ++i) mbar_init(&raw_full[i], 1), mbar_init(&raw_empty[i], NWK);
-    for (int i = 0; i < AST; ++i) mbar_init(&a_full[i], NWK), mbar_init(&a_empty[i], 1);
+    // fp16 weights: a stage is full when the workers' operand pieces and the producer's bytes are there
+    for (int i = 0; i < AST; ++i) mbar_init(&a_full[i], W16 ? NWK + 1 : NWK), mbar_init(&a_empty[i], 1);
+    for (int i = 0; i < XS; ++i) mbar_init(&x_empty[i], 1);
     mbar_init(&d_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -474,7 +482,7 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   if (tid < UM) {
-    s_scale[tid] = p.scale[tile * UM + tid];
+    s_scale[tid] = p.scale ? p.scale[tile * UM + tid] : 1.f;
     s_bias[tid] = (p.bias ? p.bias[tile * UM + tid] : 0.f) + p.ln_bias[tile * UM + tid];
     s_g[tid] = p.ln_g[tile * UM + tid];
   }
@@ -484,23 +492,29 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
   const uint32_t tmem_d = tmem_base;
 
   if (warp == NWK + 1) {
-    // ---- producer: the tile's sixteen weight blocks through the raw ring (independent of the previous kernel) -------
+    // ---- producer: the tile's sixteen weight blocks through the raw ring, or (fp16) straight into the weight stages
+    // (independent of the previous kernel) ------------------------------------------------------------------------------
     if (lane == 0) {
+      constexpr int PS = W16 ? AST : RS;                      // the ring the producer fills
+      constexpr uint32_t PB = W16 ? A_BYTES : RAW_BYTES;      // bytes per block
+      uint64_t* full = W16 ? a_full : raw_full;
+      uint64_t* empty = W16 ? a_empty : raw_empty;
+      unsigned char* ring = W16 ? as : raws;
       bool ok = true;
       int issued = 0;
       for (int kb = 0; kb < NKB && ok; ++kb) {
         if (p.withhold && kb == 3) break;  // tests only: nothing sets the barriers of block 3
-        const int st = kb % RS;
-        ok = mbar_wait(&raw_empty[st], ((kb / RS) & 1) ^ 1, p.wait_limit);
+        const int st = kb % PS;
+        ok = mbar_wait(&empty[st], ((kb / PS) & 1) ^ 1, p.wait_limit);
         if (!ok) break;
-        mbar_expect_tx(&raw_full[st], RAW_BYTES);
-        bulk_load(raws + st * RAW_BYTES, wsrc + (size_t)kb * RAW_BYTES, RAW_BYTES, &raw_full[st]);
+        mbar_expect_tx(&full[st], PB);
+        bulk_load(ring + st * PB, wsrc + (size_t)kb * PB, PB, &full[st]);
         issued = kb + 1;
       }
       if (!ok) {
         atomicOr(p.status, B200DEC_ST_TIMEOUT);
-        for (int kb = issued > RS ? issued - RS : 0; kb < issued; ++kb)  // copies in flight land before the CTA leaves
-          mbar_wait(&raw_full[kb % RS], (kb / RS) & 1, p.wait_limit);
+        for (int kb = issued > PS ? issued - PS : 0; kb < issued; ++kb)  // copies in flight land before the CTA leaves
+          mbar_wait(&full[kb % PS], (kb / PS) & 1, p.wait_limit);
       }
     }
   } else if (warp == NWK) {
@@ -517,6 +531,7 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
         for (int k = 0; k < KB / 16; ++k)
           umma_f16_n<C::IDESC>(tmem_d, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), (kb | k) != 0);
         umma_commit(&a_empty[st]);
+        if constexpr (W16) umma_commit(&x_empty[kb % XS]);
       }
       if (!ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
       umma_commit(&d_full);  // arrives when everything issued so far has completed (also after a time-out)
@@ -568,7 +583,21 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
     bool ok = true;
     const int ch = (warp & 3) * 32 + lane;  // this thread's channel of the tile (= its tensor-memory lane)
     const int pj = warp >> 2;               // and its quarter: the 16-k piece pj of a block, rows pj * UNS / 4 .. after
-    for (int kb = 0; kb < NKB && ok; kb += 2) {  // two blocks per turn
+    if constexpr (W16) {
+      // fp16 weights: the workers only keep the operand ring LOOK blocks ahead and vouch for their pieces of block kb
+      for (int kb = 0; kb < NKB; ++kb) {
+        const int nb = kb + LOOK;
+        if (nb < NKB && nb >= XS)  // the MMAs of block nb - XS, the stage's previous tenant, are done
+          ok = mbar_wait(&x_empty[nb % XS], ((nb / XS) - 1) & 1, p.wait_limit);
+        if (!ok) break;
+        request_x(nb);
+        cp_async_wait_group<LOOK>();  // this thread's pieces of operand block kb (and earlier) have landed
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[kb % AST]);
+      }
+    }
+    for (int kb = 0; kb < (W16 ? 0 : NKB) && ok; kb += 2) {  // two blocks per turn
       uint4 r[2];
 #pragma unroll
       for (int b = 0; b < 2; ++b) {
@@ -678,6 +707,17 @@ __global__ void __launch_bounds__(HeadStream<UNS>::NT, 1) head_stream_kernel(con
   }
 }
 
+// w (n, k) 16-bit row-major -> blocks [n / 128][k / 64] of 16 KB, each the image of a K-major tile with the 128-byte
+// swizzle: channel t's 128-byte row at 128 t, its 16-byte chunk c (k = 8 c .. 8 c + 7 of the block) at position c ^ (t & 7)
+__global__ void tile_f16_umma_kernel(const uint16_t* __restrict__ w, int n, int k, uint16_t* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one output element each
+  if (i >= (size_t)n * k) return;
+  const int e = i & 7, pos = (i >> 3) & 7, t = (i >> 6) & 127;
+  const size_t blk = i >> 13;
+  const int nkb = k / KB, kb = (int)(blk % nkb), mt = (int)(blk / nkb), c = pos ^ (t & 7);
+  out[i] = w[(size_t)(mt * UM + t) * k + kb * KB + c * 8 + e];
+}
+
 // q (n, k) int8 row-major -> blocks [n / 128][k / 64] of 8 KB: [16-k piece j = 0..3][channel t = 0..127][16 bytes],
 // bytes = q + 128
 __global__ void tile_int8_umma_kernel(const int8_t* __restrict__ q, int n, int k, uint8_t* __restrict__ out) {
@@ -698,11 +738,14 @@ namespace b200dec_detail {
 int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, const float* stats, int stats_slots,
                    const b200dec_norm* ln, int lda, int rows, float* part_max, int32_t* part_idx, float* logits,
                    int32_t* status, int pdl, void* stream, int wait_limit, int withhold) {
-  B200_REQUIRE(w && w->w && w->scale && (x || xg) && ln && ln->w && ln->b && part_max && part_idx && status,
+  B200_REQUIRE(w && w->w && (x || xg) && ln && ln->w && ln->b && part_max && part_idx && status,
                "head_umma: null pointer");
+  const bool w16 = w->kind == B200DEC_W_F16_UMMA;
+  B200_REQUIRE(w16 == (w->scale == nullptr) && ((uintptr_t)w->w & 15) == 0, "head_umma: scale present iff int8");
+  B200_REQUIRE(!w16 || xg, "head_umma: fp16 weights take the ready fp16 operand (b200dec_head_umma_linked)");
   B200_REQUIRE(!xg || (stats && stats_slots >= 1 && w->ln_g && w->ln_bias && ((uintptr_t)xg & 15) == 0 && lda % 8 == 0),
                "head_umma: the fp16 operand comes with its partial sums and the weight's ln_g / ln_bias");
-  B200_REQUIRE(w->kind == B200DEC_W_INT8_UMMA && w->k == D_MODEL && w->n % UM == 0, "head_umma: weight kind %d (%d, %d)",
+  B200_REQUIRE((w->kind == B200DEC_W_INT8_UMMA || w16) && w->k == D_MODEL && w->n % UM == 0, "head_umma: weight kind %d (%d, %d)",
                w->kind, w->n, w->k);
   B200_REQUIRE(rows >= 1 && rows <= 128 && lda % 4 == 0 && ((uintptr_t)x & 15) == 0, "head_umma: rows %d lda %d", rows,
                lda);
@@ -722,17 +765,16 @@ int head_umma_impl(const b200dec_weight* w, const float* x, const void* xg, cons
   a.wait_limit = wait_limit > 0 ? (uint32_t)wait_limit : WAIT_LIMIT, a.withhold = withhold;
   if (xg) {  // the ready operand: streamed, one CTA per tile whatever the rows (at most 128 partial sums per row)
     B200_REQUIRE(stats_slots <= 128, "head_umma: %d partial sums per row (at most 128)", stats_slots);
-    if (rows <= UN) {
-      e = cudaFuncSetAttribute(head_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<64>::BYTES);
-      if (e == cudaSuccess)
-        e = launch_kernel(head_stream_kernel<64>, dim3(np), dim3(HeadStream<64>::NT), HeadStream<64>::BYTES, (cudaStream_t)stream, 0,
-                          pdl, a);
-    } else {
-      e = cudaFuncSetAttribute(head_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, HeadStream<128>::BYTES);
-      if (e == cudaSuccess)
-        e = launch_kernel(head_stream_kernel<128>, dim3(np), dim3(HeadStream<128>::NT), HeadStream<128>::BYTES, (cudaStream_t)stream,
-                          0, pdl, a);
-    }
+    auto go = [&](auto kern, int threads, int bytes) {
+      cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+      return err != cudaSuccess ? err : launch_kernel(kern, dim3(np), dim3(threads), bytes, (cudaStream_t)stream, 0, pdl, a);
+    };
+    if (rows <= UN)
+      e = w16 ? go(head_stream_kernel<64, true>, HeadStream<64, true>::NT, HeadStream<64, true>::BYTES)
+              : go(head_stream_kernel<64, false>, HeadStream<64, false>::NT, HeadStream<64, false>::BYTES);
+    else
+      e = w16 ? go(head_stream_kernel<128, true>, HeadStream<128, true>::NT, HeadStream<128, true>::BYTES)
+              : go(head_stream_kernel<128, false>, HeadStream<128, false>::NT, HeadStream<128, false>::BYTES);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "head_umma (streamed operand) launch: %s", cudaGetErrorString(e));
     return 0;
   }
@@ -754,6 +796,15 @@ int b200dec_tile_int8_umma(const int8_t* q, int n, int k, void* tiled, void* str
   const size_t total = (size_t)n * k;
   tile_int8_umma_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(q, n, k, (uint8_t*)tiled);
   return check_launch("tile_int8_umma");
+}
+
+int b200dec_tile_f16_umma(const void* w16, int n, int k, void* tiled, void* stream) {
+  B200_REQUIRE(w16 && tiled && n > 0 && n % UM == 0 && k > 0 && k % KB == 0, "tile_f16_umma: (%d, %d) must be multiples of (128, 64)",
+               n, k);
+  const size_t total = (size_t)n * k;
+  tile_f16_umma_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint16_t*)w16, n, k,
+                                                                                          (uint16_t*)tiled);
+  return check_launch("tile_f16_umma");
 }
 
 int b200dec_head_umma(const b200dec_weight* w, const float* x, const b200dec_norm* ln, int lda, int rows,

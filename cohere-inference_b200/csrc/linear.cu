@@ -85,6 +85,7 @@ bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int ro
     case B200DEC_W_INT8_24: return fits_24(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_F16: return fits_f16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_UMMA:  // linear_umma.cu: fp16 rows, plain or as a LayerNorm's ready operand
+    case B200DEC_W_F16_UMMA:
       return !split && rows <= 128 && ln != 1 &&
              ((k == D_MODEL && (ksplit == 4 || ksplit == 8)) || (k == 4 * D_MODEL && ksplit == 8 && ln == 0));
   }
@@ -104,7 +105,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
                const b200dec_ln_link* link = nullptr, const KvPrefetch* pf = nullptr) {
   B200_REQUIRE(w && w->w && a, "linear: null pointer");
   B200_REQUIRE(rows >= 1 && rows <= 128, "linear: rows %d outside 1..128", rows);
-  if (w->kind == B200DEC_W_INT8_UMMA) {  // the tcgen05 kernel of linear_umma.cu
+  if (is_umma_kind(w->kind)) {  // the tcgen05 kernel of linear_umma.cu
     B200_REQUIRE(!head && link && link->status, "linear: a tcgen05 projection goes through b200dec_linear_linked with a "
                  "status word");
     return linear_umma_impl(w, a, a_kind, ln, lda, rows, out, out_kind, ldo, act, link, link->status, pdl, stream);
@@ -186,7 +187,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
 namespace b200dec_detail {
 // launches one call of linear_impl makes (1, or 2 when the rows go in two passes)
 int linear_passes(const b200dec_weight* w, int a_kind, bool ln, int rows) {
-  if (w->kind == B200DEC_W_INT8_UMMA) return (w->k == 4 * D_MODEL && rows > 64) ? 2 : 1;
+  if (is_umma_kind(w->kind)) return (w->k == 4 * D_MODEL && rows > 64) ? 2 : 1;
   const bool split = a_kind == B200DEC_A_F32_SPLIT;
   const int lnorm = !ln ? 0 : a_kind == B200DEC_A_F16_ROWS16 ? 2 : 1;
   const bool two_pass_wide = rows > 64 && w->k == 4096 && (split || lnorm != 0 || w->kind == B200DEC_W_BF16);
@@ -226,12 +227,12 @@ int b200dec_head_argmax(const b200dec_weight* w, const void* a, int a_kind, cons
 
 int b200dec_linear_stat_slots(const b200dec_weight* w) {
   if (!w) return 0;
-  return w->kind == B200DEC_W_INT8_UMMA ? (w->n / 128) * w->ksplit : (w->n / (16 * w->warps)) * w->ksplit;
+  return is_umma_kind(w->kind) ? (w->n / 128) * w->ksplit : (w->n / (16 * w->warps)) * w->ksplit;
 }
 
 int b200dec_head_partials(const b200dec_weight* w) {
   if (!w) return 0;
-  return w->kind == B200DEC_W_INT8_UMMA ? w->n / 128 : (w->n / (16 * w->warps)) * w->ksplit;
+  return is_umma_kind(w->kind) ? w->n / 128 : (w->n / (16 * w->warps)) * w->ksplit;
 }
 
 int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int k, int rows) {
@@ -242,7 +243,7 @@ int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int
 
 int64_t b200dec_tiled_bytes(int kind, int n, int k) {
   if (kind == B200DEC_W_INT8 || kind == B200DEC_W_INT8_UMMA) return (int64_t)n * k;
-  if (kind == B200DEC_W_BF16 || kind == B200DEC_W_F16) return (int64_t)n * k * 2;
+  if (kind == B200DEC_W_BF16 || kind == B200DEC_W_F16 || kind == B200DEC_W_F16_UMMA) return (int64_t)n * k * 2;
   if (kind == B200DEC_W_INT8_24) return (int64_t)n * k / 2;
   return -1;
 }

@@ -15,7 +15,10 @@
 //     epilogue: y = rstd * (acc * scale - mean * g) + ln_bias + bias (or acc * scale + bias), activation, fp16 or fp32
 //     store or add into the residual stream, and for a projection that updates the stream the next LayerNorm's
 //     operand and partial sums (b200dec_ln_link).
-// The wait for the MMAs is bounded (B200DEC_ST_TIMEOUT); tensor memory is released on every path.
+// fp16 weights (B200DEC_W_F16_UMMA, template flag W16) are stored as the images of those swizzled tiles
+// (b200dec_tile_f16_umma): one lane copies the CTA's blocks from HBM into the A tiles with `cp.async.bulk` onto an
+// mbarrier before the dependency wait, no thread touches a weight, and the MMA lane waits for that barrier.
+// The waits for the copies and the MMAs are bounded (B200DEC_ST_TIMEOUT); tensor memory is released on every path.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -97,6 +100,12 @@ DEVI void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulat
       "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+DEVI void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 DEVI void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
@@ -135,7 +144,7 @@ DEVI void tmem_ld32(uint32_t taddr, uint32_t (&d)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int MB, int KSPLIT, int NKB, bool LN>
+template <int MB, int KSPLIT, int NKB, bool LN, bool W16>
 __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p) {
   using S = USmem<MB, KSPLIT, NKB>;
   constexpr int CPR = S::CPR, GPR = CPR / 4, KSLICE = NKB * KB;
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   unsigned char* xs = smem + S::OFF_X;
   float* recv = reinterpret_cast<float*>(smem + S::OFF_RECV);  // [KSPLIT][MB][CPR]
   float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
-  __shared__ __align__(8) uint64_t d_full;
+  __shared__ __align__(8) uint64_t d_full, w_full;
   __shared__ uint32_t tmem_base;
 
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
@@ -156,8 +165,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   const int hf = warp >> 2;               // its half: 16-k pieces 2 hf, 2 hf + 1 of a block; rows hf * MB / 2 ..
 
   // ---- prologue: the CTA's weight blocks into registers (independent of the previous kernel) ----------------------
-  uint4 wr[NKB][2];
-  {
+  uint4 wr[W16 ? 1 : NKB][2];
+  if constexpr (!W16) {
     const uint8_t* wsrc = p.w + ((size_t)tile * (p.K / KB) + rank * NKB) * RAW_BYTES + ch * 16;
 #pragma unroll
     for (int b = 0; b < NKB; ++b)
@@ -166,7 +175,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   }
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&d_full)));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&w_full)));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if constexpr (W16) {  // the CTA's blocks are the tiles' images: HBM -> A tiles, no thread in between
+      const uint8_t* wsrc = p.w + ((size_t)tile * (p.K / KB) + rank * NKB) * A_BYTES;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&w_full)), "r"(NKB * A_BYTES)
+                   : "memory");
+#pragma unroll
+      for (int b = 0; b < NKB; ++b) bulk_load(as + b * A_BYTES, wsrc + (size_t)b * A_BYTES, A_BYTES, &w_full);
+    }
   }
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "n"(MB)
@@ -176,7 +193,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   // ---- widen the weights into the A tiles: they depend on nothing the previous kernel writes, so this happens in
   // front of the dependency wait, under the previous kernel's tail (the tiles are this CTA's own shared memory)
 #pragma unroll
-  for (int b = 0; b < NKB; ++b) {
+  for (int b = 0; b < (W16 ? 0 : NKB); ++b) {
     unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
@@ -227,7 +244,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   const uint32_t tmem_d = tmem_base;
 
   // ---- multiply: one lane, 4 instructions per block, completion through an mbarrier ---------------------------------
+  bool w_ok = true;
   if (tid == 0) {
+    if constexpr (W16) {
+      w_ok = mbar_wait(&w_full, 0, p.wait_limit);  // the weight tiles have landed (async proxy: no fence needed)
+      if (!w_ok) atomicOr(p.status, B200DEC_ST_TIMEOUT);
+    }
     // the descriptors of block 0; a k-step of 16 advances a tile's start by 32 bytes = 2 units of its address field, a
     // block by the tile's size (the tiles are 1 KB aligned and lie below 256 KB: no carry out of the field)
     const uint64_t da = umma_desc(smem_u32(as)), db = umma_desc(smem_u32(xs));
@@ -263,7 +285,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   const int items = p.rows * GPR;
   const int n_mine = tile * UM + rank * CPR + (tid % GPR) * 4;
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f), one4 = make_float4(1.f, 1.f, 1.f, 1.f);
-  const float4 sc = __ldg(reinterpret_cast<const float4*>(p.scale + n_mine));
+  const float4 sc = p.scale ? __ldg(reinterpret_cast<const float4*>(p.scale + n_mine)) : one4;
   const float4 gg = LN ? __ldg(reinterpret_cast<const float4*>(p.ln_g + n_mine)) : zero4;
   const float4 lb = LN ? __ldg(reinterpret_cast<const float4*>(p.ln_bias + n_mine)) : zero4;
   const float4 bb = p.bias ? __ldg(reinterpret_cast<const float4*>(p.bias + n_mine)) : zero4;
@@ -325,6 +347,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
     }
   }
   // ---- release the tensor memory ----------------------------------------------------------------------------------------
+  if constexpr (W16) {  // copies that had not landed in time get a second bounded chance before the tiles are given away
+    if (tid == 0 && !w_ok) mbar_wait(&w_full, 0, p.wait_limit);
+  }
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
@@ -332,13 +357,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   }
 }
 
-template <int MB, int KSPLIT, int NKB, bool LN>
+template <int MB, int KSPLIT, int NKB, bool LN, bool W16>
 int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
   using S = USmem<MB, KSPLIT, NKB>;
   if constexpr (S::BYTES > 227 * 1024 - 512) {
     return fail(B200DEC_EINVAL, "linear_umma: %d rows of K / %d do not fit shared memory", MB, KSPLIT);
   } else {
-    auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN>;
+    auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN, W16>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
     e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), S::BYTES, stream, KSPLIT, pdl, a);
@@ -347,23 +372,30 @@ int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
   }
 }
 
+template <int KSPLIT, int NKB, bool W16>
+int launch_rows16(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
+  if (a.rows <= 64)
+    return ln ? launch_umma<64, KSPLIT, NKB, true, W16>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false, W16>(a, pdl, s);
+  return ln ? launch_umma<128, KSPLIT, NKB, true, W16>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false, W16>(a, pdl, s);
+}
 template <int KSPLIT, int NKB>
-int launch_rows(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
-  if (a.rows <= 64) return ln ? launch_umma<64, KSPLIT, NKB, true>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false>(a, pdl, s);
-  return ln ? launch_umma<128, KSPLIT, NKB, true>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false>(a, pdl, s);
+int launch_rows(const UArgs& a, bool w16, bool ln, int pdl, cudaStream_t s) {
+  return w16 ? launch_rows16<KSPLIT, NKB, true>(a, ln, pdl, s) : launch_rows16<KSPLIT, NKB, false>(a, ln, pdl, s);
 }
 
 }  // namespace
 
 namespace b200dec_detail {
 
-// A projection whose weight is of kind B200DEC_W_INT8_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
+// A projection whose weight is of kind B200DEC_W_INT8_UMMA or B200DEC_W_F16_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
 // operand and link->stats_in its partial sums (b200dec_ln_link). w->ksplit: CTAs per cluster (K = 1024: 4 or 8;
 // K = 4096: 8, 64 rows per pass).
 int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                      void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
                      void* stream) {
-  B200_REQUIRE(w && w->w && w->scale && a && out && status, "linear_umma: null pointer");
+  B200_REQUIRE(w && w->w && a && out && status, "linear_umma: null pointer");
+  const bool w16 = w->kind == B200DEC_W_F16_UMMA;
+  B200_REQUIRE(w16 == (w->scale == nullptr) && ((uintptr_t)w->w & 15) == 0, "linear_umma: scale present iff int8");
   B200_REQUIRE((w->k == D_MODEL && (w->ksplit == 4 || w->ksplit == 8)) || (w->k == 4 * D_MODEL && w->ksplit == 8),
                "linear_umma: K %d split %d ways", w->k, w->ksplit);
   B200_REQUIRE(w->n % UM == 0, "linear_umma: N %d", w->n);
@@ -400,9 +432,9 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
     p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
     cudaStream_t s = (cudaStream_t)stream;
     int rc;
-    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, ln != nullptr, pdl, s);
-    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, ln != nullptr, pdl, s);
-    else rc = launch_rows<8, 8>(p, false, pdl, s);
+    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, w16, ln != nullptr, pdl, s);
+    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, w16, ln != nullptr, pdl, s);
+    else rc = launch_rows<8, 8>(p, w16, false, pdl, s);
     if (rc) return rc;
   }
   return 0;

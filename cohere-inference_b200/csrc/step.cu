@@ -65,7 +65,7 @@ int b200dec_step_launches(const b200dec_plan* pl, int rows) {
          linear_passes(&ly.cq, ln_kind, true, rows) + linear_passes(&ly.co, pl->a_kind, false, rows) +
          linear_passes(&ly.fc1, ln_kind, true, rows) + linear_passes(&ly.fc2, pl->a_kind, false, rows);
   }
-  n += pl->head.kind == B200DEC_W_INT8_UMMA ? 1 : linear_passes(&pl->head, pl->head_a_kind, true, rows);
+  n += is_umma_kind(pl->head.kind) ? 1 : linear_passes(&pl->head, pl->head_a_kind, true, rows);
   return n;
 }
 
@@ -122,7 +122,7 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
                      b200dec_linear_stat_slots(&l0.fc2) <= STAT_SLOTS, "step: more finishing CTAs than statistic slots");
   }
   // the tcgen05 vocabulary projection takes the last fc2's rows the same way when its weight carries the folded vectors
-  const bool head_linked = xh && pl->head.kind == B200DEC_W_INT8_UMMA && pl->head.ln_g && pl->head.ln_bias;
+  const bool head_linked = xh && is_umma_kind(pl->head.kind) && pl->head.ln_g && pl->head.ln_bias;
   auto producer = [&](const float* gamma) {
     b200dec_ln_link l{};
     l.status = pl->status, l.wait_limit = pl->wait_limit, l.withhold = (pl->withhold >> 1) & 1;
@@ -220,7 +220,7 @@ int b200dec_step_rows(const b200dec_plan* pl, int row0, int rows, void* stream) 
     B200_TRY_IN(2, linear_impl(&ly.fc2, mid, pl->a_kind, nullptr, ffn, rows, x, B200DEC_OUT_F32_ADD, D_MODEL,
                          B200DEC_ACT_NONE, pdl, stream, &p1, nullptr));
   }
-  if (pl->head.kind == B200DEC_W_INT8_UMMA)
+  if (is_umma_kind(pl->head.kind))
     B200_TRY_IN(1, head_umma_impl(&pl->head, head_linked ? nullptr : x, head_linked ? xh : nullptr, stats,
                             b200dec_linear_stat_slots(&pl->layer[pl->layers - 1].fc2), &pl->final_ln, D_MODEL, rows,
                             head_max, head_idx, logits, pl->status, pdl, stream, pl->wait_limit, pl->withhold & 1));

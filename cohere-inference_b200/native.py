@@ -14,7 +14,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200dec.so")
 
-W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA, W_F16 = 0, 1, 2, 3, 4
+W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA, W_F16, W_F16_UMMA = 0, 1, 2, 3, 4, 5
 A_F16, A_F32_SPLIT, A_F16_ROWS16 = 0, 1, 2
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
@@ -71,6 +71,7 @@ PROTOTYPES = {
     "b200dec_tiled_meta_bytes": (i64, [C.c_int, C.c_int, C.c_int]),
     "b200dec_tile_int8": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_bf16": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
+    "b200dec_tile_f16_umma": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_24": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp, vp]),
     "b200dec_embed_ln": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, Norm, Norm, vp, vp, C.c_int, C.c_int, vp,
                                    C.c_int, vp]),

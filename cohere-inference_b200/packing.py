@@ -138,7 +138,7 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    if kind == nv.W_INT8_UMMA:  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
+    if kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA):  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
         warps, ksplit = 8, (4 if (k == 1024 and n >= 3072) else 8)  # 96, 128 or 64 CTAs (the head ignores the split)
     else:
         warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
@@ -158,6 +158,9 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     elif kind == nv.W_INT8:
         q, scale = quantize_rows(w)
         nv.check(lib.b200dec_tile_int8(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
+    elif kind == nv.W_F16_UMMA:
+        wb = fp16_image(w).contiguous()
+        nv.check(lib.b200dec_tile_f16_umma(nv.ptr(wb), n, k, nv.ptr(tiled), nv.stream_ptr()))
     elif kind == nv.W_INT8_UMMA:
         q, scale = quantize_rows(w)
         nv.check(lib.b200dec_tile_int8_umma(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
@@ -189,7 +192,7 @@ def dequantized(weight: torch.Tensor, kind: int) -> torch.Tensor:
     w = _f32(weight)
     if kind == nv.W_BF16:
         return w.to(torch.bfloat16).float()
-    if kind == nv.W_F16:
+    if kind in (nv.W_F16, nv.W_F16_UMMA):
         return fp16_image(w).float()
     if kind == nv.W_INT8_24:
         w = prune_24_magnitude(w)

@@ -44,18 +44,20 @@ class _Layer:
             "fc2": (("mlp.fc2",), None, True)}
 
     def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool,
-                 umma: frozenset = frozenset()):
+                 umma: frozenset = frozenset(), small_rows: int = 0):
+        self.small = {}  # name -> the mma.sync packing of a tcgen05 projection, for buckets of up to small_rows rows
         self.norms = [(_fp32(m.weight), _fp32(m.bias), float(m.eps)) for m in
                       (layer.input_layernorm, layer.post_attention_layernorm, layer.final_layernorm)]
         for name, (paths, norm, ffn) in self.SPEC.items():
             mods = [layer.get_submodule(p) for p in paths]
             k = ffn_kind if ffn else kind
-            if name in umma and k == nv.W_INT8:  # dense int8 on the tcgen05 kernel
-                k = nv.W_INT8_UMMA
-            packed = pack_linear(torch.cat([_fp32(m.weight) for m in mods]), torch.cat([_fp32(m.bias) for m in mods]),
-                                 k, keep_reference, a_kind=a_kind, max_rows=max_rows,
-                                 ln=None if norm is None else self.norms[norm][:2])
-            setattr(self, name, packed)
+            w, b = torch.cat([_fp32(m.weight) for m in mods]), torch.cat([_fp32(m.bias) for m in mods])
+            ln = None if norm is None else self.norms[norm][:2]
+            if name in umma and k in (nv.W_INT8, nv.W_F16):  # dense weights on the tcgen05 kernel
+                if small_rows:
+                    self.small[name] = pack_linear(w, b, k, False, a_kind=a_kind, max_rows=small_rows, ln=ln)
+                k = nv.W_INT8_UMMA if k == nv.W_INT8 else nv.W_F16_UMMA
+            setattr(self, name, pack_linear(w, b, k, keep_reference, a_kind=a_kind, max_rows=max_rows, ln=ln))
 
     def projections(self) -> list[PackedLinear]:
         return [getattr(self, name) for name in self.SPEC]
@@ -88,6 +90,7 @@ class StreamDecoder:
                  head_split: bool = True, keep_reference: bool = False, chains: int = 1, attn_ring: bool = False,
                  head_umma: bool = True, kv_int8: bool = False, proj_umma: bool | str = True,
                  kv_prefetch_mb: int = 0, device_sched: bool = False, fp16_weights: bool = False,
+                 umma_above_rows: int = 16,
                  _packed: tuple | None = None):
         """model: a CohereAsrForConditionalGeneration-shaped module on a CUDA device (see synth.synthetic_model).
         int8: weight-only int8 with per-output-channel scales on every projection (fp16 activations, fp32
@@ -106,7 +109,9 @@ class StreamDecoder:
         kv_prefetch_mb: the projections between two attention launches start up to this many MB of the next launch's
         keys and values on their way into L2 (0: off). device_sched: the active list lives on the device: `admit`
         appends to it, every step drops the rows that ended and leaves the live count in `live` (pinned), so a
-        scheduler never calls set_active after an eviction."""
+        scheduler never calls set_active after an eviction. umma_above_rows: the tcgen05 layer projections serve the
+        buckets of more than this many rows, the smaller buckets run a second, mma.sync packing of the same weights
+        (0: tcgen05 in every bucket)."""
         nv.lib()  # fail now, loudly, if the CUDA library is missing
         assert not ffn_sparse or int8, "2:4 feed-forward weights are int8"
         assert not (fp16_weights and int8), "fp16_weights is a mode of its own beside int8"
@@ -137,11 +142,19 @@ class StreamDecoder:
             # proj_umma: the dense int8 projections that run on the tcgen05 kernel of csrc/linear_umma.cu: True = qkv and
             # fc1 (the two with enough multiply per CTA to gain; the narrow ones and fc2 measured 1-2 % slower there
             # than on mma.sync), "all", or a comma-separated subset of qkv,o,cq,co,fc1,fc2
-            names = "qkv,fc1" if proj_umma is True else "qkv,o,cq,co,fc1,fc2" if proj_umma == "all" else (proj_umma or "")
-            umma = frozenset(n for n in names.split(",") if n) if int8 else frozenset()
+            # (fp16 weights: none by default; with qkv and fc1 there the 64-row step measured 0.550 ms against 0.514)
+            names = ("qkv,fc1" if int8 else "") if proj_umma is True else \
+                "qkv,o,cq,co,fc1,fc2" if proj_umma == "all" else (proj_umma or "")
+            umma = frozenset(n for n in names.split(",") if n) if half_rows else frozenset()
+            # umma_above_rows: those projections run on tcgen05 in buckets of more than this many rows; the smaller
+            # buckets use a second, mma.sync packing of the same weights (at 1-16 rows the 64-row tensor-memory tile and
+            # its set-up cost 2.3 us per launch more than the 16-row mma.sync tile: 0.287 -> 0.252 ms per step at 1 row,
+            # 0.336 -> 0.311 at 16, equal at 24, tcgen05 ahead from 32). 0: tcgen05 in every bucket, one packing.
+            small = [b for b in self.buckets if b <= umma_above_rows]
+            self._small_rows = max(small) if (small and umma) else 0
             self._pack_options = dict(int8=bool(int8), fp16_weights=bool(fp16_weights), ffn_sparse=bool(ffn_sparse),
-                                      head_split=bool(head_split),
-                                      head_umma=bool(head_umma), proj_umma=",".join(sorted(umma)), max_rows=bm)
+                                      head_split=bool(head_split), head_umma=bool(head_umma),
+                                      proj_umma=",".join(sorted(umma)), max_rows=bm, small_rows=self._small_rows)
             if _packed:
                 self._load_packed(*_packed)
             else:
@@ -215,6 +228,7 @@ class StreamDecoder:
             self.chains = max(1, int(chains))
             self.side_streams = [torch.cuda.Stream(device=dev, priority=-1) for _ in range(self.chains - 1)]
             self._build_plan()
+            self._select_layers(min(self.buckets))
             self.launches_per_step = lib.b200dec_step_launches(C.byref(self.plan), min(self.buckets))
             self.weight_bytes = sum(p.stream_bytes() for ly in self.layers for p in ly.projections()) + \
                 self.head.stream_bytes()
@@ -232,8 +246,11 @@ class StreamDecoder:
         self.pos_table = dec.pos_emb.weight.detach().to(torch.bfloat16).contiguous()
         ln = lambda m: (_fp32(m.weight), _fp32(m.bias), float(m.eps))  # noqa: E731
         self.emb_ln, self.final_ln = ln(dec.embedding_layernorm), ln(dec.norm)
-        self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma) for layer in dec.layers]
-        head_kind = nv.W_INT8_UMMA if (head_umma and self.int8 and self.embed.shape[0] % 128 == 0) else kind
+        self.layers = [_Layer(layer, kind, ffn_kind, self.a_kind, bm, keep_reference, umma, self._small_rows)
+                       for layer in dec.layers]
+        head_kind = kind
+        if head_umma and kind in (nv.W_INT8, nv.W_F16) and self.embed.shape[0] % 128 == 0:
+            head_kind = nv.W_INT8_UMMA if self.int8 else nv.W_F16_UMMA
         self.head = pack_linear(model.proj_out.weight, model.proj_out.bias, head_kind, keep_reference,
                                 a_kind=self.head_a_kind, ln=self.final_ln[:2], max_rows=bm)
         # prefill: cross K/V of all layers as one (L * 2 * d, d) matrix behind the encoder projection; these run once
@@ -266,6 +283,8 @@ class StreamDecoder:
             ly.norms = [(t[f"layer{i}.ln{j}.w"], t[f"layer{i}.ln{j}.b"], eps[f"layer{i}.ln{j}"]) for j in (1, 2, 3)]
             for name in _Layer.SPEC:
                 setattr(ly, name, packed(f"layer{i}.{name}"))
+            ly.small = {name: packed(f"layer{i}.{name}.small") for name in _Layer.SPEC
+                        if f"layer{i}.{name}.small" in manifest["projections"]}
             self.layers.append(ly)
         self.head = packed("head")
         for name in ("proj", "cross"):
@@ -281,6 +300,7 @@ class StreamDecoder:
         digest."""
         digest = self.weights_digest()
         proj = {f"layer{i}.{n}": getattr(ly, n) for i, ly in enumerate(self.layers) for n in _Layer.SPEC}
+        proj.update({f"layer{i}.{n}.small": p for i, ly in enumerate(self.layers) for n, p in ly.small.items()})
         proj["head"] = self.head
         eps = {"emb_ln": self.emb_ln[2], "final_ln": self.final_ln[2]}
         eps.update({f"layer{i}.ln{j + 1}": ly.norms[j][2] for i, ly in enumerate(self.layers) for j in range(3)})
@@ -310,8 +330,10 @@ class StreamDecoder:
         if shim.device.index is None:
             shim.device = torch.device("cuda", torch.cuda.current_device())
         po = man["pack_options"]
+        if "umma_above_rows" in kw:
+            raise ValueError("umma_above_rows is a packing option: it comes from the file")
         self = cls(shim, int8=po["int8"], fp16_weights=po.get("fp16_weights", False), ffn_sparse=po["ffn_sparse"],
-                   head_split=po["head_split"],
+                   head_split=po["head_split"], umma_above_rows=po.get("small_rows", 0),
                    head_umma=po["head_umma"], proj_umma=po["proj_umma"] or False, _packed=(man, blob["tensors"]), **kw)
         if self.weights_digest() != man["sha256"]:
             raise ValueError(f"{path}: the packed weights do not match the manifest's SHA-256")
@@ -334,17 +356,23 @@ class StreamDecoder:
 
     def _build_plan(self) -> None:
         L = len(self.layers)
-        self._layer_structs = (nv.Layer * L)()
-        for i, ly in enumerate(self.layers):
-            s = self._layer_structs[i]
-            s.ln1, s.ln2, s.ln3 = (nv.norm(*n) for n in ly.norms)
-            s.qkv, s.o, s.cq, s.co = ly.qkv.struct(), ly.o.struct(), ly.cq.struct(), ly.co.struct()
-            s.fc1, s.fc2 = ly.fc1.struct(), ly.fc2.struct()
-            s.self_k, s.self_v = nv.ptr(self.self_k[i]), nv.ptr(self.self_v[i])
-            s.cross_k, s.cross_v = nv.ptr(self.cross_k[i]), nv.ptr(self.cross_v[i])
-            if self.kv_int8:
-                s.self_ks, s.self_vs = nv.ptr(self.self_ks[i]), nv.ptr(self.self_vs[i])
-                s.cross_ks, s.cross_vs = nv.ptr(self.cross_ks[i]), nv.ptr(self.cross_vs[i])
+
+        def layer_structs(small: bool):
+            structs = (nv.Layer * L)()
+            for i, ly in enumerate(self.layers):
+                s = structs[i]
+                s.ln1, s.ln2, s.ln3 = (nv.norm(*n) for n in ly.norms)
+                for name in _Layer.SPEC:
+                    setattr(s, name, ((ly.small.get(name) if small else None) or getattr(ly, name)).struct())
+                s.self_k, s.self_v = nv.ptr(self.self_k[i]), nv.ptr(self.self_v[i])
+                s.cross_k, s.cross_v = nv.ptr(self.cross_k[i]), nv.ptr(self.cross_v[i])
+                if self.kv_int8:
+                    s.self_ks, s.self_vs = nv.ptr(self.self_ks[i]), nv.ptr(self.self_vs[i])
+                    s.cross_ks, s.cross_vs = nv.ptr(self.cross_ks[i]), nv.ptr(self.cross_vs[i])
+            return structs
+        self._layer_structs = layer_structs(False)
+        # the same layers with the mma.sync packings of the tcgen05 projections, for buckets up to _small_rows rows
+        self._layer_structs_small = layer_structs(True) if self._small_rows else None
         p = nv.Plan()
         p.layers, p.heads, p.head_dim, p.act = L, self.h, self.d, self.act
         p.slots, p.seq, p.frames, p.vocab = self.slots, self.seq, self.frames, self.vocab
@@ -365,9 +393,15 @@ class StreamDecoder:
         p.flags_host = self.flags.data_ptr()
         self.plan = p
 
+    def _select_layers(self, b: int) -> None:
+        """Points the plan at the layer packings bucket b runs on (a captured graph keeps what it was captured with)."""
+        small = self._layer_structs_small is not None and b <= self._small_rows
+        self.plan.layer = C.cast(self._layer_structs_small if small else self._layer_structs, C.POINTER(nv.Layer))
+
     def _step(self, b: int) -> None:
         """Bucket b's kernels on the current stream (reference: _step, stream_decoder.py:176-199; the end flags reach
         `flags` from the pick kernel)."""
+        self._select_layers(b)
         ranges = self.row_ranges(b)
         if len(ranges) == 1:
             nv.check(nv.lib().b200dec_step(C.byref(self.plan), b, nv.stream_ptr()))
@@ -393,6 +427,7 @@ class StreamDecoder:
     def launches(self, rows: int) -> int:
         """Kernels one step of `rows` rows launches (summed over its chains)."""
         count = nv.lib().b200dec_step_launches
+        self._select_layers(rows)
         return sum(count(C.byref(self.plan), n) for _, n in self.row_ranges(rows)) + (1 if self.device_sched else 0)
 
     def row_ranges(self, b: int) -> list[tuple[int, int]]:
@@ -577,6 +612,7 @@ class StreamDecoder:
             out[name + ".w"], out[name + ".b"] = w, b
         packs = [(f"layer{i}.{n}", getattr(ly, n)) for i, ly in enumerate(self.layers)
                  for n in ("qkv", "o", "cq", "co", "fc1", "fc2")] + [("head", self.head)]
+        packs += [(f"layer{i}.{n}.small", p) for i, ly in enumerate(self.layers) for n, p in ly.small.items()]
         for name, p in packs:
             for field in ("tiled", "meta", "scale", "bias", "ln_g", "ln_bias"):
                 t = getattr(p, field)

@@ -25,10 +25,14 @@ enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* wei
                                       layer projections on fp16 rows (a_kind B200DEC_A_F16, or B200DEC_A_F16_ROWS16
                                       with a LayerNorm): N a multiple of 128, K = 1024 with w->ksplit 4 or 8, or
                                       K = 4096 with w->ksplit 8 and no LayerNorm */
-       B200DEC_W_F16 = 4 };        /* fp16 values in the layout of B200DEC_W_BF16 (b200dec_tile_bf16 moves 16-bit
+       B200DEC_W_F16 = 4,          /* fp16 values in the layout of B200DEC_W_BF16 (b200dec_tile_bf16 moves 16-bit
                                       words): no scale; multiplied as fp16 x fp16 with fp32 accumulation, so it takes
                                       every operand kind and tile the int8 weights take (fp16 rows, the linked
                                       LayerNorm, rows dealt over CTAs) */
+       B200DEC_W_F16_UMMA = 5 };   /* fp16 values as the images of the tcgen05 kernels' swizzled shared-memory tiles
+                                      (b200dec_tile_f16_umma), copied there from HBM by cp.async.bulk: no scale; the
+                                      shapes and calls of B200DEC_W_INT8_UMMA, the vocabulary projection only through
+                                      b200dec_head_umma_linked */
 enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1,  /* activation operand of a projection: one fp16, or hi + lo */
        B200DEC_A_F16_ROWS16 = 2 };  /* one fp16, and with a LayerNorm the rows handed in are its ready fp16 operand
                                       (see b200dec_ln_link) */
@@ -164,6 +168,7 @@ int64_t b200dec_tiled_bytes(int kind, int n, int k);      /* bytes of the weight
 int64_t b200dec_tiled_meta_bytes(int kind, int n, int k); /* bytes of the selector part (0 unless 2:4) */
 int b200dec_tile_int8(const int8_t* q, int n, int k, void* tiled, void* stream);
 int b200dec_tile_bf16(const void* w_bf16, int n, int k, void* tiled, void* stream);
+int b200dec_tile_f16_umma(const void* w_f16, int n, int k, void* tiled, void* stream); /* n % 128 == 0, k % 64 == 0 */
 int b200dec_tile_24(const int8_t* kept, const int32_t* words, int n, int k, void* tiled, void* meta, void* stream);
 
 /* ---- step kernels ------------------------------------------------------------------------------------------- */

@@ -80,10 +80,14 @@ def test_config1_bf16_against_transformers_golden(model16, golden_dir):
     dec.check_status()
 
 
-@pytest.mark.parametrize("mode,kw", [("bf16", {}), ("int8", dict(int8=True)), ("int8_24", dict(int8=True, ffn_sparse=True)),
+@pytest.mark.parametrize("mode,kw", [("bf16", {}), ("int8", dict(int8=True, umma_above_rows=0)),
+                                     ("int8_small_buckets_on_mma_sync", dict(int8=True)),
+                                     ("int8_24", dict(int8=True, ffn_sparse=True, umma_above_rows=0)),
                                      ("fp16", dict(fp16_weights=True)),
-                                     ("int8_kv8", dict(int8=True, kv_int8=True)),
-                                     ("int8_umma_all", dict(int8=True, proj_umma="all")),
+                                     ("fp16_umma_all", dict(fp16_weights=True, proj_umma="all", umma_above_rows=0)),
+                                     ("fp16_no_umma", dict(fp16_weights=True, proj_umma=False, head_umma=False)),
+                                     ("int8_kv8", dict(int8=True, kv_int8=True, umma_above_rows=0)),
+                                     ("int8_umma_all", dict(int8=True, proj_umma="all", umma_above_rows=0)),
                                      ("int8_no_umma", dict(int8=True, proj_umma=False)),
                                      ("int8_24_no_umma", dict(int8=True, ffn_sparse=True, proj_umma=False))])
 def test_ragged_batch_logits_and_greedy_agreement(model16, state16, mode, kw):
@@ -329,11 +333,14 @@ def test_admit_and_device_active_list_match_the_oracle(model16):
         dec.admit([9], [prompts[0]], [60])  # no such slot
 
 
-@pytest.mark.parametrize("bit,what,slots,buckets", [
-    (1, "vocabulary projection", 4, None),
-    (1, "vocabulary projection, 128-row bucket (the streamed-operand kernel)", 128, (128,)),
-    (2, "layer projections", 4, None)])
-def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, buckets):
+@pytest.mark.parametrize("bit,what,slots,buckets,mode", [
+    (1, "vocabulary projection", 4, None, dict(int8=True)),
+    (1, "vocabulary projection, 128-row bucket (the streamed-operand kernel)", 128, (128,), dict(int8=True)),
+    (2, "layer projections", 4, None, dict(int8=True, umma_above_rows=0)),
+    (1, "vocabulary projection, fp16 weight tiles by bulk copy", 4, None, dict(fp16_weights=True)),
+    (2, "layer projections, fp16 weight tiles by bulk copy", 4, None,
+     dict(fp16_weights=True, proj_umma="qkv,fc1", umma_above_rows=0))])
+def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, buckets, mode):
     """The tcgen05 kernels bound every wait. With a short limit and the test-only `withhold` switch (the producer of
     a barrier is left out, nothing faults and nothing is in flight), the wait runs out: the kernel returns, the status
     word carries the time-out, check_status raises, and the next ordinary steps on the same context give the same
@@ -344,7 +351,7 @@ def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, bucket
     memory = [rng.standard_normal((60, 1024)).astype(np.float32) for _ in range(3)]
     prompts = [rng.integers(0, 16384, 6).astype(np.int64) for _ in range(3)]
     dec = _decoder(model, slots=slots, buckets=buckets, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1,
-                   record=True, int8=True, graphs=False)
+                   record=True, graphs=False, **mode)
     want, _ = _run_teacher_forced(dec, memory, prompts, 4)
     dec.admit([0, 1, 2], [torch.from_numpy(p) for p in prompts], [60] * 3)
     dec.plan.wait_limit, dec.plan.withhold = 2048, bit
@@ -358,7 +365,8 @@ def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, bucket
     assert np.array_equal(got, want), what
 
 
-def test_packed_weights_round_trip(tmp_path):
+@pytest.mark.parametrize("mode", [dict(int8=True, ffn_sparse=True), dict(fp16_weights=True)])
+def test_packed_weights_round_trip(tmp_path, mode):
     """save_packed -> from_packed: the same digest, the same bits out of the step, without the original model; a
     changed byte is caught by the manifest's SHA-256."""
     from cohere_inference_b200 import StreamDecoder
@@ -367,7 +375,7 @@ def test_packed_weights_round_trip(tmp_path):
     memory = [rng.standard_normal((70, 1024)).astype(np.float32) for _ in range(3)]
     prompts = [rng.integers(0, 16384, 4).astype(np.int64) for _ in range(3)]
     run = dict(slots=4, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, record=True)
-    dec = _decoder(model, int8=True, ffn_sparse=True, **run)
+    dec = _decoder(model, **mode, **run)
     want, _ = _run_teacher_forced(dec, memory, prompts, 5)
     path = str(tmp_path / "decoder.b200dec")
     digest = dec.save_packed(path)
@@ -375,6 +383,7 @@ def test_packed_weights_round_trip(tmp_path):
     del dec
     again = StreamDecoder.from_packed(path, **run)
     assert again.weights_digest() == digest and again.model is None
+    assert again.fp16_weights == bool(mode.get("fp16_weights")) and again.int8 == bool(mode.get("int8"))
     got, _ = _run_teacher_forced(again, memory, prompts, 5)
     assert np.array_equal(got, want)
     blob = torch.load(path, weights_only=True)

@@ -87,6 +87,17 @@ def test_tiled_layouts(nv, pk):
                           .transpose(0, 3, 1, 2, 4, 5), t16)
     with pytest.raises(AssertionError):
         pk.pack_linear(cuda(w * 1e7), None, nv.W_F16)
+    # fp16 for the tcgen05 kernels: blocks [n / 128][k / 64] of 16 KB, each the image of a 128-byte-swizzled K-major
+    # tile: channel t's row at 128 t, its 16-byte chunk c at position c ^ (t & 7)
+    w2 = (rng.standard_normal((256, 128)) * 0.02).astype(np.float32)
+    p = pk.pack_linear(cuda(w2), None, nv.W_F16_UMMA)
+    img = pk.fp16_image(cuda(w2)).cpu().numpy()
+    tu = p.tiled.view(torch.float16).cpu().numpy().reshape(2, 2, 128, 8, 8)
+    tt = np.arange(128)
+    for pos in range(8):
+        c = pos ^ (tt & 7)  # the chunk that sits at this position of each channel's row
+        src = img.reshape(2, 128, 2, 8, 8)[:, tt, :, c, :]  # (t, mt, kb, e)
+        assert np.array_equal(tu[:, :, :, pos, :], src.transpose(1, 2, 0, 3))
     # 2:4: value byte [nt][kb][h][lane][2 s + j] = kept[row][2 G + j], G = 32 kb + 2 (4 (s / 2) + t) + (s & 1);
     # selector nibble s of word [nt][kb][h][lane] = the selector of group G
     p = pk.pack_linear(cuda(w), None, nv.W_INT8_24, keep_reference=True)
@@ -297,8 +308,9 @@ def test_linked_layernorm_error_grows_with_the_row_offset(nv, pk, offset, atol, 
 @pytest.mark.parametrize("n,act,out_kind", [(3072, "ACT_NONE", "OUT_F32"), (4096, "ACT_GELU", "OUT_F16"),
                                             (1024, "ACT_RELU", "OUT_F32")])
 @pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])
-def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
-    """The tcgen05 projection (weight kind W_INT8_UMMA): LayerNorm folded, rows handed over as the ready fp16 operand
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_F16_UMMA"])
+def test_linear_umma_layernorm(nv, pk, kind, n, act, out_kind, rows):
+    """The tcgen05 projection (weight kinds W_INT8_UMMA, and W_F16_UMMA whose tiles come by bulk copy): LayerNorm folded, rows handed over as the ready fp16 operand
     with partial sums; equals act(LayerNorm(rows) W^T + b) on the dequantised weights. Twice in a row (tensor memory
     and the barrier are set up per launch)."""
     rng = np.random.default_rng(n + rows)
@@ -310,14 +322,15 @@ def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
     b = (rng.standard_normal(n) * 0.1).astype(np.float32)
     g_d, b_d, x_d = cuda(gam), cuda(bet), cuda(x)
-    pc = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA, ln=(g_d, b_d))
+    kind = getattr(nv, kind)
+    pc = pk.pack_linear(cuda(w), cuda(b), kind, ln=(g_d, b_d))
     norm, cs = nv.norm(g_d, b_d, 1e-5), pc.struct()
     xg = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
     sums = torch.zeros(rows, 2, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     nv.check(lib.b200dec_ln_rows16(nv.ptr(x_d), nv.ptr(g_d), rows, nv.ptr(xg), nv.ptr(sums), nv.stream_ptr()))
     ok, ak = getattr(nv, out_kind), getattr(nv, act)
-    want = layer_norm(x, gam, bet, 1e-5).astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy().astype(np.float64).T + b
+    want = layer_norm(x, gam, bet, 1e-5).astype(np.float64) @ pk.dequantized(cuda(w), kind).cpu().numpy().astype(np.float64).T + b
     want = want.astype(np.float32)
     if ak != nv.ACT_NONE:
         want = activation({nv.ACT_RELU: "relu", nv.ACT_GELU: "gelu"}[ak], want)
@@ -331,7 +344,7 @@ def test_linear_umma_layernorm(nv, pk, n, act, out_kind, rows):
         np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=5e-3, rtol=2e-3 if ok == nv.OUT_F16 else 1e-4)
 
 
-@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_INT8", "W_INT8_24"])
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_INT8", "W_INT8_24", "W_F16", "W_F16_UMMA"])
 @pytest.mark.parametrize("n,k", [(1024, 1024), (1024, 4096), (3072, 1024)])
 @pytest.mark.parametrize("rows", [1, 13, 33, 50, 64, 100, 128])
 def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
@@ -349,7 +362,7 @@ def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
     cs = pc.struct()
     a_d = cuda(a)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    prod = a.astype(np.float64) @ pk.dequantized(cuda(w), nv.W_INT8_24 if kind == nv.W_INT8_24 else nv.W_INT8).cpu().numpy().astype(np.float64).T + b
+    prod = a.astype(np.float64) @ pk.dequantized(cuda(w), kind).cpu().numpy().astype(np.float64).T + b
     out = torch.zeros(rows, n, device="cuda")
     link = nv.LnLink(None, None, None, None, 0, 0, nv.ptr(status))
     nv.check(lib.b200dec_linear_linked(C.byref(cs), nv.ptr(a_d), nv.A_F16, None, k, rows, nv.ptr(out), nv.OUT_F32, n,
@@ -363,7 +376,7 @@ def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
     gam = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
     g_d = cuda(gam)
     slots = lib.b200dec_linear_stat_slots(C.byref(cs))
-    assert kind != nv.W_INT8_UMMA or slots == (n // 128) * pc.ksplit
+    assert kind not in (nv.W_INT8_UMMA, nv.W_F16_UMMA) or slots == (n // 128) * pc.ksplit
     for _ in range(2):
         x = cuda(x0.copy())
         x16 = torch.zeros(rows, n, dtype=torch.float16, device="cuda")
@@ -448,7 +461,8 @@ def test_head_argmax(nv, pk, rows, a_kind, ln):
 
 @pytest.mark.parametrize("rows", [1, 33, 64, 100])
 @pytest.mark.parametrize("n", [256, 16384])
-def test_head_umma(nv, pk, rows, n):
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_F16_UMMA"])
+def test_head_umma(nv, pk, kind, rows, n):
     """The tcgen05 vocabulary projection: logits vs fp64 on the dequantised weights (operand fp16, so the tolerance of
     the other fp16-operand projections), partials = first-index maxima of its own logits per 128 channels; twice in a
     row (tensor memory and barriers are set up per launch)."""
@@ -460,13 +474,20 @@ def test_head_umma(nv, pk, rows, n):
     gam = (1 + 0.1 * rng.standard_normal(k)).astype(np.float32)
     bet = (0.1 * rng.standard_normal(k)).astype(np.float32)
     g_d, b_d, a_d = cuda(gam), cuda(bet), cuda(a)
-    p = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA)
-    wd = pk.dequantized(cuda(w), nv.W_INT8).cpu().numpy()
+    kind = getattr(nv, kind)
+    p = pk.pack_linear(cuda(w), cuda(b), kind)
+    wd = pk.dequantized(cuda(w), kind).cpu().numpy()
     norm, ws = nv.norm(g_d, b_d, 1e-5), p.struct()
     np_ = nv.lib().b200dec_head_partials(C.byref(ws))
     assert np_ == n // 128
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    for _ in range(2):
+    if kind == nv.W_F16_UMMA:  # fp16 weight tiles go with the ready fp16 operand only: fp32 rows are refused
+        pm = torch.zeros(rows, np_, device="cuda")
+        pi = torch.zeros(rows, np_, dtype=torch.int32, device="cuda")
+        rc = nv.lib().b200dec_head_umma(C.byref(ws), nv.ptr(a_d), C.byref(norm), k, rows, nv.ptr(pm), nv.ptr(pi), None,
+                                        nv.ptr(status), 0, nv.stream_ptr())
+        assert rc == 1  # B200DEC_EINVAL
+    for _ in range(0 if kind == nv.W_F16_UMMA else 2):
         pm = torch.full((rows, np_), -7.0, device="cuda")
         pi = torch.full((rows, np_), -7, dtype=torch.int32, device="cuda")
         logits = torch.zeros(rows, n, device="cuda")
@@ -482,7 +503,7 @@ def test_head_umma(nv, pk, rows, n):
         assert np.array_equal(pm.cpu().numpy(), t.max(-1))
         assert np.array_equal(pi.cpu().numpy(), t.argmax(-1) + np.arange(np_) * 128)
     # the same rows handed over as the ready fp16 operand (row * gamma) with their sums: LayerNorm folded into the epilogue
-    pl = pk.pack_linear(cuda(w), cuda(b), nv.W_INT8_UMMA, ln=(g_d, b_d))
+    pl = pk.pack_linear(cuda(w), cuda(b), kind, ln=(g_d, b_d))
     wl = pl.struct()
     xg = torch.zeros(rows, k, dtype=torch.float16, device="cuda")
     sums = torch.zeros(rows, 2, device="cuda")

@@ -18,7 +18,9 @@ constexpr int D_MODEL = 1024;
 namespace b200dec_detail {
 
 // the weight kinds of the tcgen05 kernels (linear_umma.cu, head_umma.cu)
-inline bool is_umma_kind(int kind) { return kind == B200DEC_W_INT8_UMMA || kind == B200DEC_W_F16_UMMA; }
+inline bool is_umma_kind(int kind) {
+  return kind == B200DEC_W_INT8_UMMA || kind == B200DEC_W_F16_UMMA || kind == B200DEC_W_INT8_24_UMMA;
+}
 char* error_buffer();
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);

@@ -86,6 +86,7 @@ bool fits_any(int kind, bool split, int ln, int warps, int k, int ksplit, int ro
     case B200DEC_W_F16: return fits_f16(split, ln, warps, k, ksplit, rows);
     case B200DEC_W_INT8_UMMA:  // linear_umma.cu: fp16 rows, plain or as a LayerNorm's ready operand
     case B200DEC_W_F16_UMMA:
+    case B200DEC_W_INT8_24_UMMA:
       return !split && rows <= 128 && ln != 1 &&
              ((k == D_MODEL && (ksplit == 4 || ksplit == 8)) || (k == 4 * D_MODEL && ksplit == 8 && ln == 0));
   }
@@ -244,10 +245,12 @@ int b200dec_linear_fits(int kind, int a_kind, int ln, int warps, int ksplit, int
 int64_t b200dec_tiled_bytes(int kind, int n, int k) {
   if (kind == B200DEC_W_INT8 || kind == B200DEC_W_INT8_UMMA) return (int64_t)n * k;
   if (kind == B200DEC_W_BF16 || kind == B200DEC_W_F16 || kind == B200DEC_W_F16_UMMA) return (int64_t)n * k * 2;
-  if (kind == B200DEC_W_INT8_24) return (int64_t)n * k / 2;
+  if (kind == B200DEC_W_INT8_24 || kind == B200DEC_W_INT8_24_UMMA) return (int64_t)n * k / 2;
   return -1;
 }
-int64_t b200dec_tiled_meta_bytes(int kind, int n, int k) { return kind == B200DEC_W_INT8_24 ? (int64_t)n * k / 8 : 0; }
+int64_t b200dec_tiled_meta_bytes(int kind, int n, int k) {
+  return kind == B200DEC_W_INT8_24 || kind == B200DEC_W_INT8_24_UMMA ? (int64_t)n * k / 8 : 0;
+}
 
 int b200dec_tile_int8(const int8_t* q, int n, int k, void* tiled, void* stream) {
   B200_REQUIRE(q && tiled && n % 16 == 0 && k % 64 == 0, "tile_int8: shape (%d, %d)", n, k);

@@ -18,6 +18,9 @@
 // fp16 weights (B200DEC_W_F16_UMMA, template flag W16) are stored as the images of those swizzled tiles
 // (b200dec_tile_f16_umma): one lane copies the CTA's blocks from HBM into the A tiles with `cp.async.bulk` onto an
 // mbarrier before the dependency wait, no thread touches a weight, and the MMA lane waits for that barrier.
+// 2:4 int8 weights (B200DEC_W_INT8_24_UMMA, b200dec_tile_24_umma): a thread's 32 k of a block are 16 kept bytes and one
+// selector word of compress_24's format; it expands them to the dense fp16 tile (a byte permute per group of four from
+// a 32-entry control table, then the same exact widening) and the multiply is the dense one.
 // The waits for the copies and the MMAs are bounded (B200DEC_ST_TIMEOUT); tensor memory is released on every path.
 #include <cooperative_groups.h>
 
@@ -37,6 +40,7 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 struct UArgs {
   const uint8_t* w;
+  const uint32_t* meta;  // 2:4: the selector words
   const float* scale;
   const float* bias;     // may be null
   const __half* xg;      // (rows, lda) fp16: the operand rows (with a LayerNorm: row * gamma)
@@ -124,6 +128,14 @@ DEVI void widen16(const uint4& r, uint4& lo, uint4& hi) {
   }
   lo = make_uint4(out[0], out[1], out[2], out[3]), hi = make_uint4(out[4], out[5], out[6], out[7]);
 }
+// 4 offset-binary bytes (q + 128, k .. k + 3) -> half2(q0, q1), half2(q2, q3), exact
+DEVI void widen_u8x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t a = __byte_perm(w, 0x64646464u, 0x4140), b = __byte_perm(w, 0x64646464u, 0x4342);
+  const __half2 off = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
+  const __half2 ha = __hsub2(*reinterpret_cast<const __half2*>(&a), off);
+  const __half2 hb = __hsub2(*reinterpret_cast<const __half2*>(&b), off);
+  lo = *reinterpret_cast<const uint32_t*>(&ha), hi = *reinterpret_cast<const uint32_t*>(&hb);
+}
 DEVI float act_fn(float v, int act) {
   if (act == B200DEC_ACT_RELU) return fmaxf(v, 0.f);
   if (act == B200DEC_ACT_GELU) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
@@ -144,8 +156,10 @@ DEVI void tmem_ld32(uint32_t taddr, uint32_t (&d)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int MB, int KSPLIT, int NKB, bool LN, bool W16>
+// WK: how the weights come: 0 dense int8 blocks, 1 fp16 tile images (bulk copy), 2 2:4 int8 (kept values + selectors)
+template <int MB, int KSPLIT, int NKB, bool LN, int WK>
 __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p) {
+  constexpr bool W16 = WK == 1, W24 = WK == 2;
   using S = USmem<MB, KSPLIT, NKB>;
   constexpr int CPR = S::CPR, GPR = CPR / 4, KSLICE = NKB * KB;
   extern __shared__ unsigned char dyn_smem[];
@@ -156,6 +170,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   float2* stats = reinterpret_cast<float2*>(smem + S::OFF_STATS);
   __shared__ __align__(8) uint64_t d_full, w_full;
   __shared__ uint32_t tmem_base;
+  __shared__ uint32_t lut[32];
 
   cluster_arrive_entry();  // completed by cluster_wait_entry() before this CTA's first remote store
   cg::cluster_group cluster = cg::this_cluster();
@@ -165,13 +180,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   const int hf = warp >> 2;               // its half: 16-k pieces 2 hf, 2 hf + 1 of a block; rows hf * MB / 2 ..
 
   // ---- prologue: the CTA's weight blocks into registers (independent of the previous kernel) ----------------------
-  uint4 wr[W16 ? 1 : NKB][2];
-  if constexpr (!W16) {
+  uint4 wr[W16 ? 1 : NKB][W24 ? 1 : 2];
+  uint32_t mr[W24 ? NKB : 1];
+  if constexpr (WK == 0) {
     const uint8_t* wsrc = p.w + ((size_t)tile * (p.K / KB) + rank * NKB) * RAW_BYTES + ch * 16;
 #pragma unroll
     for (int b = 0; b < NKB; ++b)
 #pragma unroll
       for (int j = 0; j < 2; ++j) wr[b][j] = ld_stream16(wsrc + (size_t)b * RAW_BYTES + (2 * hf + j) * 2048);
+  }
+  if constexpr (W24) {  // this thread's 32 k of a block: 16 kept bytes and the eight selectors of its groups of four
+    const size_t blk0 = (size_t)tile * (p.K / KB) + rank * NKB;
+    const uint8_t* wsrc = p.w + blk0 * (RAW_BYTES / 2) + hf * 2048 + ch * 16;
+    const uint32_t* msrc = p.meta + blk0 * 256 + hf * 128 + ch;
+#pragma unroll
+    for (int b = 0; b < NKB; ++b) {
+      wr[b][0] = ld_stream16(wsrc + (size_t)b * (RAW_BYTES / 2));
+      mr[b] = ld_stream4(msrc + (size_t)b * 256);
+    }
+    // byte-permute controls: dense byte q of a group takes kept byte 0/1 (even group of the register) or 2/3 (odd) when
+    // q is the first / second kept position, else the zero byte (index 4 = 0x80 in offset binary)
+    if (tid < 32) {
+      const int i0 = tid & 3, i1 = (tid >> 2) & 3, odd = tid >> 4;
+      uint32_t ctl = 0;
+      for (int q = 0; q < 4; ++q) {
+        uint32_t sel = 4;
+        if (q == i1) sel = odd ? 3 : 1;
+        if (q == i0) sel = odd ? 2 : 0;
+        ctl |= sel << (4 * q);
+      }
+      lut[tid] = ctl;
+    }
   }
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&d_full)));
@@ -192,16 +231,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   }
   // ---- widen the weights into the A tiles: they depend on nothing the previous kernel writes, so this happens in
   // front of the dependency wait, under the previous kernel's tail (the tiles are this CTA's own shared memory)
+  if constexpr (W24) {
+    __syncthreads();  // the control table
 #pragma unroll
-  for (int b = 0; b < (W16 ? 0 : NKB); ++b) {
-    unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+    for (int b = 0; b < NKB; ++b) {
+      unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+      const uint32_t kw[4] = {wr[b][0].x ^ 0x80808080u, wr[b][0].y ^ 0x80808080u, wr[b][0].z ^ 0x80808080u,
+                              wr[b][0].w ^ 0x80808080u};
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int pj = 2 * hf + j;  // k = 16 pj .. 16 pj + 15 of the block: chunks 2 pj and 2 pj + 1 of the row
-      uint4 lo, hi;
-      widen16(wr[b][j], lo, hi);
-      *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
-      *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+      for (int c = 0; c < 4; ++c) {  // register c = groups 2 c, 2 c + 1 = k 8 c .. 8 c + 7 of the 32 = one 16-byte chunk
+        uint32_t o[4];
+        widen_u8x4(__byte_perm(kw[c], 0x80808080u, lut[(mr[b] >> (8 * c)) & 15u]), o[0], o[1]);
+        widen_u8x4(__byte_perm(kw[c], 0x80808080u, lut[((mr[b] >> (8 * c + 4)) & 15u) | 16u]), o[2], o[3]);
+        *reinterpret_cast<uint4*>(row + (((4 * hf + c) ^ (ch & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+  if constexpr (WK == 0) {
+#pragma unroll
+    for (int b = 0; b < NKB; ++b) {
+      unsigned char* row = as + b * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int pj = 2 * hf + j;  // k = 16 pj .. 16 pj + 15 of the block: chunks 2 pj and 2 pj + 1 of the row
+        uint4 lo, hi;
+        widen16(wr[b][j], lo, hi);
+        *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+      }
     }
   }
   pdl_wait();
@@ -357,13 +414,27 @@ __global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p)
   }
 }
 
-template <int MB, int KSPLIT, int NKB, bool LN, bool W16>
+// kept (n, k / 2) int8 and words (n, k / 32) of compress_24 -> blocks [n / 128][k / 64]: 4 KB of kept bytes
+// [half of the block's k][channel][16 bytes] and 256 selector words [half][channel] (a half = 32 k = one word of the row)
+__global__ void tile_24_umma_kernel(const int8_t* __restrict__ kept, const uint32_t* __restrict__ words, int n, int k,
+                                    uint8_t* __restrict__ out, uint32_t* __restrict__ meta) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one kept byte each
+  if (i >= (size_t)n * (k / 2)) return;
+  const int e = i & 15, t = (i >> 4) & 127, hf = (i >> 11) & 1;
+  const size_t blk = i >> 12;
+  const int nkb = k / KB, kb = (int)(blk % nkb), mt = (int)(blk / nkb);
+  const size_t row = (size_t)mt * UM + t;
+  out[i] = (uint8_t)kept[row * (k / 2) + kb * 32 + hf * 16 + e];
+  if (e == 0) meta[blk * 256 + hf * 128 + t] = words[row * (k / 32) + kb * 2 + hf];
+}
+
+template <int MB, int KSPLIT, int NKB, bool LN, int WK>
 int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
   using S = USmem<MB, KSPLIT, NKB>;
   if constexpr (S::BYTES > 227 * 1024 - 512) {
     return fail(B200DEC_EINVAL, "linear_umma: %d rows of K / %d do not fit shared memory", MB, KSPLIT);
   } else {
-    auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN, W16>;
+    auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN, WK>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
     e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), S::BYTES, stream, KSPLIT, pdl, a);
@@ -372,30 +443,32 @@ int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
   }
 }
 
-template <int KSPLIT, int NKB, bool W16>
-int launch_rows16(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
+template <int KSPLIT, int NKB, int WK>
+int launch_rows_wk(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
   if (a.rows <= 64)
-    return ln ? launch_umma<64, KSPLIT, NKB, true, W16>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false, W16>(a, pdl, s);
-  return ln ? launch_umma<128, KSPLIT, NKB, true, W16>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false, W16>(a, pdl, s);
+    return ln ? launch_umma<64, KSPLIT, NKB, true, WK>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false, WK>(a, pdl, s);
+  return ln ? launch_umma<128, KSPLIT, NKB, true, WK>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false, WK>(a, pdl, s);
 }
 template <int KSPLIT, int NKB>
-int launch_rows(const UArgs& a, bool w16, bool ln, int pdl, cudaStream_t s) {
-  return w16 ? launch_rows16<KSPLIT, NKB, true>(a, ln, pdl, s) : launch_rows16<KSPLIT, NKB, false>(a, ln, pdl, s);
+int launch_rows(const UArgs& a, int wk, bool ln, int pdl, cudaStream_t s) {
+  return wk == 1 ? launch_rows_wk<KSPLIT, NKB, 1>(a, ln, pdl, s)
+       : wk == 2 ? launch_rows_wk<KSPLIT, NKB, 2>(a, ln, pdl, s) : launch_rows_wk<KSPLIT, NKB, 0>(a, ln, pdl, s);
 }
 
 }  // namespace
 
 namespace b200dec_detail {
 
-// A projection whose weight is of kind B200DEC_W_INT8_UMMA or B200DEC_W_F16_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
+// A projection whose weight is of kind B200DEC_W_INT8_UMMA, B200DEC_W_F16_UMMA or B200DEC_W_INT8_24_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
 // operand and link->stats_in its partial sums (b200dec_ln_link). w->ksplit: CTAs per cluster (K = 1024: 4 or 8;
 // K = 4096: 8, 64 rows per pass).
 int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                      void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
                      void* stream) {
   B200_REQUIRE(w && w->w && a && out && status, "linear_umma: null pointer");
-  const bool w16 = w->kind == B200DEC_W_F16_UMMA;
+  const bool w16 = w->kind == B200DEC_W_F16_UMMA, w24 = w->kind == B200DEC_W_INT8_24_UMMA;
   B200_REQUIRE(w16 == (w->scale == nullptr) && ((uintptr_t)w->w & 15) == 0, "linear_umma: scale present iff int8");
+  B200_REQUIRE(w24 == (w->meta != nullptr), "linear_umma: selectors present iff 2:4");
   B200_REQUIRE((w->k == D_MODEL && (w->ksplit == 4 || w->ksplit == 8)) || (w->k == 4 * D_MODEL && w->ksplit == 8),
                "linear_umma: K %d split %d ways", w->k, w->ksplit);
   B200_REQUIRE(w->n % UM == 0, "linear_umma: N %d", w->n);
@@ -416,7 +489,7 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
   const int pass = w->k == D_MODEL ? 128 : 64;  // K = 4096: the operands of 128 rows do not fit shared memory
   for (int r0 = 0; r0 < rows; r0 += pass) {
     UArgs p{};
-    p.w = (const uint8_t*)w->w, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a + (size_t)r0 * lda;
+    p.w = (const uint8_t*)w->w, p.meta = (const uint32_t*)w->meta, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a + (size_t)r0 * lda;
     if (ln) {
       p.stats = lk.stats_in + (size_t)r0 * lk.stats_slots * 2, p.stats_slots = lk.stats_slots;
       p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
@@ -431,13 +504,24 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
     p.out_kind = out_kind, p.act = act;
     p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
     cudaStream_t s = (cudaStream_t)stream;
+    const int wk = w16 ? 1 : w24 ? 2 : 0;
     int rc;
-    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, w16, ln != nullptr, pdl, s);
-    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, w16, ln != nullptr, pdl, s);
-    else rc = launch_rows<8, 8>(p, w16, false, pdl, s);
+    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, wk, ln != nullptr, pdl, s);
+    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, wk, ln != nullptr, pdl, s);
+    else rc = launch_rows<8, 8>(p, wk, false, pdl, s);
     if (rc) return rc;
   }
   return 0;
 }
 
 }  // namespace b200dec_detail
+
+extern "C" int b200dec_tile_24_umma(const int8_t* kept, const int32_t* words, int n, int k, void* tiled, void* meta,
+                                    void* stream) {
+  B200_REQUIRE(kept && words && tiled && meta && n > 0 && n % UM == 0 && k > 0 && k % KB == 0,
+               "tile_24_umma: (%d, %d) must be multiples of (128, 64)", n, k);
+  const size_t total = (size_t)n * (k / 2);
+  tile_24_umma_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      kept, (const uint32_t*)words, n, k, (uint8_t*)tiled, (uint32_t*)meta);
+  return check_launch("tile_24_umma");
+}

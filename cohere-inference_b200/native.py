@@ -14,7 +14,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200dec.so")
 
-W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA, W_F16, W_F16_UMMA = 0, 1, 2, 3, 4, 5
+W_BF16, W_INT8, W_INT8_24, W_INT8_UMMA, W_F16, W_F16_UMMA, W_INT8_24_UMMA = 0, 1, 2, 3, 4, 5, 6
 A_F16, A_F32_SPLIT, A_F16_ROWS16 = 0, 1, 2
 OUT_F16, OUT_F32, OUT_F32_ADD = 0, 1, 2
 ACT_NONE, ACT_RELU, ACT_GELU = 0, 1, 2
@@ -73,6 +73,7 @@ PROTOTYPES = {
     "b200dec_tile_bf16": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_f16_umma": (C.c_int, [vp, C.c_int, C.c_int, vp, vp]),
     "b200dec_tile_24": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp, vp]),
+    "b200dec_tile_24_umma": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, vp, vp]),
     "b200dec_embed_ln": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, Norm, Norm, vp, vp, C.c_int, C.c_int, vp,
                                    C.c_int, vp]),
     "b200dec_layer_norm": (C.c_int, [vp, Norm, vp, C.c_int, C.c_int, C.c_int, vp]),

@@ -138,7 +138,7 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    if kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA):  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
+    if kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA, nv.W_INT8_24_UMMA):  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
         warps, ksplit = 8, (4 if (k == 1024 and n >= 3072) else 8)  # 96, 128 or 64 CTAs (the head ignores the split)
     else:
         warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)
@@ -164,11 +164,12 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     elif kind == nv.W_INT8_UMMA:
         q, scale = quantize_rows(w)
         nv.check(lib.b200dec_tile_int8_umma(nv.ptr(q), n, k, nv.ptr(tiled), nv.stream_ptr()))
-    elif kind == nv.W_INT8_24:
+    elif kind in (nv.W_INT8_24, nv.W_INT8_24_UMMA):
         q, scale = quantize_rows(prune_24_magnitude(w))
         kept, words = compress_24(q)
         meta = torch.empty(lib.b200dec_tiled_meta_bytes(kind, n, k) // 4, dtype=torch.int32, device=dev)
-        nv.check(lib.b200dec_tile_24(nv.ptr(kept), nv.ptr(words), n, k, nv.ptr(tiled), nv.ptr(meta), nv.stream_ptr()))
+        tile = lib.b200dec_tile_24 if kind == nv.W_INT8_24 else lib.b200dec_tile_24_umma
+        nv.check(tile(nv.ptr(kept), nv.ptr(words), n, k, nv.ptr(tiled), nv.ptr(meta), nv.stream_ptr()))
     else:
         raise ValueError(kind)
     torch.cuda.current_stream().synchronize()  # the temporaries above may be freed once the tilers are done
@@ -194,7 +195,7 @@ def dequantized(weight: torch.Tensor, kind: int) -> torch.Tensor:
         return w.to(torch.bfloat16).float()
     if kind in (nv.W_F16, nv.W_F16_UMMA):
         return fp16_image(w).float()
-    if kind == nv.W_INT8_24:
+    if kind in (nv.W_INT8_24, nv.W_INT8_24_UMMA):
         w = prune_24_magnitude(w)
     q, s = quantize_rows(w)
     return q.float() * s[:, None]

@@ -43,6 +43,8 @@ class _Layer:
             "fc1": (("mlp.fc1",), 2, True),
             "fc2": (("mlp.fc2",), None, True)}
 
+    UMMA_KIND = {nv.W_INT8: nv.W_INT8_UMMA, nv.W_F16: nv.W_F16_UMMA, nv.W_INT8_24: nv.W_INT8_24_UMMA}
+
     def __init__(self, layer, kind: int, ffn_kind: int, a_kind: int, max_rows: int, keep_reference: bool,
                  umma: frozenset = frozenset(), small_rows: int = 0):
         self.small = {}  # name -> the mma.sync packing of a tcgen05 projection, for buckets of up to small_rows rows
@@ -53,10 +55,10 @@ class _Layer:
             k = ffn_kind if ffn else kind
             w, b = torch.cat([_fp32(m.weight) for m in mods]), torch.cat([_fp32(m.bias) for m in mods])
             ln = None if norm is None else self.norms[norm][:2]
-            if name in umma and k in (nv.W_INT8, nv.W_F16):  # dense weights on the tcgen05 kernel
+            if name in umma and k in self.UMMA_KIND:  # on the tcgen05 kernel
                 if small_rows:
                     self.small[name] = pack_linear(w, b, k, False, a_kind=a_kind, max_rows=small_rows, ln=ln)
-                k = nv.W_INT8_UMMA if k == nv.W_INT8 else nv.W_F16_UMMA
+                k = self.UMMA_KIND[k]
             setattr(self, name, pack_linear(w, b, k, keep_reference, a_kind=a_kind, max_rows=max_rows, ln=ln))
 
     def projections(self) -> list[PackedLinear]:

@@ -29,10 +29,13 @@ enum { B200DEC_W_BF16 = 0, B200DEC_W_INT8 = 1, B200DEC_W_INT8_24 = 2,     /* wei
                                       words): no scale; multiplied as fp16 x fp16 with fp32 accumulation, so it takes
                                       every operand kind and tile the int8 weights take (fp16 rows, the linked
                                       LayerNorm, rows dealt over CTAs) */
-       B200DEC_W_F16_UMMA = 5 };   /* fp16 values as the images of the tcgen05 kernels' swizzled shared-memory tiles
+       B200DEC_W_F16_UMMA = 5,     /* fp16 values as the images of the tcgen05 kernels' swizzled shared-memory tiles
                                       (b200dec_tile_f16_umma), copied there from HBM by cp.async.bulk: no scale; the
                                       shapes and calls of B200DEC_W_INT8_UMMA, the vocabulary projection only through
                                       b200dec_head_umma_linked */
+       B200DEC_W_INT8_24_UMMA = 6 }; /* 2:4 int8 (kept values + selector words, b200dec_tile_24_umma) for the tcgen05
+                                      projection kernel, which expands them to dense tiles: the layer-projection
+                                      shapes and calls of B200DEC_W_INT8_UMMA (not the vocabulary projection) */
 enum { B200DEC_A_F16 = 0, B200DEC_A_F32_SPLIT = 1,  /* activation operand of a projection: one fp16, or hi + lo */
        B200DEC_A_F16_ROWS16 = 2 };  /* one fp16, and with a LayerNorm the rows handed in are its ready fp16 operand
                                       (see b200dec_ln_link) */
@@ -170,6 +173,8 @@ int b200dec_tile_int8(const int8_t* q, int n, int k, void* tiled, void* stream);
 int b200dec_tile_bf16(const void* w_bf16, int n, int k, void* tiled, void* stream);
 int b200dec_tile_f16_umma(const void* w_f16, int n, int k, void* tiled, void* stream); /* n % 128 == 0, k % 64 == 0 */
 int b200dec_tile_24(const int8_t* kept, const int32_t* words, int n, int k, void* tiled, void* meta, void* stream);
+int b200dec_tile_24_umma(const int8_t* kept, const int32_t* words, int n, int k, void* tiled, void* meta,
+                         void* stream); /* n % 128 == 0, k % 64 == 0 */
 
 /* ---- step kernels ------------------------------------------------------------------------------------------- */
 

@@ -87,6 +87,14 @@ def test_tiled_layouts(nv, pk):
                           .transpose(0, 3, 1, 2, 4, 5), t16)
     with pytest.raises(AssertionError):
         pk.pack_linear(cuda(w * 1e7), None, nv.W_F16)
+    # 2:4 for the tcgen05 kernel: blocks [n / 128][k / 64] of 4 KB kept bytes [half][channel][16] and 256 selector
+    # words [half][channel]: a half of a block's k is 32 k = 16 kept bytes = one word of compress_24's row
+    w3 = (rng.standard_normal((256, 128)) * 0.02).astype(np.float32)
+    p = pk.pack_linear(cuda(w3), None, nv.W_INT8_24_UMMA, keep_reference=True)
+    kept3, words3 = p.kept.cpu().numpy(), p.words.cpu().numpy()
+    assert np.array_equal(p.tiled.cpu().numpy().view(np.int8).reshape(2, 2, 2, 128, 16),
+                          kept3.reshape(2, 128, 2, 2, 16).transpose(0, 2, 3, 1, 4))
+    assert np.array_equal(p.meta.cpu().numpy().reshape(2, 2, 2, 128), words3.reshape(2, 128, 2, 2).transpose(0, 2, 3, 1))
     # fp16 for the tcgen05 kernels: blocks [n / 128][k / 64] of 16 KB, each the image of a 128-byte-swizzled K-major
     # tile: channel t's row at 128 t, its 16-byte chunk c at position c ^ (t & 7)
     w2 = (rng.standard_normal((256, 128)) * 0.02).astype(np.float32)
@@ -308,7 +316,7 @@ def test_linked_layernorm_error_grows_with_the_row_offset(nv, pk, offset, atol, 
 @pytest.mark.parametrize("n,act,out_kind", [(3072, "ACT_NONE", "OUT_F32"), (4096, "ACT_GELU", "OUT_F16"),
                                             (1024, "ACT_RELU", "OUT_F32")])
 @pytest.mark.parametrize("rows", [1, 13, 64, 100, 128])
-@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_F16_UMMA"])
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_F16_UMMA", "W_INT8_24_UMMA"])
 def test_linear_umma_layernorm(nv, pk, kind, n, act, out_kind, rows):
     """The tcgen05 projection (weight kinds W_INT8_UMMA, and W_F16_UMMA whose tiles come by bulk copy): LayerNorm folded, rows handed over as the ready fp16 operand
     with partial sums; equals act(LayerNorm(rows) W^T + b) on the dequantised weights. Twice in a row (tensor memory
@@ -344,7 +352,7 @@ def test_linear_umma_layernorm(nv, pk, kind, n, act, out_kind, rows):
         np.testing.assert_allclose(out.float().cpu().numpy(), want, atol=5e-3, rtol=2e-3 if ok == nv.OUT_F16 else 1e-4)
 
 
-@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_INT8", "W_INT8_24", "W_F16", "W_F16_UMMA"])
+@pytest.mark.parametrize("kind", ["W_INT8_UMMA", "W_INT8", "W_INT8_24", "W_F16", "W_F16_UMMA", "W_INT8_24_UMMA"])
 @pytest.mark.parametrize("n,k", [(1024, 1024), (1024, 4096), (3072, 1024)])
 @pytest.mark.parametrize("rows", [1, 13, 33, 50, 64, 100, 128])
 def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
@@ -376,7 +384,7 @@ def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
     gam = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
     g_d = cuda(gam)
     slots = lib.b200dec_linear_stat_slots(C.byref(cs))
-    assert kind not in (nv.W_INT8_UMMA, nv.W_F16_UMMA) or slots == (n // 128) * pc.ksplit
+    assert kind not in (nv.W_INT8_UMMA, nv.W_F16_UMMA, nv.W_INT8_24_UMMA) or slots == (n // 128) * pc.ksplit
     for _ in range(2):
         x = cuda(x0.copy())
         x16 = torch.zeros(rows, n, dtype=torch.float16, device="cuda")

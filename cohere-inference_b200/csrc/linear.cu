@@ -188,7 +188,7 @@ int run_linear(const b200dec_weight* w, const void* a, int a_kind, const b200dec
 namespace b200dec_detail {
 // launches one call of linear_impl makes (1, or 2 when the rows go in two passes)
 int linear_passes(const b200dec_weight* w, int a_kind, bool ln, int rows) {
-  if (is_umma_kind(w->kind)) return (w->k == 4 * D_MODEL && rows > 64) ? 2 : 1;
+  if (is_umma_kind(w->kind)) return 1;  // more than 64 rows of K = 4096 are dealt over grid.z of one launch
   const bool split = a_kind == B200DEC_A_F32_SPLIT;
   const int lnorm = !ln ? 0 : a_kind == B200DEC_A_F16_ROWS16 ? 2 : 1;
   const bool two_pass_wide = rows > 64 && w->k == 4096 && (split || lnorm != 0 || w->kind == B200DEC_W_BF16);

@@ -1,6 +1,6 @@
 // The layer projections on the fifth-generation tensor cores, for dense int8 weights:
 // out(rows, N) = act(a' W^T * scale + bias) [+ out], a' = the fp16 rows a or LayerNorm of the rows behind a ready
-// fp16 operand; rows <= 128, K = 1024 (split 4 or 8 ways) or 4096 (8 ways, 64 rows per pass), N a multiple of 128.
+// fp16 operand; rows <= 128, K = 1024 (split 4 or 8 ways) or 4096 (8 ways; above 64 rows dealt as two clusters of 64 rows per tile), N a multiple of 128.
 //
 // Same decomposition as the mma.sync kernel of linear_kernel.cuh with 128 channels per CTA and K split over a
 // cluster, but the multiply is 8-32 `tcgen05.mma` (M = 128 channels, N = 64 or 128 rows, K = 16) into tensor memory
@@ -57,6 +57,7 @@ struct UArgs {
   int lda, ldo, rows, N, K, out_kind, act, stats_slots;
   uint32_t wait_limit;  // polls before the wait for the MMAs gives up
   int withhold;         // tests only: the commit is left out, so that wait runs out
+  int deal;             // host side only: more than 64 rows go as clusters of 64 rows over grid.z, not one 128-row tile
 };
 
 // MB: row capacity (MMA N); KSPLIT: CTAs per cluster; NKB: 64-k blocks per CTA
@@ -158,8 +159,21 @@ DEVI void tmem_ld32(uint32_t taddr, uint32_t (&d)[32]) {
 
 // WK: how the weights come: 0 dense int8 blocks, 1 fp16 tile images (bulk copy), 2 2:4 int8 (kept values + selectors)
 template <int MB, int KSPLIT, int NKB, bool LN, int WK>
-__global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p) {
+__global__ void __launch_bounds__(NTHREADS, 1) linear_umma_kernel(const UArgs p_in) {
   constexpr bool W16 = WK == 1, W24 = WK == 2;
+  // rows dealt over grid.z: this cluster takes rows [MB z, MB z + MB) of the call (every pointer indexed by row moves)
+  UArgs p = p_in;
+  if (blockIdx.z) {
+    const int row0 = blockIdx.z * MB;
+    p.rows = min(MB, p.rows - row0);
+    p.xg += (size_t)row0 * p.lda;
+    p.out = (char*)p.out + (size_t)row0 * p.ldo * (p.out_kind == B200DEC_OUT_F16 ? 2 : 4);
+    if (p.stats) p.stats += (size_t)row0 * p.stats_slots * 2;
+    if (p.out16) p.out16 += (size_t)row0 * p.ldo;
+    if (p.stats_out) p.stats_out += (size_t)row0 * (gridDim.y * KSPLIT) * 2;
+  } else if (gridDim.z > 1) {
+    p.rows = min(MB, p.rows);
+  }
   using S = USmem<MB, KSPLIT, NKB>;
   constexpr int CPR = S::CPR, GPR = CPR / 4, KSLICE = NKB * KB;
   extern __shared__ unsigned char dyn_smem[];
@@ -437,7 +451,7 @@ int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
     auto kern = linear_umma_kernel<MB, KSPLIT, NKB, LN, WK>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma: smem attribute: %s", cudaGetErrorString(e));
-    e = launch_kernel(kern, dim3(KSPLIT, a.N / UM), dim3(NTHREADS), S::BYTES, stream, KSPLIT, pdl, a);
+    e = launch_kernel(kern, dim3(KSPLIT, a.N / UM, (a.rows + MB - 1) / MB), dim3(NTHREADS), S::BYTES, stream, KSPLIT, pdl, a);
     if (e != cudaSuccess) return fail(B200DEC_ECUDA, "linear_umma launch: %s", cudaGetErrorString(e));
     return 0;
   }
@@ -445,7 +459,8 @@ int launch_umma(const UArgs& a, int pdl, cudaStream_t stream) {
 
 template <int KSPLIT, int NKB, int WK>
 int launch_rows_wk(const UArgs& a, bool ln, int pdl, cudaStream_t s) {
-  if (a.rows <= 64)
+  // 64-row tiles: up to 64 rows, and above that where the rows are dealt over two clusters per tile (a.deal)
+  if (a.rows <= 64 || a.deal)
     return ln ? launch_umma<64, KSPLIT, NKB, true, WK>(a, pdl, s) : launch_umma<64, KSPLIT, NKB, false, WK>(a, pdl, s);
   return ln ? launch_umma<128, KSPLIT, NKB, true, WK>(a, pdl, s) : launch_umma<128, KSPLIT, NKB, false, WK>(a, pdl, s);
 }
@@ -461,7 +476,7 @@ namespace b200dec_detail {
 
 // A projection whose weight is of kind B200DEC_W_INT8_UMMA, B200DEC_W_F16_UMMA or B200DEC_W_INT8_24_UMMA. a: fp16 rows; with ln they are the LayerNorm's ready
 // operand and link->stats_in its partial sums (b200dec_ln_link). w->ksplit: CTAs per cluster (K = 1024: 4 or 8;
-// K = 4096: 8, 64 rows per pass).
+// K = 4096: 8).
 int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b200dec_norm* ln, int lda, int rows,
                      void* out, int out_kind, int ldo, int act, const b200dec_ln_link* link, int32_t* status, int pdl,
                      void* stream) {
@@ -485,33 +500,27 @@ int linear_umma_impl(const b200dec_weight* w, const void* a, int a_kind, const b
   B200_REQUIRE(out_kind >= 0 && out_kind <= 2, "linear_umma: out_kind %d", out_kind);
   B200_REQUIRE(!lk.out16 || (out_kind == B200DEC_OUT_F32_ADD && lk.next_gamma && lk.stats_out),
                "linear_umma: the next LayerNorm's operand goes with OUT_F32_ADD, its gamma and the sums");
-  const int slots = (w->n / UM) * w->ksplit;
-  const int pass = w->k == D_MODEL ? 128 : 64;  // K = 4096: the operands of 128 rows do not fit shared memory
-  for (int r0 = 0; r0 < rows; r0 += pass) {
-    UArgs p{};
-    p.w = (const uint8_t*)w->w, p.meta = (const uint32_t*)w->meta, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a + (size_t)r0 * lda;
-    if (ln) {
-      p.stats = lk.stats_in + (size_t)r0 * lk.stats_slots * 2, p.stats_slots = lk.stats_slots;
-      p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
-    }
-    const size_t osz = out_kind == B200DEC_OUT_F16 ? 2 : 4;
-    p.out = (char*)out + (size_t)r0 * ldo * osz, p.status = status;
-    if (lk.out16) {
-      p.next_gamma = lk.next_gamma, p.out16 = (__half*)lk.out16 + (size_t)r0 * ldo;
-      p.stats_out = lk.stats_out + (size_t)r0 * slots * 2;
-    }
-    p.lda = lda, p.ldo = ldo, p.rows = rows - r0 < pass ? rows - r0 : pass, p.N = w->n, p.K = w->k;
-    p.out_kind = out_kind, p.act = act;
-    p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
-    cudaStream_t s = (cudaStream_t)stream;
-    const int wk = w16 ? 1 : w24 ? 2 : 0;
-    int rc;
-    if (w->k == D_MODEL && w->ksplit == 4) rc = launch_rows<4, 4>(p, wk, ln != nullptr, pdl, s);
-    else if (w->k == D_MODEL) rc = launch_rows<8, 2>(p, wk, ln != nullptr, pdl, s);
-    else rc = launch_rows<8, 8>(p, wk, false, pdl, s);
-    if (rc) return rc;
+  // More than 64 rows: one 128-row tile per cluster (the wide K = 1024 projections), or the rows dealt over two
+  // clusters of 64 rows per tile in the same launch (grid.z; the second reads the tile's weights from L2): K = 4096,
+  // whose operands of 128 rows do not fit shared memory, and the 1024-wide projections, whose eight tiles would
+  // otherwise make 64 CTAs.
+  UArgs p{};
+  p.w = (const uint8_t*)w->w, p.meta = (const uint32_t*)w->meta, p.scale = w->scale, p.bias = w->bias, p.xg = (const __half*)a;
+  if (ln) {
+    p.stats = lk.stats_in, p.stats_slots = lk.stats_slots;
+    p.ln_g = w->ln_g, p.ln_bias = w->ln_bias, p.ln_eps = ln->eps;
   }
-  return 0;
+  p.out = out, p.status = status;
+  if (lk.out16) p.next_gamma = lk.next_gamma, p.out16 = (__half*)lk.out16, p.stats_out = lk.stats_out;
+  p.lda = lda, p.ldo = ldo, p.rows = rows, p.N = w->n, p.K = w->k;
+  p.out_kind = out_kind, p.act = act;
+  p.wait_limit = lk.wait_limit > 0 ? (uint32_t)lk.wait_limit : WAIT_LIMIT, p.withhold = lk.withhold;
+  p.deal = rows > 64 && (w->k != D_MODEL || w->n <= D_MODEL);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int wk = w16 ? 1 : w24 ? 2 : 0;
+  if (w->k == D_MODEL && w->ksplit == 4) return launch_rows<4, 4>(p, wk, ln != nullptr, pdl, s);
+  if (w->k == D_MODEL) return launch_rows<8, 2>(p, wk, ln != nullptr, pdl, s);
+  return launch_rows<8, 8>(p, wk, false, pdl, s);
 }
 
 }  // namespace b200dec_detail

@@ -357,7 +357,7 @@ def test_linear_umma_layernorm(nv, pk, kind, n, act, out_kind, rows):
 @pytest.mark.parametrize("rows", [1, 13, 33, 50, 64, 100, 128])
 def test_linear_plain_and_stream_update(nv, pk, kind, n, k, rows):
     """A projection without a LayerNorm (the o, cross-o and fc2 shapes) on the tcgen05 kernel (K split 4 or 8 ways,
-    K = 4096 in passes of 64 rows) and on the mma.sync kernel (fc2 at 33-64 rows: the rows dealt over two CTAs per
+    above 64 rows K = 4096 and the 1024-wide shapes as two clusters of 64 rows per tile) and on the mma.sync kernel (fc2 at 33-64 rows: the rows dealt over two CTAs per
     tile): a plain fp32 store, then the residual update that also leaves the next LayerNorm's fp16 operand and
     partial sums."""
     rng = np.random.default_rng(n + k + rows)

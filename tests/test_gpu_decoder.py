@@ -365,6 +365,28 @@ def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, bucket
     assert np.array_equal(got, want), what
 
 
+def test_small_buckets_point_at_the_mma_sync_packing():
+    """Buckets of up to `umma_above_rows` rows run the second, mma.sync packing of the tcgen05 projections; larger ones
+    the tcgen05 packing; with 0 there is one packing. Both sets multiply by the same int8 values and scales."""
+    import ctypes as C
+    from cohere_inference_b200 import native as nv
+    model = synthetic_model(0, layers=2)
+    run = dict(slots=32, max_new_tokens=8, max_prompt=8, max_audio_s=10.0, eos=-1, graphs=False)
+    dec = _decoder(model, int8=True, ffn_sparse=True, **run)
+    assert dec._small_rows == 16 and set(dec.layers[0].small) == {"qkv", "fc1"}
+    ly = dec.layers[0]
+    assert (ly.qkv.kind, ly.small["qkv"].kind) == (nv.W_INT8_UMMA, nv.W_INT8)
+    assert (ly.fc1.kind, ly.small["fc1"].kind) == (nv.W_INT8_24_UMMA, nv.W_INT8_24)
+    assert torch.equal(ly.qkv.scale, ly.small["qkv"].scale) and torch.equal(ly.fc1.scale, ly.small["fc1"].scale)
+    where = lambda: C.addressof(dec.plan.layer.contents)  # noqa: E731
+    for b in dec.buckets:
+        dec._select_layers(b)
+        assert where() == C.addressof(dec._layer_structs_small if b <= 16 else dec._layer_structs), b
+    one = _decoder(model, int8=True, ffn_sparse=True, umma_above_rows=0, **run)
+    assert one._small_rows == 0 and not one.layers[0].small and one._layer_structs_small is None
+    assert {k for k in dec.packed_tensors() if ".small." in k} and not {k for k in one.packed_tensors() if ".small." in k}
+
+
 @pytest.mark.parametrize("mode", [dict(int8=True, ffn_sparse=True), dict(fp16_weights=True)])
 def test_packed_weights_round_trip(tmp_path, mode):
     """save_packed -> from_packed: the same digest, the same bits out of the step, without the original model; a

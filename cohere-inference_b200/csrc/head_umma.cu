@@ -596,37 +596,38 @@ __global__ void __launch_bounds__(HeadStream<UNS, W16>::NT, 1) head_stream_kerne
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_full[kb % AST]);
       }
-    }
-    for (int kb = 0; kb < (W16 ? 0 : NKB) && ok; kb += 2) {  // two blocks per turn
-      uint4 r[2];
+    } else {
+      for (int kb = 0; kb < NKB && ok; kb += 2) {  // two blocks per turn
+        uint4 r[2];
 #pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        const int rs = (kb + b) % RS;
-        ok = ok && mbar_wait(&raw_full[rs], ((kb + b) / RS) & 1, p.wait_limit);
-        if (ok) r[b] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + pj * 2048 + ch * 16);
+        for (int b = 0; b < 2; ++b) {
+          const int rs = (kb + b) % RS;
+          ok = ok && mbar_wait(&raw_full[rs], ((kb + b) / RS) & 1, p.wait_limit);
+          if (ok) r[b] = *reinterpret_cast<const uint4*>(raws + rs * RAW_BYTES + pj * 2048 + ch * 16);
+        }
+        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[kb % RS]), mbar_arrive(&raw_empty[(kb + 1) % RS]);  // bytes are in registers
+        // MMAs of blocks kb - AST and kb + 1 - AST are done: their weight and operand stages are free
+#pragma unroll
+        for (int b = 0; b < 2; ++b)
+          ok = ok && mbar_wait(&a_empty[(kb + b) % AST], (((kb + b) / AST) & 1) ^ 1, p.wait_limit);
+        if (!ok) break;
+        request_x(kb + LOOK);
+        request_x(kb + 1 + LOOK);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          unsigned char* row = as + ((kb + b) % AST) * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
+          uint4 lo, hi;  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
+          widen16(r[b], lo, hi);
+          *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
+          *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
+        }
+        cp_async_wait_group<LOOK>();  // this thread's pieces of operand blocks kb and kb + 1 (and earlier) have landed
+        fence_async_shared();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[kb % AST]), mbar_arrive(&a_full[(kb + 1) % AST]);
       }
-      if (!ok) break;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[kb % RS]), mbar_arrive(&raw_empty[(kb + 1) % RS]);  // bytes are in registers
-      // MMAs of blocks kb - AST and kb + 1 - AST are done: their weight and operand stages are free
-#pragma unroll
-      for (int b = 0; b < 2; ++b)
-        ok = ok && mbar_wait(&a_empty[(kb + b) % AST], (((kb + b) / AST) & 1) ^ 1, p.wait_limit);
-      if (!ok) break;
-      request_x(kb + LOOK);
-      request_x(kb + 1 + LOOK);
-#pragma unroll
-      for (int b = 0; b < 2; ++b) {
-        unsigned char* row = as + ((kb + b) % AST) * A_BYTES + (ch >> 3) * 1024 + (ch & 7) * 128;
-        uint4 lo, hi;  // piece pj: k = 16 pj .. 16 pj + 15 = chunks 2 pj and 2 pj + 1 of the row
-        widen16(r[b], lo, hi);
-        *reinterpret_cast<uint4*>(row + (((2 * pj) ^ (ch & 7)) << 4)) = lo;
-        *reinterpret_cast<uint4*>(row + (((2 * pj + 1) ^ (ch & 7)) << 4)) = hi;
-      }
-      cp_async_wait_group<LOOK>();  // this thread's pieces of operand blocks kb and kb + 1 (and earlier) have landed
-      fence_async_shared();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&a_full[kb % AST]), mbar_arrive(&a_full[(kb + 1) % AST]);
     }
     cp_async_wait_all();  // nothing of this thread's is on its way into the rings any more (also after a time-out)
     if (!ok && lane == 0) atomicOr(p.status, B200DEC_ST_TIMEOUT);

@@ -338,8 +338,11 @@ def test_admit_and_device_active_list_match_the_oracle(model16):
     (1, "vocabulary projection, 128-row bucket (the streamed-operand kernel)", 128, (128,), dict(int8=True)),
     (2, "layer projections", 4, None, dict(int8=True, umma_above_rows=0)),
     (1, "vocabulary projection, fp16 weight tiles by bulk copy", 4, None, dict(fp16_weights=True)),
+    (1, "vocabulary projection, fp16 weight tiles, 128-row bucket", 128, (128,), dict(fp16_weights=True)),
     (2, "layer projections, fp16 weight tiles by bulk copy", 4, None,
-     dict(fp16_weights=True, proj_umma="qkv,fc1", umma_above_rows=0))])
+     dict(fp16_weights=True, proj_umma="qkv,fc1", umma_above_rows=0)),
+    (2, "layer projections, 2:4 weights expanded to dense tiles", 4, None,
+     dict(int8=True, ffn_sparse=True, proj_umma="fc1", umma_above_rows=0))])
 def test_bounded_wait_runs_out_and_the_context_survives(bit, what, slots, buckets, mode):
     """The tcgen05 kernels bound every wait. With a short limit and the test-only `withhold` switch (the producer of
     a barrier is left out, nothing faults and nothing is in flight), the wait runs out: the kernel returns, the status

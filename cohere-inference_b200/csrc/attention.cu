@@ -181,7 +181,7 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
   constexpr int U = 4;                   // keys in flight per group
   constexpr int KPW = U * GPW;           // keys per warp and iteration
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int g = lane / LPK, gl = lane % LPK, grp = warp * GPW + g;
+  const int g = lane / LPK, gl = lane % LPK;
   const int8_t* k8 = reinterpret_cast<const int8_t*>(p.k);
   const int8_t* v8 = reinterpret_cast<const int8_t*>(p.v);
   const size_t vec0 = ((size_t)s * p.H + h) * p.cap;  // index of key 0: scales, and * D the vectors
@@ -239,8 +239,9 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
     d *= p.scale_log2;
 #pragma unroll
     for (int o = 1; o < LPK; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    if (g == 0) {  // the first key this group sees: weight 1
-      m = d, l = 1.f;
+    m = d;         // every group of the warp computed the same score: the warp's running maximum starts there
+    if (g == 0) {  // and one group counts the key: weight 1
+      l = 1.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = __floats2half2_rn(vn[2 * i], vn[2 * i + 1]);
     }
@@ -283,7 +284,11 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
       const float ksc = __shfl_sync(0xffffffffu, ks_l, u * GPW + g);
       sc[u] = (k0 + u * GPW + g < end) ? d * ksc : -INFINITY;
     }
-    const float mn = fmaxf(fmaxf(m, fmaxf(sc[0], sc[1])), fmaxf(sc[2], sc[3]));
+    // one running maximum per warp (not per group): the groups' sums can be added up at the end without rescaling
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float mn = fmaxf(m, mx);
     const float a = ex2(m - mn);
     const __half2 ah = __float2half2_rn(a);
     l *= a;
@@ -306,16 +311,28 @@ DEVI void attend_range_q8(const AttnArgs& p, int r, int s, int h, int n, int sta
     }
     m = mn;
   }
-  // merge the groups
-  __syncthreads();  // the arrays may still be read by a previous pass
-  if (gl == 0) s_m[grp] = m, s_l[grp] = l;
+  // merge: a warp's groups share their maximum, so their sums add up (shuffles, in the accumulators' fp16 pairs); then
+  // one (max, sum, output) set per warp through shared memory
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float2 f = __half22float2(acc[i]);
-    s_acc[grp][gl * Q8_LANE_DIMS + 2 * i] = f.x, s_acc[grp][gl * Q8_LANE_DIMS + 2 * i + 1] = f.y;
+  for (int o = LPK; o < 32; o <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t other = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const uint32_t*>(&acc[i]), o);
+      acc[i] = __hadd2(acc[i], *reinterpret_cast<const __half2*>(&other));
+    }
+  }
+  __syncthreads();  // the arrays may still be read by a previous pass
+  if (g == 0) {
+    if (gl == 0) s_m[warp] = m, s_l[warp] = l;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __half22float2(acc[i]);
+      s_acc[warp][gl * Q8_LANE_DIMS + 2 * i] = f.x, s_acc[warp][gl * Q8_LANE_DIMS + 2 * i + 1] = f.y;
+    }
   }
   __syncthreads();
-  constexpr int NG = NTHREADS / LPK;
+  constexpr int NG = NTHREADS / 32;
   M = -1e30f, L = 0.f, O = 0.f;
   if (tid < D) {
 #pragma unroll 8

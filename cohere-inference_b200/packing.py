@@ -78,9 +78,9 @@ def tile_config(n: int, k: int, kind: int, a_kind: int = nv.A_F16, ln: bool = Fa
     pass; if none does, the first valid one (the library then makes two passes of 64 rows)."""
     fits = nv.lib().b200dec_linear_fits
     prefs = TILE_CONFIG.get((n, k), []) + [(w, s) for s in (8, 4, 2, 1) for w in (4, 8)]
+    kpb = {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_F16: 32, nv.W_INT8_24: 128}[kind]  # k per weight block of the kind
     valid = [(w, s) for w, s in prefs if n % (16 * w) == 0 and (k, s) in ((1024, 8), (1024, 4), (1024, 2), (4096, 8))
-             and (16 * w) % (8 * s) == 0 and (k // s) % {nv.W_INT8: 64, nv.W_BF16: 32, nv.W_F16: 32, nv.W_INT8_24: 128}[kind] == 0
-             and (not ln or k == 1024)]
+             and (16 * w) % (8 * s) == 0 and (k // s) % kpb == 0 and (not ln or k == 1024)]
     assert valid, f"no tile for a ({n}, {k}) projection"
     for w, s in valid:
         # a LayerNorm-folding projection of an fp16-operand decoder stages the ready fp16 rows its producer left
@@ -138,7 +138,8 @@ def pack_linear(weight: torch.Tensor, bias: torch.Tensor | None, kind: int, keep
     lib = nv.lib()
     if a_kind is None:
         a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
-    if kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA, nv.W_INT8_24_UMMA):  # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
+    # the tcgen05 kernels: 128 channels per CTA; the projections split K over a cluster
+    if kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA, nv.W_INT8_24_UMMA):
         warps, ksplit = 8, (4 if (k == 1024 and n >= 3072) else 8)  # 96, 128 or 64 CTAs (the head ignores the split)
     else:
         warps, ksplit = tile_config(n, k, kind, a_kind, ln is not None, max_rows)

@@ -33,6 +33,48 @@ def test_library_exports_every_declared_symbol():
     assert native.lib().b200dec_attention_scratch_floats(64, 16, 64) == 64 * 16 * 16 * 66
 
 
+def test_weight_kinds_sizes_and_tile_choices():
+    """The pure host side of the seven weight kinds: bytes of the tiled images, which (kind, operand, tile) combinations
+    have a kernel, and that packing.tile_config only hands out tiles the library accepts for the rows it was asked
+    for (or, failing that, for two passes of 64)."""
+    from cohere_inference_b200 import native as nv, packing as pk
+    lib = nv.lib()
+    n, k = 4096, 1024
+    per_weight = {nv.W_BF16: 2, nv.W_F16: 2, nv.W_F16_UMMA: 2, nv.W_INT8: 1, nv.W_INT8_UMMA: 1, nv.W_INT8_24: 0.5,
+                  nv.W_INT8_24_UMMA: 0.5}
+    for kind, b in per_weight.items():
+        assert lib.b200dec_tiled_bytes(kind, n, k) == int(n * k * b), kind
+        sparse = kind in (nv.W_INT8_24, nv.W_INT8_24_UMMA)
+        assert lib.b200dec_tiled_meta_bytes(kind, n, k) == (n * k // 8 if sparse else 0), kind
+    assert lib.b200dec_tiled_bytes(99, n, k) == -1
+    # the tcgen05 kinds: fp16 rows only (plain, or a LayerNorm's ready operand), K = 1024 split 4 or 8, K = 4096 split 8
+    for kind in (nv.W_INT8_UMMA, nv.W_F16_UMMA, nv.W_INT8_24_UMMA):
+        assert lib.b200dec_linear_fits(kind, nv.A_F16, 0, 8, 4, 1024, 128) == 1
+        assert lib.b200dec_linear_fits(kind, nv.A_F16_ROWS16, 1, 8, 8, 1024, 64) == 1
+        assert lib.b200dec_linear_fits(kind, nv.A_F16, 0, 8, 8, 4096, 128) == 1
+        assert lib.b200dec_linear_fits(kind, nv.A_F16, 1, 8, 4, 1024, 64) == 0         # fp32 rows to normalise
+        assert lib.b200dec_linear_fits(kind, nv.A_F32_SPLIT, 0, 8, 4, 1024, 64) == 0   # split operand
+        assert lib.b200dec_linear_fits(kind, nv.A_F16_ROWS16, 1, 8, 8, 4096, 64) == 0  # no LayerNorm over K = 4096
+        assert lib.b200dec_linear_fits(kind, nv.A_F16, 0, 8, 2, 1024, 64) == 0
+    # the mma.sync kinds: the fp16 kind takes the int8 kinds' operands, the bf16 kind has no linked LayerNorm
+    assert lib.b200dec_linear_fits(nv.W_F16, nv.A_F16_ROWS16, 1, 8, 4, 1024, 128) == 1
+    assert lib.b200dec_linear_fits(nv.W_INT8, nv.A_F16_ROWS16, 1, 8, 4, 1024, 128) == 1
+    assert lib.b200dec_linear_fits(nv.W_BF16, nv.A_F16_ROWS16, 1, 8, 4, 1024, 64) == 0
+    for kind in (nv.W_INT8, nv.W_BF16, nv.W_F16, nv.W_INT8_24):
+        a_kind = nv.A_F32_SPLIT if kind == nv.W_BF16 else nv.A_F16
+        for shape in ((3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (16384, 1024)):
+            for ln in (False, True):
+                if ln and shape[1] != 1024:
+                    continue
+                for rows in (1, 16, 64, 128):
+                    w, s = pk.tile_config(*shape, kind, a_kind, ln, rows)
+                    assert shape[0] % (16 * w) == 0 and shape[1] % s == 0
+                    linked = ln and a_kind == nv.A_F16 and kind != nv.W_BF16 and shape[1] // s <= 256
+                    q_kind = nv.A_F16_ROWS16 if linked else a_kind
+                    fits = lambda r: lib.b200dec_linear_fits(kind, q_kind, int(ln), w, s, shape[1], r)  # noqa: E731
+                    assert fits(rows) or fits(min(rows, 64)), (kind, shape, ln, rows, w, s)
+
+
 def test_structs_match_header_sizes():
     from cohere_inference_b200 import native
     assert ctypes.sizeof(native.Weight) == 72 and ctypes.sizeof(native.Norm) == 24  # 6 pointers + 5 ints, padded

@@ -50,3 +50,22 @@ def test_compress_rejects_dense():
     q = np.ones((1, 32), np.int8)
     with pytest.raises(AssertionError):
         packers.compress_24(q)
+
+
+def test_fp16_image_keeps_the_bf16_values():
+    """The 16-bit mode's weights, fp16(bf16(w)): every bf16 value of magnitude 2^-14 .. 65280 (the largest below the fp16 limit) bit for bit, the smaller
+    ones within 2^-25 (the fp16 subnormal grid), and a weight beyond the fp16 range refused."""
+    import torch
+    from cohere_inference_b200.packing import fp16_image
+    from oracle.decoder import bf16_round
+    rng = np.random.default_rng(9)
+    w = np.concatenate([rng.standard_normal(4096) * 0.02, rng.standard_normal(512) * 1e-5, rng.standard_normal(512) * 50,
+                        [0.0, -0.0, 2.0 ** -14, -(2.0 ** -14), 2.0 ** -15, 65280.0, -65280.0]]).astype(np.float32)
+    got = fp16_image(torch.from_numpy(w)).float().numpy()
+    want = bf16_round(w)
+    big = np.abs(want) >= 2.0 ** -14
+    assert np.array_equal(got[big], want[big]) and big.sum() > 4500
+    assert np.abs(got[~big] - want[~big]).max() <= 2.0 ** -25 and (~big).sum() > 400
+    with pytest.raises(AssertionError, match="fp16 range"):
+        fp16_image(torch.tensor([[0.5, 7e4]]))
+

@@ -4,13 +4,16 @@ Drop-in for kernels/stream_decoder.py:65-276 of the reference: the same construc
 `out`, `flags`, `stream`, `eos`, `max_new_tokens`, `buckets`, `slots`, `dummy`) and methods (`fill_cross`, `admit`,
 `set_active`, `step`, `reset`, `bucket`) with the same meaning, so the reference's Pipeline (kernels/pipeline.py) can
 drive it unchanged. Row r of a step works on slot active[r]; rows past the live ones point at the dummy slot; a step
-is one CUDA-graph launch per bucket of row counts; the prompt is fed by the steps themselves as forced tokens; the
-a row that ends sets its flag in pinned host memory from the step's last kernel (no copy node in the graph).
+is one CUDA-graph launch per bucket of row counts; the prompt is fed by the steps themselves as forced tokens; a row
+that ends sets its flag in pinned host memory from the step's last kernel (no copy node in the graph).
 
 What differs underneath: every kernel is hand-written CUDA for sm_100a behind a C-ABI (include/b200dec.h), there is no
 Triton and no cuBLAS on the step; `int8=True` quantises every projection of the step (also o, cross q and cross o; the
-prefill's projections keep bf16 weights), `ffn_sparse=True` additionally stores fc1/fc2 2:4; the residual stream is fp32; heads x head_dim may be
-8 x 128 or 16 x 64 and the feed-forward activation ReLU or GELU (read from model.config).
+prefill's projections keep bf16 weights), `ffn_sparse=True` additionally stores fc1/fc2 2:4, `fp16_weights=True` is the
+16-bit mode on the same kernels (the bf16 weight values as fp16); the residual stream is fp32; heads x head_dim may
+be 8 x 128 or 16 x 64 and the feed-forward activation ReLU or GELU (read from model.config). The wide projections
+(qkv, fc1) and the vocabulary projection run on tcgen05 / tensor memory, in buckets of up to `umma_above_rows` rows on
+the register-dequantising mma.sync kernel from a second packing of the same weights.
 """
 
 from __future__ import annotations
